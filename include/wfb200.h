@@ -1,0 +1,168 @@
+/*
+ * wfb200 -- C ABI of the B200-native quantized dot_general / linear library.
+ *
+ * This is the boundary a WarpForge NVIDIA backend binds with Panama FFM, the same way its
+ * CudaRuntime binds libcuda and its CublasRuntime binds libcublas
+ * (warpforge-backend-nvidia/src/main/java/io/surfworks/warpforge/backend/nvidia/cuda/CudaRuntime.java:64-130,
+ *  .../nvidia/cublas/CublasRuntime.java:116-135): every function returns an int status
+ * (0 = success), handles / device pointers / streams are 64-bit integers (JAVA_LONG),
+ * host buffers and out-parameters are plain addresses (ADDRESS), there are no structs by
+ * value and no callbacks.  Negative codes are argument / state errors found before any GPU
+ * work (the reference throws IllegalArgumentException / UnsupportedOperationException at
+ * .../nvidia/ops/DotGeneralKernel.java:54-62,80-81,183-186,221-225); positive codes carry
+ * a CUDA (1000 + cudaError) or NCCL (2000 + ncclResult) status, mirroring
+ * CudaRuntime.checkError (CudaRuntime.java:615-633).
+ *
+ * All compute runs in hand-written sm_100a kernels.  There is no CPU fallback: without a
+ * usable device wf_init fails and nothing else can be called.
+ */
+#ifndef WFB200_H
+#define WFB200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ---------------------------------------------------------------- */
+#define WF_OK 0
+#define WF_ERR_INVALID_ARGUMENT (-1) /* null pointer, negative size, bad enum            */
+#define WF_ERR_INVALID_HANDLE (-2)   /* unknown, destroyed or foreign handle             */
+#define WF_ERR_UNSUPPORTED_TYPE (-3) /* qtype with no kernel (Dequantizer.java:58-71)    */
+#define WF_ERR_SHAPE (-4)            /* K not a multiple of the block, M/N/K out of range */
+#define WF_ERR_SHARD (-5)            /* rank >= world, rows not divisible                */
+#define WF_ERR_BUSY (-6)             /* context used from two threads at once            */
+#define WF_ERR_NO_DEVICE (-7)        /* no CUDA device / driver                          */
+#define WF_ERR_NOT_SM100 (-8)        /* device is not compute capability 10.x            */
+#define WF_ERR_NCCL_UNAVAILABLE (-9) /* libnccl could not be loaded                      */
+#define WF_ERR_DEVICE_WAIT (-10)     /* a bounded device-side wait ran out (see wf_stream_sync) */
+#define WF_ERR_TOO_LARGE (-11)       /* request exceeds a fixed capacity                 */
+#define WF_ERR_CUDA_BASE 1000
+#define WF_ERR_NCCL_BASE 2000
+
+/* ---- enums (ggml type ids, as in GGUF.java:294-305) ------------------------------- */
+#define WF_QTYPE_Q4_0 2
+#define WF_QTYPE_Q8_0 8
+#define WF_QTYPE_Q4_K 14
+
+#define WF_DTYPE_F32 0
+#define WF_DTYPE_BF16 1
+
+/* GEMM operand precision for the tensor-core (prefill) path. */
+#define WF_GEMM_AUTO 0
+
+/* ---- library / context -------------------------------------------------------------
+ * Replaces CudaContext.create / close (nvidia/cuda/CudaContext.java:41-52, 624-657) and
+ * NvidiaBackend's device bookkeeping (nvidia/NvidiaBackend.java:85-138, 459-463).
+ * A context owns one device, one non-blocking compute stream, and every allocation made
+ * through it.  It is not re-entrant: concurrent calls on one context return WF_ERR_BUSY.
+ * wf_destroy frees everything; a second wf_destroy returns WF_ERR_INVALID_HANDLE. */
+int wf_version(void);
+int wf_device_count(int* count);
+int wf_init(int device, int64_t* ctx);
+int wf_destroy(int64_t ctx);
+int wf_device_info(int64_t ctx, int* sm_count, int* cc_major, int* cc_minor, int64_t* total_mem,
+                   int64_t* free_mem);
+
+/* Replaces GpuBackend.createStream / destroyStream / synchronizeStream
+ * (warpforge-core/src/main/java/io/surfworks/warpforge/core/backend/GpuBackend.java:100-130).
+ * stream 0 everywhere below means the context's own compute stream.  wf_stream_sync also
+ * reports WF_ERR_DEVICE_WAIT if a kernel gave up a bounded wait since the last sync. */
+int wf_stream_create(int64_t ctx, int64_t* stream);
+int wf_stream_destroy(int64_t ctx, int64_t stream);
+int wf_stream_sync(int64_t ctx, int64_t stream);
+
+/* Replaces CudaContext.allocate / free / copyToDevice / copyToHost
+ * (nvidia/cuda/CudaContext.java:80-150) and GpuBackend.allocateDevice / allocatePinned.
+ * Copies are asynchronous on `stream` and need a wf_stream_sync before the host buffer is
+ * reused, unless `sync` is non-zero. */
+int wf_malloc(int64_t ctx, int64_t bytes, int64_t* dptr);
+int wf_free(int64_t ctx, int64_t dptr);
+int wf_host_alloc(int64_t ctx, int64_t bytes, void** host);
+int wf_host_free(int64_t ctx, void* host);
+int wf_memcpy_h2d(int64_t ctx, int64_t dst, const void* src, int64_t bytes, int64_t stream, int sync);
+int wf_memcpy_d2h(int64_t ctx, void* dst, int64_t src, int64_t bytes, int64_t stream, int sync);
+
+/* ---- quantized weights -------------------------------------------------------------
+ * Takes the raw GGUF blocks of one [n_rows x k] tensor (blocks run along k inside a row,
+ * exactly the bytes GGUF.tensor(name) returns, GGUF.java:221-225, sized by
+ * GGUF.java:332-351) and keeps the row shard [rank*n_rows/world, (rank+1)*n_rows/world) on
+ * the device in the library's tiled layout.  The reference has no counterpart: it would
+ * dequantize to fp32 on the host (QuantizedTensorView.dequantizeToArray,
+ * warpforge-data/.../quant/QuantizedTensorView.java:161-166) and upload 4 bytes per weight.
+ * `blocks` points at the FULL tensor; only the shard is copied. */
+int wf_weight_upload(int64_t ctx, int qtype, const void* blocks, int64_t n_rows, int64_t k, int shard_rank,
+                     int shard_world, int64_t* weight);
+int wf_weight_free(int64_t ctx, int64_t weight);
+/* rows = rows held by this shard, row0 = first global row of the shard. */
+int wf_weight_info(int64_t ctx, int64_t weight, int* qtype, int64_t* rows, int64_t* k, int64_t* row0,
+                   int64_t* device_bytes);
+
+/* Replaces Dequantizer.dequantize(MemorySegment, float[], int)
+ * (warpforge-data/.../quant/Dequantizer.java:204-221 Q8_0, :251-279 Q4_0; Q4_K per the GGUF
+ * block format): fp32 values of shard rows [row0, row0+nrows), bit-identical to the CPU
+ * result, written to host memory. */
+int wf_dequant_rows(int64_t ctx, int64_t weight, int64_t row0, int64_t nrows, float* out_host);
+
+/* ---- the op -------------------------------------------------------------------------
+ * Replaces DotGeneralKernel.execute for `linear`: lhs [m,k] contracting dim 1, rhs [n,k]
+ * contracting dim 1 (nvidia/ops/DotGeneralKernel.java:169-298 with transposeB, CPU rule at
+ * warpforge-backend-cpu/.../ops/scalar/DotGeneralKernel.java:85-128), with rhs a quantized
+ * weight handle.  y[m, rows] = x[m, k] . W[rows, k]^T, fp32 accumulation, fp32 output.
+ * x_dtype is WF_DTYPE_BF16 or WF_DTYPE_F32.  x / y are device pointers (x_on_device /
+ * y_on_device non-zero) or host pointers; host buffers are staged through pinned memory
+ * and the call returns after the result is in `y`.  With device pointers the call only
+ * enqueues work on `stream`. */
+int wf_qlinear(int64_t ctx, int64_t weight, const void* x, int x_dtype, int x_on_device, int64_t m, void* y,
+               int y_on_device, int64_t stream);
+
+/* Same op with the row-sharded gather fused behind it: every rank passes its own shard
+ * handle and receives the full y[m, n_total] (rank-major row ranges).  See wf_allgather. */
+int wf_qlinear_allgather(int64_t ctx, int64_t comm, int64_t weight, const void* x_dev, int x_dtype, int64_t m,
+                         void* y_full_dev, int64_t stream);
+
+/* ---- collectives --------------------------------------------------------------------
+ * Replaces CollectiveApi.allGather(Tensor input, Tensor output)
+ * (warpforge-io/src/main/java/io/surfworks/warpforge/io/collective/CollectiveApi.java:137-146,
+ * UCC implementation at .../collective/impl/UccCollectiveImpl.java:503-543): rank r's
+ * `bytes_per_rank` land at recv + r*bytes_per_rank on every rank.  Transport is NCCL over
+ * NVLink on device buffers.  Bootstrap mirrors CollectiveConfig(worldSize, rank, ...)
+ * (.../collective/CollectiveConfig.java:15-40): rank 0 creates a 128-byte id and the
+ * caller distributes it out of band. */
+int wf_comm_get_unique_id(void* id128);
+int wf_comm_init(int64_t ctx, const void* id128, int rank, int world, int64_t* comm);
+int wf_comm_destroy(int64_t ctx, int64_t comm);
+int wf_allgather(int64_t ctx, int64_t comm, int64_t send_dev, int64_t recv_dev, int64_t bytes_per_rank,
+                 int64_t stream);
+
+/* ---- launch management -------------------------------------------------------------
+ * The reference launches every kernel with cuLaunchKernel on stream 0 and synchronizes the
+ * context after each op (nvidia/cuda/CudaContext.java:273-321, nvidia/ops/DotGeneralKernel.java:283).
+ * A decode step is hundreds of microsecond-scale kernels, so the backend instead records a
+ * sequence of device-pointer calls (wf_qlinear, wf_qlinear_allgather, wf_allgather, copies)
+ * issued on `stream` between begin and end into a CUDA graph and replays it with one launch.
+ * Only calls with device pointers may be recorded. */
+int wf_graph_begin(int64_t ctx, int64_t stream);
+int wf_graph_end(int64_t ctx, int64_t stream, int64_t* graph);
+int wf_graph_launch(int64_t ctx, int64_t graph, int64_t stream);
+int wf_graph_destroy(int64_t ctx, int64_t graph);
+
+/* ---- errors -------------------------------------------------------------------------
+ * Replaces CudaRuntime.getErrorName / checkError message formatting. */
+const char* wf_error_string(int status);
+int wf_last_error(int64_t ctx, char* buf, int64_t buf_len);
+
+/* ---- measurement helpers (used by the benchmark; CudaContext.java:519-613 has the
+ * reference's CUDA-event helpers) -------------------------------------------------- */
+int wf_event_create(int64_t ctx, int64_t* event);
+int wf_event_destroy(int64_t ctx, int64_t event);
+int wf_event_record(int64_t ctx, int64_t event, int64_t stream);
+int wf_event_elapsed_ms(int64_t ctx, int64_t start, int64_t stop, float* ms);
+/* Number of kernel launches this context has issued (product kernels only). */
+int wf_launch_count(int64_t ctx, int64_t* launches);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* WFB200_H */

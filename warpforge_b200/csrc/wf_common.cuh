@@ -1,0 +1,110 @@
+// Internal declarations shared by the translation units of libwfb200.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <mutex>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/wfb200.h"
+#include "wf_layout.cuh"
+
+namespace wf {
+
+constexpr uint32_t CTX_MAGIC = 0x57464358;     // "WFCX"
+constexpr uint32_t WEIGHT_MAGIC = 0x57465754;  // "WFWT"
+constexpr uint32_t COMM_MAGIC = 0x5746434D;    // "WFCM"
+
+// Device-side status bits, OR-ed into Context::d_status by kernels that give up a wait.
+constexpr int STATUS_GEMV_FIXUP_TIMEOUT = 1;
+constexpr int STATUS_GEMM_PIPE_TIMEOUT = 2;
+constexpr int STATUS_PEER_WAIT_TIMEOUT = 4;
+
+struct Context;
+
+struct Weight {
+    uint32_t magic = WEIGHT_MAGIC;
+    Context* ctx = nullptr;
+    WeightGeom g{};
+    int64_t row0 = 0;        // first global row of this shard
+    int64_t total_rows = 0;  // rows of the unsharded tensor
+    uint8_t* d_tiles = nullptr;
+};
+
+// Scratch for the GEMV fix-up between CTAs, one per stream that launches GEMVs.
+struct GemvScratch {
+    uint2* d_slots = nullptr;  // [ctas][128] {value bits, tag}
+    int ctas = 0;
+};
+
+struct Context {
+    uint32_t magic = CTX_MAGIC;
+    int device = 0;
+    int sm_count = 0;
+    int cc_major = 0, cc_minor = 0;
+    cudaStream_t stream = nullptr;  // the context's own compute stream
+    int* d_status = nullptr;
+    std::mutex mu;  // guards against concurrent use (try_lock -> WF_ERR_BUSY)
+    std::string last_error;
+    std::vector<cudaStream_t> streams;
+    std::vector<cudaEvent_t> events;
+    std::vector<cudaGraphExec_t> graphs;
+    int64_t capture_launches = 0;  // product kernels recorded by the capture in progress
+    std::unordered_map<cudaGraphExec_t, int64_t> graph_launches;
+    std::unordered_map<int64_t, int64_t> allocs;  // device ptr -> bytes
+    std::vector<void*> host_allocs;
+    std::vector<Weight*> weights;
+    std::unordered_map<cudaStream_t, GemvScratch> gemv_scratch;
+    // pinned staging for host-pointer calls
+    void* h_stage = nullptr;
+    int64_t h_stage_bytes = 0;
+    void* d_stage = nullptr;
+    int64_t d_stage_bytes = 0;
+    int64_t launches = 0;
+    int gemv_ctas_per_sm[3] = {0, 0, 0};
+};
+
+int set_error(Context* c, int status, const char* fmt, ...);
+int cuda_status(Context* c, cudaError_t e, const char* what);
+Context* get_context(int64_t h);
+Weight* get_weight(Context* c, int64_t h);
+cudaStream_t resolve_stream(Context* c, int64_t stream);
+int ensure_stage(Context* c, int64_t host_bytes, int64_t dev_bytes);
+
+// wf_repack.cu
+cudaError_t launch_repack(int qtype, const uint8_t* d_raw, uint8_t* d_tiles, int64_t rows, int64_t k,
+                          cudaStream_t s);
+cudaError_t launch_dequant_rows(const Weight& w, int64_t row0, int64_t nrows, float* d_out, cudaStream_t s);
+
+// wf_gemv.cu
+struct GemvCall {
+    const Weight* w;
+    const void* d_x;  // [m, k] bf16 or fp32
+    int x_dtype;
+    int64_t m;       // tokens, any value >= 1 (chunked internally)
+    float* d_y;      // y[token * ldy + col0 + row]
+    int64_t ldy;
+    int64_t col0;
+};
+int gemv_launch(Context* c, const GemvCall& call, cudaStream_t s);
+int gemv_max_tokens_per_pass(const Weight& w, int x_dtype);
+int gemv_prepare_stream(Context* c, cudaStream_t s);
+
+struct ScopedLock {
+    Context* c;
+    bool ok;
+    explicit ScopedLock(Context* ctx) : c(ctx), ok(ctx && ctx->mu.try_lock()) {}
+    ~ScopedLock() {
+        if (ok) c->mu.unlock();
+    }
+};
+
+}  // namespace wf
+
+#define WF_CUDA(c, call)                                         \
+    do {                                                         \
+        cudaError_t _e = (call);                                 \
+        if (_e != cudaSuccess) return wf::cuda_status(c, _e, #call); \
+    } while (0)
