@@ -159,6 +159,13 @@ int wf_event_create(int64_t ctx, int64_t* event);
 int wf_event_destroy(int64_t ctx, int64_t event);
 int wf_event_record(int64_t ctx, int64_t event, int64_t stream);
 int wf_event_elapsed_ms(int64_t ctx, int64_t start, int64_t stop, float* ms);
+/* Instrumentation level, the `salt` every reference kernel class is constructed with
+ * (nvidia/ops/DotGeneralKernel.java:40-43; SALT_TIMING at nvidia/cuda/CudaKernels.java:31-37).
+ * 0 = none; 2 = GEMV kernels record per-CTA globaltimer stamps (start, activations staged,
+ * loop entered, first tile landed, loop done, end) that wf_read_timing copies out as
+ * [sm_count][8] int64 nanoseconds after synchronizing the device. */
+int wf_set_salt(int64_t ctx, int salt);
+int wf_read_timing(int64_t ctx, int64_t* out, int64_t n);
 /* Number of kernel launches this context has issued (product kernels only). */
 int wf_launch_count(int64_t ctx, int64_t* launches);
 

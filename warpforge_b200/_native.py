@@ -54,6 +54,8 @@ SIGNATURES = {
     "wf_event_destroy": (c_int, [c_i64, c_i64]),
     "wf_event_record": (c_int, [c_i64, c_i64, c_i64]),
     "wf_event_elapsed_ms": (c_int, [c_i64, c_i64, c_i64, P(c_f32)]),
+    "wf_set_salt": (c_int, [c_i64, c_int]),
+    "wf_read_timing": (c_int, [c_i64, P(c_i64), c_i64]),
     "wf_launch_count": (c_int, [c_i64, P(c_i64)]),
 }
 

@@ -46,6 +46,8 @@ struct Context {
     int cc_major = 0, cc_minor = 0;
     cudaStream_t stream = nullptr;  // the context's own compute stream
     int* d_status = nullptr;
+    int salt = 0;                            // instrumentation level, 2 = kernel timing stamps
+    unsigned long long* d_timing = nullptr;  // [sm_count][8]
     std::mutex mu;  // guards against concurrent use (try_lock -> WF_ERR_BUSY)
     std::string last_error;
     std::vector<cudaStream_t> streams;

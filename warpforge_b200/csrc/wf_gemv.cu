@@ -1,9 +1,12 @@
 // Decode GEMV: y[m, rows] = x[m, K] . W[rows, K]^T for m <= 8 tokens per pass, W in the tiled
-// quantized layout of wf_layout.cuh.  HBM-bound: every weight byte is read exactly once with
-// 16-byte coalesced loads straight into registers, the 4-bit codes are turned into exact
-// small integers in bf16 with one rotate and one logic op per pair, and contracted on the
-// tensor cores (mma.m16n8k16, fp32 accumulate); block scales are applied to the fp32 block
-// sums in registers.
+// quantized layout of wf_layout.cuh.  HBM-bound: every weight byte is read exactly once.
+// A producer thread streams the CTA's contiguous share of the weight into a shared-memory
+// ring with bulk asynchronous copies (cp.async.bulk + mbarrier), as far ahead as the ring
+// is deep -- for the decode shapes the whole share is in flight from the first cycle --
+// and sixteen consumer warps pick their tile out of each ring stage with 16-byte
+// shared-memory loads.  The 4-bit codes are turned into exact small integers in bf16 with
+// one rotate and one logic op per pair and contracted on the tensor cores (mma.m16n8k16,
+// fp32 accumulate); block scales are applied to the fp32 block sums in registers.
 //
 // Codes enter the MMA with a constant offset (16 + code); the offset is cancelled by
 // starting each block's accumulator at beta * (sum of the block's activations), which is
@@ -28,16 +31,22 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <stdlib.h>
+
+#include <algorithm>
+
 #include "wf_common.cuh"
 
 namespace wf {
 
-constexpr int GEMV_WARPS = 16;
-constexpr int GEMV_THREADS = GEMV_WARPS * 32;
+constexpr int GEMV_WARPS = 16;                       // consumer warps
+constexpr int GEMV_THREADS = (GEMV_WARPS + 1) * 32;  // + one producer warp
+constexpr int GEMV_MAX_STAGES = 16;
+constexpr int GEMV_BAR_SPINS = 1 << 24;
 constexpr int GEMV_XCOLS = 8;  // columns of one mma n-tile
 constexpr int GEMV_FIXUP_SPINS = 1 << 22;
 constexpr int GEMV_SLOT_SPINS = 1 << 24;
-constexpr int GEMV_CTRL_BYTES = 128;  // arrive[] and released[] counters
+constexpr int GEMV_CTRL_BYTES = 128 + 2 * GEMV_MAX_STAGES * 8;  // arrive[], released[], abort, full[], empty[]
 
 struct GemvParams {
     const uint8_t* tiles;
@@ -51,20 +60,53 @@ struct GemvParams {
     int m;        // tokens this pass (<= 8 for bf16, <= 2 for fp32)
     int x_f32;    // 1: x is fp32 and each token is split into 3 exact bf16 columns
     int sx;       // shared-memory row stride of staged x, in bytes
+    int stages;   // ring depth, each stage holds GEMV_WARPS tiles
+    unsigned long long* timing;  // optional [ctas][8] globaltimer stamps (instrumented launches only)
 };
 
 // ---------------------------------------------------------------- small device helpers
-__device__ __forceinline__ uint4 ldg_stream(const void* p) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(p));
-    return v;
+__device__ __forceinline__ uint4 ldg_stream(const void* p) { return *reinterpret_cast<const uint4*>(p); }
+__device__ __forceinline__ uint2 ldg_stream2(const void* p) { return *reinterpret_cast<const uint2*>(p); }
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(void* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
 }
-__device__ __forceinline__ uint2 ldg_stream2(const void* p) {
-    uint2 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
-    return v;
+__device__ __forceinline__ void mbar_arrive(void* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(void* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Bounded wait: false if the phase did not complete within the spin budget.
+__device__ __forceinline__ bool mbar_wait(void* bar, uint32_t parity) {
+    const uint32_t a = smem_u32(bar);
+    for (int spins = 0; spins < GEMV_BAR_SPINS; spins++) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(a), "r"(parity)
+            : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, void* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)),
+                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+// A scratch slot element is {value bits, valid tag}.  It is written and read as ONE 64-bit
+// access so that a reader can never see the tag of one write with the value of another.
+__device__ __forceinline__ void st_slot(uint2* p, uint2 v) {
+    const unsigned long long w = ((unsigned long long)v.y << 32) | v.x;
+    asm volatile("st.relaxed.gpu.global.b64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
+}
+__device__ __forceinline__ uint2 ld_slot(const uint2* p) {
+    unsigned long long w;
+    asm volatile("ld.relaxed.gpu.global.b64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+    return make_uint2((uint32_t)w, (uint32_t)(w >> 32));
 }
 // d = a * b + c, d and c separate so that c can come straight from another register set
 __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -84,7 +126,9 @@ __device__ __forceinline__ float2 half2_bits_to_float2(uint32_t h2) {
 template <int S>
 __device__ __forceinline__ uint32_t nib2(uint32_t w, uint32_t magic) {
     const uint32_t r = (S == 0) ? w : __funnelshift_r(w, w, 4 * S);
-    return (r & 0x00780078u) | magic;
+    uint32_t v;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(v) : "r"(r), "r"(0x00780078u), "r"(magic));  // (r & mask) | magic
+    return v;
 }
 constexpr uint32_t MAGIC_16 = 0x41804180u;   // 16 + code
 constexpr uint32_t MAGIC_256 = 0x43804380u;  // 256 + 16 * code
@@ -212,10 +256,6 @@ template <> struct TileRegs<WF_QTYPE_Q4_K> {
     }
 };
 
-template <int QT> struct Depth { static constexpr int V = 4; };
-template <> struct Depth<WF_QTYPE_Q8_0> { static constexpr int V = 3; };
-template <> struct Depth<WF_QTYPE_Q4_K> { static constexpr int V = 2; };
-
 // ---------------------------------------------------------------- x staging
 // Copies x into shared memory as bf16 rows of `kp` elements (zero beyond k), row stride sx
 // bytes.  bf16 input: row = token.  fp32 input: token t becomes rows 3t, 3t+1, 3t+2 holding
@@ -298,42 +338,87 @@ __device__ void stage_x(const GemvParams& p, uint8_t* xs, float* cinit, int kp, 
 // XC = 1: exactly one live column (one bf16 token); XC = 8: up to 8 columns.
 template <int XC> struct Slots { static constexpr int N = (XC == 1) ? 4 : 2, ELEMS = 16 * XC; };
 
+// Shared-memory map (bytes): [0,32) arrive[8] | [32,64) released[8] | [64,68) abort flag |
+// [128, 128+8*MAX_STAGES) full barriers | then empty barriers | partial sums | exchange row |
+// cinit | staged x | ring stages (128-byte aligned).
 template <int QT, int XC>
 __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvParams p) {
     using T = Tile<QT>;
     using R = TileRegs<QT>;
-    constexpr int DEPTH = Depth<QT>::V;
     constexpr int NSLOT = Slots<XC>::N, ELEMS = Slots<XC>::ELEMS;
-    extern __shared__ __align__(16) uint8_t smem[];
+    constexpr uint32_t STAGE_BYTES = GEMV_WARPS * T::BYTES;
+    extern __shared__ __align__(128) uint8_t smem[];
     int* arrive = reinterpret_cast<int*>(smem);                              // [NSLOT]
     volatile int* released = reinterpret_cast<volatile int*>(smem) + 8;      // [NSLOT]
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem) + 16;
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + 128);                // [stages]
+    uint64_t* empty = full + GEMV_MAX_STAGES;                                // [stages]
     float* partial = reinterpret_cast<float*>(smem + GEMV_CTRL_BYTES);       // [NSLOT][GEMV_WARPS][ELEMS]
     float* exchange = partial + NSLOT * GEMV_WARPS * ELEMS;                  // [128]
     const int kp = p.kt * T::K;
     float4* cinit = reinterpret_cast<float4*>(exchange + 128);               // [kp/32][4]
     uint8_t* xs = reinterpret_cast<uint8_t*>(cinit + (kp >> 5) * 4);         // [xcols][sx]
     const int xcols = p.x_f32 ? 3 * p.m : p.m;
+    uint8_t* ring = smem + (((size_t)(xs - smem) + (size_t)xcols * p.sx + 127) & ~(size_t)127);
 
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, q = lane & 3;
+    // warp-uniform values, obtained in a way the compiler can see is uniform
+    const int warp = __shfl_sync(0xFFFFFFFFu, (int)(threadIdx.x >> 5), 0);
+    const int lane = threadIdx.x & 31, g = lane >> 2, q = lane & 3;
     const int total = p.rt * p.kt;
     const int t0 = (int)((int64_t)total * blockIdx.x / gridDim.x);
     const int t1 = (int)((int64_t)total * (blockIdx.x + 1) / gridDim.x);
-    const int n_my = (t0 + warp < t1) ? (t1 - t0 - warp + GEMV_WARPS - 1) / GEMV_WARPS : 0;
+    const int rounds = (t1 - t0 + GEMV_WARPS - 1) / GEMV_WARPS;
+    const int stages = p.stages;
 
-    // Weight loads first: they are in flight while the activations are staged.
-    R buf[DEPTH];
-    const uint8_t* next = p.tiles + (size_t)(t0 + warp) * T::BYTES;
-#pragma unroll
-    for (int d = 0; d < DEPTH; d++) {
-        if (d < n_my) buf[d].load(next, lane);
-        next += (size_t)GEMV_WARPS * T::BYTES;
+    // Optional timing stamps, the counterpart of the reference's SALT_TIMING kernels
+    // (nvidia/cuda/CudaKernels.java:31-37): warp 0 lane 0 records globaltimer at fixed points.
+    auto stamp = [&](int i) {
+        if (p.timing != nullptr && threadIdx.x == 0) {
+            unsigned long long tm;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tm));
+            p.timing[(size_t)blockIdx.x * 8 + i] = tm;
+        }
+    };
+    stamp(0);
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < 32; i++) reinterpret_cast<int*>(smem)[i] = 0;
+        for (int s = 0; s < stages; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], GEMV_WARPS);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-
-    if (threadIdx.x < 16) reinterpret_cast<int*>(smem)[threadIdx.x] = 0;
-    for (int i = threadIdx.x; i < (kp >> 5) * 16; i += GEMV_THREADS) reinterpret_cast<float*>(cinit)[i] = 0.f;
     __syncthreads();
+
+    // Producer: fill every stage right away; the weights do not depend on anything.
+    auto issue_round = [&](int r) {
+        const int s = r % stages;
+        const int first = t0 + r * GEMV_WARPS;
+        const uint32_t bytes = (uint32_t)min(GEMV_WARPS, t1 - first) * T::BYTES;
+        mbar_expect_tx(&full[s], bytes);
+        bulk_load(ring + (size_t)s * STAGE_BYTES, p.tiles + (size_t)first * T::BYTES, bytes, &full[s]);
+    };
+    if (warp == GEMV_WARPS && lane == 0)
+        for (int r = 0; r < min(rounds, stages); r++) issue_round(r);
+
+    // cinit entries of dead columns stay uninitialised: they only feed dead columns
     stage_x(p, xs, reinterpret_cast<float*>(cinit), kp, R::BETA);
     __syncthreads();
+    stamp(1);
+
+    if (warp == GEMV_WARPS) {  // producer warp: refill stages as the consumers release them
+        if (lane == 0) {
+            for (int r = stages; r < rounds; r++) {
+                if (!mbar_wait(&empty[r % stages], ((r / stages) - 1) & 1) || *abort_flag) {
+                    atomicOr(p.status, STATUS_GEMV_FIXUP_TIMEOUT);
+                    *abort_flag = 1;
+                    break;
+                }
+                issue_round(r);
+            }
+        }
+        return;
+    }
 
     // dead columns read the last live row: their results are computed and never stored
     const uint8_t* xrow = xs + (size_t)(g < xcols ? g : xcols - 1) * p.sx;
@@ -362,9 +447,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvParams 
             for (int u = 0; u < PER_LANE; u++) {
                 const int i = lane + 32 * u;
                 if (i < ELEMS)
-                    asm volatile("st.volatile.global.v2.u32 [%0], {%1,%2};" ::"l"(p.scratch + (size_t)blockIdx.x * 128 + i),
-                                 "r"(__float_as_uint(v[u])), "r"(1u)
-                                 : "memory");
+                    st_slot(p.scratch + (size_t)blockIdx.x * 128 + i, make_uint2(__float_as_uint(v[u]), 1u));
             }
             return;
         }
@@ -383,10 +466,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvParams 
                     uint2 e;
                     int spins = 0;
                     do {
-                        asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];"
-                                     : "=r"(e.x), "=r"(e.y)
-                                     : "l"(slot_ptr)
-                                     : "memory");
+                        e = ld_slot(slot_ptr);
                         if (e.y != 0u) break;
                         __nanosleep(32);
                     } while (++spins < GEMV_FIXUP_SPINS);
@@ -395,7 +475,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvParams 
                         gave_up = true;
                     } else {
                         v[u] += __uint_as_float(e.x);
-                        asm volatile("st.volatile.global.v2.u32 [%0], {%1,%2};" ::"l"(slot_ptr), "r"(0u), "r"(0u) : "memory");
+                        st_slot(slot_ptr, make_uint2(0u, 0u));
                     }
                 }
                 gave_up = __any_sync(0xFFFFFFFFu, gave_up);
@@ -466,42 +546,73 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvParams 
         seg_end = min((rt + 1) * p.kt, t1);
     };
 
-    int t = t0 + warp;
-    for (int i0 = 0; i0 < n_my; i0 += DEPTH) {
-#pragma unroll
-        for (int d = 0; d < DEPTH; d++) {
-            if (i0 + d < n_my) {
-                while (t >= seg_end) flush();
-                buf[d].template compute<XC>(acc, xrow, cinit, (t - rt * p.kt) * T::K, q);
-                if (i0 + d + DEPTH < n_my) buf[d].load(next, lane);
-                next += (size_t)GEMV_WARPS * T::BYTES;
-                t += GEMV_WARPS;
-            }
+    // One tile per round per warp.  Stage index and phase are tracked incrementally.
+    const int n_my = (t0 + warp < t1) ? (t1 - t0 - warp + GEMV_WARPS - 1) / GEMV_WARPS : 0;
+    int s = 0, t = t0 + warp;
+    uint32_t phase = 0;
+    const uint8_t* my_tile = ring + (size_t)warp * T::BYTES;
+    stamp(2);
+    for (int r = 0;; r++) {
+        // leave every segment that ends before my next tile (all of them once I am out of tiles)
+        while (seg_begin < t1 && (r >= n_my || t >= seg_end)) flush();
+        if (r >= rounds) break;
+        // Wait for the round's data even without a tile in it: the release below must not be
+        // counted before the stage has been refilled for this round.
+        if (!mbar_wait(&full[s], phase)) {
+            if (lane == 0) atomicOr(p.status, STATUS_GEMV_FIXUP_TIMEOUT);
+            *abort_flag = 1;
+            break;
+        }
+        if (r == 0) stamp(3);
+        if (r < n_my) {
+            R regs;
+            regs.load(my_tile + (size_t)s * STAGE_BYTES, lane);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]);
+            regs.template compute<XC>(acc, xrow, cinit, (t - rt * p.kt) * T::K, q);
+        } else if (lane == 0) {
+            mbar_arrive(&empty[s]);
+        }
+        t += GEMV_WARPS;
+        if (++s == stages) {
+            s = 0;
+            phase ^= 1u;
         }
     }
-    while (seg_begin < t1) flush();
+    stamp(4);
+    while (seg_begin < t1) flush();  // only reached after a failed wait
+    stamp(5);
 }
 
 // ---------------------------------------------------------------- host side
 template <int XC>
-static size_t gemv_smem_bytes(int kp, int xcols, int* sx_out) {
+static size_t gemv_fixed_smem(int kp, int xcols, int* sx_out) {
     const int sx = kp * 2 + 64;  // +64: consecutive rows start 16 banks apart
     if (sx_out) *sx_out = sx;
-    return GEMV_CTRL_BYTES + (size_t)Slots<XC>::N * GEMV_WARPS * Slots<XC>::ELEMS * 4 + 128 * 4 + (size_t)(kp / 32) * 64 +
-           (size_t)xcols * sx;
+    size_t b = GEMV_CTRL_BYTES + (size_t)Slots<XC>::N * GEMV_WARPS * Slots<XC>::ELEMS * 4 + 128 * 4 + (size_t)(kp / 32) * 64 +
+               (size_t)xcols * sx;
+    return (b + 127) & ~(size_t)127;
 }
 
 constexpr size_t GEMV_SMEM_LIMIT = 227 * 1024;
 
+// Ring depth that fits beside the staged activations (0 = does not fit at all).
+template <int XC>
+static int gemv_stages(int qt, int kp, int xcols) {
+    const size_t fixed = gemv_fixed_smem<XC>(kp, xcols, nullptr), stage = (size_t)GEMV_WARPS * tile_bytes(qt);
+    if (fixed + stage > GEMV_SMEM_LIMIT) return 0;
+    return (int)std::min<size_t>((GEMV_SMEM_LIMIT - fixed) / stage, GEMV_MAX_STAGES);
+}
+
 // Largest number of tokens one pass can take: bounded by the 8 mma columns (3 per fp32
-// token) and by the shared memory the staged activations need.
+// token) and by the shared memory the staged activations and a 2-deep ring need.
 int gemv_max_tokens_per_pass(const Weight& w, int x_dtype) {
     const int kp = (int)w.g.kt * tile_k(w.g.qtype);
     const int per_tok = x_dtype == WF_DTYPE_F32 ? 3 : 1;
     int best = 0;
     for (int m = 1; m * per_tok <= GEMV_XCOLS; m++)
-        if (gemv_smem_bytes<8>(kp, m * per_tok, nullptr) <= GEMV_SMEM_LIMIT) best = m;
-    if (best == 0 && per_tok == 1 && gemv_smem_bytes<1>(kp, 1, nullptr) <= GEMV_SMEM_LIMIT) best = 1;
+        if (gemv_stages<8>(w.g.qtype, kp, m * per_tok) >= 2) best = m;
+    if (best == 0 && per_tok == 1 && gemv_stages<1>(w.g.qtype, kp, 1) >= 1) best = 1;
     return best;
 }
 
@@ -559,6 +670,8 @@ int gemv_launch(Context* c, const GemvCall& call, cudaStream_t s) {
     GemvScratch& sc = c->gemv_scratch[s];
 
     const size_t esz = call.x_dtype == WF_DTYPE_F32 ? 4 : 2;
+    int max_rounds = (int)((total / grid + 1 + GEMV_WARPS - 1) / GEMV_WARPS);
+    if (const char* cap = getenv("WF_GEMV_MAX_STAGES")) max_rounds = std::max(1, std::min(max_rounds, atoi(cap)));
     for (int64_t m0 = 0; m0 < call.m; m0 += per_pass) {
         GemvParams p{};
         p.tiles = w.d_tiles;
@@ -566,6 +679,7 @@ int gemv_launch(Context* c, const GemvCall& call, cudaStream_t s) {
         p.y = call.d_y + m0 * call.ldy;
         p.scratch = sc.d_slots;
         p.status = c->d_status;
+        p.timing = c->salt >= 2 ? c->d_timing : nullptr;
         p.ldy = call.ldy;
         p.col0 = call.col0;
         p.ldx = w.g.k;
@@ -576,11 +690,14 @@ int gemv_launch(Context* c, const GemvCall& call, cudaStream_t s) {
         p.m = (int)((call.m - m0) < per_pass ? (call.m - m0) : per_pass);
         p.x_f32 = call.x_dtype == WF_DTYPE_F32;
         const int xcols = p.x_f32 ? 3 * p.m : p.m;
+        const size_t stage = (size_t)GEMV_WARPS * tile_bytes(qt);
         cudaError_t e;
         if (xcols == 1) {
-            e = launch_qt<1>(qt, p, grid, gemv_smem_bytes<1>(kp, xcols, &p.sx), s);
+            p.stages = std::min(gemv_stages<1>(qt, kp, xcols), std::max(max_rounds, 1));
+            e = launch_qt<1>(qt, p, grid, gemv_fixed_smem<1>(kp, xcols, &p.sx) + p.stages * stage, s);
         } else {
-            e = launch_qt<8>(qt, p, grid, gemv_smem_bytes<8>(kp, xcols, &p.sx), s);
+            p.stages = std::min(gemv_stages<8>(qt, kp, xcols), std::max(max_rounds, 1));
+            e = launch_qt<8>(qt, p, grid, gemv_fixed_smem<8>(kp, xcols, &p.sx) + p.stages * stage, s);
         }
         if (e != cudaSuccess) return cuda_status(c, e, "gemv launch");
         c->launches++;

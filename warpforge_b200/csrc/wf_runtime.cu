@@ -160,6 +160,7 @@ int wf_destroy(int64_t ctx) {
     if (c->h_stage) cudaFreeHost(c->h_stage);
     if (c->d_stage) cudaFree(c->d_stage);
     cudaFree(c->d_status);
+    if (c->d_timing) cudaFree(c->d_timing);
     cudaStreamDestroy(c->stream);
     c->magic = 0;
     c->mu.unlock();
@@ -522,6 +523,27 @@ int wf_event_elapsed_ms(int64_t ctx, int64_t start, int64_t stop, float* ms) {
         return WF_ERR_INVALID_HANDLE;
     WF_CUDA(c, cudaEventSynchronize(b));
     WF_CUDA(c, cudaEventElapsedTime(ms, a, b));
+    return WF_OK;
+}
+
+int wf_set_salt(int64_t ctx, int salt) {
+    WF_ENTER(ctx);
+    if (salt < 0 || salt > 2) return WF_ERR_INVALID_ARGUMENT;
+    if (salt >= 2 && !c->d_timing) {
+        WF_CUDA(c, cudaMalloc(&c->d_timing, (size_t)c->sm_count * 8 * sizeof(unsigned long long)));
+        WF_CUDA(c, cudaMemset(c->d_timing, 0, (size_t)c->sm_count * 8 * sizeof(unsigned long long)));
+    }
+    c->salt = salt;
+    return WF_OK;
+}
+
+int wf_read_timing(int64_t ctx, int64_t* out, int64_t n) {
+    WF_ENTER(ctx);
+    if (!out || n < 0) return WF_ERR_INVALID_ARGUMENT;
+    if (!c->d_timing) return set_error(c, WF_ERR_INVALID_ARGUMENT, "timing stamps are off (wf_set_salt(ctx, 2) first)");
+    const int64_t have = (int64_t)c->sm_count * 8;
+    WF_CUDA(c, cudaDeviceSynchronize());
+    WF_CUDA(c, cudaMemcpy(out, c->d_timing, (size_t)std::min(n, have) * sizeof(int64_t), cudaMemcpyDeviceToHost));
     return WF_OK;
 }
 
