@@ -1,0 +1,308 @@
+"""Benchmark of the quantized-matmul hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Workload (BASELINE config 4): the 224 Q4_0 projections of a 7B-shape Llama decoder, batch 1,
+every weight a distinct buffer (3.64 GB per token, far larger than L2, so every step reads
+HBM cold).  One step = one token = all projections in layer order, recorded once as a CUDA
+graph; with N > 1 ranks the weights are row-sharded and every projection is followed by the
+all-gather of its shards over NCCL (strong scaling: the same token stream on more GPUs).
+The dominant kernel is the Q4_0 decode GEMV, so `roofline` is the headline "Q4_0 GEMV HBM
+GB/s (% of peak)"; `gemv_sweep` adds BASELINE config 2 (the [11008x4096] / [4096x11008]
+sweep at batch 1, 4, 8), timed over 12 rotating weight copies (300 MB, larger than L2).
+
+Inputs are seeded synthetic GGUF blocks with the configs' value distributions; there is no
+dataset behind this path.  `--impl reference` times the CPU restatement of the reference's
+own path (block dequant to fp32 + sequential fp32 dot, oracle/wf_oracle.c) on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "decode_tokens_per_s_7b_q4_0"
+UNIT = "tok/s"
+WORKLOAD = ("BASELINE config 4: 7B-shape Llama decode, 224 Q4_0 projections (32 layers x "
+            "{4x[4096x4096], 2x[11008x4096], [4096x11008]}), batch 1, bf16 activations, fp32 out")
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return float(p["hbm_gbs"]), "measured (MEASURED_PEAKS.json, stream copy)"
+    return 6650.0, "fallback (earlier measurement on this pool)"
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle samples taken while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int):
+        self.rows, self.proc, self.device_index = [], None, device_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.device_index)],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self) -> dict:
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm = [float(r[1]) for r in self.rows if len(r) >= 9 and r[1].replace(".", "").isdigit()]
+        mx = [float(r[2]) for r in self.rows if len(r) >= 9 and r[2].replace(".", "").isdigit()]
+        reasons = set()
+        for r in self.rows:
+            if len(r) >= 9:
+                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def cpu_layer_time(orc, spec, threads: int, repeats: int) -> float:
+    """Seconds for one layer (7 projections, batch 1) on the CPU path."""
+    from oracle import oracle as O
+    from warpforge_b200 import quant as Q
+
+    oq = {"Q4_0": O.Q4_0, "Q8_0": O.Q8_0, "Q4_K": O.Q4_K}[spec.qtype.name]
+    mats = []
+    for i, (name, rows, k) in enumerate(spec.projections):
+        blocks = Q.synth_weight(spec.qtype, rows, k, Q.config_seed(spec.config, i))
+        x = Q.bf16_bits_to_float(Q.synth_activation_bf16(1, k, Q.config_seed(spec.config, 100 + k)))
+        mats.append((blocks, rows, k, x))
+    best = float("inf")
+    for _ in range(repeats):
+        t = time.perf_counter()
+        for blocks, rows, k, x in mats:
+            orc.qlinear(oq, blocks, rows, k, x, nthreads=threads)
+        best = min(best, time.perf_counter() - t)
+    return best
+
+
+def run_reference(args) -> None:
+    """The reference's own CPU implementation of the path (restated in C), all host threads.
+    Each step is a bounded sample: one of the 32 identical-shape layers; tokens/s follows by
+    dividing by the layer count."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import oracle as O
+    from warpforge_b200.decode import LLAMA_7B_Q4_0 as spec
+
+    orc = O.COracle()
+    threads = orc.max_threads()
+    for _ in range(max(args.warmup, 1)):
+        cpu_layer_time(orc, spec, threads, 1)
+    times = [cpu_layer_time(orc, spec, threads, 1) for _ in range(args.steps)]
+    t_layer = float(np.mean(times))
+    tok_s = 1.0 / (t_layer * spec.layers)
+    sample = f"1 of {spec.layers} layers per step (7 projections, 114 MB of Q4_0 blocks), x{spec.layers} for a token"
+    line = {"impl": "reference", "metric": METRIC, "value": tok_s, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": t_layer * spec.layers * 1e3, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "timed": sample},
+            "cpu_baseline": {"value": tok_s, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": tok_s, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def gemv_sweep(ctx, hbm_peak: float) -> list:
+    """BASELINE config 2: cold-HBM Q4_0 GEMV at batch 1/4/8 over 12 rotating weight copies."""
+    from warpforge_b200 import _native as N, quant as Q
+    from warpforge_b200.backend import QuantizedWeight
+
+    out, lib, qt = [], ctx._lib, Q.QuantizationType.Q4_0
+    copies, iters = 12, 120
+    for rows, k in ((11008, 4096), (4096, 11008)):
+        blocks = Q.synth_q4_0(rows, k, Q.config_seed(2, rows))
+        ws = [QuantizedWeight(ctx, qt, blocks, rows, k) for _ in range(copies)]
+        for m in (1, 4, 8):
+            x = Q.synth_activation_bf16(m, k, Q.config_seed(2, m))
+            dx, dy = ctx.allocate(x.nbytes), ctx.allocate(m * rows * 4)
+            ctx.copy_to_device(dx, x)
+            for i in range(copies):
+                ctx._ck("wf_qlinear", lib.wf_qlinear(ctx.handle, ws[i].handle, dx, N.WF_DTYPE_BF16, 1, m, dy, 1, 0))
+            ctx.synchronize()
+            ctx.graph_begin()
+            for i in range(iters):
+                ctx._ck("wf_qlinear", lib.wf_qlinear(ctx.handle, ws[i % copies].handle, dx, N.WF_DTYPE_BF16, 1, m, dy, 1, 0))
+            g = ctx.graph_end()
+            e0, e1 = ctx.create_event(), ctx.create_event()
+            ctx.graph_launch(g)
+            ctx.synchronize()
+            best = float("inf")
+            for _ in range(3):
+                ctx.record_event(e0)
+                ctx.graph_launch(g)
+                ctx.record_event(e1)
+                ctx.synchronize()
+                best = min(best, ctx.elapsed_ms(e0, e1) / iters)
+            alg = rows * qt.row_bytes(k) + x.nbytes + m * rows * 4
+            gbs = alg / best / 1e6
+            out.append({"shape": [rows, k], "batch": m, "us": round(best * 1e3, 3), "GB/s": round(gbs, 1),
+                        "frac_of_measured_peak": round(gbs / hbm_peak, 4), "frac_of_8TBs": round(gbs / 8000.0, 4)})
+            ctx.graph_destroy(g)
+            ctx.free(dx)
+            ctx.free(dy)
+        for w in ws:
+            w.close()
+    return out
+
+
+def run_ours(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N > 1")
+    dist = None
+    if world > 1:
+        import torch.distributed as dist  # control plane only: id exchange, barrier, max over ranks
+
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+
+    from warpforge_b200.backend import CudaContext
+    from warpforge_b200.decode import Communicator, LLAMA_7B_Q4_0, ProjectionStack
+
+    ctx = CudaContext(local_rank)
+    comm = None
+    if world > 1:
+        ids = [Communicator.create_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(ids, src=0)
+        comm = Communicator(ctx, ids[0], rank, world)
+    spec = LLAMA_7B_Q4_0
+    stack = ProjectionStack(ctx, spec, tokens=1, comm=comm)
+    stack.record()
+
+    def barrier():
+        ctx.synchronize()
+        if dist is not None:
+            dist.barrier()
+
+    for _ in range(max(args.warmup, 3)):
+        stack.step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = ctx.create_event(), ctx.create_event()
+    launches0 = ctx.launch_count()
+    barrier()
+    ctx.record_event(e0)
+    for _ in range(args.steps):
+        stack.step()
+    ctx.record_event(e1)
+    ctx.synchronize()
+    ms = ctx.elapsed_ms(e0, e1)
+    launches = ctx.launch_count() - launches0
+    barrier()
+
+    # end to end through the public step call: pinned host activations in, last output out
+    y_out = np.empty((1, spec.projections[-1][1]), np.float32)
+    pinned_in = {k: ctx.host_alloc(v.nbytes) for k, v in stack.x_host.items()}
+    pinned_out = ctx.host_alloc(y_out.nbytes)
+    for _ in range(3):
+        stack.step_host(stack.x_host, y_out, pinned_in, pinned_out)
+    barrier()
+    t = time.perf_counter()
+    ctx.record_event(e0)
+    for _ in range(args.steps):
+        stack.step_host(stack.x_host, y_out, pinned_in, pinned_out)
+    ctx.record_event(e1)
+    ctx.synchronize()
+    e2e_ms = max(ctx.elapsed_ms(e0, e1), (time.perf_counter() - t) * 1e3)
+    clocks = sampler.stop() if rank == 0 else None
+
+    if dist is not None:
+        import torch
+
+        tt = torch.tensor([ms, e2e_ms], dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = float(tt[0]), float(tt[1])
+
+    if rank == 0:
+        hbm_peak, peak_src = measured_peaks()
+        ms_step = ms / args.steps
+        tok_s = 1e3 / ms_step
+        alg_bytes = stack.algorithmic_bytes_per_step()          # this rank's shard
+        n_launch = spec.layers * len(spec.projections)
+        gbs = alg_bytes / (ms_step * 1e-3) / 1e9
+        h2d = sum(v.nbytes for v in stack.x_host.values())
+        line = {
+            "metric": METRIC, "value": tok_s, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16 activations x 4-bit codes, fp32 accumulate", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "parallelism": f"row-sharded tp{world}" if world > 1 else "single GPU",
+                       "l2": "inputs larger than L2: 3.64 GB of distinct weights per step", "bytes_per_token": spec.bytes_per_token()},
+            "e2e": {"value": 1e3 / (e2e_ms / args.steps), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": int(y_out.nbytes)},
+            "gpu_launches": int(launches),
+            "clocks": clocks,
+            "roofline": {"bound": "hbm", "kernel": "gemv_kernel<Q4_0, 1 column>", "achieved": gbs, "peak": hbm_peak, "unit": "GB/s",
+                         "frac": gbs / hbm_peak, "frac_of_8TBs_nominal": gbs / 8000.0, "peak_source": peak_src,
+                         "bytes_per_launch": alg_bytes / n_launch, "us_per_launch": ms_step * 1e3 / n_launch, "traffic": None},
+        }
+        if world == 1:
+            line["gemv_sweep"] = gemv_sweep(ctx, hbm_peak)
+            from oracle import oracle as O
+
+            orc = O.COracle()
+            threads = orc.max_threads()
+            t_layer = cpu_layer_time(orc, spec, threads, 2)
+            line["cpu_baseline"] = {"value": 1.0 / (t_layer * spec.layers), "unit": UNIT, "cores": threads, "kind": "port",
+                                    "sample": f"1 of {spec.layers} layers (7 projections), best of 2, x{spec.layers}"}
+        print(json.dumps(line), flush=True)
+    stack.close()
+    if comm is not None:
+        comm.close()
+    ctx.close()
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

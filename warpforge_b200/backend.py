@@ -133,6 +133,18 @@ class CudaContext:
     def free(self, dptr: int) -> None:
         self._ck("wf_free", self._lib.wf_free(self.handle, dptr))
 
+    def host_alloc(self, nbytes: int) -> int:
+        """Pinned host memory (GpuBackend.allocatePinned)."""
+        p = ctypes.c_void_p()
+        self._ck("wf_host_alloc", self._lib.wf_host_alloc(self.handle, nbytes, ctypes.byref(p)))
+        return p.value
+
+    def host_free(self, ptr: int) -> None:
+        self._ck("wf_host_free", self._lib.wf_host_free(self.handle, ptr))
+
+    def set_salt(self, salt: int) -> None:
+        self._ck("wf_set_salt", self._lib.wf_set_salt(self.handle, salt))
+
     def copy_to_device(self, dptr: int, host: np.ndarray, stream: int = 0, sync: bool = True) -> None:
         host = np.ascontiguousarray(host)
         self._ck("wf_memcpy_h2d", self._lib.wf_memcpy_h2d(self.handle, dptr, host.ctypes.data, host.nbytes, stream, int(sync)))

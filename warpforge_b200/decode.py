@@ -1,0 +1,162 @@
+"""Projection stacks of a decoder, run through the quantized-linear path.
+
+The timed path of the decode workloads is "the quantized projections, row-sharded": for a
+7B-shape Llama layer that is Wq, Wk, Wv, Wo [4096 x 4096], Wgate, Wup [11008 x 4096] and
+Wdown [4096 x 11008], 32 layers, every weight a distinct buffer in HBM.  Attention, norms
+and activations lie outside this path, so each projection reads a fixed activation buffer
+of its input width and the projections are issued in layer order on one stream; with more
+than one rank every projection is followed by the all-gather of its row shards.  One step
+(= one token) is recorded once as a CUDA graph and replayed.
+
+Host-side orchestration only; all arithmetic happens in libwfb200 kernels.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+from typing import List, Optional
+
+import numpy as np
+
+from . import _native as N
+from . import quant as Q
+from .backend import CudaContext, QuantizedWeight
+
+
+@dataclass(frozen=True)
+class StackSpec:
+    name: str
+    qtype: Q.QuantizationType
+    layers: int
+    projections: tuple  # (name, rows, k)
+    config: int         # BASELINE config number, used for seeding
+
+    def bytes_per_token(self) -> int:
+        """Algorithmic weight bytes one token reads: GGUF block bytes of every projection."""
+        return self.layers * sum(rows * self.qtype.row_bytes(k) for _, rows, k in self.projections)
+
+
+LLAMA_7B_Q4_0 = StackSpec("7b-shape Q4_0", Q.QuantizationType.Q4_0, 32, (
+    ("wq", 4096, 4096), ("wk", 4096, 4096), ("wv", 4096, 4096), ("wo", 4096, 4096),
+    ("wgate", 11008, 4096), ("wup", 11008, 4096), ("wdown", 4096, 11008)), 4)
+
+LLAMA_70B_Q4_K = StackSpec("70b-shape Q4_K", Q.QuantizationType.Q4_K, 80, (
+    ("wq", 8192, 8192), ("wk", 1024, 8192), ("wv", 1024, 8192), ("wo", 8192, 8192),
+    ("wgate", 28672, 8192), ("wup", 28672, 8192), ("wdown", 8192, 28672)), 5)
+
+
+class Communicator:
+    """NCCL communicator owned by the native library (wf_comm_*)."""
+
+    def __init__(self, context: CudaContext, unique_id: bytes, rank: int, world: int):
+        self.context, self.rank, self.world = context, rank, world
+        h = ctypes.c_int64()
+        buf = ctypes.create_string_buffer(unique_id, 128)
+        context._ck("wf_comm_init", context._lib.wf_comm_init(context.handle, buf, rank, world, ctypes.byref(h)))
+        self.handle = h.value
+
+    @staticmethod
+    def create_unique_id() -> bytes:
+        buf = ctypes.create_string_buffer(128)
+        N.check("wf_comm_get_unique_id", N.load().wf_comm_get_unique_id(buf))
+        return buf.raw
+
+    def all_gather(self, send_dev: int, recv_dev: int, bytes_per_rank: int, stream: int = 0) -> None:
+        c = self.context
+        c._ck("wf_allgather", c._lib.wf_allgather(c.handle, self.handle, send_dev, recv_dev, bytes_per_rank, stream))
+
+    def close(self) -> None:
+        if self.handle and self.context.handle:
+            h, self.handle = self.handle, 0
+            self.context._ck("wf_comm_destroy", self.context._lib.wf_comm_destroy(self.context.handle, h))
+
+
+class ProjectionStack:
+    def __init__(self, context: CudaContext, spec: StackSpec, tokens: int = 1, comm: Optional[Communicator] = None,
+                 layers: Optional[int] = None):
+        self.ctx, self.spec, self.m, self.comm = context, spec, tokens, comm
+        self.rank = comm.rank if comm else 0
+        self.world = comm.world if comm else 1
+        self.layers = layers if layers is not None else spec.layers
+        self.weights: List[List[QuantizedWeight]] = []
+        self.blocks = {}
+        self.x_host = {}
+        self.x_dev = {}
+        self.y_dev = {}
+        self.graph = 0
+        self._build()
+
+    def _build(self) -> None:
+        spec, ctx = self.spec, self.ctx
+        for i, (name, rows, k) in enumerate(spec.projections):
+            self.blocks[name] = Q.synth_weight(spec.qtype, rows, k, Q.config_seed(spec.config, i))
+            if k not in self.x_host:
+                self.x_host[k] = Q.synth_activation_bf16(self.m, k, Q.config_seed(spec.config, 100 + k))
+                self.x_dev[k] = ctx.allocate(self.x_host[k].nbytes)
+                ctx.copy_to_device(self.x_dev[k], self.x_host[k])
+            self.y_dev[name] = ctx.allocate(self.m * rows * 4)
+        for _ in range(self.layers):
+            self.weights.append([QuantizedWeight(ctx, spec.qtype, self.blocks[name], rows, k, self.rank, self.world)
+                                 for name, rows, k in spec.projections])
+
+    def device_weight_bytes(self) -> int:
+        return sum(w.device_bytes() for layer in self.weights for w in layer)
+
+    def algorithmic_bytes_per_step(self) -> int:
+        """GGUF block bytes this rank's shards hold, plus activations read and outputs written."""
+        spec = self.spec
+        per_layer = 0
+        for name, rows, k in spec.projections:
+            per_layer += (rows // self.world) * spec.qtype.row_bytes(k) + self.m * k * 2 + self.m * (rows // self.world) * 4
+        return per_layer * self.layers
+
+    def _issue(self, stream: int = 0) -> None:
+        ctx, lib = self.ctx, self.ctx._lib
+        for layer in self.weights:
+            for w, (name, rows, k) in zip(layer, self.spec.projections):
+                if self.comm is None:
+                    rc = lib.wf_qlinear(ctx.handle, w.handle, self.x_dev[k], N.WF_DTYPE_BF16, 1, self.m,
+                                        self.y_dev[name], 1, stream)
+                    ctx._ck("wf_qlinear", rc)
+                else:
+                    rc = lib.wf_qlinear_allgather(ctx.handle, self.comm.handle, w.handle, self.x_dev[k], N.WF_DTYPE_BF16,
+                                                  self.m, self.y_dev[name], stream)
+                    ctx._ck("wf_qlinear_allgather", rc)
+
+    def record(self, stream: int = 0) -> None:
+        """Issue one step eagerly (allocates whatever the kernels need), then record it."""
+        self._issue(stream)
+        self.ctx.synchronize(stream)
+        self.ctx.graph_begin(stream)
+        self._issue(stream)
+        self.graph = self.ctx.graph_end(stream)
+
+    def step(self, stream: int = 0) -> None:
+        self.ctx.graph_launch(self.graph, stream)
+
+    def step_host(self, x_host: dict, y_out: np.ndarray, pinned_in: dict, pinned_out: int, stream: int = 0) -> None:
+        """One token end to end: activations from pinned host memory, the step, the last
+        projection's output back to pinned host memory, then wait."""
+        ctx, lib = self.ctx, self.ctx._lib
+        for k, dptr in self.x_dev.items():
+            ctypes.memmove(pinned_in[k], x_host[k].ctypes.data, x_host[k].nbytes)
+            ctx._ck("wf_memcpy_h2d", lib.wf_memcpy_h2d(ctx.handle, dptr, pinned_in[k], x_host[k].nbytes, stream, 0))
+        self.step(stream)
+        last = self.spec.projections[-1][0]
+        ctx._ck("wf_memcpy_d2h", lib.wf_memcpy_d2h(ctx.handle, pinned_out, self.y_dev[last], y_out.nbytes, stream, 1))
+        ctypes.memmove(y_out.ctypes.data, pinned_out, y_out.nbytes)
+
+    def read_output(self, name: str) -> np.ndarray:
+        rows = dict((n, r) for n, r, _ in self.spec.projections)[name]
+        out = np.empty((self.m, rows), np.float32)
+        self.ctx.copy_to_host(out, self.y_dev[name])
+        return out
+
+    def close(self) -> None:
+        if self.graph:
+            self.ctx.graph_destroy(self.graph)
+            self.graph = 0
+        for layer in self.weights:
+            for w in layer:
+                w.close()
+        self.weights = []
