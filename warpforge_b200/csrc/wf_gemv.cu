@@ -61,6 +61,7 @@ struct GemvParams {
     int x_f32;    // 1: x is fp32 and each token is split into 3 exact bf16 columns
     int sx;       // shared-memory row stride of staged x, in bytes
     int stages;   // ring depth, each stage holds GEMV_WARPS tiles
+    int chunk_q, chunk_r;  // CTA b owns tiles [b*q + min(b,r), (b+1)*q + min(b+1,r))
     unsigned long long* timing;  // optional [ctas][8] globaltimer stamps (instrumented launches only)
 };
 
@@ -75,22 +76,37 @@ __device__ __forceinline__ void mbar_init(void* bar, int count) {
 __device__ __forceinline__ void mbar_arrive(void* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// arrive from the lanes whose `pred` is non-zero, without a branch
+__device__ __forceinline__ void mbar_arrive_if(void* bar, uint32_t pred) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %1, 0;\n\t@p mbarrier.arrive.shared::cta.b64 _, [%0];\n\t}" ::"r"(smem_u32(bar)),
+        "r"(pred)
+        : "memory");
+}
 __device__ __forceinline__ void mbar_expect_tx(void* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
 // Bounded wait: false if the phase did not complete within the spin budget.
 __device__ __forceinline__ bool mbar_wait(void* bar, uint32_t parity) {
-    const uint32_t a = smem_u32(bar);
-    for (int spins = 0; spins < GEMV_BAR_SPINS; spins++) {
-        uint32_t ok;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(ok)
-            : "r"(a), "r"(parity)
-            : "memory");
-        if (ok) return true;
-    }
-    return false;
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, q;\n\t"
+        ".reg .u32 n;\n\t"
+        "mov.u32 n, 0;\n\t"
+        "WF_WAIT_%=:\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "@p bra WF_DONE_%=;\n\t"
+        "add.u32 n, n, 1;\n\t"
+        "setp.lt.u32 q, n, %3;\n\t"
+        "@q bra WF_WAIT_%=;\n\t"
+        "WF_DONE_%=:\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"((uint32_t)GEMV_BAR_SPINS)
+        : "memory");
+    return ok != 0;
 }
 __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, void* bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)),
@@ -121,24 +137,40 @@ __device__ __forceinline__ float2 half2_bits_to_float2(uint32_t h2) {
     return __half22float2(*reinterpret_cast<const __half2*>(&h2));
 }
 
-// The codes of nibble pair S of a plane word as bf16x2 `base + scale * code`:
-// magic 0x4180 -> 16 + code, magic 0x4380 -> 256 + 16 * code.  Exact.
-template <int S>
-__device__ __forceinline__ uint32_t nib2(uint32_t w, uint32_t magic) {
-    const uint32_t r = (S == 0) ? w : __funnelshift_r(w, w, 4 * S);
-    uint32_t v;
-    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(v) : "r"(r), "r"(0x00780078u), "r"(magic));  // (r & mask) | magic
-    return v;
-}
+// Codes enter the MMA as bf16 `base + scale * code`: magic 0x4180 -> 16 + code,
+// magic 0x4380 -> 256 + 16 * code (nibble in the top four mantissa bits).  Exact.
 constexpr uint32_t MAGIC_16 = 0x41804180u;   // 16 + code
 constexpr uint32_t MAGIC_256 = 0x43804380u;  // 256 + 16 * code
 
-// d = c + sum over one 32-k block of (base + scale * code) * x, rows g / g+8 of the fragment
+// d = c + sum over one 32-k block of (base + scale * code) * x, rows g / g+8 of the fragment.
+// One asm block: three rotates and eight logic ops unpack the two words, two MMAs consume
+// them.  The temporaries live inside the block so the register allocator is free to build
+// the MMA operand tuples in place.
 __device__ __forceinline__ void block_mma(float (&d)[4], uint32_t wg, uint32_t wh, const uint4& xb, uint32_t magic,
                                           float c0, float c1, float c2, float c3) {
-    mma_bf16(d, nib2<0>(wg, magic), nib2<0>(wh, magic), nib2<1>(wg, magic), nib2<1>(wh, magic), xb.x, xb.y, c0, c1, c2, c3);
-    mma_bf16(d, nib2<2>(wg, magic), nib2<2>(wh, magic), nib2<3>(wg, magic), nib2<3>(wh, magic), xb.z, xb.w, d[0], d[1],
-             d[2], d[3]);
+    asm(
+        "{\n\t"
+        ".reg .b32 g1, g2, g3, h1, h2, h3, a0, a1, a2, a3, a4, a5, a6, a7;\n\t"
+        "shf.r.wrap.b32 g1, %4, %4, 4;\n\t"
+        "shf.r.wrap.b32 h1, %5, %5, 4;\n\t"
+        "shf.r.wrap.b32 g2, %4, %4, 8;\n\t"
+        "shf.r.wrap.b32 h2, %5, %5, 8;\n\t"
+        "shf.r.wrap.b32 g3, %4, %4, 12;\n\t"
+        "shf.r.wrap.b32 h3, %5, %5, 12;\n\t"
+        "lop3.b32 a0, %4, %14, %15, 0xEA;\n\t"
+        "lop3.b32 a1, %5, %14, %15, 0xEA;\n\t"
+        "lop3.b32 a2, g1, %14, %15, 0xEA;\n\t"
+        "lop3.b32 a3, h1, %14, %15, 0xEA;\n\t"
+        "lop3.b32 a4, g2, %14, %15, 0xEA;\n\t"
+        "lop3.b32 a5, h2, %14, %15, 0xEA;\n\t"
+        "lop3.b32 a6, g3, %14, %15, 0xEA;\n\t"
+        "lop3.b32 a7, h3, %14, %15, 0xEA;\n\t"
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {a0,a1,a2,a3}, {%6,%7}, {%10,%11,%12,%13};\n\t"
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {a4,a5,a6,a7}, {%8,%9}, {%0,%1,%2,%3};\n\t"
+        "}\n"
+        : "=&f"(d[0]), "=&f"(d[1]), "=&f"(d[2]), "=&f"(d[3])
+        : "r"(wg), "r"(wh), "r"(xb.x), "r"(xb.y), "r"(xb.z), "r"(xb.w), "f"(c0), "f"(c1), "f"(c2), "f"(c3),
+          "r"(0x00780078u), "r"(magic));
 }
 
 __device__ __forceinline__ uint32_t word_of(const uint4& v, int j) {
@@ -271,7 +303,7 @@ __device__ void stage_x(const GemvParams& p, uint8_t* xs, float* cinit, int kp, 
     const int total = p.m * groups;
     for (int idx = threadIdx.x; idx < ((total + 31) & ~31); idx += GEMV_THREADS) {  // warp-uniform trip count
         const bool live = idx < total;
-        const int t = live ? idx / groups : 0, c8 = live ? idx - t * groups : 0;
+        const int t = (live && p.m > 1) ? idx / groups : 0, c8 = live ? idx - t * groups : 0;
         const bool in_k = live && (c8 * 8 < p.k);
         float sum[3] = {0.f, 0.f, 0.f};
         if (!p.x_f32) {
@@ -364,9 +396,9 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvParams 
     // warp-uniform values, obtained in a way the compiler can see is uniform
     const int warp = __shfl_sync(0xFFFFFFFFu, (int)(threadIdx.x >> 5), 0);
     const int lane = threadIdx.x & 31, g = lane >> 2, q = lane & 3;
-    const int total = p.rt * p.kt;
-    const int t0 = (int)((int64_t)total * blockIdx.x / gridDim.x);
-    const int t1 = (int)((int64_t)total * (blockIdx.x + 1) / gridDim.x);
+    const int bx = blockIdx.x;
+    const int t0 = bx * p.chunk_q + min(bx, p.chunk_r);
+    const int t1 = t0 + p.chunk_q + (bx < p.chunk_r ? 1 : 0);
     const int rounds = (t1 - t0 + GEMV_WARPS - 1) / GEMV_WARPS;
     const int stages = p.stages;
 
@@ -455,7 +487,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvParams 
             const int te = (rt + 1) * p.kt;
             bool gave_up = false;
             for (int c = (int)blockIdx.x + 1; c < (int)gridDim.x && !gave_up; c++) {
-                const int c0 = (int)((int64_t)total * c / gridDim.x), c1 = (int)((int64_t)total * (c + 1) / gridDim.x);
+                const int c0 = c * p.chunk_q + min(c, p.chunk_r), c1 = c0 + p.chunk_q + (c < p.chunk_r ? 1 : 0);
                 if (c0 >= te) break;
                 if (c0 == c1) continue;
 #pragma unroll
@@ -542,45 +574,50 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvParams 
         }
         seg++;
         seg_begin = seg_end;
-        rt = seg_begin / p.kt;
+        rt++;  // segments advance one row-tile at a time
         seg_end = min((rt + 1) * p.kt, t1);
     };
 
-    // One tile per round per warp.  Stage index and phase are tracked incrementally.
+    // Segment by segment: an inner loop over this warp's tiles of the segment (one tile per
+    // ring round, nothing but wait / load / release / compute in it), then the flush.
+    // Stage index and phase are tracked incrementally.
     const int n_my = (t0 + warp < t1) ? (t1 - t0 - warp + GEMV_WARPS - 1) / GEMV_WARPS : 0;
     int s = 0, t = t0 + warp;
     uint32_t phase = 0;
     const uint8_t* my_tile = ring + (size_t)warp * T::BYTES;
+    const uint32_t lane_is_0 = lane == 0;
+    bool failed = false;
     stamp(2);
-    for (int r = 0;; r++) {
-        // leave every segment that ends before my next tile (all of them once I am out of tiles)
-        while (seg_begin < t1 && (r >= n_my || t >= seg_end)) flush();
-        if (r >= rounds) break;
-        // Wait for the round's data even without a tile in it: the release below must not be
-        // counted before the stage has been refilled for this round.
-        if (!mbar_wait(&full[s], phase)) {
-            if (lane == 0) atomicOr(p.status, STATUS_GEMV_FIXUP_TIMEOUT);
-            *abort_flag = 1;
-            break;
-        }
-        if (r == 0) stamp(3);
-        if (r < n_my) {
+    while (seg_begin < t1) {
+        // my tiles with index below seg_end
+        const int n_seg = (t < seg_end) ? (seg_end - t + GEMV_WARPS - 1) / GEMV_WARPS : 0;
+        int kbase = (t - rt * p.kt) * T::K;
+        for (int i = 0; i < n_seg && !failed; i++) {
+            if (!mbar_wait(&full[s], phase)) {
+                failed = true;
+                break;
+            }
             R regs;
             regs.load(my_tile + (size_t)s * STAGE_BYTES, lane);
             __syncwarp();
-            if (lane == 0) mbar_arrive(&empty[s]);
-            regs.template compute<XC>(acc, xrow, cinit, (t - rt * p.kt) * T::K, q);
-        } else if (lane == 0) {
-            mbar_arrive(&empty[s]);
+            mbar_arrive_if(&empty[s], lane_is_0);
+            regs.template compute<XC>(acc, xrow, cinit, kbase, q);
+            kbase += GEMV_WARPS * T::K;
+            t += GEMV_WARPS;
+            if (++s == stages) {
+                s = 0;
+                phase ^= 1u;
+            }
         }
-        t += GEMV_WARPS;
-        if (++s == stages) {
-            s = 0;
-            phase ^= 1u;
-        }
+        flush();
     }
     stamp(4);
-    while (seg_begin < t1) flush();  // only reached after a failed wait
+    // Only the last round can lack a tile for some warps, and its stage is never refilled, so
+    // those warps owe the producer no release.
+    if (failed) {
+        if (lane == 0) atomicOr(p.status, STATUS_GEMV_FIXUP_TIMEOUT);
+        *abort_flag = 1;
+    }
     stamp(5);
 }
 
@@ -687,6 +724,8 @@ int gemv_launch(Context* c, const GemvCall& call, cudaStream_t s) {
         p.k = (int)w.g.k;
         p.kt = (int)w.g.kt;
         p.rt = (int)w.g.rt;
+        p.chunk_q = (int)(total / grid);
+        p.chunk_r = (int)(total % grid);
         p.m = (int)((call.m - m0) < per_pass ? (call.m - m0) : per_pass);
         p.x_f32 = call.x_dtype == WF_DTYPE_F32;
         const int xcols = p.x_f32 ? 3 * p.m : p.m;
