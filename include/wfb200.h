@@ -122,6 +122,30 @@ int wf_qlinear(int64_t ctx, int64_t weight, const void* x, int x_dtype, int x_on
 int wf_qlinear_allgather(int64_t ctx, int64_t comm, int64_t weight, const void* x_dev, int x_dtype, int64_t m,
                          void* y_full_dev, int64_t stream);
 
+/* wf_qlinear for hosts that must not allocate device memory once they are running.  (No
+ * counterpart in the reference: its kernels allocate and free on every call,
+ * nvidia/ops/DotGeneralKernel.java:238-296.)  Think of an embedding application that handed
+ * all device memory to its own arena at start-up, or a serving loop with a "no allocation
+ * after warm-up" rule: there a cudaMalloc can fail for lack of memory, or stall the whole
+ * device while it synchronizes.  wf_qlinear obtains a small per-stream work area from
+ * cudaMalloc the first time a stream is used; this variant never calls cudaMalloc, cudaFree
+ * or any allocating routine.  Its work area (the slots through which thread blocks hand
+ * partial rows to each other) is a fixed 256 KiB array compiled into the library, present
+ * on every GPU that loads it until the process ends.
+ *   - x and y are DEVICE pointers (x: [m, k] bf16 or fp32, y: [m, rows] fp32); the call only
+ *     enqueues work on `stream`.
+ *   - Limit: the device may have at most 256 SMs (one slot set per SM); beyond that, and for
+ *     a K that does not fit one SM's shared memory, the call returns WF_ERR_TOO_LARGE.
+ *   - The first call on each device looks up the array's device address (and the first use
+ *     of a kernel variant sets a function attribute); make that first call before starting
+ *     any stream capture.
+ *   - All calls on one device share the one array and it keeps what the last call left in
+ *     it, so every call first clears the part it uses, on `stream`.  Two calls that can run
+ *     at the same time on the GPU (different streams, or two contexts on one device) would
+ *     use the same slots and corrupt each other: issue them on one stream, or order them. */
+int wf_qlinear_noalloc(int64_t ctx, int64_t weight, int64_t x_dev, int x_dtype, int64_t m, int64_t y_dev,
+                       int64_t stream);
+
 /* ---- collectives --------------------------------------------------------------------
  * Replaces CollectiveApi.allGather(Tensor input, Tensor output)
  * (warpforge-io/src/main/java/io/surfworks/warpforge/io/collective/CollectiveApi.java:137-146,

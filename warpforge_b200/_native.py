@@ -39,6 +39,7 @@ SIGNATURES = {
     "wf_weight_info": (c_int, [c_i64, c_i64, P(c_int), P(c_i64), P(c_i64), P(c_i64), P(c_i64)]),
     "wf_dequant_rows": (c_int, [c_i64, c_i64, c_i64, c_i64, c_vp]),
     "wf_qlinear": (c_int, [c_i64, c_i64, c_vp, c_int, c_int, c_i64, c_vp, c_int, c_i64]),
+    "wf_qlinear_noalloc": (c_int, [c_i64, c_i64, c_i64, c_int, c_i64, c_i64, c_i64]),
     "wf_qlinear_allgather": (c_int, [c_i64, c_i64, c_i64, c_vp, c_int, c_i64, c_vp, c_i64]),
     "wf_comm_get_unique_id": (c_int, [c_vp]),
     "wf_comm_init": (c_int, [c_i64, c_vp, c_int, c_int, P(c_i64)]),

@@ -93,6 +93,7 @@ struct GemvCall {
 int gemv_launch(Context* c, const GemvCall& call, cudaStream_t s);
 int gemv_max_tokens_per_pass(const Weight& w, int x_dtype);
 int gemv_prepare_stream(Context* c, cudaStream_t s);
+int gemv_launch_noalloc(Context* c, const GemvCall& call, cudaStream_t s);
 
 struct ScopedLock {
     Context* c;

@@ -744,4 +744,89 @@ int gemv_launch(Context* c, const GemvCall& call, cudaStream_t s) {
     return WF_OK;
 }
 
+// ---------------------------------------------------------------- allocation-free variant
+// Fix-up slots for wf_qlinear_noalloc live in this statically sized device array instead of
+// memory obtained from cudaMalloc.  Every GPU that loads the library carries its 256 KiB
+// until the process exits.  One array per device is shared by all calls on that device.
+constexpr int GEMV_NOALLOC_MAX_CTAS = 256;  // the kernel launches one CTA per SM
+static __device__ __align__(256) uint2 g_noalloc_slots[GEMV_NOALLOC_MAX_CTAS * 128];
+
+// In host code `g_noalloc_slots` is only a handle for the symbol, not an address the GPU can
+// use; the device address is looked up once per device, with that device current.
+static std::mutex g_noalloc_mu;
+static uint2* g_noalloc_ptr[64] = {};
+
+static int noalloc_slots_for_current_device(Context* c, uint2** out) {
+    if (c->device < 0 || c->device >= 64) return set_error(c, WF_ERR_TOO_LARGE, "device index %d beyond 63", c->device);
+    std::lock_guard<std::mutex> lk(g_noalloc_mu);
+    if (!g_noalloc_ptr[c->device]) {
+        uint2* ptr = nullptr;
+        cudaError_t e = cudaGetSymbolAddress((void**)&ptr, g_noalloc_slots);
+        if (e != cudaSuccess) return cuda_status(c, e, "cudaGetSymbolAddress(g_noalloc_slots)");
+        g_noalloc_ptr[c->device] = ptr;
+    }
+    *out = g_noalloc_ptr[c->device];
+    return WF_OK;
+}
+
+// Same kernels and the same work split as gemv_launch, but nothing is allocated: the slots
+// come from the static array above and are cleared on the stream before every launch,
+// because the array keeps whatever the previous call (possibly a failed one) left in it.
+int gemv_launch_noalloc(Context* c, const GemvCall& call, cudaStream_t s) {
+    const Weight& w = *call.w;
+    const int qt = w.g.qtype;
+    const int kp = (int)w.g.kt * tile_k(qt);
+    const int per_pass = gemv_max_tokens_per_pass(w, call.x_dtype);
+    if (per_pass < 1)
+        return set_error(c, WF_ERR_TOO_LARGE, "K=%lld needs more shared memory than one SM has", (long long)w.g.k);
+    const int64_t total = w.g.rt * w.g.kt;
+    if (total >= (1LL << 31)) return set_error(c, WF_ERR_TOO_LARGE, "weight has too many tiles");
+    if (c->sm_count > GEMV_NOALLOC_MAX_CTAS)
+        return set_error(c, WF_ERR_TOO_LARGE, "device has %d SMs; the static fix-up array covers at most %d", c->sm_count,
+                         GEMV_NOALLOC_MAX_CTAS);
+    int grid = c->sm_count;
+    if ((int64_t)grid > total) grid = (int)total;
+    if (grid < 1) return WF_OK;
+    uint2* slots = nullptr;
+    int rc = noalloc_slots_for_current_device(c, &slots);
+    if (rc != WF_OK) return rc;
+
+    const size_t esz = call.x_dtype == WF_DTYPE_F32 ? 4 : 2;
+    const int max_rounds = (int)((total / grid + 1 + GEMV_WARPS - 1) / GEMV_WARPS);
+    for (int64_t m0 = 0; m0 < call.m; m0 += per_pass) {
+        GemvParams p{};
+        p.tiles = w.d_tiles;
+        p.x = static_cast<const uint8_t*>(call.d_x) + (size_t)m0 * w.g.k * esz;
+        p.y = call.d_y + m0 * call.ldy;
+        p.scratch = slots;
+        p.status = c->d_status;
+        p.timing = nullptr;
+        p.ldy = call.ldy;
+        p.col0 = call.col0;
+        p.ldx = w.g.k;
+        p.rows = (int)w.g.rows;
+        p.k = (int)w.g.k;
+        p.kt = (int)w.g.kt;
+        p.rt = (int)w.g.rt;
+        p.chunk_q = (int)(total / grid);
+        p.chunk_r = (int)(total % grid);
+        p.m = (int)((call.m - m0) < per_pass ? (call.m - m0) : per_pass);
+        p.x_f32 = call.x_dtype == WF_DTYPE_F32;
+        const int xcols = p.x_f32 ? 3 * p.m : p.m;
+        const size_t stage = (size_t)GEMV_WARPS * tile_bytes(qt);
+        WF_CUDA(c, cudaMemsetAsync(slots, 0, (size_t)grid * 128 * sizeof(uint2), s));
+        cudaError_t e;
+        if (xcols == 1) {
+            p.stages = std::min(gemv_stages<1>(qt, kp, xcols), std::max(max_rounds, 1));
+            e = launch_qt<1>(qt, p, grid, gemv_fixed_smem<1>(kp, xcols, &p.sx) + p.stages * stage, s);
+        } else {
+            p.stages = std::min(gemv_stages<8>(qt, kp, xcols), std::max(max_rounds, 1));
+            e = launch_qt<8>(qt, p, grid, gemv_fixed_smem<8>(kp, xcols, &p.sx) + p.stages * stage, s);
+        }
+        if (e != cudaSuccess) return cuda_status(c, e, "gemv launch (no-alloc)");
+        c->launches++;
+    }
+    return WF_OK;
+}
+
 }  // namespace wf

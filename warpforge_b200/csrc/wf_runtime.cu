@@ -410,6 +410,19 @@ int wf_qlinear(int64_t ctx, int64_t weight, const void* x, int x_dtype, int x_on
     return WF_OK;
 }
 
+int wf_qlinear_noalloc(int64_t ctx, int64_t weight, int64_t x_dev, int x_dtype, int64_t m, int64_t y_dev, int64_t stream) {
+    WF_ENTER(ctx);
+    Weight* w = get_weight(c, weight);
+    if (!w) return WF_ERR_INVALID_HANDLE;
+    if (x_dtype != WF_DTYPE_BF16 && x_dtype != WF_DTYPE_F32)
+        return set_error(c, WF_ERR_INVALID_ARGUMENT, "x_dtype %d is neither BF16 nor F32", x_dtype);
+    if (m < 0 || m > (1 << 20)) return set_error(c, WF_ERR_SHAPE, "m=%lld out of range", (long long)m);
+    if (m == 0) return WF_OK;
+    if (!x_dev || !y_dev) return set_error(c, WF_ERR_INVALID_ARGUMENT, "null device pointer");
+    GemvCall call{w, reinterpret_cast<const void*>(x_dev), x_dtype, m, reinterpret_cast<float*>(y_dev), w->g.rows, 0};
+    return gemv_launch_noalloc(c, call, resolve_stream(c, stream));
+}
+
 int wf_graph_begin(int64_t ctx, int64_t stream) {
     WF_ENTER(ctx);
     cudaStream_t s = resolve_stream(c, stream);
