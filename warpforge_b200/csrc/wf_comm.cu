@@ -215,7 +215,7 @@ int wf_qlinear_allgather(int64_t ctx, int64_t comm, int64_t weight, const void* 
     }
     float* mine = k->d_tmp + (int64_t)k->world * m * rows;
     GemvCall call{w, x_dev, x_dtype, m, mine, rows, 0};
-    int rc = gemv_launch(c, call, s);
+    int rc = gemm_supported(*w, x_dtype, m) ? gemm_launch(c, call, s) : gemv_launch(c, call, s);
     if (rc != WF_OK) return rc;
     int r = nccl().AllGather(mine, k->d_tmp, (size_t)(m * rows), NCCL_FLOAT32, k->comm, s);
     if (r != NCCL_SUCCESS) return nccl_status(c, r, "ncclAllGather");

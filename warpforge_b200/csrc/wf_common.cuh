@@ -64,6 +64,8 @@ struct Context {
     int64_t h_stage_bytes = 0;
     void* d_stage = nullptr;
     int64_t d_stage_bytes = 0;
+    void* d_x16 = nullptr;  // fp16 copy of the activations for the tensor-core GEMM
+    int64_t x16_bytes = 0;
     int64_t launches = 0;
     int gemv_ctas_per_sm[3] = {0, 0, 0};
 };
@@ -94,6 +96,10 @@ int gemv_launch(Context* c, const GemvCall& call, cudaStream_t s);
 int gemv_max_tokens_per_pass(const Weight& w, int x_dtype);
 int gemv_prepare_stream(Context* c, cudaStream_t s);
 int gemv_launch_noalloc(Context* c, const GemvCall& call, cudaStream_t s);
+
+// wf_gemm.cu
+bool gemm_supported(const Weight& w, int x_dtype, int64_t m);
+int gemm_launch(Context* c, const GemvCall& call, cudaStream_t s);
 
 struct ScopedLock {
     Context* c;

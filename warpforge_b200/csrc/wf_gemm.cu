@@ -1,0 +1,511 @@
+// Prefill GEMM: y[m, rows] = x[m, K] . W[rows, K]^T for many tokens, W in the tiled quantized
+// layout of wf_layout.cuh, on the 5th-generation tensor cores.
+//
+//   D[128 weight rows x BM tokens] (fp32, in TMEM) += A[128 x 16] (fp16, smem) * B[16 x BM] (fp16, smem)
+//
+// Activations arrive as bf16; a small pre-pass rewrites each token row as fp16 times a power of two
+// (exact: fp16 has more mantissa bits than bf16, and the per-row scale keeps the row inside fp16's
+// exponent range); the epilogue multiplies the row back.
+//
+// Warp roles in one persistent CTA per SM (320 threads):
+//   warp 0      TMA producer: activation tiles [BM tokens x 64 k] with 128-byte swizzle, two per stage
+//   warp 1      MMA issuer: one elected thread issues tcgen05.mma, commits to mbarriers; owns TMEM
+//   warps 2-3   spare (keep the epilogue warps on TMEM lane quarters 0..3)
+//   warps 4-7   epilogue: tcgen05.ld the accumulator, store fp32 rows to y, release the accumulator
+//   warps 8-9   (unused slot kept for symmetry)
+//   dequant     warps 2,3,8,9: read the quantized tiles straight from global memory (coalesced 16-byte
+//               loads, the layout is already fragment-ordered), unpack 4-bit codes, apply the block
+//               scale and write fp16 rows into the swizzled A stage
+// Stages hold BK = 128 k: A = 128 rows x 128 k fp16 (two 64-k swizzle spans, 32 KB), B = BM x 128 k bf16.
+// The accumulator is double buffered in TMEM (2 x BM columns <= 512) so the epilogue of one tile
+// overlaps the main loop of the next.  Every wait is bounded; on expiry the CTA sets a status bit,
+// stops issuing work and still frees its TMEM.
+//
+// Weights are rounded once to fp16 (relative 2^-12) after the exact fp32 dequantization; products
+// and sums are fp32 in the tensor core.  Replaces the host transpose + batch_matmul_f32 of
+// warpforge-backend-nvidia/src/main/java/io/surfworks/warpforge/backend/nvidia/ops/DotGeneralKernel.java:169-298.
+#include <cuda.h>
+#include <cuda_fp16.h>
+
+#include "wf_common.cuh"
+
+namespace wf {
+
+constexpr int GEMM_BN = 128;        // weight rows per tile (UMMA M)
+constexpr int GEMM_BK = 128;        // k per stage
+constexpr int GEMM_THREADS = 320;   // 10 warps
+constexpr int GEMM_WAIT_SPINS = 1 << 26;
+constexpr int GEMM_A_BYTES = GEMM_BN * GEMM_BK * 2;  // 32 KB
+
+struct GemmParams {
+    const uint8_t* tiles;
+    float* y;
+    const float* row_unscale;  // [m] power of two that undoes the pre-pass scaling of token row m
+    int* status;
+    int64_t ldy, col0;
+    int rows, k, kt_w;   // kt_w: weight k-tiles per row-tile stripe (tile_k of the format)
+    int m;               // tokens
+    int bm;              // tokens per tile (multiple of 16, <= 256)
+    int n_tiles, m_tiles, k_blocks;  // k_blocks = ceil(k / 128)
+    int stages;
+    uint32_t idesc;
+};
+
+// ---------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ uint32_t g_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void g_mbar_init(void* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(g_smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void g_mbar_arrive(void* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(g_smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void g_mbar_expect_tx(void* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(g_smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool g_mbar_wait(void* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, q;\n\t"
+        ".reg .u32 n;\n\t"
+        "mov.u32 n, 0;\n\t"
+        "WFG_WAIT_%=:\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "@p bra WFG_DONE_%=;\n\t"
+        "add.u32 n, n, 1;\n\t"
+        "setp.lt.u32 q, n, %3;\n\t"
+        "@q bra WFG_WAIT_%=;\n\t"
+        "WFG_DONE_%=:\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}\n"
+        : "=r"(ok)
+        : "r"(g_smem_u32(bar)), "r"(parity), "r"((uint32_t)GEMM_WAIT_SPINS)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, void* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+            g_smem_u32(dst)),
+        "l"(map), "r"(x), "r"(y), "r"(g_smem_u32(bar))
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(void* smem_dst, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(g_smem_u32(smem_dst)), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(void* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(g_smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// K-major operand, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFF) >> 4);   // start address
+    d |= (uint64_t)1 << 16;                    // leading byte offset (unused with swizzle), 16 B
+    d |= (uint64_t)(1024 >> 4) << 32;          // stride byte offset: 8 rows x 128 B
+    d |= (uint64_t)1 << 46;                    // descriptor version (sm_100)
+    d |= (uint64_t)2 << 61;                    // SWIZZLE_128B
+    return d;
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// ---------------------------------------------------------------- dequantization to fp16
+__device__ __forceinline__ uint32_t pack_half2(float a, float b) {
+    __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+// the two codes of nibble pair S of a plane word, as floats (exact)
+template <int S>
+__device__ __forceinline__ void nib2_f32(uint32_t w, float& lo, float& hi) {
+    const uint32_t r = (S == 0) ? w : __funnelshift_r(w, w, 4 * S);
+    const uint32_t v = (r & 0x00780078u) | 0x41804180u;  // bf16x2 (16 + code)
+    lo = __uint_as_float(v << 16) - 16.f;
+    hi = __uint_as_float(v & 0xFFFF0000u) - 16.f;
+}
+// 8 consecutive elements of one plane word -> 8 fp16 values = a * code + b (rounded once from fp32)
+__device__ __forceinline__ uint4 word_to_half8(uint32_t w, float a, float b) {
+    float c[8];
+    nib2_f32<0>(w, c[0], c[1]);
+    nib2_f32<1>(w, c[2], c[3]);
+    nib2_f32<2>(w, c[4], c[5]);
+    nib2_f32<3>(w, c[6], c[7]);
+    uint4 o;
+    o.x = pack_half2(fmaf(a, c[0], b), fmaf(a, c[1], b));
+    o.y = pack_half2(fmaf(a, c[2], b), fmaf(a, c[3], b));
+    o.z = pack_half2(fmaf(a, c[4], b), fmaf(a, c[5], b));
+    o.w = pack_half2(fmaf(a, c[6], b), fmaf(a, c[7], b));
+    return o;
+}
+__device__ __forceinline__ uint4 words_to_half8_q8(uint32_t wh, uint32_t wl, float s) {
+    float h[8], l[8];
+    nib2_f32<0>(wh, h[0], h[1]); nib2_f32<1>(wh, h[2], h[3]); nib2_f32<2>(wh, h[4], h[5]); nib2_f32<3>(wh, h[6], h[7]);
+    nib2_f32<0>(wl, l[0], l[1]); nib2_f32<1>(wl, l[2], l[3]); nib2_f32<2>(wl, l[4], l[5]); nib2_f32<3>(wl, l[6], l[7]);
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) v[i] = s * fmaf(16.f, h[i] - 8.f, l[i]);  // exact integer, then one multiply
+    uint4 o;
+    o.x = pack_half2(v[0], v[1]); o.y = pack_half2(v[2], v[3]); o.z = pack_half2(v[4], v[5]); o.w = pack_half2(v[6], v[7]);
+    return o;
+}
+
+// A stage address of the 16-byte chunk (row r, chunk c of 16 along k): two swizzled 64-k spans
+__device__ __forceinline__ uint32_t a_chunk_off(int r, int c) {
+    return (uint32_t)((c >> 3) * (GEMM_BN * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4));
+}
+
+// One warp dequantizes one 16-row tile x 128 k of the stage: rows rt16*16 .. +15.
+template <int QT>
+__device__ __forceinline__ void dequant_rowtile(const uint8_t* tile, int kb, uint8_t* a_stage, int rt16, int lane) {
+    const int g = lane >> 2, q = lane & 3;
+    if (QT == WF_QTYPE_Q4_0) {
+        (void)kb;
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const uint4 c = __ldg(reinterpret_cast<const uint4*>(tile + h * 512 + lane * 16));
+            const uint2 sc = __ldg(reinterpret_cast<const uint2*>(tile + Tile<WF_QTYPE_Q4_0>::SCALE_OFF + g * 16 + h * 8));
+            const float2 s01 = __half22float2(*reinterpret_cast<const __half2*>(&sc.x));
+            const float2 s23 = __half22float2(*reinterpret_cast<const __half2*>(&sc.y));
+            const float s[4] = {s01.x, s01.y, s23.x, s23.y};
+            const uint32_t w[4] = {c.x, c.y, c.z, c.w};
+            const int r = rt16 * 16 + g + 8 * h;
+#pragma unroll
+            for (int j = 0; j < 4; j++)  // value = s * (code - 8)
+                *reinterpret_cast<uint4*>(a_stage + a_chunk_off(r, j * 4 + q)) = word_to_half8(w[j], s[j], -8.f * s[j]);
+        }
+    } else if (QT == WF_QTYPE_Q8_0) {
+        (void)kb;
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const uint4 ch = __ldg(reinterpret_cast<const uint4*>(tile + h * 512 + lane * 16));
+            const uint4 cl = __ldg(reinterpret_cast<const uint4*>(tile + PLANE_BYTES + h * 512 + lane * 16));
+            const uint2 sc = __ldg(reinterpret_cast<const uint2*>(tile + Tile<WF_QTYPE_Q8_0>::SCALE_OFF + g * 16 + h * 8));
+            const float2 s01 = __half22float2(*reinterpret_cast<const __half2*>(&sc.x));
+            const float2 s23 = __half22float2(*reinterpret_cast<const __half2*>(&sc.y));
+            const float s[4] = {s01.x, s01.y, s23.x, s23.y};
+            const uint32_t wh[4] = {ch.x, ch.y, ch.z, ch.w}, wl[4] = {cl.x, cl.y, cl.z, cl.w};
+            const int r = rt16 * 16 + g + 8 * h;
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+                *reinterpret_cast<uint4*>(a_stage + a_chunk_off(r, j * 4 + q)) = words_to_half8_q8(wh[j], wl[j], s[j]);
+        }
+    } else {  // Q4_K: the stage is one half (plane kb & 1) of a 256-k tile
+        using T = Tile<WF_QTYPE_Q4_K>;
+        const int pl = kb & 1;
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const uint4 c = __ldg(reinterpret_cast<const uint4*>(tile + pl * PLANE_BYTES + h * 512 + lane * 16));
+            const uint32_t dd = __ldg(reinterpret_cast<const uint32_t*>(tile + T::D_OFF + g * 8 + h * 4));
+            const uint32_t scw = __ldg(reinterpret_cast<const uint32_t*>(tile + T::SC_OFF + g * 16 + h * 8 + pl * 4));
+            const uint32_t mnw = __ldg(reinterpret_cast<const uint32_t*>(tile + T::MN_OFF + g * 16 + h * 8 + pl * 4));
+            const float2 d = __half22float2(*reinterpret_cast<const __half2*>(&dd));  // (d, dmin)
+            const uint32_t w[4] = {c.x, c.y, c.z, c.w};
+            const int r = rt16 * 16 + g + 8 * h;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {  // value = (d * sc) * code - dmin * m
+                const float a = d.x * (float)((scw >> (8 * j)) & 0xFF), b = -(d.y * (float)((mnw >> (8 * j)) & 0xFF));
+                *reinterpret_cast<uint4*>(a_stage + a_chunk_off(r, j * 4 + q)) = word_to_half8(w[j], a, b);
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------- activation pre-pass
+// One CTA per token row: x16[row] = fp16(x[row] * 2^s) with s chosen so the largest magnitude lands in
+// [2^14, 2^15); unscale[row] = 2^-s.  bf16 -> fp16 is exact whenever the scaled value is a normal fp16.
+__global__ void x_to_f16_kernel(const uint16_t* __restrict__ x, __half* __restrict__ x16, float* __restrict__ unscale, int k) {
+    __shared__ int s_emax;
+    const uint16_t* row = x + (size_t)blockIdx.x * k;
+    if (threadIdx.x == 0) s_emax = 0;
+    __syncthreads();
+    int emax = 0;
+    for (int i = threadIdx.x; i < k; i += blockDim.x) {
+        const int e = (row[i] >> 7) & 0xFF;              // bf16 biased exponent
+        emax = max(emax, e == 0xFF ? 0 : e);              // Inf / NaN do not drive the scale
+    }
+    atomicMax(&s_emax, emax);
+    __syncthreads();
+    emax = s_emax;
+    const int shift = emax == 0 ? 0 : (127 + 14) - emax;  // multiply by 2^shift
+    const float scale = __uint_as_float((uint32_t)min(max(127 + shift, 1), 254) << 23);
+    for (int i = threadIdx.x; i < k; i += blockDim.x)
+        x16[(size_t)blockIdx.x * k + i] = __float2half_rn(__uint_as_float((uint32_t)row[i] << 16) * scale);
+    if (threadIdx.x == 0) unscale[blockIdx.x] = __uint_as_float((uint32_t)min(max(127 - shift, 1), 254) << 23);
+}
+
+// ---------------------------------------------------------------- the kernel
+// smem: [0,1024) barriers + tmem slot | stages x (A 32 KB | B bm*256 B), 1024-byte aligned
+template <int QT>
+__global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint64_t* b_full = reinterpret_cast<uint64_t*>(smem);        // [8] activations landed
+    uint64_t* a_full = b_full + 8;                               // [8] weights dequantized
+    uint64_t* s_empty = a_full + 8;                              // [8] stage consumed by the MMA
+    uint64_t* acc_full = s_empty + 8;                            // [2]
+    uint64_t* acc_empty = acc_full + 2;                          // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    const uint32_t b_bytes = (uint32_t)p.bm * 256;
+    const uint32_t stage_bytes = GEMM_A_BYTES + b_bytes;
+    uint8_t* stage0 = smem + 1024;
+
+    const int warp = __shfl_sync(0xFFFFFFFFu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
+    const int stages = p.stages;
+    const int total_tiles = p.n_tiles * p.m_tiles;
+    constexpr int TILE_BYTES = Tile<QT>::BYTES;
+    constexpr int KB_PER_WTILE = Tile<QT>::K / GEMM_BK;  // stages per weight k-tile: 1 (Q4_0, Q8_0) or 2 (Q4_K)
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; s++) {
+            g_mbar_init(&b_full[s], 1);
+            g_mbar_init(&a_full[s], 4);   // four dequant warps
+            g_mbar_init(&s_empty[s], 1);
+        }
+        for (int b = 0; b < 2; b++) {
+            g_mbar_init(&acc_full[b], 1);
+            g_mbar_init(&acc_empty[b], 4);  // four epilogue warps
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    auto fail = [&]() {
+        atomicOr(p.status, STATUS_GEMM_PIPE_TIMEOUT);
+        *abort_flag = 1;
+    };
+
+    if (warp == 0) {
+        // ------------------------------------------------ TMA producer (activations)
+        if (lane == 0) {
+            int it = 0;
+            for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
+                const int mt = tile % p.m_tiles;
+                for (int kb = 0; kb < p.k_blocks; kb++, it++) {
+                    const int s = it % stages;
+                    if (it >= stages && !g_mbar_wait(&s_empty[s], ((it / stages) - 1) & 1)) { fail(); break; }
+                    uint8_t* b_stage = stage0 + (size_t)s * stage_bytes + GEMM_A_BYTES;
+                    g_mbar_expect_tx(&b_full[s], b_bytes);
+                    tma_load_2d(b_stage, &xmap, kb * GEMM_BK, mt * p.bm, &b_full[s]);
+                    tma_load_2d(b_stage + b_bytes / 2, &xmap, kb * GEMM_BK + 64, mt * p.bm, &b_full[s]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            int it = 0, local = 0;
+            for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, local++) {
+                const int buf = local & 1;
+                if (local >= 2 && !g_mbar_wait(&acc_empty[buf], ((local >> 1) - 1) & 1)) { fail(); break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(buf * p.bm);
+                bool ok = true;
+                for (int kb = 0; kb < p.k_blocks && ok; kb++, it++) {
+                    const int s = it % stages;
+                    const uint32_t ph = (it / stages) & 1;
+                    if (!g_mbar_wait(&b_full[s], ph) || !g_mbar_wait(&a_full[s], ph)) { fail(); ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = g_smem_u32(stage0 + (size_t)s * stage_bytes);
+                    const uint32_t b_addr = a_addr + GEMM_A_BYTES;
+#pragma unroll
+                    for (int kk = 0; kk < 8; kk++) {  // 8 x K16 per stage; spans of 64 k are 16 KB (A) / bm*128 B (B) apart
+                        const uint64_t ad = smem_desc_sw128(a_addr + (kk >> 2) * (GEMM_BN * 128) + (kk & 3) * 32);
+                        const uint64_t bd = smem_desc_sw128(b_addr + (kk >> 2) * (b_bytes / 2) + (kk & 3) * 32);
+                        tc_mma_f16(d_tmem, ad, bd, p.idesc, (kb | kk) != 0);
+                    }
+                    tc_commit(&s_empty[s]);  // frees the stage when these MMAs have read it
+                }
+                if (!ok) break;
+                tc_commit(&acc_full[buf]);
+            }
+        }
+    } else if (warp >= 4 && warp < 8) {
+        // ------------------------------------------------ epilogue (TMEM lane quarter = warp % 4)
+        const int quarter = warp & 3;
+        int local = 0;
+        for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, local++) {
+            const int buf = local & 1;
+            const int nt = tile / p.m_tiles, mt = tile % p.m_tiles;
+            if (!g_mbar_wait(&acc_full[buf], (local >> 1) & 1)) { if (lane == 0) fail(); break; }
+            tc_fence_after();
+            const int n = nt * GEMM_BN + quarter * 32 + lane;
+            for (int c = 0; c < p.bm; c += 32) {
+                uint32_t r[32];
+                tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * p.bm + c), r);
+                const int m0 = mt * p.bm + c;
+                if (n < p.rows) {
+#pragma unroll
+                    for (int j = 0; j < 32; j++)
+                        if (m0 + j < p.m)
+                            p.y[(int64_t)(m0 + j) * p.ldy + p.col0 + n] = __uint_as_float(r[j]) * __ldg(p.row_unscale + m0 + j);
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) g_mbar_arrive(&acc_empty[buf]);
+        }
+    } else {
+        // ------------------------------------------------ dequant warps 2, 3, 8, 9: two 16-row tiles each per stage
+        const int dq = (warp < 4) ? warp - 2 : warp - 6;  // 0..3
+        int it = 0;
+        for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
+            const int nt = tile / p.m_tiles;
+            bool ok = true;
+            for (int kb = 0; kb < p.k_blocks && ok; kb++, it++) {
+                const int s = it % stages;
+                if (it >= stages && !g_mbar_wait(&s_empty[s], ((it / stages) - 1) & 1)) { if (lane == 0) fail(); ok = false; break; }
+                uint8_t* a_stage = stage0 + (size_t)s * stage_bytes;
+#pragma unroll
+                for (int i = 0; i < 2; i++) {
+                    const int rt16 = dq * 2 + i;  // 16-row tile inside the 128-row block
+                    const int64_t wrt = (int64_t)nt * (GEMM_BN / 16) + rt16;  // weight row-tile
+                    const uint8_t* wt = p.tiles + (wrt * p.kt_w + kb / KB_PER_WTILE) * (int64_t)TILE_BYTES;
+                    dequant_rowtile<QT>(wt, kb, a_stage, rt16, lane);
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the tensor core
+                __syncwarp();
+                if (lane == 0) g_mbar_arrive(&a_full[s]);
+            }
+            if (!ok) break;
+        }
+    }
+
+    // ------------------------------------------------ teardown: TMEM is freed on every path
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+constexpr size_t GEMM_SMEM_LIMIT = 227 * 1024;
+
+bool gemm_supported(const Weight& w, int x_dtype, int64_t m) {
+    // bf16 activations, whole 128-row blocks of padded tiles exist for any row count (tiles are 16-row padded,
+    // and the loader only touches row-tiles below rt), K a multiple of 8 elements for the 16-byte TMA stride rule
+    return x_dtype == WF_DTYPE_BF16 && m > 8 && (w.g.k % 8) == 0 && encode_tiled_fn() != nullptr;
+}
+
+template <int QT>
+static cudaError_t gemm_launch_one(const GemmParams& p, const CUtensorMap& map, int grid, size_t smem, cudaStream_t s) {
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 64 && !attr_set[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_kernel<QT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM_LIMIT);
+        if (e != cudaSuccess) return e;
+        attr_set[dev] = true;
+    }
+    gemm_kernel<QT><<<grid, GEMM_THREADS, smem, s>>>(p, map);
+    return cudaGetLastError();
+}
+
+int gemm_launch(Context* c, const GemvCall& call, cudaStream_t s) {
+    const Weight& w = *call.w;
+    const int qt = w.g.qtype;
+    GemmParams p{};
+    p.tiles = w.d_tiles;
+    p.y = call.d_y;
+    p.status = c->d_status;
+    p.ldy = call.ldy;
+    p.col0 = call.col0;
+    p.rows = (int)w.g.rows;
+    p.k = (int)w.g.k;
+    p.kt_w = (int)w.g.kt;
+    p.m = (int)call.m;
+    p.bm = call.m >= 256 ? 256 : (int)((call.m + 15) / 16 * 16);
+    p.n_tiles = (int)((w.g.rows + GEMM_BN - 1) / GEMM_BN);
+    p.m_tiles = (int)((call.m + p.bm - 1) / p.bm);
+    p.k_blocks = (int)((w.g.k + GEMM_BK - 1) / GEMM_BK);
+    const size_t stage_bytes = GEMM_A_BYTES + (size_t)p.bm * 256;
+    p.stages = (int)std::min<size_t>((GEMM_SMEM_LIMIT - 1024) / stage_bytes, 8);
+    // A = fp16 weights, B = fp16 activations, D = fp32; both operands K-major
+    p.idesc = (1u << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(p.bm >> 3) << 17) | ((uint32_t)(GEMM_BN >> 4) << 24);
+
+    // the last 128-row block may reach past the padded row-tiles: the weight buffer must cover it
+    if ((int64_t)p.n_tiles * (GEMM_BN / 16) > w.g.rt_alloc)
+        return set_error(c, WF_ERR_SHAPE, "weight buffer does not cover the last 128-row block");
+
+    // activation pre-pass into the context's fp16 scratch (grown on demand)
+    const int64_t x16_bytes = ((call.m * w.g.k * 2 + 255) & ~255LL) + call.m * 4;
+    if (x16_bytes > c->x16_bytes) {
+        if (c->d_x16) cudaFree(c->d_x16);
+        c->d_x16 = nullptr;
+        c->x16_bytes = 0;
+        WF_CUDA(c, cudaMalloc(&c->d_x16, (size_t)x16_bytes));
+        c->x16_bytes = x16_bytes;
+    }
+    __half* x16 = static_cast<__half*>(c->d_x16);
+    float* unscale = reinterpret_cast<float*>(static_cast<uint8_t*>(c->d_x16) + ((call.m * w.g.k * 2 + 255) & ~255LL));
+    x_to_f16_kernel<<<(unsigned)call.m, 256, 0, s>>>(static_cast<const uint16_t*>(call.d_x), x16, unscale, (int)w.g.k);
+    WF_CUDA(c, cudaGetLastError());
+    c->launches++;
+    p.row_unscale = unscale;
+
+    CUtensorMap map;
+    const cuuint64_t dims[2] = {(cuuint64_t)w.g.k, (cuuint64_t)call.m};
+    const cuuint64_t strides[1] = {(cuuint64_t)w.g.k * 2};
+    const cuuint32_t box[2] = {64, (cuuint32_t)p.bm};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = encode_tiled_fn()(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, x16, dims, strides, box, estr,
+                                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return set_error(c, WF_ERR_CUDA_BASE + 1, "cuTensorMapEncodeTiled failed (%d)", (int)r);
+
+    const int grid = std::min(c->sm_count, p.n_tiles * p.m_tiles);
+    const size_t smem = 1024 + (size_t)p.stages * stage_bytes;
+    cudaError_t e = qt == WF_QTYPE_Q4_0   ? gemm_launch_one<WF_QTYPE_Q4_0>(p, map, grid, smem, s)
+                    : qt == WF_QTYPE_Q8_0 ? gemm_launch_one<WF_QTYPE_Q8_0>(p, map, grid, smem, s)
+                                          : gemm_launch_one<WF_QTYPE_Q4_K>(p, map, grid, smem, s);
+    if (e != cudaSuccess) return cuda_status(c, e, "gemm launch");
+    c->launches++;
+    return WF_OK;
+}
+
+}  // namespace wf

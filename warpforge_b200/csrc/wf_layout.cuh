@@ -78,7 +78,8 @@ struct WeightGeom {
     int64_t k;     // logical K
     int64_t rt;    // row tiles  = ceil(rows / 16)
     int64_t kt;    // k tiles    = ceil(k / TILE_K)
-    int64_t bytes() const { return rt * kt * (int64_t)tile_bytes(qtype); }
+    int64_t rt_alloc;  // row tiles allocated: rt rounded up to 8, so a 128-row GEMM block never leaves the buffer
+    int64_t bytes() const { return rt_alloc * kt * (int64_t)tile_bytes(qtype); }
 };
 
 }  // namespace wf

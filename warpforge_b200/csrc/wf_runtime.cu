@@ -159,6 +159,7 @@ int wf_destroy(int64_t ctx) {
     for (cudaStream_t s : c->streams) cudaStreamDestroy(s);
     if (c->h_stage) cudaFreeHost(c->h_stage);
     if (c->d_stage) cudaFree(c->d_stage);
+    if (c->d_x16) cudaFree(c->d_x16);
     cudaFree(c->d_status);
     if (c->d_timing) cudaFree(c->d_timing);
     cudaStreamDestroy(c->stream);
@@ -299,6 +300,7 @@ int wf_weight_upload(int64_t ctx, int qtype, const void* blocks, int64_t n_rows,
     w->g.k = k;
     w->g.rt = (rows + TILE_ROWS - 1) / TILE_ROWS;
     w->g.kt = (k + tile_k(qtype) - 1) / tile_k(qtype);
+    w->g.rt_alloc = (w->g.rt + 7) / 8 * 8;
     w->row0 = row0;
     w->total_rows = n_rows;
     const int64_t raw_bytes = rows * row_bytes;
@@ -397,7 +399,8 @@ int wf_qlinear(int64_t ctx, int64_t weight, const void* x, int x_dtype, int x_on
         if (!y_on_device) d_y = reinterpret_cast<float*>(static_cast<uint8_t*>(c->d_stage) + yo);
     }
     GemvCall call{w, d_x, x_dtype, m, d_y, w->g.rows, 0};
-    int rc = gemv_launch(c, call, s);
+    // many tokens: tensor-core GEMM; a few tokens: the HBM-bound GEMV
+    int rc = gemm_supported(*w, x_dtype, m) ? gemm_launch(c, call, s) : gemv_launch(c, call, s);
     if (rc != WF_OK) return rc;
     if (!y_on_device) {
         const int64_t yo = (xb + 255) & ~255LL;
