@@ -7,15 +7,14 @@
 // (exact: fp16 has more mantissa bits than bf16, and the per-row scale keeps the row inside fp16's
 // exponent range); the epilogue multiplies the row back.
 //
-// Warp roles in one persistent CTA per SM (320 threads):
+// Warp roles in one persistent CTA per SM (448 threads):
 //   warp 0      TMA producer: activation tiles [BM tokens x 64 k] with 128-byte swizzle, two per stage
 //   warp 1      MMA issuer: one elected thread issues tcgen05.mma, commits to mbarriers; owns TMEM
-//   warps 2-3   spare (keep the epilogue warps on TMEM lane quarters 0..3)
-//   warps 4-7   epilogue: tcgen05.ld the accumulator, store fp32 rows to y, release the accumulator
-//   warps 8-9   (unused slot kept for symmetry)
-//   dequant     warps 2,3,8,9: read the quantized tiles straight from global memory (coalesced 16-byte
+//   warps 4-7   epilogue (TMEM lane quarter = warp % 4): tcgen05.ld the accumulator, store fp32 rows
+//               to y, release the accumulator
+//   warps 2,3,8-13  dequant: read the quantized tiles straight from global memory (coalesced 16-byte
 //               loads, the layout is already fragment-ordered), unpack 4-bit codes, apply the block
-//               scale and write fp16 rows into the swizzled A stage
+//               scale and write fp16 rows into the swizzled A stage; one 16-row tile per warp and stage
 // Stages hold BK = 128 k: A = 128 rows x 128 k fp16 (two 64-k swizzle spans, 32 KB), B = BM x 128 k bf16.
 // The accumulator is double buffered in TMEM (2 x BM columns <= 512) so the epilogue of one tile
 // overlaps the main loop of the next.  Every wait is bounded; on expiry the CTA sets a status bit,
@@ -33,7 +32,7 @@ namespace wf {
 
 constexpr int GEMM_BN = 128;        // weight rows per tile (UMMA M)
 constexpr int GEMM_BK = 128;        // k per stage
-constexpr int GEMM_THREADS = 320;   // 10 warps
+constexpr int GEMM_THREADS = 448;   // 14 warps: TMA, MMA, 4 epilogue, 8 dequant
 constexpr int GEMM_WAIT_SPINS = 1 << 26;
 constexpr int GEMM_A_BYTES = GEMM_BN * GEMM_BK * 2;  // 32 KB
 
@@ -142,11 +141,12 @@ template <int S>
 __device__ __forceinline__ void nib2_f32(uint32_t w, float& lo, float& hi) {
     const uint32_t r = (S == 0) ? w : __funnelshift_r(w, w, 4 * S);
     const uint32_t v = (r & 0x00780078u) | 0x41804180u;  // bf16x2 (16 + code)
-    lo = __uint_as_float(v << 16) - 16.f;
-    hi = __uint_as_float(v & 0xFFFF0000u) - 16.f;
+    lo = __uint_as_float(v << 16);                        // 16 + code, the caller folds the 16 away
+    hi = __uint_as_float(v & 0xFFFF0000u);
 }
-// 8 consecutive elements of one plane word -> 8 fp16 values = a * code + b (rounded once from fp32)
+// 8 consecutive elements of one plane word -> 8 fp16 values = a * code + b
 __device__ __forceinline__ uint4 word_to_half8(uint32_t w, float a, float b) {
+    b = fmaf(-16.f, a, b);  // the unpacked values are 16 + code
     float c[8];
     nib2_f32<0>(w, c[0], c[1]);
     nib2_f32<1>(w, c[2], c[3]);
@@ -165,7 +165,7 @@ __device__ __forceinline__ uint4 words_to_half8_q8(uint32_t wh, uint32_t wl, flo
     nib2_f32<0>(wl, l[0], l[1]); nib2_f32<1>(wl, l[2], l[3]); nib2_f32<2>(wl, l[4], l[5]); nib2_f32<3>(wl, l[6], l[7]);
     float v[8];
 #pragma unroll
-    for (int i = 0; i < 8; i++) v[i] = s * fmaf(16.f, h[i] - 8.f, l[i]);  // exact integer, then one multiply
+    for (int i = 0; i < 8; i++) v[i] = s * (fmaf(16.f, h[i], l[i]) - 400.f);  // 16(hi-8)+lo exactly, then one multiply
     uint4 o;
     o.x = pack_half2(v[0], v[1]); o.y = pack_half2(v[2], v[3]); o.z = pack_half2(v[4], v[5]); o.w = pack_half2(v[6], v[7]);
     return o;
@@ -280,7 +280,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmParams 
     if (threadIdx.x == 0) {
         for (int s = 0; s < stages; s++) {
             g_mbar_init(&b_full[s], 1);
-            g_mbar_init(&a_full[s], 4);   // four dequant warps
+            g_mbar_init(&a_full[s], 8);   // eight dequant warps
             g_mbar_init(&s_empty[s], 1);
         }
         for (int b = 0; b < 2; b++) {
@@ -372,8 +372,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmParams 
             if (lane == 0) g_mbar_arrive(&acc_empty[buf]);
         }
     } else {
-        // ------------------------------------------------ dequant warps 2, 3, 8, 9: two 16-row tiles each per stage
-        const int dq = (warp < 4) ? warp - 2 : warp - 6;  // 0..3
+        // ------------------------------------------------ dequant warps 2, 3, 8..13: one 16-row tile each per stage
+        const int dq = (warp < 4) ? warp - 2 : warp - 6;  // 0..7
         int it = 0;
         for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
             const int nt = tile / p.m_tiles;
@@ -382,9 +382,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmParams 
                 const int s = it % stages;
                 if (it >= stages && !g_mbar_wait(&s_empty[s], ((it / stages) - 1) & 1)) { if (lane == 0) fail(); ok = false; break; }
                 uint8_t* a_stage = stage0 + (size_t)s * stage_bytes;
-#pragma unroll
-                for (int i = 0; i < 2; i++) {
-                    const int rt16 = dq * 2 + i;  // 16-row tile inside the 128-row block
+                {
+                    const int rt16 = dq;  // 16-row tile inside the 128-row block
                     const int64_t wrt = (int64_t)nt * (GEMM_BN / 16) + rt16;  // weight row-tile
                     const uint8_t* wt = p.tiles + (wrt * p.kt_w + kb / KB_PER_WTILE) * (int64_t)TILE_BYTES;
                     dequant_rowtile<QT>(wt, kb, a_stage, rt16, lane);
