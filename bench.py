@@ -197,13 +197,25 @@ def run_ours(args) -> None:
 
     ctx = CudaContext(local_rank)
     comm = None
-    if world > 1:
-        ids = [Communicator.create_unique_id() if rank == 0 else None]
-        dist.broadcast_object_list(ids, src=0)
-        comm = Communicator(ctx, ids[0], rank, world)
     spec = LLAMA_7B_Q4_0
-    stack = ProjectionStack(ctx, spec, tokens=1, comm=comm)
-    stack.record()
+    mode = args.mode if args.mode != "auto" else ("program" if world > 1 else "graph")
+    if mode == "program":
+        # one persistent kernel per token and rank; the row-shard gather is fused into the GEMV
+        # epilogue (peer stores), so no communicator is needed
+        stack = ProjectionStack(ctx, spec, tokens=1, rank=rank, world=world)
+        handles = None
+        if world > 1:
+            handles = [None] * world
+            dist.all_gather_object(handles, stack.export_buffers())
+        stack.build_program(handles)
+        stack.mode = "program"
+    else:
+        if world > 1:
+            ids = [Communicator.create_unique_id() if rank == 0 else None]
+            dist.broadcast_object_list(ids, src=0)
+            comm = Communicator(ctx, ids[0], rank, world)
+        stack = ProjectionStack(ctx, spec, tokens=1, comm=comm)
+        stack.record()
 
     def barrier():
         ctx.synchronize()
@@ -264,6 +276,9 @@ def run_ours(args) -> None:
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16 activations x 4-bit codes, fp32 accumulate", "data": "synthetic",
             "config": {"workload": WORKLOAD, "parallelism": f"row-sharded tp{world}" if world > 1 else "single GPU",
+                       "execution": ("one persistent kernel per token, gather fused into the GEMV epilogue (peer stores)"
+                                     if mode == "program" else "CUDA graph of one GEMV kernel per projection"
+                                     + (" + NCCL all-gather" if world > 1 else "")),
                        "l2": "inputs larger than L2: 3.64 GB of distinct weights per step", "bytes_per_token": spec.bytes_per_token()},
             "e2e": {"value": 1e3 / (e2e_ms / args.steps), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": int(y_out.nbytes)},
             "gpu_launches": int(launches),
@@ -297,6 +312,8 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--mode", default="auto", choices=["auto", "graph", "program"],
+                    help="graph: one kernel per projection; program: one persistent kernel per token (default for N > 1)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -160,6 +160,40 @@ int wf_comm_destroy(int64_t ctx, int64_t comm);
 int wf_allgather(int64_t ctx, int64_t comm, int64_t send_dev, int64_t recv_dev, int64_t bytes_per_rank,
                  int64_t stream);
 
+/* ---- decode programs ----------------------------------------------------------------
+ * A decode step is a fixed list of quantized projections.  The reference would run it as
+ * one Backend.execute per op from GraphExecutor's loop (warpforge-core/.../graph/GraphExecutor.java:75-104),
+ * each with its own launch and synchronisation; a program runs the whole list as ONE
+ * persistent kernel per GPU, streaming the weights of consecutive ops back to back.
+ *   weights[n_ops]           weight handles, all of one quantization type
+ *   x_dev[n_ops]             bf16 activations [m, k] each op reads (device pointers)
+ *   y_dev[n_ops * world]     for op o and rank r the address, valid on THIS device, of rank r's
+ *                            fp32 output buffer [m, n_total] (own buffer at r == rank; peers'
+ *                            buffers through wf_ipc_import).  Every rank writes its row shard
+ *                            into all of them: the all-gather of CollectiveApi.allGather fused
+ *                            into the GEMV epilogue.
+ *   flags[n_ops]             WF_OP_NEW_X: stage x before this op (else it reuses the previous op's);
+ *                            WF_OP_DEPENDS: x was produced by earlier ops of the program, so all CTAs
+ *                            (and all ranks) synchronise first
+ *   peer_flags[world]        world > 1: address on this device of every rank's flag array
+ *                            (8 * world bytes, zeroed once), own at [rank]
+ * m is 1..8 tokens.  Waits inside the kernel are bounded (WF_ERR_DEVICE_WAIT at the next sync). */
+#define WF_OP_NEW_X 1
+#define WF_OP_DEPENDS 2
+int wf_program_create(int64_t ctx, int n_ops, const int64_t* weights, const int64_t* x_dev, const int64_t* y_dev,
+                      const int* flags, int64_t m, int world, int rank, const int64_t* peer_flags, int64_t* program);
+int wf_program_run(int64_t ctx, int64_t program, int64_t stream);
+int wf_program_destroy(int64_t ctx, int64_t program);
+/* With wf_set_salt(ctx, 2) before wf_program_create: [sm_count][64] globaltimer stamps of the first ops
+ * (kernel start, then per op: start, after barrier, after staging, after compute). */
+int wf_program_read_timing(int64_t ctx, int64_t program, int64_t* out, int64_t n);
+/* Peer access to a wf_malloc'ed buffer of another process on the same node (the role
+ * GpuBackend.registerForRdma plays for the reference's host-memory collectives,
+ * nvidia/NvidiaBackend.java:244-259): a 64-byte handle to hand to the peers out of band. */
+int wf_ipc_export(int64_t ctx, int64_t dptr, void* handle64);
+int wf_ipc_import(int64_t ctx, const void* handle64, int64_t* dptr);
+int wf_ipc_close(int64_t ctx, int64_t dptr);
+
 /* ---- launch management -------------------------------------------------------------
  * The reference launches every kernel with cuLaunchKernel on stream 0 and synchronizes the
  * context after each op (nvidia/cuda/CudaContext.java:273-321, nvidia/ops/DotGeneralKernel.java:283).

@@ -45,6 +45,13 @@ SIGNATURES = {
     "wf_comm_init": (c_int, [c_i64, c_vp, c_int, c_int, P(c_i64)]),
     "wf_comm_destroy": (c_int, [c_i64, c_i64]),
     "wf_allgather": (c_int, [c_i64, c_i64, c_i64, c_i64, c_i64, c_i64]),
+    "wf_program_create": (c_int, [c_i64, c_int, P(c_i64), P(c_i64), P(c_i64), P(c_int), c_i64, c_int, c_int, P(c_i64), P(c_i64)]),
+    "wf_program_run": (c_int, [c_i64, c_i64, c_i64]),
+    "wf_program_destroy": (c_int, [c_i64, c_i64]),
+    "wf_program_read_timing": (c_int, [c_i64, c_i64, P(c_i64), c_i64]),
+    "wf_ipc_export": (c_int, [c_i64, c_i64, c_vp]),
+    "wf_ipc_import": (c_int, [c_i64, c_vp, P(c_i64)]),
+    "wf_ipc_close": (c_int, [c_i64, c_i64]),
     "wf_graph_begin": (c_int, [c_i64, c_i64]),
     "wf_graph_end": (c_int, [c_i64, c_i64, P(c_i64)]),
     "wf_graph_launch": (c_int, [c_i64, c_i64, c_i64]),

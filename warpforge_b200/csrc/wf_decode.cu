@@ -1,0 +1,663 @@
+// A decode step as ONE persistent kernel: a "program" of quantized GEMVs (the projections of
+// a token, in order) run by one CTA per SM.  The weight tiles of consecutive projections flow
+// through the same shared-memory ring without a break: the producer thread of each CTA walks
+// the whole program and keeps issuing bulk copies whenever a stage frees, so HBM stays busy
+// while the consumer warps finish one projection, synchronise, and stage the next
+// activations.  This removes the per-launch prologue and tail that dominate microsecond-scale
+// GEMV kernels.
+//
+// Projections that read an earlier projection's output are separated by a grid barrier
+// (arrive counter + release word in global memory, bounded spins).  With row-sharded tensor
+// parallelism every rank writes its rows of y straight into all ranks' y buffers (peer
+// stores over NVLink) and the grid barrier is extended by one flag exchange between the
+// ranks' first CTAs -- the all-gather is fused into the GEMV epilogue; no collective is
+// launched.  (No multicast loads and no waits between separately launched kernels on one
+// GPU are involved: each rank runs exactly one kernel on its own GPU.)
+//
+// Per-op work split, fix-up between CTAs and the arithmetic are those of gemv_kernel
+// (wf_gemv.cu); the arithmetic replaces the reference's per-op launches at
+// warpforge-backend-nvidia/src/main/java/io/surfworks/warpforge/backend/nvidia/ops/DotGeneralKernel.java:263-283.
+#include <string.h>
+
+#include "wf_gemv_core.cuh"
+
+namespace wf {
+
+constexpr int PROG_MAX_WORLD = 8;
+constexpr int PROG_BARRIER_SPINS = 1 << 24;
+constexpr int OP_NEW_X = 1;    // stage activations before this op (otherwise it reuses the staged ones)
+constexpr int OP_DEPENDS = 2;  // the activations were produced by earlier ops: grid (and rank) barrier first
+
+struct ProgOp {
+    const uint8_t* tiles;
+    const void* x;
+    float* y[PROG_MAX_WORLD];  // this op's output buffer on every rank (own rank included), peer-mapped
+    int64_t ldy, col0;
+    int rows, k, kt, rt;
+    int chunk_q, chunk_r;
+    int flags, pad;
+};
+
+struct ProgSync {                     // device memory owned by the program
+    unsigned long long arrive;        // CTAs arrived at grid barriers, monotonic
+    unsigned long long release;       // barriers released on this rank, monotonic
+    unsigned long long epoch;         // barriers completed by earlier runs
+    unsigned int done_ctas;           // CTAs that left the current run
+    unsigned int pad;
+};
+
+struct ProgParams {
+    const ProgOp* ops;
+    int n_ops, m;
+    uint2* scratch;                   // [2][ctas][128] fix-up slots, alternating by op
+    int* status;
+    ProgSync* sync;
+    unsigned long long* peer_flags[PROG_MAX_WORLD];  // rank r's flag array [world]; I write slot [my rank] on every peer
+    int world, rank;
+    int stages, sx, kp_max;
+    int n_barriers;
+    unsigned long long* timing;  // optional [ctas][64]: globaltimer at op boundaries of the first ops (salt 2)
+};
+
+__device__ __forceinline__ unsigned long long ld_acquire_gpu(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ unsigned long long ld_relaxed_gpu(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(unsigned long long* p, unsigned long long v) {
+    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ void st_release_gpu(unsigned long long* p, unsigned long long v) {
+    asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+
+template <int XC> struct PSlots { static constexpr int N = (XC == 1) ? 4 : 2, ELEMS = 16 * XC; };
+
+// Shared memory: ctrl | partial sums | cinit (kp_max) | staged x | ring.
+template <int QT, int XC>
+__global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_program_kernel(const ProgParams P) {
+    using T = Tile<QT>;
+    using R = TileRegs<QT>;
+    constexpr int NSLOT = PSlots<XC>::N, ELEMS = PSlots<XC>::ELEMS;
+    constexpr uint32_t STAGE_BYTES = GEMV_WARPS * T::BYTES;
+    extern __shared__ __align__(128) uint8_t smem[];
+    int* arrive = reinterpret_cast<int*>(smem);                              // [NSLOT]
+    volatile int* released = reinterpret_cast<volatile int*>(smem) + 8;      // [NSLOT]
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem) + 16;
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + 128);
+    uint64_t* empty = full + GEMV_MAX_STAGES;
+    float* partial = reinterpret_cast<float*>(smem + GEMV_CTRL_BYTES);       // [NSLOT][GEMV_WARPS][ELEMS]
+    float4* cinit = reinterpret_cast<float4*>(partial + NSLOT * GEMV_WARPS * ELEMS);  // [kp_max/32][4]
+    uint8_t* xs = reinterpret_cast<uint8_t*>(cinit + (P.kp_max >> 5) * 4);   // [m][sx]
+    uint8_t* ring = smem + (((size_t)(xs - smem) + (size_t)P.m * P.sx + 127) & ~(size_t)127);
+
+    const int warp = __shfl_sync(0xFFFFFFFFu, (int)(threadIdx.x >> 5), 0);
+    const int lane = threadIdx.x & 31, g = lane >> 2, q = lane & 3;
+    const int bx = blockIdx.x, stages = P.stages;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < 32; i++) reinterpret_cast<int*>(smem)[i] = 0;
+        for (int s = 0; s < stages; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], GEMV_WARPS);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    if (warp == GEMV_WARPS) {
+        // ------------------------------------------------ producer: the whole program, as far ahead as the ring allows
+        if (lane == 0) {
+            int R_ = 0;  // global round counter
+            for (int o = 0; o < P.n_ops && !*abort_flag; o++) {
+                const ProgOp& op = P.ops[o];
+                const int t0 = bx * op.chunk_q + min(bx, op.chunk_r);
+                const int t1 = t0 + op.chunk_q + (bx < op.chunk_r ? 1 : 0);
+                for (int first = t0; first < t1; first += GEMV_WARPS, R_++) {
+                    const int s = R_ % stages;
+                    if (R_ >= stages && !mbar_wait(&empty[s], ((R_ / stages) - 1) & 1)) {
+                        atomicOr(P.status, STATUS_GEMV_FIXUP_TIMEOUT);
+                        *abort_flag = 1;
+                        break;
+                    }
+                    const uint32_t bytes = (uint32_t)min(GEMV_WARPS, t1 - first) * T::BYTES;
+                    mbar_expect_tx(&full[s], bytes);
+                    bulk_load(ring + (size_t)s * STAGE_BYTES, op.tiles + (size_t)first * T::BYTES, bytes, &full[s]);
+                }
+            }
+        }
+        return;
+    }
+
+    // ---------------------------------------------------- consumers
+    const unsigned long long epoch = ld_acquire_gpu(&P.sync->epoch);
+    const uint8_t* xrow = xs + (size_t)(g < P.m ? g : P.m - 1) * P.sx;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    int seg = 0;            // segments flushed so far (all warps flush every segment, so this agrees CTA-wide)
+    int s = 0;
+    uint32_t phase = 0;
+    int barriers = 0;
+    bool failed = false;
+    const uint32_t lane_is_0 = lane == 0;
+    const uint32_t my_tile = smem_u32(ring) + warp * T::BYTES + lane * 16;
+    const uint32_t x32 = smem_u32(xrow) + q * 16, c32 = smem_u32(cinit) + (XC == 1 ? 0 : q * 16);
+    const uint32_t live = (XC == 1) ? (uint32_t)(g == 0) : 1u;
+
+    int stamp_i = 0;
+    auto stamp = [&]() {
+        if (P.timing != nullptr && threadIdx.x == 0 && stamp_i < 64) {
+            unsigned long long tm;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tm));
+            P.timing[(size_t)bx * 64 + stamp_i] = tm;
+        }
+        stamp_i++;
+    };
+    stamp();
+    auto consumers_sync = [&]() { asm volatile("bar.sync 1, %0;" ::"n"(GEMV_WARPS * 32) : "memory"); };
+
+    // Grid barrier number `barriers` of this run, extended over the ranks when world > 1.
+    auto grid_barrier = [&]() {
+        consumers_sync();  // every warp of this CTA has written its y values and passed its flushes
+        if (threadIdx.x == 0) {
+            const unsigned long long idx = epoch + (unsigned long long)barriers + 1;  // 1-based barrier number
+            const unsigned long long want = idx * gridDim.x;
+            bool ok = true;
+            int spins = 0;
+            if (P.world == 1) {
+                // one rank: every CTA watches the arrival counter itself (one memory round trip fewer)
+                __threadfence();
+                atomicAdd(&P.sync->arrive, 1ULL);
+                while (ld_relaxed_gpu(&P.sync->arrive) < want && ++spins < PROG_BARRIER_SPINS) {
+                }
+                ok = spins < PROG_BARRIER_SPINS;
+                __threadfence();
+            } else {
+                __threadfence_system();
+                atomicAdd(&P.sync->arrive, 1ULL);
+                if (bx == 0) {
+                    while (ld_relaxed_gpu(&P.sync->arrive) < want && ++spins < PROG_BARRIER_SPINS) {
+                    }
+                    ok = spins < PROG_BARRIER_SPINS;
+                    __threadfence_system();
+                    for (int r = 0; r < P.world; r++) st_release_sys(P.peer_flags[r] + P.rank, idx);
+                    for (int r = 0; r < P.world && ok; r++) {
+                        spins = 0;
+                        while (ld_acquire_sys(P.peer_flags[P.rank] + r) < idx && ++spins < PROG_BARRIER_SPINS) {
+                        }
+                        ok = spins < PROG_BARRIER_SPINS;
+                    }
+                    st_release_gpu(&P.sync->release, idx);  // released even after a timeout: nobody spins on
+                } else {
+                    while (ld_relaxed_gpu(&P.sync->release) < idx && ++spins < PROG_BARRIER_SPINS) {
+                    }
+                    ok = spins < PROG_BARRIER_SPINS;
+                    __threadfence_system();
+                }
+            }
+            if (!ok) atomicOr(P.status, STATUS_PEER_WAIT_TIMEOUT);
+        }
+        barriers++;
+        consumers_sync();
+    };
+
+    for (int o = 0; o < P.n_ops; o++) {
+        const ProgOp& op = P.ops[o];
+        const int flags = op.flags;
+        const int kt = op.kt;
+        const int t0 = bx * op.chunk_q + min(bx, op.chunk_r);
+        const int t1 = t0 + op.chunk_q + (bx < op.chunk_r ? 1 : 0);
+        uint2* slots = P.scratch + (size_t)(o & 1) * gridDim.x * 128;
+
+        stamp();  // op start (4 stamps per op: start, after barrier, after staging, after compute)
+        if (flags & OP_NEW_X) {
+            if (flags & OP_DEPENDS) grid_barrier();
+            else consumers_sync();  // the staged activations are about to be replaced
+            stamp();
+            GemvParams sp{};
+            sp.x = op.x;
+            sp.m = P.m;
+            sp.k = op.k;
+            sp.ldx = op.k;
+            sp.x_f32 = 0;
+            sp.sx = P.sx;
+            stage_x(sp, xs, reinterpret_cast<float*>(cinit), kt * T::K, R::BETA, GEMV_WARPS * 32, XC == 1);
+            consumers_sync();
+            stamp();
+        } else {
+            stamp();
+            stamp();
+        }
+
+        int seg_begin = t0;
+        int rt = (t0 < t1) ? t0 / kt : 0;
+        int seg_end = min((rt + 1) * kt, t1);
+        int t = t0 + warp;
+        int done_op = 0;  // tiles (= ring rounds) this warp has consumed in this op
+
+        while (seg_begin < t1) {
+            const int n_seg = (t < seg_end) ? (seg_end - t + GEMV_WARPS - 1) / GEMV_WARPS : 0;
+            int kbase = (t - rt * kt) * T::K;
+            for (int i = 0; i < n_seg && !failed; i++) {
+                if (!mbar_wait(&full[s], phase)) {
+                    failed = true;
+                    break;
+                }
+                R regs;
+                regs.load(my_tile + s * STAGE_BYTES, lane);
+                __syncwarp();
+                mbar_arrive_if(&empty[s], lane_is_0);
+                regs.template compute<XC>(acc, x32 + kbase * 2, c32 + (kbase >> 5) * cinit_block_bytes<XC>(), live);
+                kbase += GEMV_WARPS * T::K;
+                t += GEMV_WARPS;
+                done_op++;
+                if (++s == stages) {
+                    s = 0;
+                    phase ^= 1u;
+                }
+            }
+            // ---- flush this segment
+            {
+                const int slot = seg % NSLOT, gen = seg / NSLOT;
+                if (gen > 0) {
+                    int spins = 0;
+                    while (released[slot] < gen && ++spins < GEMV_SLOT_SPINS) {
+                    }
+                    if (released[slot] < gen && lane == 0) atomicOr(P.status, STATUS_GEMV_FIXUP_TIMEOUT);
+                }
+                float* mine = partial + ((size_t)slot * GEMV_WARPS + warp) * ELEMS;
+                if (XC == 1) {
+                    if (q == 0) {
+                        mine[g] = acc[0];
+                        mine[g + 8] = acc[2];
+                    }
+                } else {
+                    mine[(2 * q) * 16 + g] = acc[0];
+                    mine[(2 * q + 1) * 16 + g] = acc[1];
+                    mine[(2 * q) * 16 + g + 8] = acc[2];
+                    mine[(2 * q + 1) * 16 + g + 8] = acc[3];
+                }
+                acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+                __syncwarp();
+                int old = 0;
+                if (lane == 0) {
+                    __threadfence_block();
+                    old = atomicAdd(&arrive[slot], 1);
+                }
+                old = __shfl_sync(0xFFFFFFFFu, old, 0);
+                if (old == GEMV_WARPS * (gen + 1) - 1) {  // last warp to leave the segment finishes it
+                    __threadfence_block();
+                    constexpr int PER_LANE = (ELEMS + 31) / 32;
+                    float v[PER_LANE];
+#pragma unroll
+                    for (int u = 0; u < PER_LANE; u++) {
+                        const int i = lane + 32 * u;
+                        v[u] = 0.f;
+                        if (i < ELEMS) {
+                            const float* src = partial + (size_t)slot * GEMV_WARPS * ELEMS + i;
+#pragma unroll
+                            for (int w = 0; w < GEMV_WARPS; w++) v[u] += src[w * ELEMS];
+                        }
+                    }
+                    const bool starts = seg_begin == rt * kt, ends = seg_end == (rt + 1) * kt;
+                    if (!starts) {  // publish my piece; the slot's previous value (two ops ago) must have been taken
+#pragma unroll
+                        for (int u = 0; u < PER_LANE; u++) {
+                            const int i = lane + 32 * u;
+                            if (i >= ELEMS) continue;
+                            uint2* sp = slots + (size_t)bx * 128 + i;
+                            int spins = 0;
+                            while (ld_slot(sp).y != 0u && ++spins < GEMV_FIXUP_SPINS) __nanosleep(32);
+                            if (spins >= GEMV_FIXUP_SPINS) atomicOr(P.status, STATUS_GEMV_FIXUP_TIMEOUT);
+                            st_slot(sp, make_uint2(__float_as_uint(v[u]), 1u));
+                        }
+                    } else {
+                        if (!ends) {  // owner: add the following CTAs' pieces in CTA order
+                            const int te = (rt + 1) * kt;
+                            bool gave_up = false;
+                            for (int c = bx + 1; c < (int)gridDim.x && !gave_up; c++) {
+                                const int c0 = c * op.chunk_q + min(c, op.chunk_r), c1 = c0 + op.chunk_q + (c < op.chunk_r ? 1 : 0);
+                                if (c0 >= te) break;
+                                if (c0 == c1) continue;
+#pragma unroll
+                                for (int u = 0; u < PER_LANE; u++) {
+                                    const int i = lane + 32 * u;
+                                    if (i >= ELEMS) continue;
+                                    uint2* sp = slots + (size_t)c * 128 + i;
+                                    uint2 e;
+                                    int spins = 0;
+                                    do {
+                                        e = ld_slot(sp);
+                                        if (e.y != 0u) break;
+                                        __nanosleep(32);
+                                    } while (++spins < GEMV_FIXUP_SPINS);
+                                    if (e.y == 0u) {
+                                        atomicOr(P.status, STATUS_GEMV_FIXUP_TIMEOUT);
+                                        gave_up = true;
+                                    } else {
+                                        v[u] += __uint_as_float(e.x);
+                                        st_slot(sp, make_uint2(0u, 0u));
+                                    }
+                                }
+                                gave_up = __any_sync(0xFFFFFFFFu, gave_up);
+                            }
+                        }
+                        // y goes to every rank's buffer: the row-shard gather happens here
+#pragma unroll
+                        for (int u = 0; u < PER_LANE; u++) {
+                            const int i = lane + 32 * u, col = i >> 4, n = rt * 16 + (i & 15);
+                            if (i < ELEMS && col < P.m && n < op.rows) {
+                                const int64_t off = (int64_t)col * op.ldy + op.col0 + n;
+                                for (int r = 0; r < P.world; r++) op.y[r][off] = v[u];
+                            }
+                        }
+                    }
+                    __syncwarp();
+                    if (lane == 0) {
+                        __threadfence_block();
+                        released[slot] = gen + 1;
+                    }
+                }
+                seg++;
+                seg_begin = seg_end;
+                rt++;
+                seg_end = min((rt + 1) * kt, t1);
+            }
+            if (failed) break;
+        }
+        stamp();
+        if (failed) break;
+        // Only the op's last round can lack a tile for some warps.  Its stage is refilled for the next
+        // op, so those warps still wait for the round's data (keeping their release in order) and
+        // release the stage.
+        if (done_op < (t1 - t0 + GEMV_WARPS - 1) / GEMV_WARPS) {
+            if (!mbar_wait(&full[s], phase)) {
+                failed = true;
+                break;
+            }
+            mbar_arrive_if(&empty[s], lane_is_0);
+            if (++s == stages) {
+                s = 0;
+                phase ^= 1u;
+            }
+        }
+    }
+    if (failed) {
+        if (lane == 0) atomicOr(P.status, STATUS_GEMV_FIXUP_TIMEOUT);
+        *abort_flag = 1;
+    }
+
+    // ---- leave: the last CTA out advances the epoch for the next run
+    consumers_sync();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        const unsigned int d = atomicAdd(&P.sync->done_ctas, 1u);
+        if (d == gridDim.x - 1) {
+            P.sync->done_ctas = 0;
+            // CTAs that skipped barriers after a failure would leave `arrive` short: resynchronise it
+            P.sync->arrive = (epoch + (unsigned long long)P.n_barriers) * gridDim.x;
+            __threadfence();
+            st_release_gpu(&P.sync->epoch, epoch + (unsigned long long)P.n_barriers);
+        }
+    }
+}
+
+// ---------------------------------------------------------------- host side
+struct Program {
+    uint32_t magic = 0x57465047;  // "WFPG"
+    Context* ctx = nullptr;
+    int qtype = 0, n_ops = 0, m = 0, world = 1, rank = 0;
+    ProgOp* d_ops = nullptr;
+    ProgSync* d_sync = nullptr;
+    uint2* d_scratch = nullptr;
+    unsigned long long* d_timing = nullptr;
+    ProgParams params{};
+    size_t smem = 0;
+    int grid = 0;
+};
+
+static std::mutex g_prog_mu;
+static std::vector<Program*> g_programs;
+
+static Program* get_program(Context* c, int64_t h) {
+    Program* p = reinterpret_cast<Program*>(h);
+    std::lock_guard<std::mutex> lk(g_prog_mu);
+    if (!p || std::find(g_programs.begin(), g_programs.end(), p) == g_programs.end() || p->magic != 0x57465047 || p->ctx != c)
+        return nullptr;
+    return p;
+}
+
+template <int QT, int XC>
+static cudaError_t program_launch(const Program& pr, cudaStream_t s) {
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 64 && !attr_set[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(gemv_program_kernel<QT, XC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (e != cudaSuccess) return e;
+        attr_set[dev] = true;
+    }
+    gemv_program_kernel<QT, XC><<<pr.grid, GEMV_THREADS, pr.smem, s>>>(pr.params);
+    return cudaGetLastError();
+}
+
+}  // namespace wf
+
+using namespace wf;
+
+extern "C" {
+
+int wf_program_create(int64_t ctx, int n_ops, const int64_t* weights, const int64_t* x_dev, const int64_t* y_dev, const int* flags,
+                      int64_t m, int world, int rank, const int64_t* peer_flags, int64_t* program) {
+    Context* c = get_context(ctx);
+    if (!c) return WF_ERR_INVALID_HANDLE;
+    ScopedLock lk(c);
+    if (!lk.ok) return WF_ERR_BUSY;
+    if (!weights || !x_dev || !y_dev || !flags || !program || n_ops < 1) return set_error(c, WF_ERR_INVALID_ARGUMENT, "null pointer or empty program");
+    *program = 0;
+    if (m < 1 || m > 8) return set_error(c, WF_ERR_SHAPE, "a program takes 1..8 bf16 tokens, got %lld", (long long)m);
+    if (world < 1 || world > PROG_MAX_WORLD || rank < 0 || rank >= world) return set_error(c, WF_ERR_SHARD, "rank %d outside world %d (max %d)", rank, world, PROG_MAX_WORLD);
+    if (world > 1 && !peer_flags) return set_error(c, WF_ERR_INVALID_ARGUMENT, "peer flag arrays are required for world > 1");
+    WF_CUDA(c, cudaSetDevice(c->device));
+
+    std::vector<ProgOp> ops((size_t)n_ops);
+    int qt = 0, kp_max = 0, n_barriers = 0;
+    const int grid = c->sm_count;
+    for (int o = 0; o < n_ops; o++) {
+        Weight* w = get_weight(c, weights[o]);
+        if (!w) return set_error(c, WF_ERR_INVALID_HANDLE, "op %d: bad weight handle", o);
+        if (o == 0) qt = w->g.qtype;
+        if (w->g.qtype != qt) return set_error(c, WF_ERR_UNSUPPORTED_TYPE, "op %d: all weights of a program must share one quantization type", o);
+        if (w->total_rows != w->g.rows * world || w->row0 != w->g.rows * rank)
+            return set_error(c, WF_ERR_SHARD, "op %d: weight shard does not match rank %d of %d", o, rank, world);
+        const int64_t total = w->g.rt * w->g.kt;
+        if (total >= (1LL << 31)) return set_error(c, WF_ERR_TOO_LARGE, "op %d: too many tiles", o);
+        ProgOp& op = ops[o];
+        op.tiles = w->d_tiles;
+        op.x = reinterpret_cast<const void*>(x_dev[o]);
+        for (int r = 0; r < world; r++) {
+            op.y[r] = reinterpret_cast<float*>(y_dev[(size_t)o * world + r]);
+            if (!op.y[r]) return set_error(c, WF_ERR_INVALID_ARGUMENT, "op %d: null output pointer for rank %d", o, r);
+        }
+        if (!op.x) return set_error(c, WF_ERR_INVALID_ARGUMENT, "op %d: null activation pointer", o);
+        op.ldy = w->total_rows;
+        op.col0 = w->row0;
+        op.rows = (int)w->g.rows;
+        op.k = (int)w->g.k;
+        op.kt = (int)w->g.kt;
+        op.rt = (int)w->g.rt;
+        op.chunk_q = (int)(total / grid);
+        op.chunk_r = (int)(total % grid);
+        op.flags = (o == 0 ? (flags[o] | OP_NEW_X) : flags[o]) & (OP_NEW_X | OP_DEPENDS);
+        if ((op.flags & OP_DEPENDS) && !(op.flags & OP_NEW_X)) op.flags |= OP_NEW_X;
+        if (o == 0) op.flags &= ~OP_DEPENDS;  // nothing of this run precedes the first op
+        if (op.flags & OP_DEPENDS) n_barriers++;
+        kp_max = std::max(kp_max, op.kt * tile_k(qt));
+    }
+    // shared memory: ctrl + partial + cinit + x + ring
+    const int xc = (m == 1) ? 1 : 8;
+    const int nslot = xc == 1 ? 4 : 2, elems = 16 * xc;
+    const int sx = kp_max * 2 + 64;
+    size_t fixed = GEMV_CTRL_BYTES + (size_t)nslot * GEMV_WARPS * elems * 4 + (size_t)(kp_max / 32) * 64 + (size_t)m * sx;
+    fixed = (fixed + 127) & ~(size_t)127;
+    const size_t stage = (size_t)GEMV_WARPS * tile_bytes(qt);
+    if (fixed + 2 * stage > 227 * 1024) return set_error(c, WF_ERR_TOO_LARGE, "K=%d with %lld tokens does not fit one SM's shared memory", kp_max, (long long)m);
+    const int stages = (int)std::min<size_t>((227 * 1024 - fixed) / stage, GEMV_MAX_STAGES);
+
+    Program* pr = new Program();
+    pr->ctx = c;
+    pr->qtype = qt;
+    pr->n_ops = n_ops;
+    pr->m = (int)m;
+    pr->world = world;
+    pr->rank = rank;
+    pr->grid = grid;
+    pr->smem = fixed + (size_t)stages * stage;
+    cudaError_t e = cudaMalloc(&pr->d_ops, sizeof(ProgOp) * (size_t)n_ops);
+    if (e == cudaSuccess) e = cudaMalloc(&pr->d_sync, sizeof(ProgSync));
+    if (e == cudaSuccess) e = cudaMalloc(&pr->d_scratch, (size_t)2 * grid * 128 * sizeof(uint2));
+    if (e == cudaSuccess) e = cudaMemcpy(pr->d_ops, ops.data(), sizeof(ProgOp) * (size_t)n_ops, cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMemset(pr->d_sync, 0, sizeof(ProgSync));
+    if (e == cudaSuccess) e = cudaMemset(pr->d_scratch, 0, (size_t)2 * grid * 128 * sizeof(uint2));
+    if (e != cudaSuccess) {
+        cudaFree(pr->d_ops);
+        cudaFree(pr->d_sync);
+        cudaFree(pr->d_scratch);
+        delete pr;
+        return cuda_status(c, e, "program allocation");
+    }
+    ProgParams& P = pr->params;
+    P.ops = pr->d_ops;
+    P.n_ops = n_ops;
+    P.m = (int)m;
+    P.scratch = pr->d_scratch;
+    P.status = c->d_status;
+    P.sync = pr->d_sync;
+    for (int r = 0; r < world; r++) P.peer_flags[r] = world > 1 ? reinterpret_cast<unsigned long long*>(peer_flags[r]) : nullptr;
+    P.world = world;
+    P.rank = rank;
+    P.stages = stages;
+    P.sx = sx;
+    P.kp_max = kp_max;
+    P.n_barriers = n_barriers;
+    P.timing = nullptr;
+    if (c->salt >= 2) {
+        if (cudaMalloc(&pr->d_timing, (size_t)grid * 64 * 8) == cudaSuccess) {
+            cudaMemset(pr->d_timing, 0, (size_t)grid * 64 * 8);
+            P.timing = pr->d_timing;
+        }
+    }
+    {
+        std::lock_guard<std::mutex> g(g_prog_mu);
+        g_programs.push_back(pr);
+    }
+    *program = reinterpret_cast<int64_t>(pr);
+    return WF_OK;
+}
+
+int wf_program_run(int64_t ctx, int64_t program, int64_t stream) {
+    Context* c = get_context(ctx);
+    if (!c) return WF_ERR_INVALID_HANDLE;
+    ScopedLock lk(c);
+    if (!lk.ok) return WF_ERR_BUSY;
+    Program* pr = get_program(c, program);
+    if (!pr) return WF_ERR_INVALID_HANDLE;
+    WF_CUDA(c, cudaSetDevice(c->device));
+    cudaStream_t s = resolve_stream(c, stream);
+    const int qt = pr->qtype;
+    cudaError_t e;
+    if (pr->m == 1)
+        e = qt == WF_QTYPE_Q4_0 ? program_launch<WF_QTYPE_Q4_0, 1>(*pr, s) : qt == WF_QTYPE_Q8_0 ? program_launch<WF_QTYPE_Q8_0, 1>(*pr, s) : program_launch<WF_QTYPE_Q4_K, 1>(*pr, s);
+    else
+        e = qt == WF_QTYPE_Q4_0 ? program_launch<WF_QTYPE_Q4_0, 8>(*pr, s) : qt == WF_QTYPE_Q8_0 ? program_launch<WF_QTYPE_Q8_0, 8>(*pr, s) : program_launch<WF_QTYPE_Q4_K, 8>(*pr, s);
+    if (e != cudaSuccess) return cuda_status(c, e, "program launch");
+    c->launches++;
+    return WF_OK;
+}
+
+int wf_program_read_timing(int64_t ctx, int64_t program, int64_t* out, int64_t n) {
+    Context* c = get_context(ctx);
+    if (!c) return WF_ERR_INVALID_HANDLE;
+    ScopedLock lk(c);
+    if (!lk.ok) return WF_ERR_BUSY;
+    Program* pr = get_program(c, program);
+    if (!pr) return WF_ERR_INVALID_HANDLE;
+    if (!out || n < 0 || !pr->d_timing) return set_error(c, WF_ERR_INVALID_ARGUMENT, "timing stamps are off (wf_set_salt(ctx, 2) before wf_program_create)");
+    WF_CUDA(c, cudaSetDevice(c->device));
+    WF_CUDA(c, cudaDeviceSynchronize());
+    WF_CUDA(c, cudaMemcpy(out, pr->d_timing, (size_t)std::min<int64_t>(n, (int64_t)pr->grid * 64) * 8, cudaMemcpyDeviceToHost));
+    return WF_OK;
+}
+
+int wf_program_destroy(int64_t ctx, int64_t program) {
+    Context* c = get_context(ctx);
+    if (!c) return WF_ERR_INVALID_HANDLE;
+    ScopedLock lk(c);
+    if (!lk.ok) return WF_ERR_BUSY;
+    Program* pr = get_program(c, program);
+    if (!pr) return WF_ERR_INVALID_HANDLE;
+    {
+        std::lock_guard<std::mutex> g(g_prog_mu);
+        g_programs.erase(std::find(g_programs.begin(), g_programs.end(), pr));
+    }
+    cudaSetDevice(c->device);
+    cudaDeviceSynchronize();
+    cudaFree(pr->d_ops);
+    cudaFree(pr->d_sync);
+    cudaFree(pr->d_scratch);
+    if (pr->d_timing) cudaFree(pr->d_timing);
+    pr->magic = 0;
+    delete pr;
+    return WF_OK;
+}
+
+// ---- peer memory: the handle a rank hands to its peers so they can store into its buffers
+int wf_ipc_export(int64_t ctx, int64_t dptr, void* handle64) {
+    Context* c = get_context(ctx);
+    if (!c) return WF_ERR_INVALID_HANDLE;
+    ScopedLock lk(c);
+    if (!lk.ok) return WF_ERR_BUSY;
+    if (!dptr || !handle64) return WF_ERR_INVALID_ARGUMENT;
+    WF_CUDA(c, cudaSetDevice(c->device));
+    cudaIpcMemHandle_t h;
+    WF_CUDA(c, cudaIpcGetMemHandle(&h, reinterpret_cast<void*>(dptr)));
+    static_assert(sizeof(h) == 64, "IPC handle size");
+    memcpy(handle64, &h, 64);
+    return WF_OK;
+}
+
+int wf_ipc_import(int64_t ctx, const void* handle64, int64_t* dptr) {
+    Context* c = get_context(ctx);
+    if (!c) return WF_ERR_INVALID_HANDLE;
+    ScopedLock lk(c);
+    if (!lk.ok) return WF_ERR_BUSY;
+    if (!dptr || !handle64) return WF_ERR_INVALID_ARGUMENT;
+    WF_CUDA(c, cudaSetDevice(c->device));
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, 64);
+    void* p = nullptr;
+    WF_CUDA(c, cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+    *dptr = reinterpret_cast<int64_t>(p);
+    return WF_OK;
+}
+
+int wf_ipc_close(int64_t ctx, int64_t dptr) {
+    Context* c = get_context(ctx);
+    if (!c) return WF_ERR_INVALID_HANDLE;
+    ScopedLock lk(c);
+    if (!lk.ok) return WF_ERR_BUSY;
+    WF_CUDA(c, cudaSetDevice(c->device));
+    WF_CUDA(c, cudaIpcCloseMemHandle(reinterpret_cast<void*>(dptr)));
+    return WF_OK;
+}
+
+}  // extern "C"

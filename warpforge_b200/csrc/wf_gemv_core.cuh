@@ -1,0 +1,388 @@
+// Device-side building blocks of the decode GEMV, shared by the single-op kernel (wf_gemv.cu)
+// and the persistent multi-op kernel (wf_decode.cu): shared-memory ring primitives, the unpack +
+// tensor-core block routine, the per-format tile code and the activation staging.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <stdlib.h>
+
+#include <algorithm>
+
+#include "wf_common.cuh"
+
+namespace wf {
+
+constexpr int GEMV_WARPS = 16;                       // consumer warps
+constexpr int GEMV_THREADS = (GEMV_WARPS + 1) * 32;  // + one producer warp
+constexpr int GEMV_MAX_STAGES = 16;
+constexpr int GEMV_BAR_SPINS = 1 << 24;
+constexpr int GEMV_XCOLS = 8;  // columns of one mma n-tile
+constexpr int GEMV_FIXUP_SPINS = 1 << 22;
+constexpr int GEMV_SLOT_SPINS = 1 << 24;
+constexpr int GEMV_CTRL_BYTES = 128 + 2 * GEMV_MAX_STAGES * 8;  // arrive[], released[], abort, full[], empty[]
+
+struct GemvParams {
+    const uint8_t* tiles;
+    const void* x;
+    float* y;
+    uint2* scratch;
+    int* status;
+    int64_t ldy, col0;
+    int64_t ldx;  // elements between consecutive tokens of x
+    int rows, k, kt, rt;
+    int m;        // tokens this pass (<= 8 for bf16, <= 2 for fp32)
+    int x_f32;    // 1: x is fp32 and each token is split into 3 exact bf16 columns
+    int sx;       // shared-memory row stride of staged x, in bytes
+    int stages;   // ring depth, each stage holds GEMV_WARPS tiles
+    int chunk_q, chunk_r;  // CTA b owns tiles [b*q + min(b,r), (b+1)*q + min(b+1,r))
+    unsigned long long* timing;  // optional [ctas][8] globaltimer stamps (instrumented launches only)
+};
+
+// ---------------------------------------------------------------- small device helpers
+// shared-memory loads by 32-bit shared address (no generic-pointer arithmetic in the hot loop)
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t a) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+    return v;
+}
+// Per 32-k block: the B fragment (8 activations of this lane's column) and the accumulator start.
+//   XC = 8: every lane loads its own column (16 bytes) and its float4 of start values.
+//   XC = 1: only column 0 is live.  The four lanes that own it (g == 0) load the activations --
+//           a predicated load touches one quarter-warp instead of four -- and the start value is a
+//           single float read by all lanes at one address (a broadcast).  Dead columns compute on
+//           whatever the registers hold; their results are never stored.
+template <int XC>
+__device__ __forceinline__ void fetch_block(uint32_t xaddr, uint32_t caddr, uint32_t live, uint4& xb, float4& ci) {
+    if (XC == 1) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %5, 0;\n\t@p ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n\t}"
+            : "+r"(xb.x), "+r"(xb.y), "+r"(xb.z), "+r"(xb.w)
+            : "r"(xaddr), "r"(live));
+        float c;
+        asm volatile("ld.shared.f32 %0, [%1];" : "=f"(c) : "r"(caddr));
+        ci = make_float4(c, c, c, c);
+    } else {
+        xb = lds128(xaddr);
+        const uint4 t = lds128(caddr);
+        ci = make_float4(__uint_as_float(t.x), __uint_as_float(t.y), __uint_as_float(t.z), __uint_as_float(t.w));
+    }
+}
+// Offsets of block `blk` inside the start-value table: one float (XC = 1) or [4] float4 (XC = 8).
+template <int XC> __device__ __forceinline__ constexpr int cinit_block_bytes() { return XC == 1 ? 4 : 64; }
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(void* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(void* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// arrive from the lanes whose `pred` is non-zero, without a branch
+__device__ __forceinline__ void mbar_arrive_if(void* bar, uint32_t pred) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %1, 0;\n\t@p mbarrier.arrive.shared::cta.b64 _, [%0];\n\t}" ::"r"(smem_u32(bar)),
+        "r"(pred)
+        : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(void* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Bounded wait: false if the phase did not complete within the spin budget.
+__device__ __forceinline__ bool mbar_wait(void* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, q;\n\t"
+        ".reg .u32 n;\n\t"
+        "mov.u32 n, 0;\n\t"
+        "WF_WAIT_%=:\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "@p bra WF_DONE_%=;\n\t"
+        "add.u32 n, n, 1;\n\t"
+        "setp.lt.u32 q, n, %3;\n\t"
+        "@q bra WF_WAIT_%=;\n\t"
+        "WF_DONE_%=:\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"((uint32_t)GEMV_BAR_SPINS)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, void* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)),
+                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+// A scratch slot element is {value bits, valid tag}.  It is written and read as ONE 64-bit
+// access so that a reader can never see the tag of one write with the value of another.
+__device__ __forceinline__ void st_slot(uint2* p, uint2 v) {
+    const unsigned long long w = ((unsigned long long)v.y << 32) | v.x;
+    asm volatile("st.relaxed.gpu.global.b64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
+}
+__device__ __forceinline__ uint2 ld_slot(const uint2* p) {
+    unsigned long long w;
+    asm volatile("ld.relaxed.gpu.global.b64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+    return make_uint2((uint32_t)w, (uint32_t)(w >> 32));
+}
+// d = a * b + c, d and c separate so that c can come straight from another register set
+__device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1, float c0, float c1, float c2, float c3) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%10,%11,%12,%13};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c0), "f"(c1), "f"(c2), "f"(c3));
+}
+__device__ __forceinline__ float2 half2_bits_to_float2(uint32_t h2) {
+    return __half22float2(*reinterpret_cast<const __half2*>(&h2));
+}
+
+// Codes enter the MMA as bf16 `base + scale * code`: magic 0x4180 -> 16 + code,
+// magic 0x4380 -> 256 + 16 * code (nibble in the top four mantissa bits).  Exact.
+constexpr uint32_t MAGIC_16 = 0x41804180u;   // 16 + code
+constexpr uint32_t MAGIC_256 = 0x43804380u;  // 256 + 16 * code
+
+// d = c + sum over one 32-k block of (base + scale * code) * x, rows g / g+8 of the fragment.
+// One asm block: three rotates and eight logic ops unpack the two words, two MMAs consume
+// them.  The temporaries live inside the block so the register allocator is free to build
+// the MMA operand tuples in place.
+__device__ __forceinline__ void block_mma(float (&d)[4], uint32_t wg, uint32_t wh, const uint4& xb, uint32_t magic,
+                                          float c0, float c1, float c2, float c3) {
+    asm(
+        "{\n\t"
+        ".reg .b32 g1, g2, g3, h1, h2, h3, a0, a1, a2, a3, a4, a5, a6, a7;\n\t"
+        "shf.r.wrap.b32 g1, %4, %4, 4;\n\t"
+        "shf.r.wrap.b32 h1, %5, %5, 4;\n\t"
+        "shf.r.wrap.b32 g2, %4, %4, 8;\n\t"
+        "shf.r.wrap.b32 h2, %5, %5, 8;\n\t"
+        "shf.r.wrap.b32 g3, %4, %4, 12;\n\t"
+        "shf.r.wrap.b32 h3, %5, %5, 12;\n\t"
+        "lop3.b32 a0, %4, %14, %15, 0xEA;\n\t"
+        "lop3.b32 a1, %5, %14, %15, 0xEA;\n\t"
+        "lop3.b32 a2, g1, %14, %15, 0xEA;\n\t"
+        "lop3.b32 a3, h1, %14, %15, 0xEA;\n\t"
+        "lop3.b32 a4, g2, %14, %15, 0xEA;\n\t"
+        "lop3.b32 a5, h2, %14, %15, 0xEA;\n\t"
+        "lop3.b32 a6, g3, %14, %15, 0xEA;\n\t"
+        "lop3.b32 a7, h3, %14, %15, 0xEA;\n\t"
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {a0,a1,a2,a3}, {%6,%7}, {%10,%11,%12,%13};\n\t"
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {a4,a5,a6,a7}, {%8,%9}, {%0,%1,%2,%3};\n\t"
+        "}\n"
+        : "=&f"(d[0]), "=&f"(d[1]), "=&f"(d[2]), "=&f"(d[3])
+        : "r"(wg), "r"(wh), "r"(xb.x), "r"(xb.y), "r"(xb.z), "r"(xb.w), "f"(c0), "f"(c1), "f"(c2), "f"(c3),
+          "r"(0x00780078u), "r"(magic));
+}
+
+__device__ __forceinline__ uint32_t word_of(const uint4& v, int j) {
+    return j == 0 ? v.x : j == 1 ? v.y : j == 2 ? v.z : v.w;
+}
+
+// ---------------------------------------------------------------- per-format tile code
+// BETA: factor on "sum of the block's activations" that cancels the offsets the codes carry
+// into the MMA.
+template <int QT> struct TileRegs;
+
+template <> struct TileRegs<WF_QTYPE_Q4_0> {
+    static constexpr float BETA = -24.f;  // (16 + code) - 24 = code - 8
+    uint4 c[2], s;
+    // t = shared address of the tile + lane * 16
+    __device__ __forceinline__ void load(uint32_t t, int lane) {
+        c[0] = lds128(t);
+        c[1] = lds128(t + 512);
+        s = lds128(t - lane * 16 + Tile<WF_QTYPE_Q4_0>::SCALE_OFF + (lane >> 2) * 16);
+    }
+    template <int XC>
+    // xaddr: shared address of this lane's activations for k = kbase (row + q * 16 bytes);
+    // caddr: shared address of the start value(s) of block kbase / 32; live: lane owns a live column
+    __device__ __forceinline__ void compute(float (&acc)[4], uint32_t xaddr, uint32_t caddr, uint32_t live) const {
+        uint4 xb = make_uint4(0u, 0u, 0u, 0u);
+        float4 ci;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            fetch_block<XC>(xaddr + j * 64, caddr + j * cinit_block_bytes<XC>(), live, xb, ci);
+            float d[4];
+            block_mma(d, word_of(c[0], j), word_of(c[1], j), xb, MAGIC_16, ci.x, ci.y, ci.z, ci.w);
+            const float2 dg = half2_bits_to_float2(j < 2 ? s.x : s.y), dh = half2_bits_to_float2(j < 2 ? s.z : s.w);
+            const float sg = (j & 1) ? dg.y : dg.x, sh = (j & 1) ? dh.y : dh.x;
+            acc[0] = fmaf(sg, d[0], acc[0]);
+            acc[2] = fmaf(sh, d[2], acc[2]);
+            if (XC > 1) {
+                acc[1] = fmaf(sg, d[1], acc[1]);
+                acc[3] = fmaf(sh, d[3], acc[3]);
+            }
+        }
+    }
+};
+
+template <> struct TileRegs<WF_QTYPE_Q8_0> {
+    static constexpr float BETA = -400.f;  // (256 + 16 hi) + (16 + lo) - 400 = 16 (hi - 8) + lo
+    uint4 c[4], s;                         // c[0..1] high plane rows g / g+8, c[2..3] low plane
+    __device__ __forceinline__ void load(uint32_t t, int lane) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) c[i] = lds128(t + i * 512);
+        s = lds128(t - lane * 16 + Tile<WF_QTYPE_Q8_0>::SCALE_OFF + (lane >> 2) * 16);
+    }
+    template <int XC>
+    // xaddr: shared address of this lane's activations for k = kbase (row + q * 16 bytes);
+    // caddr: shared address of the start value(s) of block kbase / 32; live: lane owns a live column
+    __device__ __forceinline__ void compute(float (&acc)[4], uint32_t xaddr, uint32_t caddr, uint32_t live) const {
+        uint4 xb = make_uint4(0u, 0u, 0u, 0u);
+        float4 ci;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            fetch_block<XC>(xaddr + j * 64, caddr + j * cinit_block_bytes<XC>(), live, xb, ci);
+            float d[4];
+            block_mma(d, word_of(c[0], j), word_of(c[1], j), xb, MAGIC_256, ci.x, ci.y, ci.z, ci.w);
+            block_mma(d, word_of(c[2], j), word_of(c[3], j), xb, MAGIC_16, d[0], d[1], d[2], d[3]);
+            const float2 dg = half2_bits_to_float2(j < 2 ? s.x : s.y), dh = half2_bits_to_float2(j < 2 ? s.z : s.w);
+            const float sg = (j & 1) ? dg.y : dg.x, sh = (j & 1) ? dh.y : dh.x;
+            acc[0] = fmaf(sg, d[0], acc[0]);
+            acc[2] = fmaf(sh, d[2], acc[2]);
+            if (XC > 1) {
+                acc[1] = fmaf(sg, d[1], acc[1]);
+                acc[3] = fmaf(sh, d[3], acc[3]);
+            }
+        }
+    }
+};
+
+// byte `i` of w times d, exactly: (2^23 + byte) * d - 2^23 * d
+__device__ __forceinline__ float byte_times(uint32_t w, int i, float d, float neg_big_d) {
+    const float f = __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540u + i));
+    return fmaf(f, d, neg_big_d);
+}
+
+template <> struct TileRegs<WF_QTYPE_Q4_K> {
+    static constexpr float BETA = -16.f;  // (16 + code) - 16 = code
+    uint4 c[4], sc, mn;                   // c[0..1] sub-blocks 0..3 rows g / g+8, c[2..3] sub-blocks 4..7
+    uint2 dd;                             // (d, dmin) of row g, of row g+8
+    __device__ __forceinline__ void load(uint32_t t, int lane) {
+        using T = Tile<WF_QTYPE_Q4_K>;
+#pragma unroll
+        for (int i = 0; i < 4; i++) c[i] = lds128(t + i * 512);
+        const uint32_t base = t - lane * 16;
+        dd = lds64(base + T::D_OFF + (lane >> 2) * 8);
+        sc = lds128(base + T::SC_OFF + (lane >> 2) * 16);
+        mn = lds128(base + T::MN_OFF + (lane >> 2) * 16);
+    }
+    template <int XC>
+    // xaddr: shared address of this lane's activations for k = kbase (row + q * 16 bytes);
+    // caddr: shared address of the start value(s) of block kbase / 32; live: lane owns a live column
+    __device__ __forceinline__ void compute(float (&acc)[4], uint32_t xaddr, uint32_t caddr, uint32_t live) const {
+        uint4 xb = make_uint4(0u, 0u, 0u, 0u);
+        float4 ci;
+        const float2 g = half2_bits_to_float2(dd.x), h = half2_bits_to_float2(dd.y);  // (d, dmin)
+        const float BIG = 8388608.f;
+        // the min term -dmin*m*X comes from cinit = -16*X as (dmin/16) * m * cinit
+        const float gm = g.y * 0.0625f, hm = h.y * 0.0625f;
+        const float ngd = -BIG * g.x, ngm = -BIG * gm, nhd = -BIG * h.x, nhm = -BIG * hm;
+#pragma unroll
+        for (int jj = 0; jj < 8; jj++) {
+            fetch_block<XC>(xaddr + jj * 64, caddr + jj * cinit_block_bytes<XC>(), live, xb, ci);
+            float d[4];
+            block_mma(d, word_of(c[(jj >> 2) * 2], jj & 3), word_of(c[(jj >> 2) * 2 + 1], jj & 3), xb, MAGIC_16, ci.x,
+                      ci.y, ci.z, ci.w);
+            const float ag = byte_times(jj < 4 ? sc.x : sc.y, jj & 3, g.x, ngd);  // d * sc, exact
+            const float ah = byte_times(jj < 4 ? sc.z : sc.w, jj & 3, h.x, nhd);
+            const float cg = byte_times(jj < 4 ? mn.x : mn.y, jj & 3, gm, ngm);  // dmin * m / 16, exact
+            const float ch = byte_times(jj < 4 ? mn.z : mn.w, jj & 3, hm, nhm);
+            acc[0] = fmaf(ag, d[0], fmaf(cg, ci.x, acc[0]));
+            acc[2] = fmaf(ah, d[2], fmaf(ch, ci.z, acc[2]));
+            if (XC > 1) {
+                acc[1] = fmaf(ag, d[1], fmaf(cg, ci.y, acc[1]));
+                acc[3] = fmaf(ah, d[3], fmaf(ch, ci.w, acc[3]));
+            }
+        }
+    }
+};
+
+// ---------------------------------------------------------------- x staging
+// Copies x into shared memory as bf16 rows of `kp` elements (zero beyond k), row stride sx
+// bytes.  bf16 input: row = token.  fp32 input: token t becomes rows 3t, 3t+1, 3t+2 holding
+// an exact three-way bf16 split (x = hi + mid + lo), so fp32 activations lose nothing.
+// Also fills cinit[kp/32][4]: for block b and column pair q the float4
+// {beta*X(b,2q), beta*X(b,2q+1), same, same}, X = fp32 sum of the block's 32 activations.
+__device__ __forceinline__ uint32_t pack_bf16_trunc(float a, float b) {
+    return (__float_as_uint(a) >> 16) | (__float_as_uint(b) & 0xFFFF0000u);
+}
+
+// one_col: write the start values as one float per block (column 0 only) instead of [4] float4
+static __device__ void stage_x(const GemvParams& p, uint8_t* xs, float* cinit, int kp, float beta, int nthreads, bool one_col) {
+    const int groups = kp >> 3;  // 8 elements per thread step
+    const int total = p.m * groups;
+    for (int idx = threadIdx.x; idx < ((total + 31) & ~31); idx += nthreads) {  // warp-uniform trip count
+        const bool live = idx < total;
+        const int t = (live && p.m > 1) ? idx / groups : 0, c8 = live ? idx - t * groups : 0;
+        const bool in_k = live && (c8 * 8 < p.k);
+        float sum[3] = {0.f, 0.f, 0.f};
+        if (!p.x_f32) {
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (in_k) v = __ldcg(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.x) + (size_t)t * p.ldx + c8 * 8));
+            if (live) *reinterpret_cast<uint4*>(xs + (size_t)t * p.sx + c8 * 16) = v;
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                sum[0] += __uint_as_float(w[i] << 16);
+                sum[0] += __uint_as_float(w[i] & 0xFFFF0000u);
+            }
+        } else {
+            float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            if (in_k) {
+                const float4* src =
+                    reinterpret_cast<const float4*>(static_cast<const float*>(p.x) + (size_t)t * p.ldx + c8 * 8);
+                const float4 a = __ldcg(src), b = __ldcg(src + 1);
+                f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+            }
+            uint32_t hi[4], mid[4], lo[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float x0 = f[2 * i], x1 = f[2 * i + 1];
+                const float h0 = __uint_as_float(__float_as_uint(x0) & 0xFFFF0000u);
+                const float h1 = __uint_as_float(__float_as_uint(x1) & 0xFFFF0000u);
+                const float r0 = x0 - h0, r1 = x1 - h1;
+                const float m0 = __uint_as_float(__float_as_uint(r0) & 0xFFFF0000u);
+                const float m1 = __uint_as_float(__float_as_uint(r1) & 0xFFFF0000u);
+                const float l0 = r0 - m0, l1 = r1 - m1;  // at most 8 significant bits left: exact in bf16
+                hi[i] = pack_bf16_trunc(h0, h1);
+                mid[i] = pack_bf16_trunc(m0, m1);
+                lo[i] = pack_bf16_trunc(l0, l1);
+                sum[0] += h0 + h1;
+                sum[1] += m0 + m1;
+                sum[2] += l0 + l1;
+            }
+            if (live) {
+                *reinterpret_cast<uint4*>(xs + (size_t)(3 * t) * p.sx + c8 * 16) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                *reinterpret_cast<uint4*>(xs + (size_t)(3 * t + 1) * p.sx + c8 * 16) = make_uint4(mid[0], mid[1], mid[2], mid[3]);
+                *reinterpret_cast<uint4*>(xs + (size_t)(3 * t + 2) * p.sx + c8 * 16) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+            }
+        }
+        // 4 consecutive threads hold one 32-element block (groups is a multiple of 4)
+#pragma unroll
+        for (int s = 0; s < 3; s++) {
+            sum[s] += __shfl_xor_sync(0xFFFFFFFFu, sum[s], 1);
+            sum[s] += __shfl_xor_sync(0xFFFFFFFFu, sum[s], 2);
+        }
+        if (live && (threadIdx.x & 3) == 0) {
+            if (one_col) {
+                cinit[c8 >> 2] = beta * sum[0];
+                continue;
+            }
+            float* blk = cinit + (size_t)(c8 >> 2) * 16;  // [q][4]
+            const int parts = p.x_f32 ? 3 : 1;
+            for (int s = 0; s < parts; s++) {
+                const int col = p.x_f32 ? 3 * t + s : t;
+                const float v = beta * sum[s];
+                blk[(col >> 1) * 4 + (col & 1)] = v;
+                blk[(col >> 1) * 4 + (col & 1) + 2] = v;
+            }
+        }
+    }
+}
+
+}  // namespace wf

@@ -73,10 +73,11 @@ class Communicator:
 
 class ProjectionStack:
     def __init__(self, context: CudaContext, spec: StackSpec, tokens: int = 1, comm: Optional[Communicator] = None,
-                 layers: Optional[int] = None):
+                 layers: Optional[int] = None, rank: int = 0, world: int = 1):
         self.ctx, self.spec, self.m, self.comm = context, spec, tokens, comm
-        self.rank = comm.rank if comm else 0
-        self.world = comm.world if comm else 1
+        self.rank = comm.rank if comm else rank
+        self.world = comm.world if comm else world
+        self.mode = "graph"  # "graph": one kernel (+ NCCL all-gather) per projection; "program": one persistent kernel
         self.layers = layers if layers is not None else spec.layers
         self.weights: List[List[QuantizedWeight]] = []
         self.blocks = {}
@@ -123,6 +124,68 @@ class ProjectionStack:
                                                   self.m, self.y_dev[name], stream)
                     ctx._ck("wf_qlinear_allgather", rc)
 
+    # ---- the step as one persistent kernel ("program")
+    OP_NEW_X, OP_DEPENDS = 1, 2
+
+    def op_flags(self) -> List[int]:
+        """Dependencies of a decoder layer: Wq/Wk/Wv read one input, Wo reads attention's output,
+        Wgate/Wup read one input, Wdown reads the MLP product; each new input depends on what came
+        before, so it needs every CTA (and rank) to have finished the previous projections."""
+        new = self.OP_NEW_X | self.OP_DEPENDS
+        per_layer = {"wq": new, "wo": new, "wgate": new, "wdown": new}
+        return [per_layer.get(name, 0) for _ in range(self.layers) for name, _, _ in self.spec.projections]
+
+    def export_buffers(self) -> dict:
+        """IPC handles of this rank's output buffers and flag array, for the peers."""
+        ctx, lib = self.ctx, self.ctx._lib
+        if not hasattr(self, "flag_dev"):
+            self.flag_dev = ctx.allocate(256)
+            ctx.copy_to_device(self.flag_dev, np.zeros(64, np.uint32))
+        out = {}
+        for name, ptr in list(self.y_dev.items()) + [("__flags__", self.flag_dev)]:
+            h = ctypes.create_string_buffer(64)
+            ctx._ck("wf_ipc_export", lib.wf_ipc_export(ctx.handle, ptr, h))
+            out[name] = h.raw
+        return out
+
+    def build_program(self, peer_handles: Optional[List[dict]] = None) -> None:
+        """peer_handles[r] = export_buffers() of rank r (None for a single rank)."""
+        ctx, lib = self.ctx, self.ctx._lib
+        world, rank = self.world, self.rank
+        y_of = [dict(self.y_dev) for _ in range(world)]
+        flags_of = [0] * world
+        self._imported = []
+        if world > 1:
+            flags_of[rank] = self.flag_dev
+            for r in range(world):
+                if r == rank:
+                    continue
+                for name, raw in peer_handles[r].items():
+                    p = ctypes.c_int64()
+                    ctx._ck("wf_ipc_import", lib.wf_ipc_import(ctx.handle, ctypes.create_string_buffer(raw, 64), ctypes.byref(p)))
+                    self._imported.append(p.value)
+                    if name == "__flags__":
+                        flags_of[r] = p.value
+                    else:
+                        y_of[r][name] = p.value
+        weights, xs, ys = [], [], []
+        for layer in self.weights:
+            for w, (name, rows, k) in zip(layer, self.spec.projections):
+                weights.append(w.handle)
+                xs.append(self.x_dev[k])
+                ys.extend(y_of[r][name] for r in range(world))
+        n = len(weights)
+        arr = lambda v, t: (t * len(v))(*v)
+        prog = ctypes.c_int64()
+        ctx._ck("wf_program_create", lib.wf_program_create(
+            ctx.handle, n, arr(weights, ctypes.c_int64), arr(xs, ctypes.c_int64), arr(ys, ctypes.c_int64),
+            arr(self.op_flags(), ctypes.c_int), self.m, world, rank,
+            arr(flags_of, ctypes.c_int64) if world > 1 else None, ctypes.byref(prog)))
+        self.program = prog.value
+
+    def run_program(self, stream: int = 0) -> None:
+        self.ctx._ck("wf_program_run", self.ctx._lib.wf_program_run(self.ctx.handle, self.program, stream))
+
     def record(self, stream: int = 0) -> None:
         """Issue one step eagerly (allocates whatever the kernels need), then record it."""
         self._issue(stream)
@@ -132,7 +195,10 @@ class ProjectionStack:
         self.graph = self.ctx.graph_end(stream)
 
     def step(self, stream: int = 0) -> None:
-        self.ctx.graph_launch(self.graph, stream)
+        if self.mode == "program":
+            self.run_program(stream)
+        else:
+            self.ctx.graph_launch(self.graph, stream)
 
     def step_host(self, x_host: dict, y_out: np.ndarray, pinned_in: dict, pinned_out: int, stream: int = 0) -> None:
         """One token end to end: activations from pinned host memory, the step, the last
@@ -153,6 +219,9 @@ class ProjectionStack:
         return out
 
     def close(self) -> None:
+        if getattr(self, "program", 0):
+            self.ctx._ck("wf_program_destroy", self.ctx._lib.wf_program_destroy(self.ctx.handle, self.program))
+            self.program = 0
         if self.graph:
             self.ctx.graph_destroy(self.graph)
             self.graph = 0
