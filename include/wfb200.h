@@ -167,21 +167,22 @@ int wf_allgather(int64_t ctx, int64_t comm, int64_t send_dev, int64_t recv_dev, 
  * persistent kernel per GPU, streaming the weights of consecutive ops back to back.
  *   weights[n_ops]           weight handles, all of one quantization type
  *   x_dev[n_ops]             bf16 activations [m, k] each op reads (device pointers)
- *   y_dev[n_ops * world]     for op o and rank r the address, valid on THIS device, of rank r's
- *                            fp32 output buffer [m, n_total] (own buffer at r == rank; peers'
- *                            buffers through wf_ipc_import).  Every rank writes its row shard
- *                            into all of them: the all-gather of CollectiveApi.allGather fused
- *                            into the GEMV epilogue.
+ *   y_dev[n_ops]             this rank's fp32 output buffer [m, n_total] of each op; after the run it
+ *                            holds ALL rows (own shard computed here, the others gathered)
  *   flags[n_ops]             WF_OP_NEW_X: stage x before this op (else it reuses the previous op's);
  *                            WF_OP_DEPENDS: x was produced by earlier ops of the program, so all CTAs
- *                            (and all ranks) synchronise first
- *   peer_flags[world]        world > 1: address on this device of every rank's flag array
- *                            (8 * world bytes, zeroed once), own at [rank]
+ *                            (and all ranks' rows) must be complete first
+ *   landing_dev[n_ops*world] world > 1: for op o and rank r the address, valid on THIS device, of rank
+ *                            r's landing buffer for that op (8 * m * n_total bytes, zeroed once; own at
+ *                            r == rank, peers' through wf_ipc_import).  Ranks store their rows into each
+ *                            other's landing buffers from inside the GEMV epilogue -- the all-gather of
+ *                            CollectiveApi.allGather without a collective call.  A landing buffer may
+ *                            be shared by ops at least two WF_OP_DEPENDS apart.
  * m is 1..8 tokens.  Waits inside the kernel are bounded (WF_ERR_DEVICE_WAIT at the next sync). */
 #define WF_OP_NEW_X 1
 #define WF_OP_DEPENDS 2
 int wf_program_create(int64_t ctx, int n_ops, const int64_t* weights, const int64_t* x_dev, const int64_t* y_dev,
-                      const int* flags, int64_t m, int world, int rank, const int64_t* peer_flags, int64_t* program);
+                      const int* flags, int64_t m, int world, int rank, const int64_t* landing_dev, int64_t* program);
 int wf_program_run(int64_t ctx, int64_t program, int64_t stream);
 int wf_program_destroy(int64_t ctx, int64_t program);
 /* With wf_set_salt(ctx, 2) before wf_program_create: [sm_count][64] globaltimer stamps of the first ops

@@ -7,10 +7,12 @@
 // GEMV kernels.
 //
 // Projections that read an earlier projection's output are separated by a grid barrier
-// (arrive counter + release word in global memory, bounded spins).  With row-sharded tensor
-// parallelism every rank writes its rows of y straight into all ranks' y buffers (peer
-// stores over NVLink) and the grid barrier is extended by one flag exchange between the
-// ranks' first CTAs -- the all-gather is fused into the GEMV epilogue; no collective is
+// (an arrival counter in global memory, bounded spins).  With row-sharded tensor parallelism
+// the all-gather is fused into the GEMV epilogue: every rank stores its rows of y into the
+// other ranks' landing buffers over NVLink as 8-byte {value, tag} words -- one store carries
+// the data and the proof that it arrived, so no fence and no flag round trip is needed --
+// and before the barrier each rank's CTAs poll their slice of the landing buffer until the
+// tag of the current barrier shows, copying the values into the plain y.  No collective is
 // launched.  (No multicast loads and no waits between separately launched kernels on one
 // GPU are involved: each rank runs exactly one kernel on its own GPU.)
 //
@@ -31,7 +33,9 @@ constexpr int OP_DEPENDS = 2;  // the activations were produced by earlier ops: 
 struct ProgOp {
     const uint8_t* tiles;
     const void* x;
-    float* y[PROG_MAX_WORLD];  // this op's output buffer on every rank (own rank included), peer-mapped
+    float* y;                  // this rank's plain fp32 output [m, n_total]
+    uint2* ll[PROG_MAX_WORLD]; // every rank's landing buffer for this op [m, n_total] {value, tag}; own at [rank]
+    int n_total, pad2;
     int64_t ldy, col0;
     int rows, k, kt, rt;
     int chunk_q, chunk_r;
@@ -52,7 +56,6 @@ struct ProgParams {
     uint2* scratch;                   // [2][ctas][128] fix-up slots, alternating by op
     int* status;
     ProgSync* sync;
-    unsigned long long* peer_flags[PROG_MAX_WORLD];  // rank r's flag array [world]; I write slot [my rank] on every peer
     int world, rank;
     int stages, sx, kp_max;
     int n_barriers;
@@ -79,6 +82,16 @@ __device__ __forceinline__ void st_release_sys(unsigned long long* p, unsigned l
 }
 __device__ __forceinline__ void st_release_gpu(unsigned long long* p, unsigned long long v) {
     asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+
+__device__ __forceinline__ void st_slot_sys(uint2* p, uint2 v) {
+    const unsigned long long w = ((unsigned long long)v.y << 32) | v.x;
+    asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
+}
+__device__ __forceinline__ uint2 ld_slot_sys(const uint2* p) {
+    unsigned long long w;
+    asm volatile("ld.relaxed.sys.global.b64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+    return make_uint2((uint32_t)w, (uint32_t)(w >> 32));
 }
 
 template <int XC> struct PSlots { static constexpr int N = (XC == 1) ? 4 : 2, ELEMS = 16 * XC; };
@@ -165,46 +178,51 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_program_kernel(const Pro
     stamp();
     auto consumers_sync = [&]() { asm volatile("bar.sync 1, %0;" ::"n"(GEMV_WARPS * 32) : "memory"); };
 
-    // Grid barrier number `barriers` of this run, extended over the ranks when world > 1.
-    auto grid_barrier = [&]() {
-        consumers_sync();  // every warp of this CTA has written its y values and passed its flushes
-        if (threadIdx.x == 0) {
-            const unsigned long long idx = epoch + (unsigned long long)barriers + 1;  // 1-based barrier number
-            const unsigned long long want = idx * gridDim.x;
-            bool ok = true;
-            int spins = 0;
-            if (P.world == 1) {
-                // one rank: every CTA watches the arrival counter itself (one memory round trip fewer)
-                __threadfence();
-                atomicAdd(&P.sync->arrive, 1ULL);
-                while (ld_relaxed_gpu(&P.sync->arrive) < want && ++spins < PROG_BARRIER_SPINS) {
+    // Landing: wait for the other ranks' rows of ops [first, last) and copy them into y.
+    // The CTAs split the elements; each element is polled until it carries this barrier's tag.
+    int land_from = 0;
+    auto land = [&](int first, int last, unsigned int tag) {
+        if (P.world == 1) return;
+        for (int o2 = first; o2 < last; o2++) {
+            const ProgOp& op2 = P.ops[o2];
+            const int total = P.m * op2.n_total;
+            const uint2* mine = op2.ll[P.rank];
+            for (int e = bx * (GEMV_WARPS * 32) + threadIdx.x; e < total; e += gridDim.x * (GEMV_WARPS * 32)) {
+                const int col = e % op2.n_total;
+                if (col >= (int)op2.col0 && col < (int)op2.col0 + op2.rows) continue;  // my own rows are already in y
+                uint2 v;
+                int spins = 0;
+                do {
+                    v = ld_slot_sys(mine + e);
+                    if (v.y == tag) break;
+                    __nanosleep(20);
+                } while (++spins < GEMV_FIXUP_SPINS);
+                if (v.y != tag) {
+                    atomicOr(P.status, STATUS_PEER_WAIT_TIMEOUT);
+                    break;
                 }
-                ok = spins < PROG_BARRIER_SPINS;
-                __threadfence();
-            } else {
-                __threadfence_system();
-                atomicAdd(&P.sync->arrive, 1ULL);
-                if (bx == 0) {
-                    while (ld_relaxed_gpu(&P.sync->arrive) < want && ++spins < PROG_BARRIER_SPINS) {
-                    }
-                    ok = spins < PROG_BARRIER_SPINS;
-                    __threadfence_system();
-                    for (int r = 0; r < P.world; r++) st_release_sys(P.peer_flags[r] + P.rank, idx);
-                    for (int r = 0; r < P.world && ok; r++) {
-                        spins = 0;
-                        while (ld_acquire_sys(P.peer_flags[P.rank] + r) < idx && ++spins < PROG_BARRIER_SPINS) {
-                        }
-                        ok = spins < PROG_BARRIER_SPINS;
-                    }
-                    st_release_gpu(&P.sync->release, idx);  // released even after a timeout: nobody spins on
-                } else {
-                    while (ld_relaxed_gpu(&P.sync->release) < idx && ++spins < PROG_BARRIER_SPINS) {
-                    }
-                    ok = spins < PROG_BARRIER_SPINS;
-                    __threadfence_system();
-                }
+                op2.y[e] = __uint_as_float(v.x);
             }
-            if (!ok) atomicOr(P.status, STATUS_PEER_WAIT_TIMEOUT);
+        }
+    };
+
+    // Grid barrier number `barriers` of this run; with several ranks the landing comes first, so
+    // that after the barrier every rank's y holds all rows.
+    auto grid_barrier = [&](int o_now) {
+        consumers_sync();  // every warp of this CTA has written its y values and passed its flushes
+        const unsigned long long idx = epoch + (unsigned long long)barriers + 1;  // 1-based barrier number
+        land(land_from, o_now, (unsigned int)idx);
+        land_from = o_now;
+        if (P.world > 1) consumers_sync();
+        if (threadIdx.x == 0) {
+            const unsigned long long want = idx * gridDim.x;
+            int spins = 0;
+            __threadfence();
+            atomicAdd(&P.sync->arrive, 1ULL);
+            while (ld_relaxed_gpu(&P.sync->arrive) < want && ++spins < PROG_BARRIER_SPINS) {
+            }
+            if (spins >= PROG_BARRIER_SPINS) atomicOr(P.status, STATUS_PEER_WAIT_TIMEOUT);
+            __threadfence();
         }
         barriers++;
         consumers_sync();
@@ -220,7 +238,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_program_kernel(const Pro
 
         stamp();  // op start (4 stamps per op: start, after barrier, after staging, after compute)
         if (flags & OP_NEW_X) {
-            if (flags & OP_DEPENDS) grid_barrier();
+            if (flags & OP_DEPENDS) grid_barrier(o);
             else consumers_sync();  // the staged activations are about to be replaced
             stamp();
             GemvParams sp{};
@@ -357,7 +375,10 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_program_kernel(const Pro
                             const int i = lane + 32 * u, col = i >> 4, n = rt * 16 + (i & 15);
                             if (i < ELEMS && col < P.m && n < op.rows) {
                                 const int64_t off = (int64_t)col * op.ldy + op.col0 + n;
-                                for (int r = 0; r < P.world; r++) op.y[r][off] = v[u];
+                                op.y[off] = v[u];
+                                const uint2 word = make_uint2(__float_as_uint(v[u]), (unsigned int)(epoch + (unsigned long long)barriers + 1));
+                                for (int r = 0; r < P.world; r++)
+                                    if (r != P.rank) st_slot_sys(op.ll[r] + off, word);
                             }
                         }
                     }
@@ -396,6 +417,10 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_program_kernel(const Pro
         *abort_flag = 1;
     }
 
+    // ---- the rows of the last ops land before the kernel ends (tag of the barrier that never comes)
+    consumers_sync();
+    if (!failed) land(land_from, P.n_ops, (unsigned int)(epoch + (unsigned long long)barriers + 1));
+
     // ---- leave: the last CTA out advances the epoch for the next run
     consumers_sync();
     if (threadIdx.x == 0) {
@@ -404,9 +429,9 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_program_kernel(const Pro
         if (d == gridDim.x - 1) {
             P.sync->done_ctas = 0;
             // CTAs that skipped barriers after a failure would leave `arrive` short: resynchronise it
-            P.sync->arrive = (epoch + (unsigned long long)P.n_barriers) * gridDim.x;
+            P.sync->arrive = (epoch + (unsigned long long)P.n_barriers + 1) * gridDim.x;
             __threadfence();
-            st_release_gpu(&P.sync->epoch, epoch + (unsigned long long)P.n_barriers);
+            st_release_gpu(&P.sync->epoch, epoch + (unsigned long long)P.n_barriers + 1);  // +1: the final landing's tag
         }
     }
 }
@@ -457,7 +482,7 @@ using namespace wf;
 extern "C" {
 
 int wf_program_create(int64_t ctx, int n_ops, const int64_t* weights, const int64_t* x_dev, const int64_t* y_dev, const int* flags,
-                      int64_t m, int world, int rank, const int64_t* peer_flags, int64_t* program) {
+                      int64_t m, int world, int rank, const int64_t* landing_dev, int64_t* program) {
     Context* c = get_context(ctx);
     if (!c) return WF_ERR_INVALID_HANDLE;
     ScopedLock lk(c);
@@ -466,7 +491,7 @@ int wf_program_create(int64_t ctx, int n_ops, const int64_t* weights, const int6
     *program = 0;
     if (m < 1 || m > 8) return set_error(c, WF_ERR_SHAPE, "a program takes 1..8 bf16 tokens, got %lld", (long long)m);
     if (world < 1 || world > PROG_MAX_WORLD || rank < 0 || rank >= world) return set_error(c, WF_ERR_SHARD, "rank %d outside world %d (max %d)", rank, world, PROG_MAX_WORLD);
-    if (world > 1 && !peer_flags) return set_error(c, WF_ERR_INVALID_ARGUMENT, "peer flag arrays are required for world > 1");
+    if (world > 1 && !landing_dev) return set_error(c, WF_ERR_INVALID_ARGUMENT, "landing buffers are required for world > 1");
     WF_CUDA(c, cudaSetDevice(c->device));
 
     std::vector<ProgOp> ops((size_t)n_ops);
@@ -484,10 +509,13 @@ int wf_program_create(int64_t ctx, int n_ops, const int64_t* weights, const int6
         ProgOp& op = ops[o];
         op.tiles = w->d_tiles;
         op.x = reinterpret_cast<const void*>(x_dev[o]);
+        op.y = reinterpret_cast<float*>(y_dev[o]);
+        if (!op.y) return set_error(c, WF_ERR_INVALID_ARGUMENT, "op %d: null output pointer", o);
         for (int r = 0; r < world; r++) {
-            op.y[r] = reinterpret_cast<float*>(y_dev[(size_t)o * world + r]);
-            if (!op.y[r]) return set_error(c, WF_ERR_INVALID_ARGUMENT, "op %d: null output pointer for rank %d", o, r);
+            op.ll[r] = world > 1 ? reinterpret_cast<uint2*>(landing_dev[(size_t)o * world + r]) : nullptr;
+            if (world > 1 && !op.ll[r]) return set_error(c, WF_ERR_INVALID_ARGUMENT, "op %d: null landing buffer for rank %d", o, r);
         }
+        op.n_total = (int)w->total_rows;
         if (!op.x) return set_error(c, WF_ERR_INVALID_ARGUMENT, "op %d: null activation pointer", o);
         op.ldy = w->total_rows;
         op.col0 = w->row0;
@@ -542,7 +570,6 @@ int wf_program_create(int64_t ctx, int n_ops, const int64_t* weights, const int6
     P.scratch = pr->d_scratch;
     P.status = c->d_status;
     P.sync = pr->d_sync;
-    for (int r = 0; r < world; r++) P.peer_flags[r] = world > 1 ? reinterpret_cast<unsigned long long*>(peer_flags[r]) : nullptr;
     P.world = world;
     P.rank = rank;
     P.stages = stages;

@@ -136,13 +136,16 @@ class ProjectionStack:
         return [per_layer.get(name, 0) for _ in range(self.layers) for name, _, _ in self.spec.projections]
 
     def export_buffers(self) -> dict:
-        """IPC handles of this rank's output buffers and flag array, for the peers."""
+        """IPC handles of this rank's landing buffers (one per output buffer), for the peers."""
         ctx, lib = self.ctx, self.ctx._lib
-        if not hasattr(self, "flag_dev"):
-            self.flag_dev = ctx.allocate(256)
-            ctx.copy_to_device(self.flag_dev, np.zeros(64, np.uint32))
+        if not hasattr(self, "landing_dev"):
+            self.landing_dev = {}
+            for name, rows, _ in self.spec.projections:
+                nbytes = self.m * rows * 8
+                self.landing_dev[name] = ctx.allocate(nbytes)
+                ctx.copy_to_device(self.landing_dev[name], np.zeros(nbytes, np.uint8))
         out = {}
-        for name, ptr in list(self.y_dev.items()) + [("__flags__", self.flag_dev)]:
+        for name, ptr in self.landing_dev.items():
             h = ctypes.create_string_buffer(64)
             ctx._ck("wf_ipc_export", lib.wf_ipc_export(ctx.handle, ptr, h))
             out[name] = h.raw
@@ -152,11 +155,10 @@ class ProjectionStack:
         """peer_handles[r] = export_buffers() of rank r (None for a single rank)."""
         ctx, lib = self.ctx, self.ctx._lib
         world, rank = self.world, self.rank
-        y_of = [dict(self.y_dev) for _ in range(world)]
-        flags_of = [0] * world
         self._imported = []
+        landing_of = [dict() for _ in range(world)]
         if world > 1:
-            flags_of[rank] = self.flag_dev
+            landing_of[rank] = dict(self.landing_dev)
             for r in range(world):
                 if r == rank:
                     continue
@@ -164,23 +166,22 @@ class ProjectionStack:
                     p = ctypes.c_int64()
                     ctx._ck("wf_ipc_import", lib.wf_ipc_import(ctx.handle, ctypes.create_string_buffer(raw, 64), ctypes.byref(p)))
                     self._imported.append(p.value)
-                    if name == "__flags__":
-                        flags_of[r] = p.value
-                    else:
-                        y_of[r][name] = p.value
-        weights, xs, ys = [], [], []
+                    landing_of[r][name] = p.value
+        weights, xs, ys, lls = [], [], [], []
         for layer in self.weights:
             for w, (name, rows, k) in zip(layer, self.spec.projections):
                 weights.append(w.handle)
                 xs.append(self.x_dev[k])
-                ys.extend(y_of[r][name] for r in range(world))
+                ys.append(self.y_dev[name])
+                if world > 1:
+                    lls.extend(landing_of[r][name] for r in range(world))
         n = len(weights)
         arr = lambda v, t: (t * len(v))(*v)
         prog = ctypes.c_int64()
         ctx._ck("wf_program_create", lib.wf_program_create(
             ctx.handle, n, arr(weights, ctypes.c_int64), arr(xs, ctypes.c_int64), arr(ys, ctypes.c_int64),
             arr(self.op_flags(), ctypes.c_int), self.m, world, rank,
-            arr(flags_of, ctypes.c_int64) if world > 1 else None, ctypes.byref(prog)))
+            arr(lls, ctypes.c_int64) if world > 1 else None, ctypes.byref(prog)))
         self.program = prog.value
 
     def run_program(self, stream: int = 0) -> None:
