@@ -63,9 +63,10 @@ __device__ __forceinline__ void fetch_block(uint32_t xaddr, uint32_t caddr, uint
             "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %5, 0;\n\t@p ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n\t}"
             : "+r"(xb.x), "+r"(xb.y), "+r"(xb.z), "+r"(xb.w)
             : "r"(xaddr), "r"(live));
+        // the start value is added after the MMA (the MMA's C operand would need it in four registers)
         float c;
         asm volatile("ld.shared.f32 %0, [%1];" : "=f"(c) : "r"(caddr));
-        ci = make_float4(c, c, c, c);
+        ci = make_float4(c, 0.f, c, 0.f);
     } else {
         xb = lds128(xaddr);
         const uint4 t = lds128(caddr);
@@ -207,7 +208,13 @@ template <> struct TileRegs<WF_QTYPE_Q4_0> {
         for (int j = 0; j < 4; j++) {
             fetch_block<XC>(xaddr + j * 64, caddr + j * cinit_block_bytes<XC>(), live, xb, ci);
             float d[4];
-            block_mma(d, word_of(c[0], j), word_of(c[1], j), xb, MAGIC_16, ci.x, ci.y, ci.z, ci.w);
+            if (XC == 1) {
+                block_mma(d, word_of(c[0], j), word_of(c[1], j), xb, MAGIC_16, 0.f, 0.f, 0.f, 0.f);
+                d[0] += ci.x;
+                d[2] += ci.z;
+            } else {
+                block_mma(d, word_of(c[0], j), word_of(c[1], j), xb, MAGIC_16, ci.x, ci.y, ci.z, ci.w);
+            }
             const float2 dg = half2_bits_to_float2(j < 2 ? s.x : s.y), dh = half2_bits_to_float2(j < 2 ? s.z : s.w);
             const float sg = (j & 1) ? dg.y : dg.x, sh = (j & 1) ? dh.y : dh.x;
             acc[0] = fmaf(sg, d[0], acc[0]);
@@ -238,8 +245,15 @@ template <> struct TileRegs<WF_QTYPE_Q8_0> {
         for (int j = 0; j < 4; j++) {
             fetch_block<XC>(xaddr + j * 64, caddr + j * cinit_block_bytes<XC>(), live, xb, ci);
             float d[4];
-            block_mma(d, word_of(c[0], j), word_of(c[1], j), xb, MAGIC_256, ci.x, ci.y, ci.z, ci.w);
+            if (XC == 1)
+                block_mma(d, word_of(c[0], j), word_of(c[1], j), xb, MAGIC_256, 0.f, 0.f, 0.f, 0.f);
+            else
+                block_mma(d, word_of(c[0], j), word_of(c[1], j), xb, MAGIC_256, ci.x, ci.y, ci.z, ci.w);
             block_mma(d, word_of(c[2], j), word_of(c[3], j), xb, MAGIC_16, d[0], d[1], d[2], d[3]);
+            if (XC == 1) {
+                d[0] += ci.x;
+                d[2] += ci.z;
+            }
             const float2 dg = half2_bits_to_float2(j < 2 ? s.x : s.y), dh = half2_bits_to_float2(j < 2 ? s.z : s.w);
             const float sg = (j & 1) ? dg.y : dg.x, sh = (j & 1) ? dh.y : dh.x;
             acc[0] = fmaf(sg, d[0], acc[0]);
@@ -286,8 +300,15 @@ template <> struct TileRegs<WF_QTYPE_Q4_K> {
         for (int jj = 0; jj < 8; jj++) {
             fetch_block<XC>(xaddr + jj * 64, caddr + jj * cinit_block_bytes<XC>(), live, xb, ci);
             float d[4];
-            block_mma(d, word_of(c[(jj >> 2) * 2], jj & 3), word_of(c[(jj >> 2) * 2 + 1], jj & 3), xb, MAGIC_16, ci.x,
-                      ci.y, ci.z, ci.w);
+            if (XC == 1) {
+                block_mma(d, word_of(c[(jj >> 2) * 2], jj & 3), word_of(c[(jj >> 2) * 2 + 1], jj & 3), xb, MAGIC_16, 0.f, 0.f,
+                          0.f, 0.f);
+                d[0] += ci.x;
+                d[2] += ci.z;
+            } else {
+                block_mma(d, word_of(c[(jj >> 2) * 2], jj & 3), word_of(c[(jj >> 2) * 2 + 1], jj & 3), xb, MAGIC_16, ci.x,
+                          ci.y, ci.z, ci.w);
+            }
             const float ag = byte_times(jj < 4 ? sc.x : sc.y, jj & 3, g.x, ngd);  // d * sc, exact
             const float ah = byte_times(jj < 4 ? sc.z : sc.w, jj & 3, h.x, nhd);
             const float cg = byte_times(jj < 4 ? mn.x : mn.y, jj & 3, gm, ngm);  // dmin * m / 16, exact
