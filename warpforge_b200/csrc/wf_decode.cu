@@ -94,21 +94,15 @@ __device__ __forceinline__ uint2 ld_slot_sys(const uint2* p) {
     return make_uint2((uint32_t)w, (uint32_t)(w >> 32));
 }
 
-template <int XC> struct PSlots { static constexpr int N = (XC == 1) ? 4 : 2, ELEMS = 16 * XC; };
-
 // Shared memory: ctrl | partial sums | cinit (kp_max) | staged x | ring.
 template <int QT, int XC>
 __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_program_kernel(const ProgParams P) {
     using T = Tile<QT>;
     using R = TileRegs<QT>;
-    constexpr int NSLOT = PSlots<XC>::N, ELEMS = PSlots<XC>::ELEMS;
-    constexpr uint32_t STAGE_BYTES = GEMV_WARPS * T::BYTES;
+    constexpr int NSLOT = Slots<XC>::N, ELEMS = Slots<XC>::ELEMS;
     extern __shared__ __align__(128) uint8_t smem[];
-    int* arrive = reinterpret_cast<int*>(smem);                              // [NSLOT]
-    volatile int* released = reinterpret_cast<volatile int*>(smem) + 8;      // [NSLOT]
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem) + 16;
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem + 128);
-    uint64_t* empty = full + GEMV_MAX_STAGES;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem);
+    const BarrierSet bar = barrier_set(smem);
     float* partial = reinterpret_cast<float*>(smem + GEMV_CTRL_BYTES);       // [NSLOT][GEMV_WARPS][ELEMS]
     float4* cinit = reinterpret_cast<float4*>(partial + NSLOT * GEMV_WARPS * ELEMS);  // [kp_max/32][4]
     uint8_t* xs = reinterpret_cast<uint8_t*>(cinit + (P.kp_max >> 5) * 4);   // [m][sx]
@@ -119,34 +113,20 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_program_kernel(const Pro
     const int bx = blockIdx.x, stages = P.stages;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < 32; i++) reinterpret_cast<int*>(smem)[i] = 0;
-        for (int s = 0; s < stages; s++) {
-            mbar_init(&full[s], 1);
-            mbar_init(&empty[s], GEMV_WARPS);
-        }
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        *abort_flag = 0;
+        barrier_set_init<XC>(bar, stages);
     }
     __syncthreads();
 
     if (warp == GEMV_WARPS) {
         // ------------------------------------------------ producer: the whole program, as far ahead as the ring allows
         if (lane == 0) {
-            int R_ = 0;  // global round counter
+            WalkState pos;
             for (int o = 0; o < P.n_ops && !*abort_flag; o++) {
                 const ProgOp& op = P.ops[o];
                 const int t0 = bx * op.chunk_q + min(bx, op.chunk_r);
                 const int t1 = t0 + op.chunk_q + (bx < op.chunk_r ? 1 : 0);
-                for (int first = t0; first < t1; first += GEMV_WARPS, R_++) {
-                    const int s = R_ % stages;
-                    if (R_ >= stages && !mbar_wait(&empty[s], ((R_ / stages) - 1) & 1)) {
-                        atomicOr(P.status, STATUS_GEMV_FIXUP_TIMEOUT);
-                        *abort_flag = 1;
-                        break;
-                    }
-                    const uint32_t bytes = (uint32_t)min(GEMV_WARPS, t1 - first) * T::BYTES;
-                    mbar_expect_tx(&full[s], bytes);
-                    bulk_load(ring + (size_t)s * STAGE_BYTES, op.tiles + (size_t)first * T::BYTES, bytes, &full[s]);
-                }
+                produce_share<QT>(op.tiles, t0, t1, ring, bar, stages, pos, abort_flag);
             }
         }
         return;
@@ -156,13 +136,9 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_program_kernel(const Pro
     const unsigned long long epoch = ld_acquire_gpu(&P.sync->epoch);
     const uint8_t* xrow = xs + (size_t)(g < P.m ? g : P.m - 1) * P.sx;
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    int seg = 0;            // segments flushed so far (all warps flush every segment, so this agrees CTA-wide)
-    int s = 0;
-    uint32_t phase = 0;
+    WalkState st;
     int barriers = 0;
     bool failed = false;
-    const uint32_t lane_is_0 = lane == 0;
-    const uint32_t my_tile = smem_u32(ring) + warp * T::BYTES + lane * 16;
     const uint32_t x32 = smem_u32(xrow) + q * 16, c32 = smem_u32(cinit) + (XC == 1 ? 0 : q * 16);
     const uint32_t live = (XC == 1) ? (uint32_t)(g == 0) : 1u;
 
@@ -176,7 +152,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_program_kernel(const Pro
         stamp_i++;
     };
     stamp();
-    auto consumers_sync = [&]() { asm volatile("bar.sync 1, %0;" ::"n"(GEMV_WARPS * 32) : "memory"); };
+    auto consumers_sync = [&]() { asm volatile("bar.sync 1, %0;" ::"n"(GEMV_CONSUMERS) : "memory"); };
 
     // Landing: wait for the other ranks' rows of ops [first, last) and copy them into y.
     // The CTAs split the elements; each element is polled until it carries this barrier's tag.
@@ -187,7 +163,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_program_kernel(const Pro
             const ProgOp& op2 = P.ops[o2];
             const int total = P.m * op2.n_total;
             const uint2* mine = op2.ll[P.rank];
-            for (int e = bx * (GEMV_WARPS * 32) + threadIdx.x; e < total; e += gridDim.x * (GEMV_WARPS * 32)) {
+            for (int e = bx * GEMV_CONSUMERS + threadIdx.x; e < total; e += gridDim.x * GEMV_CONSUMERS) {
                 const int col = e % op2.n_total;
                 if (col >= (int)op2.col0 && col < (int)op2.col0 + op2.rows) continue;  // my own rows are already in y
                 uint2 v;
@@ -209,7 +185,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_program_kernel(const Pro
     // Grid barrier number `barriers` of this run; with several ranks the landing comes first, so
     // that after the barrier every rank's y holds all rows.
     auto grid_barrier = [&](int o_now) {
-        consumers_sync();  // every warp of this CTA has written its y values and passed its flushes
+        consumers_sync();  // every warp of this CTA has written its y values and passed its reductions
         const unsigned long long idx = epoch + (unsigned long long)barriers + 1;  // 1-based barrier number
         land(land_from, o_now, (unsigned int)idx);
         land_from = o_now;
@@ -228,7 +204,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_program_kernel(const Pro
         consumers_sync();
     };
 
-    for (int o = 0; o < P.n_ops; o++) {
+    for (int o = 0; o < P.n_ops && !failed; o++) {
         const ProgOp& op = P.ops[o];
         const int flags = op.flags;
         const int kt = op.kt;
@@ -248,7 +224,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_program_kernel(const Pro
             sp.ldx = op.k;
             sp.x_f32 = 0;
             sp.sx = P.sx;
-            stage_x(sp, xs, reinterpret_cast<float*>(cinit), kt * T::K, R::BETA, GEMV_WARPS * 32, XC == 1);
+            stage_x(sp, xs, reinterpret_cast<float*>(cinit), kt * T::K, R::BETA, GEMV_CONSUMERS, XC == 1);
             consumers_sync();
             stamp();
         } else {
@@ -256,165 +232,28 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_program_kernel(const Pro
             stamp();
         }
 
-        int seg_begin = t0;
-        int rt = (t0 < t1) ? t0 / kt : 0;
-        int seg_end = min((rt + 1) * kt, t1);
-        int t = t0 + warp;
-        int done_op = 0;  // tiles (= ring rounds) this warp has consumed in this op
-
-        while (seg_begin < t1) {
-            const int n_seg = (t < seg_end) ? (seg_end - t + GEMV_WARPS - 1) / GEMV_WARPS : 0;
-            int kbase = (t - rt * kt) * T::K;
-            for (int i = 0; i < n_seg && !failed; i++) {
-                if (!mbar_wait(&full[s], phase)) {
-                    failed = true;
-                    break;
-                }
-                R regs;
-                regs.load(my_tile + s * STAGE_BYTES, lane);
-                __syncwarp();
-                mbar_arrive_if(&empty[s], lane_is_0);
-                regs.template compute<XC>(acc, x32 + kbase * 2, c32 + (kbase >> 5) * cinit_block_bytes<XC>(), live);
-                kbase += GEMV_WARPS * T::K;
-                t += GEMV_WARPS;
-                done_op++;
-                if (++s == stages) {
-                    s = 0;
-                    phase ^= 1u;
+        // y goes to every rank's buffer: the row-shard gather happens here
+        auto emit = [&](int rt, const float* buf) {
+            for (int i = lane; i < ELEMS; i += 32) {
+                const int col = i >> 4, n = rt * 16 + (i & 15);
+                if (col < P.m && n < op.rows) {
+                    const int64_t off = (int64_t)col * op.ldy + op.col0 + n;
+                    const float v = buf[i];
+                    op.y[off] = v;
+                    const uint2 word = make_uint2(__float_as_uint(v), (unsigned int)(epoch + (unsigned long long)barriers + 1));
+                    for (int r = 0; r < P.world; r++)
+                        if (r != P.rank) st_slot_sys(op.ll[r] + off, word);
                 }
             }
-            // ---- flush this segment
-            {
-                const int slot = seg % NSLOT, gen = seg / NSLOT;
-                if (gen > 0) {
-                    int spins = 0;
-                    while (released[slot] < gen && ++spins < GEMV_SLOT_SPINS) {
-                    }
-                    if (released[slot] < gen && lane == 0) atomicOr(P.status, STATUS_GEMV_FIXUP_TIMEOUT);
-                }
-                float* mine = partial + ((size_t)slot * GEMV_WARPS + warp) * ELEMS;
-                if (XC == 1) {
-                    if (q == 0) {
-                        mine[g] = acc[0];
-                        mine[g + 8] = acc[2];
-                    }
-                } else {
-                    mine[(2 * q) * 16 + g] = acc[0];
-                    mine[(2 * q + 1) * 16 + g] = acc[1];
-                    mine[(2 * q) * 16 + g + 8] = acc[2];
-                    mine[(2 * q + 1) * 16 + g + 8] = acc[3];
-                }
-                acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
-                __syncwarp();
-                int old = 0;
-                if (lane == 0) {
-                    __threadfence_block();
-                    old = atomicAdd(&arrive[slot], 1);
-                }
-                old = __shfl_sync(0xFFFFFFFFu, old, 0);
-                if (old == GEMV_WARPS * (gen + 1) - 1) {  // last warp to leave the segment finishes it
-                    __threadfence_block();
-                    constexpr int PER_LANE = (ELEMS + 31) / 32;
-                    float v[PER_LANE];
-#pragma unroll
-                    for (int u = 0; u < PER_LANE; u++) {
-                        const int i = lane + 32 * u;
-                        v[u] = 0.f;
-                        if (i < ELEMS) {
-                            const float* src = partial + (size_t)slot * GEMV_WARPS * ELEMS + i;
-#pragma unroll
-                            for (int w = 0; w < GEMV_WARPS; w++) v[u] += src[w * ELEMS];
-                        }
-                    }
-                    const bool starts = seg_begin == rt * kt, ends = seg_end == (rt + 1) * kt;
-                    if (!starts) {  // publish my piece; the slot's previous value (two ops ago) must have been taken
-#pragma unroll
-                        for (int u = 0; u < PER_LANE; u++) {
-                            const int i = lane + 32 * u;
-                            if (i >= ELEMS) continue;
-                            uint2* sp = slots + (size_t)bx * 128 + i;
-                            int spins = 0;
-                            while (ld_slot(sp).y != 0u && ++spins < GEMV_FIXUP_SPINS) __nanosleep(32);
-                            if (spins >= GEMV_FIXUP_SPINS) atomicOr(P.status, STATUS_GEMV_FIXUP_TIMEOUT);
-                            st_slot(sp, make_uint2(__float_as_uint(v[u]), 1u));
-                        }
-                    } else {
-                        if (!ends) {  // owner: add the following CTAs' pieces in CTA order
-                            const int te = (rt + 1) * kt;
-                            bool gave_up = false;
-                            for (int c = bx + 1; c < (int)gridDim.x && !gave_up; c++) {
-                                const int c0 = c * op.chunk_q + min(c, op.chunk_r), c1 = c0 + op.chunk_q + (c < op.chunk_r ? 1 : 0);
-                                if (c0 >= te) break;
-                                if (c0 == c1) continue;
-#pragma unroll
-                                for (int u = 0; u < PER_LANE; u++) {
-                                    const int i = lane + 32 * u;
-                                    if (i >= ELEMS) continue;
-                                    uint2* sp = slots + (size_t)c * 128 + i;
-                                    uint2 e;
-                                    int spins = 0;
-                                    do {
-                                        e = ld_slot(sp);
-                                        if (e.y != 0u) break;
-                                        __nanosleep(32);
-                                    } while (++spins < GEMV_FIXUP_SPINS);
-                                    if (e.y == 0u) {
-                                        atomicOr(P.status, STATUS_GEMV_FIXUP_TIMEOUT);
-                                        gave_up = true;
-                                    } else {
-                                        v[u] += __uint_as_float(e.x);
-                                        st_slot(sp, make_uint2(0u, 0u));
-                                    }
-                                }
-                                gave_up = __any_sync(0xFFFFFFFFu, gave_up);
-                            }
-                        }
-                        // y goes to every rank's buffer: the row-shard gather happens here
-#pragma unroll
-                        for (int u = 0; u < PER_LANE; u++) {
-                            const int i = lane + 32 * u, col = i >> 4, n = rt * 16 + (i & 15);
-                            if (i < ELEMS && col < P.m && n < op.rows) {
-                                const int64_t off = (int64_t)col * op.ldy + op.col0 + n;
-                                op.y[off] = v[u];
-                                const uint2 word = make_uint2(__float_as_uint(v[u]), (unsigned int)(epoch + (unsigned long long)barriers + 1));
-                                for (int r = 0; r < P.world; r++)
-                                    if (r != P.rank) st_slot_sys(op.ll[r] + off, word);
-                            }
-                        }
-                    }
-                    __syncwarp();
-                    if (lane == 0) {
-                        __threadfence_block();
-                        released[slot] = gen + 1;
-                    }
-                }
-                seg++;
-                seg_begin = seg_end;
-                rt++;
-                seg_end = min((rt + 1) * kt, t1);
-            }
-            if (failed) break;
-        }
+        };
+        consume_share<QT, XC>(t0, t1, kt, op.chunk_q, op.chunk_r, warp, lane, smem_u32(ring), bar, partial, stages, st, x32, c32,
+                              live, slots, P.status, smem_u32(const_cast<int*>(abort_flag)), acc, emit);
+        if (*abort_flag) failed = true;
         stamp();
-        if (failed) break;
-        // Only the op's last round can lack a tile for some warps.  Its stage is refilled for the next
-        // op, so those warps still wait for the round's data (keeping their release in order) and
-        // release the stage.
-        if (done_op < (t1 - t0 + GEMV_WARPS - 1) / GEMV_WARPS) {
-            if (!mbar_wait(&full[s], phase)) {
-                failed = true;
-                break;
-            }
-            mbar_arrive_if(&empty[s], lane_is_0);
-            if (++s == stages) {
-                s = 0;
-                phase ^= 1u;
-            }
-        }
     }
     if (failed) {
         if (lane == 0) atomicOr(P.status, STATUS_GEMV_FIXUP_TIMEOUT);
-        *abort_flag = 1;
+        drain_after_abort();
     }
 
     // ---- the rows of the last ops land before the kernel ends (tag of the barrier that never comes)
@@ -533,7 +372,7 @@ int wf_program_create(int64_t ctx, int n_ops, const int64_t* weights, const int6
     }
     // shared memory: ctrl + partial + cinit + x + ring
     const int xc = (m == 1) ? 1 : 8;
-    const int nslot = xc == 1 ? 4 : 2, elems = 16 * xc;
+    const int nslot = xc == 1 ? Slots<1>::N : Slots<8>::N, elems = 16 * xc;
     const int sx = kp_max * 2 + 64;
     size_t fixed = GEMV_CTRL_BYTES + (size_t)nslot * GEMV_WARPS * elems * 4 + (size_t)(kp_max / 32) * 64 + (size_t)m * sx;
     fixed = (fixed + 127) & ~(size_t)127;

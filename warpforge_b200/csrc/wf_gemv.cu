@@ -17,13 +17,13 @@
 // every SM reads the same number of bytes whatever the matrix shape.  Inside a CTA the
 // warps take tiles round-robin, so the CTA as a whole reads memory sequentially.  A chunk
 // is a sequence of segments, one per row-tile it touches; when a warp leaves a segment it
-// parks its partial sums in shared memory and bumps an arrival counter, and the last warp
-// to arrive adds the sixteen partials in warp order (deterministic) -- nobody waits at a
-// barrier.  A row-tile cut by a chunk boundary is finished by the CTA that holds its
-// beginning: the following CTAs compute their piece first and publish it to a scratch
-// slot tagged valid; the owner, which reaches that row-tile last, adds the pieces in CTA
-// order, clears the tags and writes y.  The owner's wait is bounded; on expiry it sets a
-// status bit instead of spinning on.
+// parks its partial sums in shared memory and arrives on an mbarrier -- it never waits for
+// the other warps -- and one warp per segment, taken in turn and one segment late, adds the
+// sixteen partials in warp order (deterministic).  A row-tile cut by a chunk boundary is
+// finished by the CTA that holds its beginning: the following CTAs compute their piece
+// first and publish it to a scratch slot tagged valid; the owner, which reaches that
+// row-tile last, adds the pieces in CTA order, clears the tags and writes y.  The owner's
+// wait is bounded; on expiry it sets a status bit instead of spinning on.
 //
 // Replaces the fp32 batch_matmul_f32 launch of
 // warpforge-backend-nvidia/src/main/java/io/surfworks/warpforge/backend/nvidia/ops/DotGeneralKernel.java:263-281
@@ -33,28 +33,19 @@
 namespace wf {
 
 // ---------------------------------------------------------------- the kernel
-// XC = 1: exactly one live column (one bf16 token); XC = 8: up to 8 columns.
-template <int XC> struct Slots { static constexpr int N = (XC == 1) ? 4 : 2, ELEMS = 16 * XC; };
-
-// Shared-memory map (bytes): [0,32) arrive[8] | [32,64) released[8] | [64,68) abort flag |
-// [128, 128+8*MAX_STAGES) full barriers | then empty barriers | partial sums | exchange row |
-// cinit | staged x | ring stages (128-byte aligned).
+// Shared-memory map (bytes): [0,4) abort flag | [128, 128 + GEMV_CTRL_BYTES) barriers |
+// partial sums [N][GEMV_WARPS][ELEMS] | cinit | staged x | ring stages (128-byte aligned).
 template <int QT, int XC>
 __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvParams p) {
     using T = Tile<QT>;
     using R = TileRegs<QT>;
     constexpr int NSLOT = Slots<XC>::N, ELEMS = Slots<XC>::ELEMS;
-    constexpr uint32_t STAGE_BYTES = GEMV_WARPS * T::BYTES;
     extern __shared__ __align__(128) uint8_t smem[];
-    int* arrive = reinterpret_cast<int*>(smem);                              // [NSLOT]
-    volatile int* released = reinterpret_cast<volatile int*>(smem) + 8;      // [NSLOT]
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem) + 16;
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem + 128);                // [stages]
-    uint64_t* empty = full + GEMV_MAX_STAGES;                                // [stages]
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem);
+    const BarrierSet bar = barrier_set(smem);
     float* partial = reinterpret_cast<float*>(smem + GEMV_CTRL_BYTES);       // [NSLOT][GEMV_WARPS][ELEMS]
-    float* exchange = partial + NSLOT * GEMV_WARPS * ELEMS;                  // [128]
     const int kp = p.kt * T::K;
-    float4* cinit = reinterpret_cast<float4*>(exchange + 128);               // [kp/32][4]
+    float4* cinit = reinterpret_cast<float4*>(partial + NSLOT * GEMV_WARPS * ELEMS);  // [kp/32][4]
     uint8_t* xs = reinterpret_cast<uint8_t*>(cinit + (kp >> 5) * 4);         // [xcols][sx]
     const int xcols = p.x_f32 ? 3 * p.m : p.m;
     uint8_t* ring = smem + (((size_t)(xs - smem) + (size_t)xcols * p.sx + 127) & ~(size_t)127);
@@ -65,7 +56,6 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvParams 
     const int bx = blockIdx.x;
     const int t0 = bx * p.chunk_q + min(bx, p.chunk_r);
     const int t1 = t0 + p.chunk_q + (bx < p.chunk_r ? 1 : 0);
-    const int rounds = (t1 - t0 + GEMV_WARPS - 1) / GEMV_WARPS;
     const int stages = p.stages;
 
     // Optional timing stamps, the counterpart of the reference's SALT_TIMING kernels
@@ -77,214 +67,64 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvParams 
             p.timing[(size_t)blockIdx.x * 8 + i] = tm;
         }
     };
-    stamp(0);
+    // Launched with programmatic stream serialization: the next kernel of the stream may take an SM
+    // as soon as this CTA has left it, and streams its weights (which no kernel writes) while
+    // the rest of this grid is still running.  Everything that touches memory a previous
+    // kernel may have written -- activations, y, scratch slots, status -- comes after
+    // griddepcontrol.wait, which returns once the whole previous grid has completed.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (threadIdx.x == 0) {
-        for (int i = 0; i < 32; i++) reinterpret_cast<int*>(smem)[i] = 0;
-        for (int s = 0; s < stages; s++) {
-            mbar_init(&full[s], 1);
-            mbar_init(&empty[s], GEMV_WARPS);
-        }
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        *abort_flag = 0;
+        barrier_set_init<XC>(bar, stages);
     }
     __syncthreads();
 
-    // Producer: fill every stage right away; the weights do not depend on anything.
-    auto issue_round = [&](int r) {
-        const int s = r % stages;
-        const int first = t0 + r * GEMV_WARPS;
-        const uint32_t bytes = (uint32_t)min(GEMV_WARPS, t1 - first) * T::BYTES;
-        mbar_expect_tx(&full[s], bytes);
-        bulk_load(ring + (size_t)s * STAGE_BYTES, p.tiles + (size_t)first * T::BYTES, bytes, &full[s]);
-    };
-    if (warp == GEMV_WARPS && lane == 0)
-        for (int r = 0; r < min(rounds, stages); r++) issue_round(r);
-
-    // cinit entries of dead columns stay uninitialised: they only feed dead columns
-    stage_x(p, xs, reinterpret_cast<float*>(cinit), kp, R::BETA, GEMV_THREADS, XC == 1);
-    __syncthreads();
-    stamp(1);
-
-    if (warp == GEMV_WARPS) {  // producer warp: refill stages as the consumers release them
+    if (warp == GEMV_WARPS) {  // producer warp: the weights do not depend on anything, start at once
         if (lane == 0) {
-            for (int r = stages; r < rounds; r++) {
-                if (!mbar_wait(&empty[r % stages], ((r / stages) - 1) & 1) || *abort_flag) {
-                    atomicOr(p.status, STATUS_GEMV_FIXUP_TIMEOUT);
-                    *abort_flag = 1;
-                    break;
-                }
-                issue_round(r);
-            }
+            WalkState pos;
+            produce_share<QT>(p.tiles, t0, t1, ring, bar, stages, pos, abort_flag);
         }
         return;
     }
+
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    stamp(0);
+    // cinit entries of dead columns stay uninitialised: they only feed dead columns
+    stage_x(p, xs, reinterpret_cast<float*>(cinit), kp, R::BETA, GEMV_CONSUMERS, XC == 1);
+    asm volatile("bar.sync 1, %0;" ::"n"(GEMV_CONSUMERS) : "memory");
+    stamp(1);
 
     // dead columns read the last live row: their results are computed and never stored
     const uint8_t* xrow = xs + (size_t)(g < xcols ? g : xcols - 1) * p.sx;
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
 
-    int seg = 0, seg_begin = t0;
-    int rt = (t0 < t1) ? t0 / p.kt : 0;
-    int seg_end = min((rt + 1) * p.kt, t1);
-
-    auto finish_segment = [&](int slot) {  // run by the last warp to arrive, all 32 lanes
-        constexpr int PER_LANE = (ELEMS + 31) / 32;
-        float v[PER_LANE];
-#pragma unroll
-        for (int u = 0; u < PER_LANE; u++) {
-            const int i = lane + 32 * u;
-            v[u] = 0.f;
-            if (i < ELEMS) {
-                const float* src = partial + (size_t)slot * GEMV_WARPS * ELEMS + i;
-#pragma unroll
-                for (int w = 0; w < GEMV_WARPS; w++) v[u] += src[w * ELEMS];
-            }
-        }
-        const bool starts = seg_begin == rt * p.kt, ends = seg_end == (rt + 1) * p.kt;
-        if (!starts) {  // a piece of a row-tile owned by an earlier CTA: publish it
-#pragma unroll
-            for (int u = 0; u < PER_LANE; u++) {
-                const int i = lane + 32 * u;
-                if (i < ELEMS)
-                    st_slot(p.scratch + (size_t)blockIdx.x * 128 + i, make_uint2(__float_as_uint(v[u]), 1u));
-            }
-            return;
-        }
-        if (!ends) {  // owner of a row-tile that continues in the following CTAs
-            const int te = (rt + 1) * p.kt;
-            bool gave_up = false;
-            for (int c = (int)blockIdx.x + 1; c < (int)gridDim.x && !gave_up; c++) {
-                const int c0 = c * p.chunk_q + min(c, p.chunk_r), c1 = c0 + p.chunk_q + (c < p.chunk_r ? 1 : 0);
-                if (c0 >= te) break;
-                if (c0 == c1) continue;
-#pragma unroll
-                for (int u = 0; u < PER_LANE; u++) {
-                    const int i = lane + 32 * u;
-                    if (i >= ELEMS) continue;
-                    uint2* slot_ptr = p.scratch + (size_t)c * 128 + i;
-                    uint2 e;
-                    int spins = 0;
-                    do {
-                        e = ld_slot(slot_ptr);
-                        if (e.y != 0u) break;
-                        __nanosleep(32);
-                    } while (++spins < GEMV_FIXUP_SPINS);
-                    if (e.y == 0u) {
-                        atomicOr(p.status, STATUS_GEMV_FIXUP_TIMEOUT);
-                        gave_up = true;
-                    } else {
-                        v[u] += __uint_as_float(e.x);
-                        st_slot(slot_ptr, make_uint2(0u, 0u));
-                    }
-                }
-                gave_up = __any_sync(0xFFFFFFFFu, gave_up);
-            }
-        }
-        // element i = col * 16 + row
+    // y of one finished row-tile, from a shared-memory buffer (element i = column * 16 + row)
+    auto emit = [&](int rt, const float* buf) {
         if (!p.x_f32) {
-#pragma unroll
-            for (int u = 0; u < PER_LANE; u++) {
-                const int i = lane + 32 * u, col = i >> 4, n = rt * 16 + (i & 15);
-                if (i < ELEMS && col < p.m && n < p.rows) p.y[(int64_t)col * p.ldy + p.col0 + n] = v[u];
+            for (int i = lane; i < ELEMS; i += 32) {
+                const int col = i >> 4, n = rt * 16 + (i & 15);
+                if (col < p.m && n < p.rows) p.y[(int64_t)col * p.ldy + p.col0 + n] = buf[i];
             }
         } else {  // columns 3t, 3t+1, 3t+2 are the hi / mid / lo parts of token t
-#pragma unroll
-            for (int u = 0; u < PER_LANE; u++)
-                if (lane + 32 * u < ELEMS) exchange[lane + 32 * u] = v[u];
-            __syncwarp();
             for (int i = lane; i < 16 * p.m; i += 32) {
                 const int tok = i >> 4, r = i & 15, n = rt * 16 + r;
                 if (n < p.rows)
                     p.y[(int64_t)tok * p.ldy + p.col0 + n] =
-                        (exchange[(3 * tok + 2) * 16 + r] + exchange[(3 * tok + 1) * 16 + r]) + exchange[(3 * tok) * 16 + r];
+                        (buf[(3 * tok + 2) * 16 + r] + buf[(3 * tok + 1) * 16 + r]) + buf[(3 * tok) * 16 + r];
             }
-            __syncwarp();
         }
     };
 
-    auto flush = [&]() {
-        const int slot = seg % NSLOT, gen = seg / NSLOT;
-        if (gen > 0) {  // the slot's previous use must have been reduced already
-            int spins = 0;
-            while (released[slot] < gen && ++spins < GEMV_SLOT_SPINS) {
-            }
-            if (released[slot] < gen && lane == 0) atomicOr(p.status, STATUS_GEMV_FIXUP_TIMEOUT);
-        }
-        float* mine = partial + ((size_t)slot * GEMV_WARPS + warp) * ELEMS;
-        if (XC == 1) {
-            if (q == 0) {
-                mine[g] = acc[0];
-                mine[g + 8] = acc[2];
-            }
-        } else {
-            mine[(2 * q) * 16 + g] = acc[0];
-            mine[(2 * q + 1) * 16 + g] = acc[1];
-            mine[(2 * q) * 16 + g + 8] = acc[2];
-            mine[(2 * q + 1) * 16 + g + 8] = acc[3];
-        }
-        acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
-        __syncwarp();
-        int old = 0;
-        if (lane == 0) {
-            __threadfence_block();
-            old = atomicAdd(&arrive[slot], 1);
-        }
-        old = __shfl_sync(0xFFFFFFFFu, old, 0);
-        if (old == GEMV_WARPS * (gen + 1) - 1) {
-            __threadfence_block();
-            finish_segment(slot);
-            __syncwarp();
-            if (lane == 0) {
-                __threadfence_block();
-                released[slot] = gen + 1;
-            }
-        }
-        seg++;
-        seg_begin = seg_end;
-        rt++;  // segments advance one row-tile at a time
-        seg_end = min((rt + 1) * p.kt, t1);
-    };
-
-    // Segment by segment: an inner loop over this warp's tiles of the segment (one tile per
-    // ring round, nothing but wait / load / release / compute in it), then the flush.
-    // Stage index and phase are tracked incrementally.
-    const int n_my = (t0 + warp < t1) ? (t1 - t0 - warp + GEMV_WARPS - 1) / GEMV_WARPS : 0;
-    int s = 0, t = t0 + warp;
-    uint32_t phase = 0;
-    const uint32_t my_tile = smem_u32(ring) + warp * T::BYTES + lane * 16;
     const uint32_t x32 = smem_u32(xrow) + q * 16, c32 = smem_u32(cinit) + (XC == 1 ? 0 : q * 16);
     const uint32_t live = (XC == 1) ? (uint32_t)(g == 0) : 1u;
-    const uint32_t lane_is_0 = lane == 0;
-    bool failed = false;
     stamp(2);
-    while (seg_begin < t1) {
-        // my tiles with index below seg_end
-        const int n_seg = (t < seg_end) ? (seg_end - t + GEMV_WARPS - 1) / GEMV_WARPS : 0;
-        int kbase = (t - rt * p.kt) * T::K;
-        for (int i = 0; i < n_seg && !failed; i++) {
-            if (!mbar_wait(&full[s], phase)) {
-                failed = true;
-                break;
-            }
-            R regs;
-            regs.load(my_tile + s * STAGE_BYTES, lane);
-            __syncwarp();
-            mbar_arrive_if(&empty[s], lane_is_0);
-            regs.template compute<XC>(acc, x32 + kbase * 2, c32 + (kbase >> 5) * cinit_block_bytes<XC>(), live);
-            kbase += GEMV_WARPS * T::K;
-            t += GEMV_WARPS;
-            if (++s == stages) {
-                s = 0;
-                phase ^= 1u;
-            }
-        }
-        flush();
-    }
+    WalkState st;
+    consume_share<QT, XC>(t0, t1, p.kt, p.chunk_q, p.chunk_r, warp, lane, smem_u32(ring), bar, partial, stages, st, x32, c32,
+                          live, p.scratch, p.status, smem_u32(const_cast<int*>(abort_flag)), acc, emit);
     stamp(4);
-    // Only the last round can lack a tile for some warps, and its stage is never refilled, so
-    // those warps owe the producer no release.
-    if (failed) {
+    if (*abort_flag) {  // a wait ran out somewhere in this CTA
         if (lane == 0) atomicOr(p.status, STATUS_GEMV_FIXUP_TIMEOUT);
-        *abort_flag = 1;
+        drain_after_abort();
     }
     stamp(5);
 }
@@ -294,8 +134,7 @@ template <int XC>
 static size_t gemv_fixed_smem(int kp, int xcols, int* sx_out) {
     const int sx = kp * 2 + 64;  // +64: consecutive rows start 16 banks apart
     if (sx_out) *sx_out = sx;
-    size_t b = GEMV_CTRL_BYTES + (size_t)Slots<XC>::N * GEMV_WARPS * Slots<XC>::ELEMS * 4 + 128 * 4 + (size_t)(kp / 32) * 64 +
-               (size_t)xcols * sx;
+    size_t b = GEMV_CTRL_BYTES + (size_t)Slots<XC>::N * GEMV_WARPS * Slots<XC>::ELEMS * 4 + (size_t)(kp / 32) * 64 + (size_t)xcols * sx;
     return (b + 127) & ~(size_t)127;
 }
 
@@ -332,8 +171,17 @@ static cudaError_t launch_one(const GemvParams& p, int grid, size_t smem, cudaSt
         if (e != cudaSuccess) return e;
         attr_set[dev] = true;
     }
-    gemv_kernel<QT, XC><<<grid, GEMV_THREADS, smem, s>>>(p);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(GEMV_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, gemv_kernel<QT, XC>, p);
 }
 
 template <int XC>

@@ -1,6 +1,8 @@
 // Device-side building blocks of the decode GEMV, shared by the single-op kernel (wf_gemv.cu)
-// and the persistent multi-op kernel (wf_decode.cu): shared-memory ring primitives, the unpack +
-// tensor-core block routine, the per-format tile code and the activation staging.
+// and the persistent multi-op kernel (wf_decode.cu): shared-memory ring primitives, the walk over
+// a CTA's share of a weight (producer and consumer side, segment reduction, fix-up between
+// CTAs), the unpack + tensor-core block routine, the per-format tile code and the activation
+// staging.
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -13,13 +15,18 @@
 namespace wf {
 
 constexpr int GEMV_WARPS = 16;                       // consumer warps
+constexpr int GEMV_CONSUMERS = GEMV_WARPS * 32;
 constexpr int GEMV_THREADS = (GEMV_WARPS + 1) * 32;  // + one producer warp
 constexpr int GEMV_MAX_STAGES = 16;
 constexpr int GEMV_BAR_SPINS = 1 << 24;
 constexpr int GEMV_XCOLS = 8;  // columns of one mma n-tile
 constexpr int GEMV_FIXUP_SPINS = 1 << 22;
 constexpr int GEMV_SLOT_SPINS = 1 << 24;
-constexpr int GEMV_CTRL_BYTES = 128 + 2 * GEMV_MAX_STAGES * 8;  // arrive[], released[], abort, full[], empty[]
+constexpr int GEMV_MAX_SLOTS = 8;  // partial-sum slots a CTA rotates through
+// control block: abort flag | full[MAX_STAGES] | empty[MAX_STAGES] | done[MAX_SLOTS] | vacant[MAX_SLOTS]
+constexpr int GEMV_CTRL_BYTES = 128 + (2 * GEMV_MAX_STAGES + 2 * GEMV_MAX_SLOTS) * 8;
+// XC = 1: one live column; XC = 8: up to 8.  N partial-sum slots of [GEMV_WARPS][ELEMS] floats.
+template <int XC> struct Slots { static constexpr int N = (XC == 1) ? 8 : 4, ELEMS = 16 * XC; };
 
 struct GemvParams {
     const uint8_t* tiles;
@@ -73,6 +80,22 @@ __device__ __forceinline__ void fetch_block(uint32_t xaddr, uint32_t caddr, uint
         ci = make_float4(__uint_as_float(t.x), __uint_as_float(t.y), __uint_as_float(t.z), __uint_as_float(t.w));
     }
 }
+// XC = 1, four consecutive blocks (128 k) at once: one predicate, four predicated 16-byte loads of
+// the activations and ONE 16-byte broadcast load of the four start values.
+__device__ __forceinline__ void fetch_four_blocks_one_column(uint32_t xaddr, uint32_t caddr, uint32_t live, uint4 (&xb)[4],
+                                                             float (&c)[4]) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %22, 0;\n\t"
+        "@p ld.shared.v4.u32 {%0,%1,%2,%3}, [%20];\n\t"
+        "@p ld.shared.v4.u32 {%4,%5,%6,%7}, [%20+64];\n\t"
+        "@p ld.shared.v4.u32 {%8,%9,%10,%11}, [%20+128];\n\t"
+        "@p ld.shared.v4.u32 {%12,%13,%14,%15}, [%20+192];\n\t"
+        "ld.shared.v4.f32 {%16,%17,%18,%19}, [%21];\n\t}"
+        : "+r"(xb[0].x), "+r"(xb[0].y), "+r"(xb[0].z), "+r"(xb[0].w), "+r"(xb[1].x), "+r"(xb[1].y), "+r"(xb[1].z), "+r"(xb[1].w),
+          "+r"(xb[2].x), "+r"(xb[2].y), "+r"(xb[2].z), "+r"(xb[2].w), "+r"(xb[3].x), "+r"(xb[3].y), "+r"(xb[3].z), "+r"(xb[3].w),
+          "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+        : "r"(xaddr), "r"(caddr), "r"(live));
+}
 // Offsets of block `blk` inside the start-value table: one float (XC = 1) or [4] float4 (XC = 8).
 template <int XC> __device__ __forceinline__ constexpr int cinit_block_bytes() { return XC == 1 ? 4 : 64; }
 
@@ -114,6 +137,38 @@ __device__ __forceinline__ bool mbar_wait(void* bar, uint32_t parity) {
         : "r"(smem_u32(bar)), "r"(parity), "r"((uint32_t)GEMV_BAR_SPINS)
         : "memory");
     return ok != 0;
+}
+// The hot-loop form: one try_wait and a branch when the phase is already complete.  Otherwise spin,
+// bounded, and leave early once any thread of the CTA has raised the abort word (shared address
+// `abort32`); a wait that runs out raises it.  After an abort the data the caller goes on to use is
+// garbage -- the kernel reports the failure through its status word and the host discards y.
+__device__ __forceinline__ void mbar_wait_or_abort(void* bar, uint32_t parity, uint32_t abort32) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, q;\n\t"
+        ".reg .u32 n, a;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%0], %1;\n\t"
+        "@p bra WF_OK_%=;\n\t"
+        "mov.u32 n, 0;\n\t"
+        "WF_SPIN_%=:\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%0], %1;\n\t"
+        "@p bra WF_OK_%=;\n\t"
+        "ld.volatile.shared.u32 a, [%2];\n\t"
+        "setp.ne.u32 q, a, 0;\n\t"
+        "@q bra WF_OK_%=;\n\t"
+        "add.u32 n, n, 1;\n\t"
+        "setp.lt.u32 q, n, %3;\n\t"
+        "@q bra WF_SPIN_%=;\n\t"
+        "st.volatile.shared.u32 [%2], 1;\n\t"
+        "WF_OK_%=:\n\t"
+        "}\n" ::"r"(smem_u32(bar)),
+        "r"(parity), "r"(abort32), "r"((uint32_t)GEMV_BAR_SPINS)
+        : "memory");
+}
+// After an abort: give this CTA's bulk copies still in flight time to land before its shared memory
+// is handed to another CTA (about a millisecond, bounded).
+__device__ __forceinline__ void drain_after_abort() {
+    for (int i = 0; i < 1000; i++) __nanosleep(1000);
 }
 __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, void* bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)),
@@ -202,26 +257,33 @@ template <> struct TileRegs<WF_QTYPE_Q4_0> {
     // xaddr: shared address of this lane's activations for k = kbase (row + q * 16 bytes);
     // caddr: shared address of the start value(s) of block kbase / 32; live: lane owns a live column
     __device__ __forceinline__ void compute(float (&acc)[4], uint32_t xaddr, uint32_t caddr, uint32_t live) const {
-        uint4 xb = make_uint4(0u, 0u, 0u, 0u);
-        float4 ci;
+        const float2 s0 = half2_bits_to_float2(s.x), s1 = half2_bits_to_float2(s.y);  // row g, blocks 0..3
+        const float2 s2 = half2_bits_to_float2(s.z), s3 = half2_bits_to_float2(s.w);  // row g + 8
+        const float sg[4] = {s0.x, s0.y, s1.x, s1.y}, sh[4] = {s2.x, s2.y, s3.x, s3.y};
+        if (XC == 1) {
+            uint4 xb[4] = {make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u),
+                           make_uint4(0u, 0u, 0u, 0u)};
+            float ci[4];
+            fetch_four_blocks_one_column(xaddr, caddr, live, xb, ci);
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-            fetch_block<XC>(xaddr + j * 64, caddr + j * cinit_block_bytes<XC>(), live, xb, ci);
-            float d[4];
-            if (XC == 1) {
-                block_mma(d, word_of(c[0], j), word_of(c[1], j), xb, MAGIC_16, 0.f, 0.f, 0.f, 0.f);
-                d[0] += ci.x;
-                d[2] += ci.z;
-            } else {
-                block_mma(d, word_of(c[0], j), word_of(c[1], j), xb, MAGIC_16, ci.x, ci.y, ci.z, ci.w);
+            for (int j = 0; j < 4; j++) {
+                float d[4];
+                block_mma(d, word_of(c[0], j), word_of(c[1], j), xb[j], MAGIC_16, 0.f, 0.f, 0.f, 0.f);
+                acc[0] = fmaf(sg[j], d[0] + ci[j], acc[0]);
+                acc[2] = fmaf(sh[j], d[2] + ci[j], acc[2]);
             }
-            const float2 dg = half2_bits_to_float2(j < 2 ? s.x : s.y), dh = half2_bits_to_float2(j < 2 ? s.z : s.w);
-            const float sg = (j & 1) ? dg.y : dg.x, sh = (j & 1) ? dh.y : dh.x;
-            acc[0] = fmaf(sg, d[0], acc[0]);
-            acc[2] = fmaf(sh, d[2], acc[2]);
-            if (XC > 1) {
-                acc[1] = fmaf(sg, d[1], acc[1]);
-                acc[3] = fmaf(sh, d[3], acc[3]);
+        } else {
+            uint4 xb;
+            float4 ci;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                fetch_block<XC>(xaddr + j * 64, caddr + j * cinit_block_bytes<XC>(), live, xb, ci);
+                float d[4];
+                block_mma(d, word_of(c[0], j), word_of(c[1], j), xb, MAGIC_16, ci.x, ci.y, ci.z, ci.w);
+                acc[0] = fmaf(sg[j], d[0], acc[0]);
+                acc[2] = fmaf(sh[j], d[2], acc[2]);
+                acc[1] = fmaf(sg[j], d[1], acc[1]);
+                acc[3] = fmaf(sh[j], d[3], acc[3]);
             }
         }
     }
@@ -322,6 +384,231 @@ template <> struct TileRegs<WF_QTYPE_Q4_K> {
         }
     }
 };
+
+// ---------------------------------------------------------------- walking a CTA's share of a weight
+// A CTA owns tiles [t0, t1) of the weight (row-tile major, k-tile minor), delivered through the
+// ring in rounds of GEMV_WARPS consecutive tiles; consumer warp w takes tile w of every round.
+// The share is a sequence of segments, one per row-tile it touches.  When a warp leaves a
+// segment it parks its partial sums in slot (segment mod N) and arrives on the slot's `done`
+// barrier -- nothing more, it does not wait for anybody.  One warp per segment, taken in turn,
+// is the segment's reducer: one segment later, when the other warps have normally long
+// arrived, it waits on `done`, adds the sixteen partials in warp order, finishes the row-tile
+// (fix-up between CTAs, y) and marks the slot vacant.
+struct BarrierSet {
+    uint64_t *full, *empty;   // [stages]: data of a round has landed / all warps have taken their tile
+    uint64_t *done, *vacant;  // [Slots::N]: all warps have parked their partials / the reducer has read them
+};
+__device__ __forceinline__ BarrierSet barrier_set(uint8_t* smem) {
+    BarrierSet b;
+    b.full = reinterpret_cast<uint64_t*>(smem + 128);
+    b.empty = b.full + GEMV_MAX_STAGES;
+    b.done = b.empty + GEMV_MAX_STAGES;
+    b.vacant = b.done + GEMV_MAX_SLOTS;
+    return b;
+}
+template <int XC>
+__device__ __forceinline__ void barrier_set_init(const BarrierSet& b, int stages) {
+    for (int s = 0; s < stages; s++) {
+        mbar_init(&b.full[s], 1);
+        mbar_init(&b.empty[s], GEMV_WARPS);
+    }
+    for (int s = 0; s < Slots<XC>::N; s++) {
+        mbar_init(&b.done[s], GEMV_WARPS);
+        mbar_init(&b.vacant[s], 1);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+// Position in the ring (stage, laps walked) and the number of segments flushed so far; both
+// carry over from one weight to the next in the multi-op kernel.
+struct WalkState {
+    int s = 0;
+    uint32_t lap = 0;
+    int seg = 0;
+    __device__ __forceinline__ void advance(int stages) {
+        if (++s == stages) {
+            s = 0;
+            lap++;
+        }
+    }
+};
+
+// Producer (one thread): issue every round of the share, waiting for a stage to be released once
+// the ring has been filled.  Stops early when the CTA has aborted.
+template <int QT>
+__device__ __forceinline__ void produce_share(const uint8_t* tiles, int t0, int t1, uint8_t* ring, const BarrierSet& bar,
+                                              int stages, WalkState& pos, volatile int* abort_flag) {
+    using T = Tile<QT>;
+    constexpr uint32_t STAGE_BYTES = GEMV_WARPS * T::BYTES;
+    const uint32_t abort32 = smem_u32(const_cast<int*>(abort_flag));
+    for (int first = t0; first < t1; first += GEMV_WARPS) {
+        if (pos.lap > 0) mbar_wait_or_abort(&bar.empty[pos.s], (pos.lap - 1) & 1, abort32);
+        if (*abort_flag) return;
+        const uint32_t bytes = (uint32_t)min(GEMV_WARPS, t1 - first) * T::BYTES;
+        mbar_expect_tx(&bar.full[pos.s], bytes);
+        bulk_load(ring + (size_t)pos.s * STAGE_BYTES, tiles + (size_t)first * T::BYTES, bytes, &bar.full[pos.s]);
+        pos.advance(stages);
+    }
+}
+
+// Accumulator fragment -> a partial-sum buffer, element i = column * 16 + row; clears the fragment.
+template <int XC>
+__device__ __forceinline__ void store_fragment(float* buf, float (&acc)[4], int g, int q) {
+    if (XC == 1) {
+        if (q == 0) {
+            buf[g] = acc[0];
+            buf[g + 8] = acc[2];
+        }
+    } else {
+        buf[(2 * q) * 16 + g] = acc[0];
+        buf[(2 * q + 1) * 16 + g] = acc[1];
+        buf[(2 * q) * 16 + g + 8] = acc[2];
+        buf[(2 * q + 1) * 16 + g + 8] = acc[3];
+    }
+    acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+}
+
+// Fix-up between CTAs.  A row-tile cut by a share boundary is finished by the CTA that holds its
+// first k-tile (the owner).  The following CTAs publish their piece to their scratch slot as
+// {value, 1} words; the owner adds the pieces in CTA order, clears the tags and emits the
+// row-tile.  All waits are bounded; on expiry a status bit is set.
+template <int ELEMS>
+__device__ __forceinline__ void publish_piece(uint2* slot, const float (&v)[(ELEMS + 31) / 32], int lane, int* status) {
+#pragma unroll
+    for (int u = 0; u < (ELEMS + 31) / 32; u++) {
+        const int i = lane + 32 * u;
+        if (i >= ELEMS) continue;
+        int spins = 0;  // the slot's previous content must have been taken before it is overwritten
+        while (ld_slot(slot + i).y != 0u && ++spins < GEMV_FIXUP_SPINS) __nanosleep(32);
+        if (spins >= GEMV_FIXUP_SPINS) atomicOr(status, STATUS_GEMV_FIXUP_TIMEOUT);
+        st_slot(slot + i, make_uint2(__float_as_uint(v[u]), 1u));
+    }
+}
+template <int ELEMS>
+__device__ __forceinline__ void collect_pieces(uint2* slots, float (&v)[(ELEMS + 31) / 32], int lane, int row_end,
+                                               int chunk_q, int chunk_r, int* status) {
+    bool gave_up = false;
+    for (int c = (int)blockIdx.x + 1; c < (int)gridDim.x && !gave_up; c++) {
+        const int c0 = c * chunk_q + min(c, chunk_r), c1 = c0 + chunk_q + (c < chunk_r ? 1 : 0);
+        if (c0 >= row_end) break;
+        if (c0 == c1) continue;
+#pragma unroll
+        for (int u = 0; u < (ELEMS + 31) / 32; u++) {
+            const int i = lane + 32 * u;
+            if (i >= ELEMS) continue;
+            uint2* sp = slots + (size_t)c * 128 + i;
+            uint2 e;
+            int spins = 0;
+            do {
+                e = ld_slot(sp);
+                if (e.y != 0u) break;
+                __nanosleep(32);
+            } while (++spins < GEMV_FIXUP_SPINS);
+            if (e.y == 0u) {
+                atomicOr(status, STATUS_GEMV_FIXUP_TIMEOUT);
+                gave_up = true;
+            } else {
+                v[u] += __uint_as_float(e.x);
+                st_slot(sp, make_uint2(0u, 0u));
+            }
+        }
+        gave_up = __any_sync(0xFFFFFFFFu, gave_up);
+    }
+}
+
+// Consumer warp: this warp's tiles of the share, segment by segment.  emit(row_tile, buf) writes
+// one finished row-tile from a shared-memory buffer (element i = column * 16 + row) and is run
+// by all 32 lanes of the segment's reducer.  Waits that run out raise the CTA's abort word.
+template <int QT, int XC, class Emit>
+__device__ __forceinline__ void consume_share(int t0, int t1, int kt, int chunk_q, int chunk_r, int warp, int lane,
+                                              uint32_t ring32, const BarrierSet& bar, float* partial, int stages,
+                                              WalkState& st, uint32_t x32, uint32_t c32, uint32_t live, uint2* slots,
+                                              int* status, uint32_t abort32, float (&acc)[4], Emit&& emit) {
+    using T = Tile<QT>;
+    using R = TileRegs<QT>;
+    constexpr int NSLOT = Slots<XC>::N, ELEMS = Slots<XC>::ELEMS, PER_LANE = (ELEMS + 31) / 32;
+    constexpr uint32_t STAGE_BYTES = GEMV_WARPS * T::BYTES;
+    const int g = lane >> 2, q = lane & 3;
+    const uint32_t my_tile = ring32 + warp * T::BYTES + lane * 16;
+    const uint32_t lane_is_0 = lane == 0;
+
+    // finish segment number sg (row-tile rt, tiles [sb, se) of it in this share)
+    auto reduce = [&](int sg, int rt, int sb, int se) {
+        const int slot = sg % NSLOT, gen = sg / NSLOT;
+        mbar_wait_or_abort(&bar.done[slot], gen & 1, abort32);
+        float* buf = partial + (size_t)slot * GEMV_WARPS * ELEMS;
+        float v[PER_LANE];
+#pragma unroll
+        for (int u = 0; u < PER_LANE; u++) {
+            const int i = lane + 32 * u;
+            v[u] = 0.f;
+            if (i < ELEMS) {
+#pragma unroll
+                for (int w = 0; w < GEMV_WARPS; w++) v[u] += buf[w * ELEMS + i];
+            }
+        }
+        const bool starts = sb == rt * kt, ends = se == (rt + 1) * kt;
+        if (!starts) {
+            publish_piece<ELEMS>(slots + (size_t)blockIdx.x * 128, v, lane, status);
+        } else {
+            if (!ends) collect_pieces<ELEMS>(slots, v, lane, (rt + 1) * kt, chunk_q, chunk_r, status);
+            __syncwarp();  // every lane has read what it needs of the slot: reuse its first row as emit's buffer
+#pragma unroll
+            for (int u = 0; u < PER_LANE; u++)
+                if (lane + 32 * u < ELEMS) buf[lane + 32 * u] = v[u];
+            __syncwarp();
+            emit(rt, buf);
+        }
+        __syncwarp();
+        mbar_arrive_if(&bar.vacant[slot], lane_is_0);
+    };
+
+    int seg_begin = t0, rt = (t0 < t1) ? t0 / kt : 0;
+    int seg_end = min((rt + 1) * kt, t1);
+    int t = t0 + warp;
+    int prev_rt = 0, prev_begin = 0, prev_end = 0;
+    bool have_prev = false;
+    while (seg_begin < t1) {
+        uint32_t xa = x32 + (t - rt * kt) * (T::K * 2), ca = c32 + (t - rt * kt) * ((T::K >> 5) * cinit_block_bytes<XC>());
+        for (; t < seg_end; t += GEMV_WARPS) {  // my tiles below seg_end
+            mbar_wait_or_abort(&bar.full[st.s], st.lap & 1, abort32);
+            R regs;
+            regs.load(my_tile + st.s * STAGE_BYTES, lane);
+            __syncwarp();
+            mbar_arrive_if(&bar.empty[st.s], lane_is_0);
+            regs.template compute<XC>(acc, xa, ca, live);
+            xa += GEMV_WARPS * T::K * 2;
+            ca += GEMV_WARPS * (T::K >> 5) * cinit_block_bytes<XC>();
+            st.advance(stages);
+        }
+        // park my partial sums of this segment
+        const int slot = st.seg % NSLOT, gen = st.seg / NSLOT;
+        if (gen > 0) mbar_wait_or_abort(&bar.vacant[slot], (gen - 1) & 1, abort32);
+        store_fragment<XC>(partial + ((size_t)slot * GEMV_WARPS + warp) * ELEMS, acc, g, q);
+        __syncwarp();
+        mbar_arrive_if(&bar.done[slot], lane_is_0);
+        // the previous segment's reducer does its duty now
+        if (have_prev && warp == (st.seg - 1) % GEMV_WARPS) reduce(st.seg - 1, prev_rt, prev_begin, prev_end);
+        prev_rt = rt;
+        prev_begin = seg_begin;
+        prev_end = seg_end;
+        have_prev = true;
+        st.seg++;
+        seg_begin = seg_end;
+        rt++;
+        seg_end = min((rt + 1) * kt, t1);
+    }
+    if (have_prev && warp == (st.seg - 1) % GEMV_WARPS) reduce(st.seg - 1, prev_rt, prev_begin, prev_end);
+    // A warp without a tile in the share's last round still waits for that round and releases it,
+    // so that every stage collects its GEMV_WARPS releases.  (t ran past t1 by less than a round;
+    // the warp missed the last round iff the share's last round does not reach its position.)
+    const int n = t1 - t0;
+    if (n > 0 && (n % GEMV_WARPS) != 0 && warp >= (n % GEMV_WARPS)) {
+        mbar_wait_or_abort(&bar.full[st.s], st.lap & 1, abort32);
+        mbar_arrive_if(&bar.empty[st.s], lane_is_0);
+        st.advance(stages);
+    }
+}
 
 // ---------------------------------------------------------------- x staging
 // Copies x into shared memory as bf16 rows of `kp` elements (zero beyond k), row stride sx
