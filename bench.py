@@ -198,7 +198,7 @@ def run_ours(args) -> None:
     ctx = CudaContext(local_rank)
     comm = None
     spec = LLAMA_7B_Q4_0
-    mode = args.mode if args.mode != "auto" else ("program" if world > 1 else "graph")
+    mode = args.mode if args.mode != "auto" else "program"
     if mode == "program":
         # one persistent kernel per token and rank; the row-shard gather is fused into the GEMV
         # epilogue (peer stores), so no communicator is needed

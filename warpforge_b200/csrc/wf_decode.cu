@@ -43,11 +43,11 @@ struct ProgOp {
 };
 
 struct ProgSync {                     // device memory owned by the program
-    unsigned long long arrive;        // CTAs arrived at grid barriers, monotonic
-    unsigned long long release;       // barriers released on this rank, monotonic
+    unsigned long long arrive;        // CTAs arrived at grid barriers, monotonic; alone on its 128-byte line
+    unsigned long long pad0[15];
     unsigned long long epoch;         // barriers completed by earlier runs
     unsigned int done_ctas;           // CTAs that left the current run
-    unsigned int pad;
+    unsigned int pad1;
 };
 
 struct ProgParams {

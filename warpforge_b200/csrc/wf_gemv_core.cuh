@@ -624,14 +624,29 @@ __device__ __forceinline__ uint32_t pack_bf16_trunc(float a, float b) {
 static __device__ void stage_x(const GemvParams& p, uint8_t* xs, float* cinit, int kp, float beta, int nthreads, bool one_col) {
     const int groups = kp >> 3;  // 8 elements per thread step
     const int total = p.m * groups;
-    for (int idx = threadIdx.x; idx < ((total + 31) & ~31); idx += nthreads) {  // warp-uniform trip count
+    constexpr int U = 4;  // bf16 path: four independent loads in flight per thread
+    for (int idx0 = threadIdx.x; idx0 < ((total + 31) & ~31); idx0 += nthreads * (p.x_f32 ? 1 : U)) {  // warp-uniform trip counts
+      uint4 pre[U];
+      if (!p.x_f32) {
+#pragma unroll
+          for (int u = 0; u < U; u++) {
+              const int idx = idx0 + u * nthreads;
+              const int t = (idx < total && p.m > 1) ? idx / groups : 0, c8 = idx < total ? idx - t * groups : 0;
+              pre[u] = make_uint4(0, 0, 0, 0);
+              if (idx < total && c8 * 8 < p.k)
+                  pre[u] = __ldcg(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.x) + (size_t)t * p.ldx + c8 * 8));
+          }
+      }
+#pragma unroll
+      for (int u = 0; u < U; u++) {
+        const int idx = idx0 + u * nthreads;
+        if ((p.x_f32 && u > 0) || (idx & ~31) >= ((total + 31) & ~31)) break;  // warp-uniform
         const bool live = idx < total;
         const int t = (live && p.m > 1) ? idx / groups : 0, c8 = live ? idx - t * groups : 0;
         const bool in_k = live && (c8 * 8 < p.k);
         float sum[3] = {0.f, 0.f, 0.f};
         if (!p.x_f32) {
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (in_k) v = __ldcg(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.x) + (size_t)t * p.ldx + c8 * 8));
+            const uint4 v = pre[u];
             if (live) *reinterpret_cast<uint4*>(xs + (size_t)t * p.sx + c8 * 16) = v;
             const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
@@ -690,6 +705,7 @@ static __device__ void stage_x(const GemvParams& p, uint8_t* xs, float* cinit, i
                 blk[(col >> 1) * 4 + (col & 1) + 2] = v;
             }
         }
+      }
     }
 }
 
