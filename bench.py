@@ -37,6 +37,12 @@ WORKLOAD = ("BASELINE config 4: 7B-shape Llama decode, 224 Q4_0 projections (32 
             "{4x[4096x4096], 2x[11008x4096], [4096x11008]}), batch 1, bf16 activations, fp32 out")
 
 
+# DRAM traffic of the decode kernels, from an ncu capture of two layers of this workload
+# (dram__bytes_read.sum + dram__bytes_write.sum = 232.25 MB for 2 layers, profiles/gemv_program_q4_0_decode_7b.md);
+# traffic grows in proportion to the layers run and splits evenly over row shards.
+NCU_TRAFFIC_BYTES_PER_LAYER = 232.25e6 / 2
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -202,7 +208,7 @@ def run_ours(args) -> None:
     if mode == "program":
         # one persistent kernel per token and rank; the row-shard gather is fused into the GEMV
         # epilogue (peer stores), so no communicator is needed
-        stack = ProjectionStack(ctx, spec, tokens=1, rank=rank, world=world)
+        stack = ProjectionStack(ctx, spec, tokens=1, rank=rank, world=world, layers=args.layers or None)
         handles = None
         if world > 1:
             handles = [None] * world
@@ -214,7 +220,7 @@ def run_ours(args) -> None:
             ids = [Communicator.create_unique_id() if rank == 0 else None]
             dist.broadcast_object_list(ids, src=0)
             comm = Communicator(ctx, ids[0], rank, world)
-        stack = ProjectionStack(ctx, spec, tokens=1, comm=comm)
+        stack = ProjectionStack(ctx, spec, tokens=1, comm=comm, layers=args.layers or None)
         stack.record()
 
     def barrier():
@@ -242,18 +248,20 @@ def run_ours(args) -> None:
 
     # end to end through the public step call: pinned host activations in, last output out
     y_out = np.empty((1, spec.projections[-1][1]), np.float32)
-    pinned_in = {k: ctx.host_alloc(v.nbytes) for k, v in stack.x_host.items()}
-    pinned_out = ctx.host_alloc(y_out.nbytes)
-    for _ in range(3):
-        stack.step_host(stack.x_host, y_out, pinned_in, pinned_out)
-    barrier()
-    t = time.perf_counter()
-    ctx.record_event(e0)
-    for _ in range(args.steps):
-        stack.step_host(stack.x_host, y_out, pinned_in, pinned_out)
-    ctx.record_event(e1)
-    ctx.synchronize()
-    e2e_ms = max(ctx.elapsed_ms(e0, e1), (time.perf_counter() - t) * 1e3)
+    e2e_ms = float("nan")
+    if not args.kernel_only:
+        pinned_in = {k: ctx.host_alloc(v.nbytes) for k, v in stack.x_host.items()}
+        pinned_out = ctx.host_alloc(y_out.nbytes)
+        for _ in range(3):
+            stack.step_host(stack.x_host, y_out, pinned_in, pinned_out)
+        barrier()
+        t = time.perf_counter()
+        ctx.record_event(e0)
+        for _ in range(args.steps):
+            stack.step_host(stack.x_host, y_out, pinned_in, pinned_out)
+        ctx.record_event(e1)
+        ctx.synchronize()
+        e2e_ms = max(ctx.elapsed_ms(e0, e1), (time.perf_counter() - t) * 1e3)
     clocks = sampler.stop() if rank == 0 else None
 
     if dist is not None:
@@ -268,7 +276,7 @@ def run_ours(args) -> None:
         ms_step = ms / args.steps
         tok_s = 1e3 / ms_step
         alg_bytes = stack.algorithmic_bytes_per_step()          # this rank's shard
-        n_launch = spec.layers * len(spec.projections)
+        n_launch = 1 if mode == "program" else stack.layers * len(spec.projections)
         gbs = alg_bytes / (ms_step * 1e-3) / 1e9
         h2d = sum(v.nbytes for v in stack.x_host.values())
         line = {
@@ -283,11 +291,17 @@ def run_ours(args) -> None:
             "e2e": {"value": 1e3 / (e2e_ms / args.steps), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": int(y_out.nbytes)},
             "gpu_launches": int(launches),
             "clocks": clocks,
-            "roofline": {"bound": "hbm", "kernel": "gemv_kernel<Q4_0, 1 column>", "achieved": gbs, "peak": hbm_peak, "unit": "GB/s",
+            "roofline": {"bound": "hbm", "kernel": ("gemv_program_kernel" if mode == "program" else "gemv_kernel") + "<Q4_0, 1 column>", "achieved": gbs, "peak": hbm_peak, "unit": "GB/s",
                          "frac": gbs / hbm_peak, "frac_of_8TBs_nominal": gbs / 8000.0, "peak_source": peak_src,
-                         "bytes_per_launch": alg_bytes / n_launch, "us_per_launch": ms_step * 1e3 / n_launch, "traffic": None},
+                         "bytes_per_launch": alg_bytes / n_launch, "us_per_launch": ms_step * 1e3 / n_launch,
+                         "traffic": NCU_TRAFFIC_BYTES_PER_LAYER * stack.layers / world / n_launch,
+                         "traffic_source": "ncu dram bytes of a 2-layer capture, scaled by layers (and 1 / ranks)"},
         }
-        if world == 1:
+        if stack.layers != spec.layers:
+            line["partial"] = f"{stack.layers} of {spec.layers} layers: a profiling run, not a bench value"
+        if args.kernel_only:
+            line["e2e"] = None
+        if world == 1 and not args.kernel_only:
             line["gemv_sweep"] = gemv_sweep(ctx, hbm_peak)
             from oracle import oracle as O
 
@@ -313,7 +327,11 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--mode", default="auto", choices=["auto", "graph", "program"],
-                    help="graph: one kernel per projection; program: one persistent kernel per token (default for N > 1)")
+                    help="program: one persistent kernel per token (default); graph: one kernel per projection in a CUDA graph")
+    ap.add_argument("--layers", type=int, default=0,
+                    help="profiling aid: run only this many of the 32 layers (the line is then marked partial and is not a bench value)")
+    ap.add_argument("--kernel-only", action="store_true",
+                    help="profiling aid: only the device-timed steps (no end-to-end leg, no GEMV sweep, no CPU baseline)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
