@@ -91,7 +91,7 @@ for name, rows, k in st.spec.projections:
     assert np.max(np.abs(got - want)) <= 1e-3 * np.max(np.abs(want)), name
 dist.barrier()
 st.close(); ctx.close(); dist.destroy_process_group()
-print("RANK_OK", rank)
+os.write(1, f"RANK_OK {rank}\n".encode())  # one write per rank: the two ranks share the pipe
 """
 
 
