@@ -66,6 +66,9 @@ struct Context {
     int64_t d_stage_bytes = 0;
     void* d_x16 = nullptr;  // fp16 copy of the activations for the tensor-core GEMM
     int64_t x16_bytes = 0;
+    float* d_gemm_partial = nullptr;       // [sm_count][256][128] pieces of tiles cut by a share boundary
+    unsigned int* d_gemm_ready = nullptr;  // [sm_count][4] launch number whose piece is complete, per 32-row quarter
+    unsigned int gemm_launches = 0;
     int64_t launches = 0;
     int gemv_ctas_per_sm[3] = {0, 0, 0};
 };

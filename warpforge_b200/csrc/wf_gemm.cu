@@ -17,7 +17,14 @@
 //               scale and write fp16 rows into the swizzled A stage; one 16-row tile per warp and stage
 // Stages hold BK = 128 k: A = 128 rows x 128 k fp16 (two 64-k swizzle spans, 32 KB), B = BM x 128 k bf16.
 // The accumulator is double buffered in TMEM (2 x BM columns <= 512) so the epilogue of one tile
-// overlaps the main loop of the next.  Every wait is bounded; on expiry the CTA sets a status bit,
+// overlaps the main loop of the next.
+//
+// Work split ("stream-K"): all (tile, k-block) steps form one sequence in tile order, cut into
+// equal contiguous shares, one per CTA, so every SM does the same number of MMA steps whatever the
+// tile count.  A tile cut by a share boundary is finished by the CTA that holds its first
+// k-block: the CTAs holding the rest reach their piece first (it is the head of their share),
+// write it to a scratch buffer and publish the launch number; the owner reaches the tile last,
+// adds the pieces in CTA order (deterministic) and writes y.  The owner's wait is bounded.  Every wait is bounded; on expiry the CTA sets a status bit,
 // stops issuing work and still frees its TMEM.
 //
 // Weights are rounded once to fp16 (relative 2^-12) after the exact fp32 dequantization; products
@@ -48,7 +55,29 @@ struct GemmParams {
     int n_tiles, m_tiles, k_blocks;  // k_blocks = ceil(k / 128)
     int stages;
     uint32_t idesc;
+    // stream-K: the (tile, k-block) units form one sequence, CTA b owns units [b*q + min(b,r), ...)
+    int unit_q, unit_r;
+    float* partial;        // [ctas][bm][128] fp32: a CTA's piece of a tile that begins in an earlier CTA
+    unsigned int* ready;   // [ctas][4] launch number whose piece (per 32-row quarter) is complete in `partial`
+    unsigned int launch;   // this launch's number (never 0)
 };
+
+// One CTA's share of the unit sequence, cut into segments: a segment is a run of k-blocks of one tile.
+struct GemmSegment {
+    int tile, kb0, kb1;  // k-blocks [kb0, kb1) of `tile`
+};
+__device__ __forceinline__ void cta_units(const GemmParams& p, int cta, int& u0, int& u1) {
+    u0 = cta * p.unit_q + min(cta, p.unit_r);
+    u1 = u0 + p.unit_q + (cta < p.unit_r ? 1 : 0);
+}
+// the segment that starts at unit u (u < u1)
+__device__ __forceinline__ GemmSegment segment_at(const GemmParams& p, int u, int u1) {
+    GemmSegment g;
+    g.tile = u / p.k_blocks;
+    g.kb0 = u - g.tile * p.k_blocks;
+    g.kb1 = min(p.k_blocks, g.kb0 + (u1 - u));
+    return g;
+}
 
 // ---------------------------------------------------------------- PTX wrappers
 __device__ __forceinline__ uint32_t g_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -107,6 +136,14 @@ __device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t adesc, uint
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
         "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_u32(const unsigned int* p) {
+    unsigned int v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_u32(unsigned int* p, unsigned int v) {
+    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 // K-major operand, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
 __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
@@ -273,7 +310,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmParams 
 
     const int warp = __shfl_sync(0xFFFFFFFFu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
     const int stages = p.stages;
-    const int total_tiles = p.n_tiles * p.m_tiles;
+    int u0, u1;
+    cta_units(p, blockIdx.x, u0, u1);
     constexpr int TILE_BYTES = Tile<QT>::BYTES;
     constexpr int KB_PER_WTILE = Tile<QT>::K / GEMM_BK;  // stages per weight k-tile: 1 (Q4_0, Q8_0) or 2 (Q4_K)
 
@@ -305,9 +343,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmParams 
         // ------------------------------------------------ TMA producer (activations)
         if (lane == 0) {
             int it = 0;
-            for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
-                const int mt = tile % p.m_tiles;
-                for (int kb = 0; kb < p.k_blocks; kb++, it++) {
+            for (int u = u0; u < u1 && !*abort_flag;) {
+                const GemmSegment g = segment_at(p, u, u1);
+                const int mt = g.tile % p.m_tiles;
+                for (int kb = g.kb0; kb < g.kb1; kb++, it++) {
                     const int s = it % stages;
                     if (it >= stages && !g_mbar_wait(&s_empty[s], ((it / stages) - 1) & 1)) { fail(); break; }
                     uint8_t* b_stage = stage0 + (size_t)s * stage_bytes + GEMM_A_BYTES;
@@ -315,19 +354,21 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmParams 
                     tma_load_2d(b_stage, &xmap, kb * GEMM_BK, mt * p.bm, &b_full[s]);
                     tma_load_2d(b_stage + b_bytes / 2, &xmap, kb * GEMM_BK + 64, mt * p.bm, &b_full[s]);
                 }
+                u += g.kb1 - g.kb0;
             }
         }
     } else if (warp == 1) {
         // ------------------------------------------------ MMA issuer
         if (lane == 0) {
             int it = 0, local = 0;
-            for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, local++) {
+            for (int u = u0; u < u1 && !*abort_flag; local++) {
+                const GemmSegment g = segment_at(p, u, u1);
                 const int buf = local & 1;
                 if (local >= 2 && !g_mbar_wait(&acc_empty[buf], ((local >> 1) - 1) & 1)) { fail(); break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(buf * p.bm);
                 bool ok = true;
-                for (int kb = 0; kb < p.k_blocks && ok; kb++, it++) {
+                for (int kb = g.kb0; kb < g.kb1 && ok; kb++, it++) {
                     const int s = it % stages;
                     const uint32_t ph = (it / stages) & 1;
                     if (!g_mbar_wait(&b_full[s], ph) || !g_mbar_wait(&a_full[s], ph)) { fail(); ok = false; break; }
@@ -338,28 +379,65 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmParams 
                     for (int kk = 0; kk < 8; kk++) {  // 8 x K16 per stage; spans of 64 k are 16 KB (A) / bm*128 B (B) apart
                         const uint64_t ad = smem_desc_sw128(a_addr + (kk >> 2) * (GEMM_BN * 128) + (kk & 3) * 32);
                         const uint64_t bd = smem_desc_sw128(b_addr + (kk >> 2) * (b_bytes / 2) + (kk & 3) * 32);
-                        tc_mma_f16(d_tmem, ad, bd, p.idesc, (kb | kk) != 0);
+                        tc_mma_f16(d_tmem, ad, bd, p.idesc, ((kb - g.kb0) | kk) != 0);
                     }
                     tc_commit(&s_empty[s]);  // frees the stage when these MMAs have read it
                 }
                 if (!ok) break;
                 tc_commit(&acc_full[buf]);
+                u += g.kb1 - g.kb0;
             }
         }
     } else if (warp >= 4 && warp < 8) {
         // ------------------------------------------------ epilogue (TMEM lane quarter = warp % 4)
         const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;  // weight row inside the 128-row block
         int local = 0;
-        for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, local++) {
+        for (int u = u0; u < u1 && !*abort_flag; local++) {
+            const GemmSegment g = segment_at(p, u, u1);
             const int buf = local & 1;
-            const int nt = tile / p.m_tiles, mt = tile % p.m_tiles;
+            const int nt = g.tile / p.m_tiles, mt = g.tile % p.m_tiles;
             if (!g_mbar_wait(&acc_full[buf], (local >> 1) & 1)) { if (lane == 0) fail(); break; }
             tc_fence_after();
-            const int n = nt * GEMM_BN + quarter * 32 + lane;
+            const int n = nt * GEMM_BN + row;
+            const bool starts = g.kb0 == 0, ends = g.kb1 == p.k_blocks;
+            // Owner of a tile that continues in the following CTAs: their pieces must be complete.
+            // They were computed at the head of those CTAs' shares, long before this tail of mine.
+            int last_cta = (int)blockIdx.x;
+            if (starts && !ends) {
+                const int tile_end = (g.tile + 1) * p.k_blocks;
+                bool gave_up = false;
+                for (int c = (int)blockIdx.x + 1; c < (int)gridDim.x; c++) {
+                    int c0, c1;
+                    cta_units(p, c, c0, c1);
+                    if (c0 >= tile_end) break;
+                    if (c0 == c1) continue;
+                    last_cta = c;
+                    int spins = 0;  // the same quarter of the other CTA wrote the rows this warp is going to add
+                    while (ld_acquire_u32(p.ready + c * 4 + quarter) != p.launch && ++spins < GEMM_WAIT_SPINS) __nanosleep(64);
+                    if (spins >= GEMM_WAIT_SPINS) gave_up = true;
+                }
+                if (gave_up) { if (lane == 0) fail(); break; }
+            }
+            float* mine = p.partial + (size_t)blockIdx.x * p.bm * GEMM_BN;
             for (int c = 0; c < p.bm; c += 32) {
                 uint32_t r[32];
                 tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * p.bm + c), r);
                 const int m0 = mt * p.bm + c;
+                if (!starts) {  // my piece of a tile owned by an earlier CTA: token-major, 128 rows contiguous
+#pragma unroll
+                    for (int j = 0; j < 32; j++) mine[(size_t)(c + j) * GEMM_BN + row] = __uint_as_float(r[j]);
+                    continue;
+                }
+                for (int cc = (int)blockIdx.x + 1; cc <= last_cta; cc++) {  // pieces in CTA order
+                    int c0, c1;
+                    cta_units(p, cc, c0, c1);
+                    if (c0 == c1) continue;
+                    const float* piece = p.partial + (size_t)cc * p.bm * GEMM_BN;
+#pragma unroll
+                    for (int j = 0; j < 32; j++)
+                        r[j] = __float_as_uint(__uint_as_float(r[j]) + __ldcg(piece + (size_t)(c + j) * GEMM_BN + row));
+                }
                 if (n < p.rows) {
 #pragma unroll
                     for (int j = 0; j < 32; j++)
@@ -368,17 +446,24 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmParams 
                 }
             }
             tc_fence_before();
+            if (!starts) {  // publish this warp's 32 rows of the piece
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) st_release_u32(p.ready + blockIdx.x * 4 + quarter, p.launch);
+            }
             __syncwarp();
             if (lane == 0) g_mbar_arrive(&acc_empty[buf]);
+            u += g.kb1 - g.kb0;
         }
     } else {
         // ------------------------------------------------ dequant warps 2, 3, 8..13: one 16-row tile each per stage
         const int dq = (warp < 4) ? warp - 2 : warp - 6;  // 0..7
         int it = 0;
-        for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
-            const int nt = tile / p.m_tiles;
+        for (int u = u0; u < u1 && !*abort_flag;) {
+            const GemmSegment g = segment_at(p, u, u1);
+            const int nt = g.tile / p.m_tiles;
             bool ok = true;
-            for (int kb = 0; kb < p.k_blocks && ok; kb++, it++) {
+            for (int kb = g.kb0; kb < g.kb1 && ok; kb++, it++) {
                 const int s = it % stages;
                 if (it >= stages && !g_mbar_wait(&s_empty[s], ((it / stages) - 1) & 1)) { if (lane == 0) fail(); ok = false; break; }
                 uint8_t* a_stage = stage0 + (size_t)s * stage_bytes;
@@ -393,6 +478,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmParams 
                 if (lane == 0) g_mbar_arrive(&a_full[s]);
             }
             if (!ok) break;
+            u += g.kb1 - g.kb0;
         }
     }
 
@@ -497,7 +583,21 @@ int gemm_launch(Context* c, const GemvCall& call, cudaStream_t s) {
                                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return set_error(c, WF_ERR_CUDA_BASE + 1, "cuTensorMapEncodeTiled failed (%d)", (int)r);
 
-    const int grid = std::min(c->sm_count, p.n_tiles * p.m_tiles);
+    // stream-K shares and the scratch the CTAs hand pieces of cut tiles through
+    const int64_t units = (int64_t)p.n_tiles * p.m_tiles * p.k_blocks;
+    if (units >= (1LL << 31)) return set_error(c, WF_ERR_TOO_LARGE, "GEMM has too many tile steps");
+    const int grid = (int)std::min<int64_t>(c->sm_count, units);
+    p.unit_q = (int)(units / grid);
+    p.unit_r = (int)(units % grid);
+    if (!c->d_gemm_partial) {
+        WF_CUDA(c, cudaMalloc(&c->d_gemm_partial, (size_t)c->sm_count * 256 * GEMM_BN * sizeof(float)));
+        WF_CUDA(c, cudaMalloc(&c->d_gemm_ready, (size_t)c->sm_count * 4 * sizeof(unsigned int)));
+        WF_CUDA(c, cudaMemset(c->d_gemm_ready, 0, (size_t)c->sm_count * 4 * sizeof(unsigned int)));
+    }
+    p.partial = c->d_gemm_partial;
+    p.ready = c->d_gemm_ready;
+    if (++c->gemm_launches == 0) c->gemm_launches = 1;  // 0 means "nothing published"
+    p.launch = c->gemm_launches;
     const size_t smem = 1024 + (size_t)p.stages * stage_bytes;
     cudaError_t e = qt == WF_QTYPE_Q4_0   ? gemm_launch_one<WF_QTYPE_Q4_0>(p, map, grid, smem, s)
                     : qt == WF_QTYPE_Q8_0 ? gemm_launch_one<WF_QTYPE_Q8_0>(p, map, grid, smem, s)

@@ -160,6 +160,8 @@ int wf_destroy(int64_t ctx) {
     if (c->h_stage) cudaFreeHost(c->h_stage);
     if (c->d_stage) cudaFree(c->d_stage);
     if (c->d_x16) cudaFree(c->d_x16);
+    if (c->d_gemm_partial) cudaFree(c->d_gemm_partial);
+    if (c->d_gemm_ready) cudaFree(c->d_gemm_ready);
     cudaFree(c->d_status);
     if (c->d_timing) cudaFree(c->d_timing);
     cudaStreamDestroy(c->stream);
