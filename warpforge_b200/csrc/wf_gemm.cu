@@ -169,42 +169,67 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 }
 
 // ---------------------------------------------------------------- dequantization to fp16
+// A plane word holds the codes of 8 consecutive elements: rotated back by PLANE_ROT, nibble p of the
+// low half is element 2p and nibble p of the high half element 2p + 1.  As fp16 bit patterns
+//   (w & 0x000F000F) | 0x64006400  =  (1024 + e0, 1024 + e1)      codes in mantissa bits 3..0
+//   (w & 0x00F000F0) | 0x54005400  =  (  64 + e2,   64 + e3)      codes in mantissa bits 7..4
+// and the same two masks on the word rotated by a further 8 bits give elements 4..7.  Two rotates and
+// four logic ops per 8 codes; everything after that runs on the half / float pipes.
+struct Codes8 {
+    uint32_t k[2];  // 1024 + code: elements (0,1), (4,5)
+    uint32_t h[2];  // 64 + code:   elements (2,3), (6,7)
+};
+__device__ __forceinline__ Codes8 unpack8(uint32_t w) {
+    const uint32_t a = __funnelshift_r(w, w, PLANE_ROT), b = __funnelshift_r(w, w, PLANE_ROT + 8);
+    Codes8 c;
+    c.k[0] = (a & 0x000F000Fu) | 0x64006400u;
+    c.h[0] = (a & 0x00F000F0u) | 0x54005400u;
+    c.k[1] = (b & 0x000F000Fu) | 0x64006400u;
+    c.h[1] = (b & 0x00F000F0u) | 0x54005400u;
+    return c;
+}
+__device__ __forceinline__ __half2 as_half2(uint32_t v) { return *reinterpret_cast<__half2*>(&v); }
+__device__ __forceinline__ uint32_t as_u32(__half2 v) { return *reinterpret_cast<uint32_t*>(&v); }
+
+// Q4_0: s * (code - 8) with s an fp16 value.  code - 8 is exact in fp16 and the product is rounded
+// once, exactly like the fp32 product rounded to fp16.
+__device__ __forceinline__ uint4 word_to_half8_q4_0(uint32_t w, __half2 s2) {
+    const Codes8 c = unpack8(w);
+    const __half2 m1032 = __float2half2_rn(-1032.f), m72 = __float2half2_rn(-72.f);
+    uint4 o;
+    o.x = as_u32(__hmul2(__hadd2(as_half2(c.k[0]), m1032), s2));
+    o.y = as_u32(__hmul2(__hadd2(as_half2(c.h[0]), m72), s2));
+    o.z = as_u32(__hmul2(__hadd2(as_half2(c.k[1]), m1032), s2));
+    o.w = as_u32(__hmul2(__hadd2(as_half2(c.h[1]), m72), s2));
+    return o;
+}
+// Q8_0: s * (16 (hi - 8) + lo): the integer is exact in fp16 (|q| <= 128), one rounding in the product.
+__device__ __forceinline__ uint4 words_to_half8_q8(uint32_t wh, uint32_t wl, __half2 s2) {
+    const Codes8 h = unpack8(wh), l = unpack8(wl);
+    const __half2 m1032 = __float2half2_rn(-1032.f), m72 = __float2half2_rn(-72.f);
+    const __half2 m1024 = __float2half2_rn(-1024.f), m64 = __float2half2_rn(-64.f), sixteen = __float2half2_rn(16.f);
+    uint4 o;
+    o.x = as_u32(__hmul2(__hfma2(sixteen, __hadd2(as_half2(h.k[0]), m1032), __hadd2(as_half2(l.k[0]), m1024)), s2));
+    o.y = as_u32(__hmul2(__hfma2(sixteen, __hadd2(as_half2(h.h[0]), m72), __hadd2(as_half2(l.h[0]), m64)), s2));
+    o.z = as_u32(__hmul2(__hfma2(sixteen, __hadd2(as_half2(h.k[1]), m1032), __hadd2(as_half2(l.k[1]), m1024)), s2));
+    o.w = as_u32(__hmul2(__hfma2(sixteen, __hadd2(as_half2(h.h[1]), m72), __hadd2(as_half2(l.h[1]), m64)), s2));
+    return o;
+}
+// Q4_K: a * code + b in fp32 (a = d * sc and b = -dmin * m are exact in fp32), rounded once to fp16.
 __device__ __forceinline__ uint32_t pack_half2(float a, float b) {
     __half2 h = __floats2half2_rn(a, b);
     return *reinterpret_cast<uint32_t*>(&h);
 }
-// the two codes of nibble pair S of a plane word, as floats (exact)
-template <int S>
-__device__ __forceinline__ void nib2_f32(uint32_t w, float& lo, float& hi) {
-    const uint32_t r = (S == 0) ? w : __funnelshift_r(w, w, 4 * S);
-    const uint32_t v = (r & 0x00780078u) | 0x41804180u;  // bf16x2 (16 + code)
-    lo = __uint_as_float(v << 16);                        // 16 + code, the caller folds the 16 away
-    hi = __uint_as_float(v & 0xFFFF0000u);
-}
-// 8 consecutive elements of one plane word -> 8 fp16 values = a * code + b
 __device__ __forceinline__ uint4 word_to_half8(uint32_t w, float a, float b) {
-    b = fmaf(-16.f, a, b);  // the unpacked values are 16 + code
-    float c[8];
-    nib2_f32<0>(w, c[0], c[1]);
-    nib2_f32<1>(w, c[2], c[3]);
-    nib2_f32<2>(w, c[4], c[5]);
-    nib2_f32<3>(w, c[6], c[7]);
+    const Codes8 c = unpack8(w);
+    const float bk = fmaf(-1024.f, a, b), bh = fmaf(-64.f, a, b);  // the unpacked values carry 1024 / 64
+    const float2 f0 = __half22float2(as_half2(c.k[0])), f1 = __half22float2(as_half2(c.h[0]));
+    const float2 f2 = __half22float2(as_half2(c.k[1])), f3 = __half22float2(as_half2(c.h[1]));
     uint4 o;
-    o.x = pack_half2(fmaf(a, c[0], b), fmaf(a, c[1], b));
-    o.y = pack_half2(fmaf(a, c[2], b), fmaf(a, c[3], b));
-    o.z = pack_half2(fmaf(a, c[4], b), fmaf(a, c[5], b));
-    o.w = pack_half2(fmaf(a, c[6], b), fmaf(a, c[7], b));
-    return o;
-}
-__device__ __forceinline__ uint4 words_to_half8_q8(uint32_t wh, uint32_t wl, float s) {
-    float h[8], l[8];
-    nib2_f32<0>(wh, h[0], h[1]); nib2_f32<1>(wh, h[2], h[3]); nib2_f32<2>(wh, h[4], h[5]); nib2_f32<3>(wh, h[6], h[7]);
-    nib2_f32<0>(wl, l[0], l[1]); nib2_f32<1>(wl, l[2], l[3]); nib2_f32<2>(wl, l[4], l[5]); nib2_f32<3>(wl, l[6], l[7]);
-    float v[8];
-#pragma unroll
-    for (int i = 0; i < 8; i++) v[i] = s * (fmaf(16.f, h[i], l[i]) - 400.f);  // 16(hi-8)+lo exactly, then one multiply
-    uint4 o;
-    o.x = pack_half2(v[0], v[1]); o.y = pack_half2(v[2], v[3]); o.z = pack_half2(v[4], v[5]); o.w = pack_half2(v[6], v[7]);
+    o.x = pack_half2(fmaf(a, f0.x, bk), fmaf(a, f0.y, bk));
+    o.y = pack_half2(fmaf(a, f1.x, bh), fmaf(a, f1.y, bh));
+    o.z = pack_half2(fmaf(a, f2.x, bk), fmaf(a, f2.y, bk));
+    o.w = pack_half2(fmaf(a, f3.x, bh), fmaf(a, f3.y, bh));
     return o;
 }
 
@@ -223,14 +248,13 @@ __device__ __forceinline__ void dequant_rowtile(const uint8_t* tile, int kb, uin
         for (int h = 0; h < 2; h++) {
             const uint4 c = __ldg(reinterpret_cast<const uint4*>(tile + h * 512 + lane * 16));
             const uint2 sc = __ldg(reinterpret_cast<const uint2*>(tile + Tile<WF_QTYPE_Q4_0>::SCALE_OFF + g * 16 + h * 8));
-            const float2 s01 = __half22float2(*reinterpret_cast<const __half2*>(&sc.x));
-            const float2 s23 = __half22float2(*reinterpret_cast<const __half2*>(&sc.y));
-            const float s[4] = {s01.x, s01.y, s23.x, s23.y};
+            const __half2 s01 = as_half2(sc.x), s23 = as_half2(sc.y);  // block scales 0..3 of this row, fp16
+            const __half2 s[4] = {__low2half2(s01), __high2half2(s01), __low2half2(s23), __high2half2(s23)};
             const uint32_t w[4] = {c.x, c.y, c.z, c.w};
             const int r = rt16 * 16 + g + 8 * h;
 #pragma unroll
             for (int j = 0; j < 4; j++)  // value = s * (code - 8)
-                *reinterpret_cast<uint4*>(a_stage + a_chunk_off(r, j * 4 + q)) = word_to_half8(w[j], s[j], -8.f * s[j]);
+                *reinterpret_cast<uint4*>(a_stage + a_chunk_off(r, j * 4 + q)) = word_to_half8_q4_0(w[j], s[j]);
         }
     } else if (QT == WF_QTYPE_Q8_0) {
         (void)kb;
@@ -239,9 +263,8 @@ __device__ __forceinline__ void dequant_rowtile(const uint8_t* tile, int kb, uin
             const uint4 ch = __ldg(reinterpret_cast<const uint4*>(tile + h * 512 + lane * 16));
             const uint4 cl = __ldg(reinterpret_cast<const uint4*>(tile + PLANE_BYTES + h * 512 + lane * 16));
             const uint2 sc = __ldg(reinterpret_cast<const uint2*>(tile + Tile<WF_QTYPE_Q8_0>::SCALE_OFF + g * 16 + h * 8));
-            const float2 s01 = __half22float2(*reinterpret_cast<const __half2*>(&sc.x));
-            const float2 s23 = __half22float2(*reinterpret_cast<const __half2*>(&sc.y));
-            const float s[4] = {s01.x, s01.y, s23.x, s23.y};
+            const __half2 s01 = as_half2(sc.x), s23 = as_half2(sc.y);
+            const __half2 s[4] = {__low2half2(s01), __high2half2(s01), __low2half2(s23), __high2half2(s23)};
             const uint32_t wh[4] = {ch.x, ch.y, ch.z, ch.w}, wl[4] = {cl.x, cl.y, cl.z, cl.w};
             const int r = rt16 * 16 + g + 8 * h;
 #pragma unroll
@@ -419,7 +442,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmParams 
                 }
                 if (gave_up) { if (lane == 0) fail(); break; }
             }
-            float* mine = p.partial + (size_t)blockIdx.x * p.bm * GEMM_BN;
+            // room for 256 tokens per CTA: columns are moved 32 at a time, also past a BM that is not a multiple of 32
+            float* mine = p.partial + (size_t)blockIdx.x * 256 * GEMM_BN;
             for (int c = 0; c < p.bm; c += 32) {
                 uint32_t r[32];
                 tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * p.bm + c), r);
@@ -433,7 +457,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmParams 
                     int c0, c1;
                     cta_units(p, cc, c0, c1);
                     if (c0 == c1) continue;
-                    const float* piece = p.partial + (size_t)cc * p.bm * GEMM_BN;
+                    const float* piece = p.partial + (size_t)cc * 256 * GEMM_BN;
 #pragma unroll
                     for (int j = 0; j < 32; j++)
                         r[j] = __float_as_uint(__uint_as_float(r[j]) + __ldcg(piece + (size_t)(c + j) * GEMM_BN + row));

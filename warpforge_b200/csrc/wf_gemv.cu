@@ -205,23 +205,17 @@ int gemv_prepare_stream(Context* c, cudaStream_t s) {
     return WF_OK;
 }
 
-int gemv_launch(Context* c, const GemvCall& call, cudaStream_t s) {
+// One launch per pass of up to `per_pass` tokens.  `slots` are the fix-up slots to use;
+// clear_slots: zero them on the stream before every launch (for slots that may hold leftovers).
+static int launch_passes(Context* c, const GemvCall& call, cudaStream_t s, uint2* slots, bool clear_slots,
+                         unsigned long long* timing, const char* what) {
     const Weight& w = *call.w;
     const int qt = w.g.qtype;
     const int kp = (int)w.g.kt * tile_k(qt);
     const int per_pass = gemv_max_tokens_per_pass(w, call.x_dtype);
-    if (per_pass < 1)
-        return set_error(c, WF_ERR_TOO_LARGE, "K=%lld needs more shared memory than one SM has", (long long)w.g.k);
     const int64_t total = w.g.rt * w.g.kt;
-    if (total >= (1LL << 31)) return set_error(c, WF_ERR_TOO_LARGE, "weight has too many tiles");
     int grid = c->sm_count;
     if ((int64_t)grid > total) grid = (int)total;
-    if (grid < 1) return WF_OK;
-
-    int prc = gemv_prepare_stream(c, s);
-    if (prc != WF_OK) return prc;
-    GemvScratch& sc = c->gemv_scratch[s];
-
     const size_t esz = call.x_dtype == WF_DTYPE_F32 ? 4 : 2;
     int max_rounds = (int)((total / grid + 1 + GEMV_WARPS - 1) / GEMV_WARPS);
     if (const char* cap = getenv("WF_GEMV_MAX_STAGES")) max_rounds = std::max(1, std::min(max_rounds, atoi(cap)));
@@ -230,9 +224,9 @@ int gemv_launch(Context* c, const GemvCall& call, cudaStream_t s) {
         p.tiles = w.d_tiles;
         p.x = static_cast<const uint8_t*>(call.d_x) + (size_t)m0 * w.g.k * esz;
         p.y = call.d_y + m0 * call.ldy;
-        p.scratch = sc.d_slots;
+        p.scratch = slots;
         p.status = c->d_status;
-        p.timing = c->salt >= 2 ? c->d_timing : nullptr;
+        p.timing = timing;
         p.ldy = call.ldy;
         p.col0 = call.col0;
         p.ldx = w.g.k;
@@ -246,6 +240,7 @@ int gemv_launch(Context* c, const GemvCall& call, cudaStream_t s) {
         p.x_f32 = call.x_dtype == WF_DTYPE_F32;
         const int xcols = p.x_f32 ? 3 * p.m : p.m;
         const size_t stage = (size_t)GEMV_WARPS * tile_bytes(qt);
+        if (clear_slots) WF_CUDA(c, cudaMemsetAsync(slots, 0, (size_t)grid * 128 * sizeof(uint2), s));
         cudaError_t e;
         if (xcols == 1) {
             p.stages = std::min(gemv_stages<1>(qt, kp, xcols), std::max(max_rounds, 1));
@@ -254,10 +249,26 @@ int gemv_launch(Context* c, const GemvCall& call, cudaStream_t s) {
             p.stages = std::min(gemv_stages<8>(qt, kp, xcols), std::max(max_rounds, 1));
             e = launch_qt<8>(qt, p, grid, gemv_fixed_smem<8>(kp, xcols, &p.sx) + p.stages * stage, s);
         }
-        if (e != cudaSuccess) return cuda_status(c, e, "gemv launch");
+        if (e != cudaSuccess) return cuda_status(c, e, what);
         c->launches++;
     }
     return WF_OK;
+}
+
+static int check_shape(Context* c, const Weight& w, int x_dtype) {
+    if (gemv_max_tokens_per_pass(w, x_dtype) < 1)
+        return set_error(c, WF_ERR_TOO_LARGE, "K=%lld needs more shared memory than one SM has", (long long)w.g.k);
+    if (w.g.rt * w.g.kt >= (1LL << 31)) return set_error(c, WF_ERR_TOO_LARGE, "weight has too many tiles");
+    return WF_OK;
+}
+
+int gemv_launch(Context* c, const GemvCall& call, cudaStream_t s) {
+    int rc = check_shape(c, *call.w, call.x_dtype);
+    if (rc != WF_OK) return rc;
+    if (call.w->g.rt * call.w->g.kt < 1) return WF_OK;
+    rc = gemv_prepare_stream(c, s);
+    if (rc != WF_OK) return rc;
+    return launch_passes(c, call, s, c->gemv_scratch[s].d_slots, false, c->salt >= 2 ? c->d_timing : nullptr, "gemv launch");
 }
 
 // ---------------------------------------------------------------- allocation-free variant
@@ -289,60 +300,16 @@ static int noalloc_slots_for_current_device(Context* c, uint2** out) {
 // come from the static array above and are cleared on the stream before every launch,
 // because the array keeps whatever the previous call (possibly a failed one) left in it.
 int gemv_launch_noalloc(Context* c, const GemvCall& call, cudaStream_t s) {
-    const Weight& w = *call.w;
-    const int qt = w.g.qtype;
-    const int kp = (int)w.g.kt * tile_k(qt);
-    const int per_pass = gemv_max_tokens_per_pass(w, call.x_dtype);
-    if (per_pass < 1)
-        return set_error(c, WF_ERR_TOO_LARGE, "K=%lld needs more shared memory than one SM has", (long long)w.g.k);
-    const int64_t total = w.g.rt * w.g.kt;
-    if (total >= (1LL << 31)) return set_error(c, WF_ERR_TOO_LARGE, "weight has too many tiles");
+    int rc = check_shape(c, *call.w, call.x_dtype);
+    if (rc != WF_OK) return rc;
     if (c->sm_count > GEMV_NOALLOC_MAX_CTAS)
         return set_error(c, WF_ERR_TOO_LARGE, "device has %d SMs; the static fix-up array covers at most %d", c->sm_count,
                          GEMV_NOALLOC_MAX_CTAS);
-    int grid = c->sm_count;
-    if ((int64_t)grid > total) grid = (int)total;
-    if (grid < 1) return WF_OK;
+    if (call.w->g.rt * call.w->g.kt < 1) return WF_OK;
     uint2* slots = nullptr;
-    int rc = noalloc_slots_for_current_device(c, &slots);
+    rc = noalloc_slots_for_current_device(c, &slots);
     if (rc != WF_OK) return rc;
-
-    const size_t esz = call.x_dtype == WF_DTYPE_F32 ? 4 : 2;
-    const int max_rounds = (int)((total / grid + 1 + GEMV_WARPS - 1) / GEMV_WARPS);
-    for (int64_t m0 = 0; m0 < call.m; m0 += per_pass) {
-        GemvParams p{};
-        p.tiles = w.d_tiles;
-        p.x = static_cast<const uint8_t*>(call.d_x) + (size_t)m0 * w.g.k * esz;
-        p.y = call.d_y + m0 * call.ldy;
-        p.scratch = slots;
-        p.status = c->d_status;
-        p.timing = nullptr;
-        p.ldy = call.ldy;
-        p.col0 = call.col0;
-        p.ldx = w.g.k;
-        p.rows = (int)w.g.rows;
-        p.k = (int)w.g.k;
-        p.kt = (int)w.g.kt;
-        p.rt = (int)w.g.rt;
-        p.chunk_q = (int)(total / grid);
-        p.chunk_r = (int)(total % grid);
-        p.m = (int)((call.m - m0) < per_pass ? (call.m - m0) : per_pass);
-        p.x_f32 = call.x_dtype == WF_DTYPE_F32;
-        const int xcols = p.x_f32 ? 3 * p.m : p.m;
-        const size_t stage = (size_t)GEMV_WARPS * tile_bytes(qt);
-        WF_CUDA(c, cudaMemsetAsync(slots, 0, (size_t)grid * 128 * sizeof(uint2), s));
-        cudaError_t e;
-        if (xcols == 1) {
-            p.stages = std::min(gemv_stages<1>(qt, kp, xcols), std::max(max_rounds, 1));
-            e = launch_qt<1>(qt, p, grid, gemv_fixed_smem<1>(kp, xcols, &p.sx) + p.stages * stage, s);
-        } else {
-            p.stages = std::min(gemv_stages<8>(qt, kp, xcols), std::max(max_rounds, 1));
-            e = launch_qt<8>(qt, p, grid, gemv_fixed_smem<8>(kp, xcols, &p.sx) + p.stages * stage, s);
-        }
-        if (e != cudaSuccess) return cuda_status(c, e, "gemv launch (no-alloc)");
-        c->launches++;
-    }
-    return WF_OK;
+    return launch_passes(c, call, s, slots, true, nullptr, "gemv launch (no-alloc)");
 }
 
 }  // namespace wf
