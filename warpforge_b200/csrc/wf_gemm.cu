@@ -238,59 +238,96 @@ __device__ __forceinline__ uint32_t a_chunk_off(int r, int c) {
     return (uint32_t)((c >> 3) * (GEMM_BN * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4));
 }
 
-// One warp dequantizes one 16-row tile x 128 k of the stage: rows rt16*16 .. +15.
-template <int QT>
-__device__ __forceinline__ void dequant_rowtile(const uint8_t* tile, int kb, uint8_t* a_stage, int rt16, int lane) {
-    const int g = lane >> 2, q = lane & 3;
-    if (QT == WF_QTYPE_Q4_0) {
+// One warp dequantizes one 16-row tile x 128 k of the stage: rows rt16*16 .. +15.  The work is split
+// into load (global memory -> registers) and store (registers -> fp16 in the swizzled stage): the
+// weights come from HBM, and the loads of the next step are issued into a second register set
+// before the current step is converted, so their latency is off the stage hand-over path.
+template <int QT> struct DequantRegs;
+
+template <> struct DequantRegs<WF_QTYPE_Q4_0> {
+    uint4 c[2];
+    uint2 sc[2];
+    __device__ __forceinline__ void load(const uint8_t* tile, int kb, int lane) {
         (void)kb;
+        const int g = lane >> 2;
 #pragma unroll
         for (int h = 0; h < 2; h++) {
-            const uint4 c = __ldg(reinterpret_cast<const uint4*>(tile + h * 512 + lane * 16));
-            const uint2 sc = __ldg(reinterpret_cast<const uint2*>(tile + Tile<WF_QTYPE_Q4_0>::SCALE_OFF + g * 16 + h * 8));
-            const __half2 s01 = as_half2(sc.x), s23 = as_half2(sc.y);  // block scales 0..3 of this row, fp16
+            c[h] = __ldg(reinterpret_cast<const uint4*>(tile + h * 512 + lane * 16));
+            sc[h] = __ldg(reinterpret_cast<const uint2*>(tile + Tile<WF_QTYPE_Q4_0>::SCALE_OFF + g * 16 + h * 8));
+        }
+    }
+    __device__ __forceinline__ void store(uint8_t* a_stage, int rt16, int lane) const {
+        const int g = lane >> 2, q = lane & 3;
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const __half2 s01 = as_half2(sc[h].x), s23 = as_half2(sc[h].y);  // block scales 0..3 of this row, fp16
             const __half2 s[4] = {__low2half2(s01), __high2half2(s01), __low2half2(s23), __high2half2(s23)};
-            const uint32_t w[4] = {c.x, c.y, c.z, c.w};
+            const uint32_t w[4] = {c[h].x, c[h].y, c[h].z, c[h].w};
             const int r = rt16 * 16 + g + 8 * h;
 #pragma unroll
             for (int j = 0; j < 4; j++)  // value = s * (code - 8)
                 *reinterpret_cast<uint4*>(a_stage + a_chunk_off(r, j * 4 + q)) = word_to_half8_q4_0(w[j], s[j]);
         }
-    } else if (QT == WF_QTYPE_Q8_0) {
+    }
+};
+
+template <> struct DequantRegs<WF_QTYPE_Q8_0> {
+    uint4 ch[2], cl[2];
+    uint2 sc[2];
+    __device__ __forceinline__ void load(const uint8_t* tile, int kb, int lane) {
         (void)kb;
+        const int g = lane >> 2;
 #pragma unroll
         for (int h = 0; h < 2; h++) {
-            const uint4 ch = __ldg(reinterpret_cast<const uint4*>(tile + h * 512 + lane * 16));
-            const uint4 cl = __ldg(reinterpret_cast<const uint4*>(tile + PLANE_BYTES + h * 512 + lane * 16));
-            const uint2 sc = __ldg(reinterpret_cast<const uint2*>(tile + Tile<WF_QTYPE_Q8_0>::SCALE_OFF + g * 16 + h * 8));
-            const __half2 s01 = as_half2(sc.x), s23 = as_half2(sc.y);
+            ch[h] = __ldg(reinterpret_cast<const uint4*>(tile + h * 512 + lane * 16));
+            cl[h] = __ldg(reinterpret_cast<const uint4*>(tile + PLANE_BYTES + h * 512 + lane * 16));
+            sc[h] = __ldg(reinterpret_cast<const uint2*>(tile + Tile<WF_QTYPE_Q8_0>::SCALE_OFF + g * 16 + h * 8));
+        }
+    }
+    __device__ __forceinline__ void store(uint8_t* a_stage, int rt16, int lane) const {
+        const int g = lane >> 2, q = lane & 3;
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const __half2 s01 = as_half2(sc[h].x), s23 = as_half2(sc[h].y);
             const __half2 s[4] = {__low2half2(s01), __high2half2(s01), __low2half2(s23), __high2half2(s23)};
-            const uint32_t wh[4] = {ch.x, ch.y, ch.z, ch.w}, wl[4] = {cl.x, cl.y, cl.z, cl.w};
+            const uint32_t wh[4] = {ch[h].x, ch[h].y, ch[h].z, ch[h].w}, wl[4] = {cl[h].x, cl[h].y, cl[h].z, cl[h].w};
             const int r = rt16 * 16 + g + 8 * h;
 #pragma unroll
             for (int j = 0; j < 4; j++)
                 *reinterpret_cast<uint4*>(a_stage + a_chunk_off(r, j * 4 + q)) = words_to_half8_q8(wh[j], wl[j], s[j]);
         }
-    } else {  // Q4_K: the stage is one half (plane kb & 1) of a 256-k tile
+    }
+};
+
+template <> struct DequantRegs<WF_QTYPE_Q4_K> {  // the stage is one half (plane kb & 1) of a 256-k tile
+    uint4 c[2];
+    uint32_t dd[2], scw[2], mnw[2];
+    __device__ __forceinline__ void load(const uint8_t* tile, int kb, int lane) {
         using T = Tile<WF_QTYPE_Q4_K>;
-        const int pl = kb & 1;
+        const int g = lane >> 2, pl = kb & 1;
 #pragma unroll
         for (int h = 0; h < 2; h++) {
-            const uint4 c = __ldg(reinterpret_cast<const uint4*>(tile + pl * PLANE_BYTES + h * 512 + lane * 16));
-            const uint32_t dd = __ldg(reinterpret_cast<const uint32_t*>(tile + T::D_OFF + g * 8 + h * 4));
-            const uint32_t scw = __ldg(reinterpret_cast<const uint32_t*>(tile + T::SC_OFF + g * 16 + h * 8 + pl * 4));
-            const uint32_t mnw = __ldg(reinterpret_cast<const uint32_t*>(tile + T::MN_OFF + g * 16 + h * 8 + pl * 4));
-            const float2 d = __half22float2(*reinterpret_cast<const __half2*>(&dd));  // (d, dmin)
-            const uint32_t w[4] = {c.x, c.y, c.z, c.w};
+            c[h] = __ldg(reinterpret_cast<const uint4*>(tile + pl * PLANE_BYTES + h * 512 + lane * 16));
+            dd[h] = __ldg(reinterpret_cast<const uint32_t*>(tile + T::D_OFF + g * 8 + h * 4));
+            scw[h] = __ldg(reinterpret_cast<const uint32_t*>(tile + T::SC_OFF + g * 16 + h * 8 + pl * 4));
+            mnw[h] = __ldg(reinterpret_cast<const uint32_t*>(tile + T::MN_OFF + g * 16 + h * 8 + pl * 4));
+        }
+    }
+    __device__ __forceinline__ void store(uint8_t* a_stage, int rt16, int lane) const {
+        const int g = lane >> 2, q = lane & 3;
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const float2 d = __half22float2(as_half2(dd[h]));  // (d, dmin)
+            const uint32_t w[4] = {c[h].x, c[h].y, c[h].z, c[h].w};
             const int r = rt16 * 16 + g + 8 * h;
 #pragma unroll
             for (int j = 0; j < 4; j++) {  // value = (d * sc) * code - dmin * m
-                const float a = d.x * (float)((scw >> (8 * j)) & 0xFF), b = -(d.y * (float)((mnw >> (8 * j)) & 0xFF));
+                const float a = d.x * (float)((scw[h] >> (8 * j)) & 0xFF), b = -(d.y * (float)((mnw[h] >> (8 * j)) & 0xFF));
                 *reinterpret_cast<uint4*>(a_stage + a_chunk_off(r, j * 4 + q)) = word_to_half8(w[j], a, b);
             }
         }
     }
-}
+};
 
 // ---------------------------------------------------------------- activation pre-pass
 // One CTA per token row: x16[row] = fp16(x[row] * 2^s) with s chosen so the largest magnitude lands in
@@ -481,28 +518,36 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmParams 
         }
     } else {
         // ------------------------------------------------ dequant warps 2, 3, 8..13: one 16-row tile each per stage
-        const int dq = (warp < 4) ? warp - 2 : warp - 6;  // 0..7
-        int it = 0;
-        for (int u = u0; u < u1 && !*abort_flag;) {
-            const GemmSegment g = segment_at(p, u, u1);
-            const int nt = g.tile / p.m_tiles;
-            bool ok = true;
-            for (int kb = g.kb0; kb < g.kb1 && ok; kb++, it++) {
-                const int s = it % stages;
-                if (it >= stages && !g_mbar_wait(&s_empty[s], ((it / stages) - 1) & 1)) { if (lane == 0) fail(); ok = false; break; }
-                uint8_t* a_stage = stage0 + (size_t)s * stage_bytes;
-                {
-                    const int rt16 = dq;  // 16-row tile inside the 128-row block
-                    const int64_t wrt = (int64_t)nt * (GEMM_BN / 16) + rt16;  // weight row-tile
-                    const uint8_t* wt = p.tiles + (wrt * p.kt_w + kb / KB_PER_WTILE) * (int64_t)TILE_BYTES;
-                    dequant_rowtile<QT>(wt, kb, a_stage, rt16, lane);
-                }
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the tensor core
-                __syncwarp();
-                if (lane == 0) g_mbar_arrive(&a_full[s]);
+        const int dq = (warp < 4) ? warp - 2 : warp - 6;  // 0..7 = 16-row tile inside the 128-row block
+        // weight tile of unit u (tile-major, k-block minor), this warp's 16-row tile of the 128-row block
+        auto weight_tile = [&](int u) {
+            const int tile = u / p.k_blocks, kb = u - tile * p.k_blocks;
+            const int64_t wrt = (int64_t)(tile / p.m_tiles) * (GEMM_BN / 16) + dq;
+            return p.tiles + (wrt * p.kt_w + kb / KB_PER_WTILE) * (int64_t)TILE_BYTES;
+        };
+        // one step: wait for the stage, convert the registers loaded one step ago, hand the stage over
+        auto finish_step = [&](const DequantRegs<QT>& regs, int it) {
+            const int s = it % stages;
+            if (it >= stages && !g_mbar_wait(&s_empty[s], ((it / stages) - 1) & 1)) {
+                if (lane == 0) fail();
+                return false;
             }
-            if (!ok) break;
-            u += g.kb1 - g.kb0;
+            regs.store(stage0 + (size_t)s * stage_bytes, dq, lane);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the tensor core
+            __syncwarp();
+            if (lane == 0) g_mbar_arrive(&a_full[s]);
+            return true;
+        };
+        // two register sets in turn: the loads of step u + 1 are in flight while step u is converted
+        DequantRegs<QT> ra, rb;
+        int it = 0;
+        if (u0 < u1) ra.load(weight_tile(u0), u0 % p.k_blocks, lane);
+        for (int u = u0; u < u1 && !*abort_flag; u += 2, it += 2) {
+            if (u + 1 < u1) rb.load(weight_tile(u + 1), (u + 1) % p.k_blocks, lane);
+            if (!finish_step(ra, it)) break;
+            if (u + 1 >= u1) break;
+            if (u + 2 < u1) ra.load(weight_tile(u + 2), (u + 2) % p.k_blocks, lane);
+            if (!finish_step(rb, it + 1)) break;
         }
     }
 
