@@ -378,7 +378,8 @@ int wf_program_create(int64_t ctx, int n_ops, const int64_t* weights, const int6
     fixed = (fixed + 127) & ~(size_t)127;
     const size_t stage = (size_t)GEMV_WARPS * tile_bytes(qt);
     if (fixed + 2 * stage > 227 * 1024) return set_error(c, WF_ERR_TOO_LARGE, "K=%d with %lld tokens does not fit one SM's shared memory", kp_max, (long long)m);
-    const int stages = (int)std::min<size_t>((227 * 1024 - fixed) / stage, GEMV_MAX_STAGES);
+    // the ring also carries the next projections' weights across barriers: a little deeper than the single-op kernel's
+    const int stages = (int)std::min<size_t>((227 * 1024 - fixed) / stage, GEMV_USE_STAGES + 2);
 
     Program* pr = new Program();
     pr->ctx = c;

