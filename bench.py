@@ -38,9 +38,9 @@ WORKLOAD = ("BASELINE config 4: 7B-shape Llama decode, 224 Q4_0 projections (32 
 
 
 # DRAM traffic of the decode kernels, from an ncu capture of two layers of this workload
-# (dram__bytes_read.sum + dram__bytes_write.sum = 232.25 MB for 2 layers, profiles/gemv_program_q4_0_decode_7b.md);
+# (dram__bytes_read.sum + dram__bytes_write.sum = 231.63 MB for 2 layers, profiles/gemv_program_q4_0_decode_7b.md);
 # traffic grows in proportion to the layers run and splits evenly over row shards.
-NCU_TRAFFIC_BYTES_PER_LAYER = 232.25e6 / 2
+NCU_TRAFFIC_BYTES_PER_LAYER = 231.63e6 / 2
 
 
 def measured_peaks():
