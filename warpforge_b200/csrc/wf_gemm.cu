@@ -332,23 +332,60 @@ template <> struct DequantRegs<WF_QTYPE_Q4_K> {  // the stage is one half (plane
 // ---------------------------------------------------------------- activation pre-pass
 // One CTA per token row: x16[row] = fp16(x[row] * 2^s) with s chosen so the largest magnitude lands in
 // [2^14, 2^15); unscale[row] = 2^-s.  bf16 -> fp16 is exact whenever the scaled value is a normal fp16.
-__global__ void x_to_f16_kernel(const uint16_t* __restrict__ x, __half* __restrict__ x16, float* __restrict__ unscale, int k) {
+// The row is read once: every thread keeps its 16-byte pieces in registers between the exponent scan
+// and the conversion (up to 4 pieces = K <= 8192 at 256 threads; longer rows re-read the rest).
+constexpr int XPRE_THREADS = 256, XPRE_KEEP = 4;
+__global__ void __launch_bounds__(XPRE_THREADS) x_to_f16_kernel(const uint16_t* __restrict__ x, __half* __restrict__ x16,
+                                                                float* __restrict__ unscale, int k) {
     __shared__ int s_emax;
-    const uint16_t* row = x + (size_t)blockIdx.x * k;
+    const uint4* row = reinterpret_cast<const uint4*>(x + (size_t)blockIdx.x * k);  // k is a multiple of 8
+    uint4* out = reinterpret_cast<uint4*>(x16 + (size_t)blockIdx.x * k);
+    const int pieces = k >> 3;
     if (threadIdx.x == 0) s_emax = 0;
     __syncthreads();
+    auto emax_of = [](uint4 v) {
+        int m = 0;
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int e0 = (w[i] >> 7) & 0xFF, e1 = (w[i] >> 23) & 0xFF;  // bf16 biased exponents
+            m = max(m, e0 == 0xFF ? 0 : e0);                              // Inf / NaN do not drive the scale
+            m = max(m, e1 == 0xFF ? 0 : e1);
+        }
+        return m;
+    };
+    uint4 keep[XPRE_KEEP];
     int emax = 0;
-    for (int i = threadIdx.x; i < k; i += blockDim.x) {
-        const int e = (row[i] >> 7) & 0xFF;              // bf16 biased exponent
-        emax = max(emax, e == 0xFF ? 0 : e);              // Inf / NaN do not drive the scale
+#pragma unroll
+    for (int u = 0; u < XPRE_KEEP; u++) {
+        const int i = threadIdx.x + u * XPRE_THREADS;
+        keep[u] = i < pieces ? __ldg(row + i) : make_uint4(0, 0, 0, 0);
+        emax = max(emax, emax_of(keep[u]));
     }
-    atomicMax(&s_emax, emax);
+    for (int i = threadIdx.x + XPRE_KEEP * XPRE_THREADS; i < pieces; i += XPRE_THREADS) emax = max(emax, emax_of(__ldg(row + i)));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) emax = max(emax, __shfl_xor_sync(0xFFFFFFFFu, emax, o));
+    if ((threadIdx.x & 31) == 0) atomicMax(&s_emax, emax);
     __syncthreads();
     emax = s_emax;
     const int shift = emax == 0 ? 0 : (127 + 14) - emax;  // multiply by 2^shift
     const float scale = __uint_as_float((uint32_t)min(max(127 + shift, 1), 254) << 23);
-    for (int i = threadIdx.x; i < k; i += blockDim.x)
-        x16[(size_t)blockIdx.x * k + i] = __float2half_rn(__uint_as_float((uint32_t)row[i] << 16) * scale);
+    auto convert = [scale](uint4 v) {
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const __half2 h = __floats2half2_rn(__uint_as_float(w[i] << 16) * scale, __uint_as_float(w[i] & 0xFFFF0000u) * scale);
+            o[i] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+        return make_uint4(o[0], o[1], o[2], o[3]);
+    };
+#pragma unroll
+    for (int u = 0; u < XPRE_KEEP; u++) {
+        const int i = threadIdx.x + u * XPRE_THREADS;
+        if (i < pieces) out[i] = convert(keep[u]);
+    }
+    for (int i = threadIdx.x + XPRE_KEEP * XPRE_THREADS; i < pieces; i += XPRE_THREADS) out[i] = convert(__ldg(row + i));
     if (threadIdx.x == 0) unscale[blockIdx.x] = __uint_as_float((uint32_t)min(max(127 - shift, 1), 254) << 23);
 }
 
@@ -637,7 +674,7 @@ int gemm_launch(Context* c, const GemvCall& call, cudaStream_t s) {
     }
     __half* x16 = static_cast<__half*>(c->d_x16);
     float* unscale = reinterpret_cast<float*>(static_cast<uint8_t*>(c->d_x16) + ((call.m * w.g.k * 2 + 255) & ~255LL));
-    x_to_f16_kernel<<<(unsigned)call.m, 256, 0, s>>>(static_cast<const uint16_t*>(call.d_x), x16, unscale, (int)w.g.k);
+    x_to_f16_kernel<<<(unsigned)call.m, XPRE_THREADS, 0, s>>>(static_cast<const uint16_t*>(call.d_x), x16, unscale, (int)w.g.k);
     WF_CUDA(c, cudaGetLastError());
     c->launches++;
     p.row_unscale = unscale;
