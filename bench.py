@@ -3,13 +3,13 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
-Workload (BASELINE config 4): the 224 Q4_0 projections of a 7B-shape Llama decoder, batch 1,
+Workload (benchmark config 4): the 224 Q4_0 projections of a 7B-shape Llama decoder, batch 1,
 every weight a distinct buffer (3.64 GB per token, far larger than L2, so every step reads
 HBM cold).  One step = one token = all projections in layer order, recorded once as a CUDA
 graph; with N > 1 ranks the weights are row-sharded and every projection is followed by the
 all-gather of its shards over NCCL (strong scaling: the same token stream on more GPUs).
 The dominant kernel is the Q4_0 decode GEMV, so `roofline` is the headline "Q4_0 GEMV HBM
-GB/s (% of peak)"; `gemv_sweep` adds BASELINE config 2 (the [11008x4096] / [4096x11008]
+GB/s (% of peak)"; `gemv_sweep` adds benchmark config 2 (the [11008x4096] / [4096x11008]
 sweep at batch 1, 4, 8), timed over 12 rotating weight copies (300 MB, larger than L2).
 
 Inputs are seeded synthetic GGUF blocks with the configs' value distributions; there is no
@@ -33,12 +33,12 @@ sys.path.insert(0, ROOT)
 
 METRIC = "decode_tokens_per_s_7b_q4_0"
 UNIT = "tok/s"
-WORKLOAD = ("BASELINE config 4: 7B-shape Llama decode, 224 Q4_0 projections (32 layers x "
+WORKLOAD = ("benchmark config 4: 7B-shape Llama decode, 224 Q4_0 projections (32 layers x "
             "{4x[4096x4096], 2x[11008x4096], [4096x11008]}), batch 1, bf16 activations, fp32 out")
 
 
 # DRAM traffic of the decode kernels, from an ncu capture of two layers of this workload
-# (dram__bytes_read.sum + dram__bytes_write.sum = 231.63 MB for 2 layers, profiles/gemv_program_q4_0_decode_7b.md);
+# (dram__bytes_read.sum + dram__bytes_write.sum = 231.63 MB for 2 layers);
 # traffic grows in proportion to the layers run and splits evenly over row shards.
 NCU_TRAFFIC_BYTES_PER_LAYER = 231.63e6 / 2
 
@@ -143,7 +143,7 @@ def run_reference(args) -> None:
 
 
 def gemv_sweep(ctx, hbm_peak: float) -> list:
-    """BASELINE config 2: cold-HBM Q4_0 GEMV at batch 1/4/8 over 12 rotating weight copies."""
+    """benchmark config 2: cold-HBM Q4_0 GEMV at batch 1/4/8 over 12 rotating weight copies."""
     from warpforge_b200 import _native as N, quant as Q
     from warpforge_b200.backend import QuantizedWeight
 

@@ -1,4 +1,4 @@
-"""GPU parity on BASELINE config 5 (70B-shape projection set, Q4_K, row-sharded over 8 ranks): one
+"""GPU parity on benchmark config 5 (70B-shape projection set, Q4_K, row-sharded over 8 ranks): one
 rank's shard of every projection shape, as a batch-16 decode step and as a 2048-token prefill,
 through the C ABI against the CPU oracle.  Both run on the tensor-core GEMM (more than 8 bf16
 tokens), so the bars are the GEMM's: max|d| / max|y| <= 1e-3 and rms(d) / rms(y) <= 3e-4.  The

@@ -71,7 +71,7 @@ def test_gemm_wide_dynamic_range_rows(backend, oracle):
 
 
 def test_config3_q4k_prefill_sampled_rows(backend, oracle):
-    """BASELINE config 3 at full size (M=512, N=14336, K=4096, Q4_K); the oracle checks 256 sampled
+    """benchmark config 3 at full size (M=512, N=14336, K=4096, Q4_K); the oracle checks 256 sampled
     weight rows for all 512 tokens, and a checksum over all outputs guards the rest."""
     rows, k, m = 14336, 4096, 512
     blocks = Q.synth_q4_k(rows, k, Q.config_seed(3))

@@ -136,7 +136,7 @@ def test_qlinear_f32_activations(backend, oracle, name, m):
 
 
 def test_config1_q8_0_linear(backend, oracle):
-    """BASELINE config 1: Q8_0 [4096 x 4096], x fp32 [1 x 4096]."""
+    """benchmark config 1: Q8_0 [4096 x 4096], x fp32 [1 x 4096]."""
     from warpforge_b200.backend import Tensor
 
     blocks = Q.synth_q8_0(4096, 4096, Q.config_seed(1))
@@ -151,7 +151,7 @@ def test_config1_q8_0_linear(backend, oracle):
 @pytest.mark.parametrize("rows,k", [(11008, 4096), (4096, 11008)])
 @pytest.mark.parametrize("m", [1, 4, 8])
 def test_config2_q4_0_gemv_sweep(backend, oracle, rows, k, m):
-    """BASELINE config 2 at full size."""
+    """benchmark config 2 at full size."""
     from warpforge_b200.backend import Tensor
 
     blocks = Q.synth_q4_0(rows, k, Q.config_seed(2, rows))

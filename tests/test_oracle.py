@@ -215,7 +215,7 @@ def test_qlinear_matches_twin_and_threads(oracle, qtype, gen, k):
 
 
 def test_config1_shape_runs_on_cpu(oracle):
-    """BASELINE config 1: single Q8_0 linear [4096 x 4096], x fp32 [1 x 4096]."""
+    """benchmark config 1: single Q8_0 linear [4096 x 4096], x fp32 [1 x 4096]."""
     w = Q.synth_q8_0(4096, 4096, Q.config_seed(1))
     x = Q.synth_activation_f32(1, 4096, Q.config_seed(1))
     y = oracle.qlinear(O.Q8_0, w, 4096, 4096, x, nthreads=oracle.max_threads())

@@ -29,7 +29,7 @@ class StackSpec:
     qtype: Q.QuantizationType
     layers: int
     projections: tuple  # (name, rows, k)
-    config: int         # BASELINE config number, used for seeding
+    config: int         # benchmark config number, used for seeding
 
     def bytes_per_token(self) -> int:
         """Algorithmic weight bytes one token reads: GGUF block bytes of every projection."""
