@@ -5,12 +5,16 @@
 
 Workload (benchmark config 4): the 224 Q4_0 projections of a 7B-shape Llama decoder, batch 1,
 every weight a distinct buffer (3.64 GB per token, far larger than L2, so every step reads
-HBM cold).  One step = one token = all projections in layer order, recorded once as a CUDA
-graph; with N > 1 ranks the weights are row-sharded and every projection is followed by the
-all-gather of its shards over NCCL (strong scaling: the same token stream on more GPUs).
+HBM cold).  One step = one token = all projections in layer order, run as ONE persistent
+kernel per GPU (`--mode graph`: one kernel per projection, recorded once as a CUDA graph).
+With N > 1 ranks the weights are row-sharded and every rank ends with all rows of every
+projection: the persistent kernel stores its rows into the other ranks' buffers over NVLink
+from inside the GEMV epilogue (graph mode: an NCCL all-gather after every projection).
+Strong scaling: the same token stream on more GPUs.
 The dominant kernel is the Q4_0 decode GEMV, so `roofline` is the headline "Q4_0 GEMV HBM
 GB/s (% of peak)"; `gemv_sweep` adds benchmark config 2 (the [11008x4096] / [4096x11008]
-sweep at batch 1, 4, 8), timed over 12 rotating weight copies (300 MB, larger than L2).
+sweep at batch 1, 4, 8), one launch per call, timed over 12 rotating weight copies (300 MB,
+larger than L2).
 
 Inputs are seeded synthetic GGUF blocks with the configs' value distributions; there is no
 dataset behind this path.  `--impl reference` times the CPU restatement of the reference's
