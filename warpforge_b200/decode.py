@@ -132,8 +132,14 @@ class ProjectionStack:
         Wgate/Wup read one input, Wdown reads the MLP product; each new input depends on what came
         before, so it needs every CTA (and rank) to have finished the previous projections."""
         new = self.OP_NEW_X | self.OP_DEPENDS
-        per_layer = {"wq": new, "wo": new, "wgate": new, "wdown": new}
-        return [per_layer.get(name, 0) for _ in range(self.layers) for name, _, _ in self.spec.projections]
+        starts_group = {"wq", "wo", "wgate", "wdown"}
+        flags, prev_k = [], None
+        for _ in range(self.layers):
+            for name, _, k in self.spec.projections:
+                # a projection that reads another buffer than its predecessor always stages anew
+                flags.append(new if (name in starts_group or k != prev_k) else 0)
+                prev_k = k
+        return flags
 
     def export_buffers(self) -> dict:
         """IPC handles of this rank's landing buffers (one per output buffer), for the peers."""
