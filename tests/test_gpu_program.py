@@ -64,6 +64,59 @@ def test_program_rejects_bad_arguments():
         ctx.close()
 
 
+def test_peer_wait_runs_out_and_is_reported(oracle):
+    """Failure detection without a GPU fault: rank 0 of a two-rank program runs alone, so the rows
+    of the absent rank never land.  The kernel's bounded waits run out, the kernel ends by itself,
+    the next synchronisation reports WF_ERR_DEVICE_WAIT, and the context stays usable."""
+    import ctypes
+
+    from warpforge_b200 import _native as N
+    from warpforge_b200.backend import CudaContext, QuantizedWeight
+
+    ctx = CudaContext(0)
+    lib = ctx._lib
+    try:
+        rows, k, world = 256, 256, 2
+        qt = Q.QuantizationType.Q4_0
+        blocks = Q.synth_q4_0(rows, k, 31)
+        xb = Q.synth_activation_bf16(1, k, 31)
+        dx = ctx.allocate(xb.nbytes)
+        ctx.copy_to_device(dx, xb)
+        ws = [QuantizedWeight(ctx, qt, blocks, rows, k, 0, world) for _ in range(2)]  # rank 0's shard, twice
+        ys = [ctx.allocate(rows * 4) for _ in range(2)]
+        landing = []
+        for _ in range(2 * world):  # [op][rank]; the "peer" buffers are local memory nobody reads
+            p = ctx.allocate(rows * 8)
+            ctx.copy_to_device(p, np.zeros(rows * 8, np.uint8))
+            landing.append(p)
+        arr = lambda v, t: (t * len(v))(*v)
+        prog = ctypes.c_int64()
+        N.check("create", lib.wf_program_create(
+            ctx.handle, 2, arr([w.handle for w in ws], ctypes.c_int64), arr([dx, dx], ctypes.c_int64), arr(ys, ctypes.c_int64),
+            arr([N.WF_OP_NEW_X, N.WF_OP_NEW_X | N.WF_OP_DEPENDS], ctypes.c_int), 1, world, 0, arr(landing, ctypes.c_int64),
+            ctypes.byref(prog)), ctx.handle)
+        N.check("run", lib.wf_program_run(ctx.handle, prog.value, 0), ctx.handle)
+        with pytest.raises(N.WfError) as err:
+            ctx.synchronize()
+        assert err.value.status == N.WF_ERR_DEVICE_WAIT
+        # rank 0's own rows were still computed correctly
+        got = np.empty((1, rows), np.float32)
+        ctx.copy_to_host(got, ys[0])
+        want = oracle.qlinear(O.Q4_0, blocks, rows, k, Q.bf16_bits_to_float(xb), nthreads=2)
+        half = rows // world
+        assert np.max(np.abs(got[:, :half] - want[:, :half])) <= 1e-3 * np.max(np.abs(want))
+        N.check("destroy", lib.wf_program_destroy(ctx.handle, prog.value), ctx.handle)
+        # the context is still usable: an ordinary call gives the right answer and a clean status
+        w = QuantizedWeight(ctx, qt, blocks, rows, k)
+        dy = ctx.allocate(rows * 4)
+        N.check("qlinear", lib.wf_qlinear(ctx.handle, w.handle, dx, N.WF_DTYPE_BF16, 1, 1, dy, 1, 0), ctx.handle)
+        ctx.synchronize()
+        ctx.copy_to_host(got, dy)
+        assert np.max(np.abs(got - want)) <= 1e-3 * np.max(np.abs(want))
+    finally:
+        ctx.close()
+
+
 _TWO_RANK = r"""
 import os, sys
 sys.path.insert(0, %r)
