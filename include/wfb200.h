@@ -113,7 +113,9 @@ int wf_dequant_rows(int64_t ctx, int64_t weight, int64_t row0, int64_t nrows, fl
  * x_dtype is WF_DTYPE_BF16 or WF_DTYPE_F32.  x / y are device pointers (x_on_device /
  * y_on_device non-zero) or host pointers; host buffers are staged through pinned memory
  * and the call returns after the result is in `y`.  With device pointers the call only
- * enqueues work on `stream`. */
+ * enqueues work on `stream`.  Up to 8 bf16 tokens (2 fp32 tokens) per pass run on the decode GEMV;
+ * more bf16 tokens run on the tensor-core GEMM, whose activation copy and tile-piece scratch belong
+ * to the context: many-token calls of one context must not overlap on different streams. */
 int wf_qlinear(int64_t ctx, int64_t weight, const void* x, int x_dtype, int x_on_device, int64_t m, void* y,
                int y_on_device, int64_t stream);
 
