@@ -256,6 +256,17 @@ def test_error_paths(backend):
     lib = N.load()
     assert lib.wf_weight_free(backend.cuda_context.handle, 12345) == N.WF_ERR_INVALID_HANDLE
     assert lib.wf_qlinear(backend.cuda_context.handle, w.handle, None, 1, 0, 1, None, 0, 0) == N.WF_ERR_INVALID_ARGUMENT
+    # device pointers the kernels would fault on are refused before anything is launched
+    import ctypes
+
+    ctx = backend.cuda_context
+    dx, dy = ctx.allocate(4096), ctx.allocate(4096)
+    vp = ctypes.c_void_p
+    assert lib.wf_qlinear(ctx.handle, w.handle, vp(dx + 2), N.WF_DTYPE_BF16, 1, 1, vp(dy), 1, 0) == N.WF_ERR_INVALID_ARGUMENT
+    assert lib.wf_qlinear(ctx.handle, w.handle, vp(dx), N.WF_DTYPE_BF16, 1, 1, vp(dy + 2), 1, 0) == N.WF_ERR_INVALID_ARGUMENT
+    assert lib.wf_qlinear_noalloc(ctx.handle, w.handle, dx + 8, N.WF_DTYPE_BF16, 1, dy, 0) == N.WF_ERR_INVALID_ARGUMENT
+    assert lib.wf_qlinear(ctx.handle, w.handle, vp(dx), N.WF_DTYPE_BF16, 1, 1, vp(dy), 1, 0) == N.WF_OK
+    ctx.synchronize()
 
 
 def test_backend_lifecycle():

@@ -187,6 +187,8 @@ int wf_qlinear_allgather(int64_t ctx, int64_t comm, int64_t weight, const void* 
     if (m < 0 || m > (1 << 20)) return set_error(c, WF_ERR_SHAPE, "m=%lld out of range", (long long)m);
     if (m == 0) return WF_OK;
     if (!x_dev || !y_full_dev) return set_error(c, WF_ERR_INVALID_ARGUMENT, "null pointer");
+    if ((reinterpret_cast<uintptr_t>(x_dev) & 15) || (reinterpret_cast<uintptr_t>(y_full_dev) & 3))
+        return set_error(c, WF_ERR_INVALID_ARGUMENT, "device pointers must be aligned (activations 16 bytes, output 4 bytes)");
     if (w->total_rows != w->g.rows * k->world || w->row0 != w->g.rows * k->rank)
         return set_error(c, WF_ERR_SHARD, "weight shard (row0=%lld rows=%lld of %lld) does not match rank %d of %d",
                          (long long)w->row0, (long long)w->g.rows, (long long)w->total_rows, k->rank, k->world);
@@ -215,7 +217,7 @@ int wf_qlinear_allgather(int64_t ctx, int64_t comm, int64_t weight, const void* 
     }
     float* mine = k->d_tmp + (int64_t)k->world * m * rows;
     GemvCall call{w, x_dev, x_dtype, m, mine, rows, 0};
-    int rc = gemm_supported(*w, x_dtype, m) ? gemm_launch(c, call, s) : gemv_launch(c, call, s);
+    int rc = gemm_supported(*w, x_dtype, m, call.d_x) ? gemm_launch(c, call, s) : gemv_launch(c, call, s);
     if (rc != WF_OK) return rc;
     int r = nccl().AllGather(mine, k->d_tmp, (size_t)(m * rows), NCCL_FLOAT32, k->comm, s);
     if (r != NCCL_SUCCESS) return nccl_status(c, r, "ncclAllGather");

@@ -101,7 +101,7 @@ int gemv_prepare_stream(Context* c, cudaStream_t s);
 int gemv_launch_noalloc(Context* c, const GemvCall& call, cudaStream_t s);
 
 // wf_gemm.cu
-bool gemm_supported(const Weight& w, int x_dtype, int64_t m);
+bool gemm_supported(const Weight& w, int x_dtype, int64_t m, const void* d_x);
 int gemm_launch(Context* c, const GemvCall& call, cudaStream_t s);
 
 struct ScopedLock {

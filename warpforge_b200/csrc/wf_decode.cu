@@ -356,6 +356,8 @@ int wf_program_create(int64_t ctx, int n_ops, const int64_t* weights, const int6
         }
         op.n_total = (int)w->total_rows;
         if (!op.x) return set_error(c, WF_ERR_INVALID_ARGUMENT, "op %d: null activation pointer", o);
+        if ((x_dev[o] & 15) || (y_dev[o] & 3))
+            return set_error(c, WF_ERR_INVALID_ARGUMENT, "op %d: misaligned pointer (activations 16 bytes, output 4 bytes)", o);
         op.ldy = w->total_rows;
         op.col0 = w->row0;
         op.rows = (int)w->g.rows;

@@ -383,6 +383,11 @@ int wf_qlinear(int64_t ctx, int64_t weight, const void* x, int x_dtype, int x_on
     if (m < 0 || m > (1 << 20)) return set_error(c, WF_ERR_SHAPE, "m=%lld out of range", (long long)m);
     if (m == 0) return WF_OK;
     if (!x || !y) return set_error(c, WF_ERR_INVALID_ARGUMENT, "null pointer");
+    // the kernels read activations in 16-byte pieces and write fp32: reject pointers they would fault on
+    if (x_on_device && (reinterpret_cast<uintptr_t>(x) & 15))
+        return set_error(c, WF_ERR_INVALID_ARGUMENT, "device activation pointer must be 16-byte aligned");
+    if (y_on_device && (reinterpret_cast<uintptr_t>(y) & 3))
+        return set_error(c, WF_ERR_INVALID_ARGUMENT, "device output pointer must be 4-byte aligned");
     cudaStream_t s = resolve_stream(c, stream);
     const int64_t xb = m * w->g.k * (x_dtype == WF_DTYPE_F32 ? 4 : 2), yb = m * w->g.rows * 4;
     const void* d_x = x;
@@ -402,7 +407,7 @@ int wf_qlinear(int64_t ctx, int64_t weight, const void* x, int x_dtype, int x_on
     }
     GemvCall call{w, d_x, x_dtype, m, d_y, w->g.rows, 0};
     // many tokens: tensor-core GEMM; a few tokens: the HBM-bound GEMV
-    int rc = gemm_supported(*w, x_dtype, m) ? gemm_launch(c, call, s) : gemv_launch(c, call, s);
+    int rc = gemm_supported(*w, x_dtype, m, call.d_x) ? gemm_launch(c, call, s) : gemv_launch(c, call, s);
     if (rc != WF_OK) return rc;
     if (!y_on_device) {
         const int64_t yo = (xb + 255) & ~255LL;
@@ -424,6 +429,8 @@ int wf_qlinear_noalloc(int64_t ctx, int64_t weight, int64_t x_dev, int x_dtype, 
     if (m < 0 || m > (1 << 20)) return set_error(c, WF_ERR_SHAPE, "m=%lld out of range", (long long)m);
     if (m == 0) return WF_OK;
     if (!x_dev || !y_dev) return set_error(c, WF_ERR_INVALID_ARGUMENT, "null device pointer");
+    if ((x_dev & 15) || (y_dev & 3))
+        return set_error(c, WF_ERR_INVALID_ARGUMENT, "device pointers must be aligned (activations 16 bytes, output 4 bytes)");
     GemvCall call{w, reinterpret_cast<const void*>(x_dev), x_dtype, m, reinterpret_cast<float*>(y_dev), w->g.rows, 0};
     return gemv_launch_noalloc(c, call, resolve_stream(c, stream));
 }
