@@ -83,22 +83,6 @@ __device__ __forceinline__ void fetch_block(uint32_t xaddr, uint32_t caddr, uint
         ci = make_float4(__uint_as_float(t.x), __uint_as_float(t.y), __uint_as_float(t.z), __uint_as_float(t.w));
     }
 }
-// XC = 1, four consecutive blocks (128 k) at once: one predicate, four predicated 16-byte loads of
-// the activations and ONE 16-byte broadcast load of the four start values.
-__device__ __forceinline__ void fetch_four_blocks_one_column(uint32_t xaddr, uint32_t caddr, uint32_t live, uint4 (&xb)[4],
-                                                             float (&c)[4]) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %22, 0;\n\t"
-        "@p ld.shared.v4.u32 {%0,%1,%2,%3}, [%20];\n\t"
-        "@p ld.shared.v4.u32 {%4,%5,%6,%7}, [%20+64];\n\t"
-        "@p ld.shared.v4.u32 {%8,%9,%10,%11}, [%20+128];\n\t"
-        "@p ld.shared.v4.u32 {%12,%13,%14,%15}, [%20+192];\n\t"
-        "ld.shared.v4.f32 {%16,%17,%18,%19}, [%21];\n\t}"
-        : "+r"(xb[0].x), "+r"(xb[0].y), "+r"(xb[0].z), "+r"(xb[0].w), "+r"(xb[1].x), "+r"(xb[1].y), "+r"(xb[1].z), "+r"(xb[1].w),
-          "+r"(xb[2].x), "+r"(xb[2].y), "+r"(xb[2].z), "+r"(xb[2].w), "+r"(xb[3].x), "+r"(xb[3].y), "+r"(xb[3].z), "+r"(xb[3].w),
-          "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
-        : "r"(xaddr), "r"(caddr), "r"(live));
-}
 // Offsets of block `blk` inside the start-value table: one float (XC = 1) or [4] float4 (XC = 8).
 template <int XC> __device__ __forceinline__ constexpr int cinit_block_bytes() { return XC == 1 ? 4 : 64; }
 
@@ -264,10 +248,14 @@ template <> struct TileRegs<WF_QTYPE_Q4_0> {
         const float2 s2 = half2_bits_to_float2(s.z), s3 = half2_bits_to_float2(s.w);  // row g + 8
         const float sg[4] = {s0.x, s0.y, s1.x, s1.y}, sh[4] = {s2.x, s2.y, s3.x, s3.y};
         if (XC == 1) {
-            uint4 xb[4] = {make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u),
-                           make_uint4(0u, 0u, 0u, 0u)};
-            float ci[4];
-            fetch_four_blocks_one_column(xaddr, caddr, live, xb, ci);
+            // All lanes load (the lanes of the dead columns read the live column's activations: their MMA
+            // columns are never read).  One 16-byte load of the four start values.
+            uint4 xb[4];
+            (void)live;
+#pragma unroll
+            for (int j = 0; j < 4; j++) xb[j] = lds128(xaddr + j * 64);
+            const uint4 t = lds128(caddr);
+            const float ci[4] = {__uint_as_float(t.x), __uint_as_float(t.y), __uint_as_float(t.z), __uint_as_float(t.w)};
 #pragma unroll
             for (int j = 0; j < 4; j++) {
                 float d[4];
