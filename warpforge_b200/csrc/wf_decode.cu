@@ -126,7 +126,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_program_kernel(const Pro
                 const ProgOp& op = P.ops[o];
                 const int t0 = bx * op.chunk_q + min(bx, op.chunk_r);
                 const int t1 = t0 + op.chunk_q + (bx < op.chunk_r ? 1 : 0);
-                produce_share<QT>(op.tiles, t0, t1, ring, bar, stages, pos, abort_flag);
+                produce_share<QT>(op.tiles, t0, t1, smem_u32(ring), bar, stages, pos, abort_flag);
             }
         }
         return;

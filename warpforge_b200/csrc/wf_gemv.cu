@@ -82,7 +82,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvParams 
     if (warp == GEMV_WARPS) {  // producer warp: the weights do not depend on anything, start at once
         if (lane == 0) {
             WalkState pos;
-            produce_share<QT>(p.tiles, t0, t1, ring, bar, stages, pos, abort_flag);
+            produce_share<QT>(p.tiles, t0, t1, smem_u32(ring), bar, stages, pos, abort_flag);
         }
         return;
     }

@@ -87,49 +87,29 @@ __device__ __forceinline__ void fetch_block(uint32_t xaddr, uint32_t caddr, uint
 template <int XC> __device__ __forceinline__ constexpr int cinit_block_bytes() { return XC == 1 ? 4 : 64; }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(void* bar, int count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+// Barriers are addressed by their 32-bit shared-memory address throughout: no generic-pointer
+// arithmetic or address-space conversion in the hot loops.
+__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
-__device__ __forceinline__ void mbar_arrive(void* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 // arrive from the lanes whose `pred` is non-zero, without a branch
-__device__ __forceinline__ void mbar_arrive_if(void* bar, uint32_t pred) {
+__device__ __forceinline__ void mbar_arrive_if(uint32_t bar, uint32_t pred) {
     asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %1, 0;\n\t@p mbarrier.arrive.shared::cta.b64 _, [%0];\n\t}" ::"r"(smem_u32(bar)),
+        "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %1, 0;\n\t@p mbarrier.arrive.shared::cta.b64 _, [%0];\n\t}" ::"r"(bar),
         "r"(pred)
         : "memory");
 }
-__device__ __forceinline__ void mbar_expect_tx(void* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-// Bounded wait: false if the phase did not complete within the spin budget.
-__device__ __forceinline__ bool mbar_wait(void* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p, q;\n\t"
-        ".reg .u32 n;\n\t"
-        "mov.u32 n, 0;\n\t"
-        "WF_WAIT_%=:\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "@p bra WF_DONE_%=;\n\t"
-        "add.u32 n, n, 1;\n\t"
-        "setp.lt.u32 q, n, %3;\n\t"
-        "@q bra WF_WAIT_%=;\n\t"
-        "WF_DONE_%=:\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t"
-        "}\n"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity), "r"((uint32_t)GEMV_BAR_SPINS)
-        : "memory");
-    return ok != 0;
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
 // The hot-loop form: one try_wait and a branch when the phase is already complete.  Otherwise spin,
 // bounded, and leave early once any thread of the CTA has raised the abort word (shared address
 // `abort32`); a wait that runs out raises it.  After an abort the data the caller goes on to use is
 // garbage -- the kernel reports the failure through its status word and the host discards y.
-__device__ __forceinline__ void mbar_wait_or_abort(void* bar, uint32_t parity, uint32_t abort32) {
+__device__ __forceinline__ void mbar_wait_or_abort(uint32_t bar, uint32_t parity, uint32_t abort32) {
     asm volatile(
         "{\n\t"
         ".reg .pred p, q;\n\t"
@@ -148,7 +128,7 @@ __device__ __forceinline__ void mbar_wait_or_abort(void* bar, uint32_t parity, u
         "@q bra WF_SPIN_%=;\n\t"
         "st.volatile.shared.u32 [%2], 1;\n\t"
         "WF_OK_%=:\n\t"
-        "}\n" ::"r"(smem_u32(bar)),
+        "}\n" ::"r"(bar),
         "r"(parity), "r"(abort32), "r"((uint32_t)GEMV_BAR_SPINS)
         : "memory");
 }
@@ -157,9 +137,9 @@ __device__ __forceinline__ void mbar_wait_or_abort(void* bar, uint32_t parity, u
 __device__ __forceinline__ void drain_after_abort() {
     for (int i = 0; i < 1000; i++) __nanosleep(1000);
 }
-__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, void* bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)),
-                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
+                 "r"(bytes), "r"(bar)
                  : "memory");
 }
 // A scratch slot element is {value bits, valid tag}.  It is written and read as ONE 64-bit
@@ -385,27 +365,27 @@ template <> struct TileRegs<WF_QTYPE_Q4_K> {
 // is the segment's reducer: one segment later, when the other warps have normally long
 // arrived, it waits on `done`, adds the sixteen partials in warp order, finishes the row-tile
 // (fix-up between CTAs, y) and marks the slot vacant.
-struct BarrierSet {
-    uint64_t *full, *empty;   // [stages]: data of a round has landed / all warps have taken their tile
-    uint64_t *done, *vacant;  // [Slots::N]: all warps have parked their partials / the reducer has read them
+struct BarrierSet {            // 32-bit shared addresses of the barrier arrays (8 bytes per barrier)
+    uint32_t full, empty;      // [stages]: data of a round has landed / all warps have taken their tile
+    uint32_t done, vacant;     // [Slots::N]: all warps have parked their partials / the reducer has read them
 };
 __device__ __forceinline__ BarrierSet barrier_set(uint8_t* smem) {
     BarrierSet b;
-    b.full = reinterpret_cast<uint64_t*>(smem + 128);
-    b.empty = b.full + GEMV_MAX_STAGES;
-    b.done = b.empty + GEMV_MAX_STAGES;
-    b.vacant = b.done + GEMV_MAX_SLOTS;
+    b.full = smem_u32(smem + 128);
+    b.empty = b.full + GEMV_MAX_STAGES * 8;
+    b.done = b.empty + GEMV_MAX_STAGES * 8;
+    b.vacant = b.done + GEMV_MAX_SLOTS * 8;
     return b;
 }
 template <int XC>
 __device__ __forceinline__ void barrier_set_init(const BarrierSet& b, int stages) {
     for (int s = 0; s < stages; s++) {
-        mbar_init(&b.full[s], 1);
-        mbar_init(&b.empty[s], GEMV_WARPS);
+        mbar_init(b.full + s * 8, 1);
+        mbar_init(b.empty + s * 8, GEMV_WARPS);
     }
     for (int s = 0; s < Slots<XC>::N; s++) {
-        mbar_init(&b.done[s], GEMV_WARPS);
-        mbar_init(&b.vacant[s], 1);
+        mbar_init(b.done + s * 8, GEMV_WARPS);
+        mbar_init(b.vacant + s * 8, 1);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
@@ -427,17 +407,17 @@ struct WalkState {
 // Producer (one thread): issue every round of the share, waiting for a stage to be released once
 // the ring has been filled.  Stops early when the CTA has aborted.
 template <int QT>
-__device__ __forceinline__ void produce_share(const uint8_t* tiles, int t0, int t1, uint8_t* ring, const BarrierSet& bar,
+__device__ __forceinline__ void produce_share(const uint8_t* tiles, int t0, int t1, uint32_t ring32, const BarrierSet& bar,
                                               int stages, WalkState& pos, volatile int* abort_flag) {
     using T = Tile<QT>;
     constexpr uint32_t STAGE_BYTES = GEMV_WARPS * T::BYTES;
     const uint32_t abort32 = smem_u32(const_cast<int*>(abort_flag));
     for (int first = t0; first < t1; first += GEMV_WARPS) {
-        if (pos.lap > 0) mbar_wait_or_abort(&bar.empty[pos.s], (pos.lap - 1) & 1, abort32);
+        if (pos.lap > 0) mbar_wait_or_abort(bar.empty + pos.s * 8, (pos.lap - 1) & 1, abort32);
         if (*abort_flag) return;
         const uint32_t bytes = (uint32_t)min(GEMV_WARPS, t1 - first) * T::BYTES;
-        mbar_expect_tx(&bar.full[pos.s], bytes);
-        bulk_load(ring + (size_t)pos.s * STAGE_BYTES, tiles + (size_t)first * T::BYTES, bytes, &bar.full[pos.s]);
+        mbar_expect_tx(bar.full + pos.s * 8, bytes);
+        bulk_load(ring32 + pos.s * STAGE_BYTES, tiles + (size_t)first * T::BYTES, bytes, bar.full + pos.s * 8);
         pos.advance(stages);
     }
 }
@@ -526,7 +506,7 @@ __device__ __forceinline__ void consume_share(int t0, int t1, int kt, int chunk_
     // finish segment number sg (row-tile rt, tiles [sb, se) of it in this share)
     auto reduce = [&](int sg, int rt, int sb, int se) {
         const int slot = sg % NSLOT, gen = sg / NSLOT;
-        mbar_wait_or_abort(&bar.done[slot], gen & 1, abort32);
+        mbar_wait_or_abort(bar.done + slot * 8, gen & 1, abort32);
         float* buf = partial + (size_t)slot * GEMV_WARPS * ELEMS;
         float v[PER_LANE];
 #pragma unroll
@@ -551,7 +531,7 @@ __device__ __forceinline__ void consume_share(int t0, int t1, int kt, int chunk_
             emit(rt, buf);
         }
         __syncwarp();
-        mbar_arrive_if(&bar.vacant[slot], lane_is_0);
+        mbar_arrive_if(bar.vacant + slot * 8, lane_is_0);
     };
 
     int seg_begin = t0, rt = (t0 < t1) ? t0 / kt : 0;
@@ -562,11 +542,11 @@ __device__ __forceinline__ void consume_share(int t0, int t1, int kt, int chunk_
     while (seg_begin < t1) {
         uint32_t xa = x32 + (t - rt * kt) * (T::K * 2), ca = c32 + (t - rt * kt) * ((T::K >> 5) * cinit_block_bytes<XC>());
         for (; t < seg_end; t += GEMV_WARPS) {  // my tiles below seg_end
-            mbar_wait_or_abort(&bar.full[st.s], st.lap & 1, abort32);
+            mbar_wait_or_abort(bar.full + st.s * 8, st.lap & 1, abort32);
             R regs;
             regs.load(my_tile + st.s * STAGE_BYTES, lane);
             __syncwarp();
-            mbar_arrive_if(&bar.empty[st.s], lane_is_0);
+            mbar_arrive_if(bar.empty + st.s * 8, lane_is_0);
             regs.template compute<XC>(acc, xa, ca, live);
             xa += GEMV_WARPS * T::K * 2;
             ca += GEMV_WARPS * (T::K >> 5) * cinit_block_bytes<XC>();
@@ -574,10 +554,10 @@ __device__ __forceinline__ void consume_share(int t0, int t1, int kt, int chunk_
         }
         // park my partial sums of this segment
         const int slot = st.seg % NSLOT, gen = st.seg / NSLOT;
-        if (gen > 0) mbar_wait_or_abort(&bar.vacant[slot], (gen - 1) & 1, abort32);
+        if (gen > 0) mbar_wait_or_abort(bar.vacant + slot * 8, (gen - 1) & 1, abort32);
         store_fragment<XC>(partial + ((size_t)slot * GEMV_WARPS + warp) * ELEMS, acc, g, q);
         __syncwarp();
-        mbar_arrive_if(&bar.done[slot], lane_is_0);
+        mbar_arrive_if(bar.done + slot * 8, lane_is_0);
         // the previous segment's reducer does its duty now
         if (have_prev && warp == (st.seg - 1) % GEMV_WARPS) reduce(st.seg - 1, prev_rt, prev_begin, prev_end);
         prev_rt = rt;
@@ -595,8 +575,8 @@ __device__ __forceinline__ void consume_share(int t0, int t1, int kt, int chunk_
     // the warp missed the last round iff the share's last round does not reach its position.)
     const int n = t1 - t0;
     if (n > 0 && (n % GEMV_WARPS) != 0 && warp >= (n % GEMV_WARPS)) {
-        mbar_wait_or_abort(&bar.full[st.s], st.lap & 1, abort32);
-        mbar_arrive_if(&bar.empty[st.s], lane_is_0);
+        mbar_wait_or_abort(bar.full + st.s * 8, st.lap & 1, abort32);
+        mbar_arrive_if(bar.empty + st.s * 8, lane_is_0);
         st.advance(stages);
     }
 }
