@@ -38,6 +38,7 @@ extern "C" {
 #define WF_ERR_NCCL_UNAVAILABLE (-9) /* libnccl could not be loaded                      */
 #define WF_ERR_DEVICE_WAIT (-10)     /* a bounded device-side wait ran out (see wf_stream_sync) */
 #define WF_ERR_TOO_LARGE (-11)       /* request exceeds a fixed capacity                 */
+#define WF_ERR_GGUF (-12)            /* not a GGUF file, unsupported version or type, truncated */
 #define WF_ERR_CUDA_BASE 1000
 #define WF_ERR_NCCL_BASE 2000
 
@@ -98,6 +99,43 @@ int wf_weight_free(int64_t ctx, int64_t weight);
 /* rows = rows held by this shard, row0 = first global row of the shard. */
 int wf_weight_info(int64_t ctx, int64_t weight, int* qtype, int64_t* rows, int64_t* k, int64_t* row0,
                    int64_t* device_bytes);
+
+/* ---- GGUF files ---------------------------------------------------------------------
+ * Replaces GGUF.open / tensorInfo / tensor / metadata / close for the weights of this path
+ * (warpforge-data/src/main/java/io/surfworks/warpforge/data/format/GGUF.java:96-176 open and
+ * header parse, :206-225 tensor lookup and data slice, :294-351 ggml type numbers and block
+ * sizes, :357-470 value decoding).  The file is memory-mapped read-only and stays mapped
+ * until wf_gguf_close; handles are process-wide and need no device, so a file can be
+ * inspected without a context.  Failures the reference reports as exceptions come back as
+ * WF_ERR_GGUF with the reference's message in `err` ("Invalid GGUF magic: ...", "File too
+ * small to be a GGUF file: ...", "Unsupported GGUF version: ...", "Unknown GGML type: ...");
+ * a name that is not in the file is WF_ERR_INVALID_ARGUMENT ("No tensor named: ...").
+ * Dimensions are in file order: dims[0] varies fastest, so a linear weight [n_rows, k] is
+ * stored as {k, n_rows}; unused entries of dims8 are 1.  `offset` is relative to the data
+ * section, whose start wf_gguf_info reports (header end rounded up to general.alignment,
+ * default 32).  Metadata values are rendered as text (numbers in decimal, booleans as
+ * true/false, arrays as their first elements in brackets). */
+int wf_gguf_open(const char* path, int64_t* gguf, char* err, int64_t err_len);
+int wf_gguf_close(int64_t gguf);
+int wf_gguf_info(int64_t gguf, int* version, int64_t* tensor_count, int64_t* metadata_count, int64_t* data_offset,
+                 int* alignment, int64_t* file_size);
+int wf_gguf_tensor_name(int64_t gguf, int64_t index, char* buf, int64_t n);
+int wf_gguf_tensor_info(int64_t gguf, const char* name, int* ggml_type, int* n_dims, int64_t* dims8, int64_t* offset,
+                        int64_t* size);
+int wf_gguf_tensor_data(int64_t gguf, const char* name, const void** data, int64_t* size);
+int wf_gguf_metadata(int64_t gguf, int64_t index, char* key, int64_t key_len, char* value, int64_t value_len);
+
+/* wf_weight_upload straight from the mapping: the 2-D tensor `name` ({k, n_rows} in the
+ * file) becomes a device-resident row shard without the bytes passing through the caller.
+ * q4_0_order says how a Q4_0 block's 16 quant bytes map to its 32 elements:
+ * WF_Q4_0_ORDER_REFERENCE is the order Dequantizer.java:251-279 reads (byte i holds
+ * elements 2i and 2i+1), WF_Q4_0_ORDER_GGML the order ggml writes (byte i holds elements i
+ * and i+16).  The device layout is the same either way, so the choice costs nothing at
+ * run time; it is ignored for the other types. */
+#define WF_Q4_0_ORDER_REFERENCE 0
+#define WF_Q4_0_ORDER_GGML 1
+int wf_gguf_upload(int64_t ctx, int64_t gguf, const char* name, int shard_rank, int shard_world, int q4_0_order,
+                   int64_t* weight);
 
 /* Replaces Dequantizer.dequantize(MemorySegment, float[], int)
  * (warpforge-data/.../quant/Dequantizer.java:204-221 Q8_0, :251-279 Q4_0; Q4_K per the GGUF

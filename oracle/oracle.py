@@ -209,6 +209,20 @@ def np_dequant_q4_0(blocks, n: int) -> np.ndarray:
     return (vals * d[:, None]).astype(np.float32).ravel()[:n]
 
 
+def q4_0_ggml_to_reference_order(blocks) -> np.ndarray:
+    """Q4_0 blocks in ggml's nibble order (byte i = elements i and i+16) rewritten in the order the
+    reference's Dequantizer.java:251-279 reads (byte i = elements 2i and 2i+1); scales untouched."""
+    blk = np.asarray(blocks, np.uint8).reshape(-1, 18).copy()
+    qs = blk[:, 2:]
+    elems = np.concatenate([qs & 0x0F, qs >> 4], axis=1)  # [nb, 32] in element order
+    blk[:, 2:] = elems[:, 0::2] | (elems[:, 1::2] << 4)
+    return blk.ravel()
+
+
+def np_dequant_q4_0_ggml(blocks, n: int) -> np.ndarray:
+    return np_dequant_q4_0(q4_0_ggml_to_reference_order(blocks), n)
+
+
 def np_q4k_scales_mins(s: np.ndarray):
     """s: [nb, 12] uint8 -> (sc [nb, 8], m [nb, 8]) as in wfo_q4k_scale_min."""
     s = s.astype(np.uint8)

@@ -223,3 +223,16 @@ def test_config1_shape_runs_on_cpu(oracle):
     wf = oracle.dequant(O.Q8_0, w, 4096 * 4096).reshape(4096, 4096)
     ref64 = x.astype(np.float64) @ wf.astype(np.float64).T
     assert np.max(np.abs(y - ref64)) / np.max(np.abs(ref64)) < 1e-5
+
+
+def test_q4_0_ggml_order_against_gguf_package(oracle):
+    """Blocks in ggml's nibble order, rewritten to the reference's order, dequantize (by the
+    reference's rule) to exactly what the gguf package makes of the original blocks."""
+    gguf = pytest.importorskip("gguf")
+    from gguf import quants
+
+    w = Q.synth_q4_0(8, 256, 11)
+    want = quants.dequantize(w.reshape(-1, 18), gguf.GGMLQuantizationType.Q4_0).astype(np.float32).ravel()
+    got = oracle.dequant(O.Q4_0, O.q4_0_ggml_to_reference_order(w), 8 * 256)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    assert np.array_equal(O.np_dequant_q4_0_ggml(w, 8 * 256).view(np.uint32), want.view(np.uint32))

@@ -16,6 +16,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libwfb200.so")
 
 c_int, c_i64, c_vp, c_f32 = ctypes.c_int, ctypes.c_int64, ctypes.c_void_p, ctypes.c_float
+c_char_p = ctypes.c_char_p
 P = ctypes.POINTER
 
 # name -> (restype, argtypes); must list every function declared in include/wfb200.h
@@ -35,6 +36,14 @@ SIGNATURES = {
     "wf_memcpy_h2d": (c_int, [c_i64, c_i64, c_vp, c_i64, c_i64, c_int]),
     "wf_memcpy_d2h": (c_int, [c_i64, c_vp, c_i64, c_i64, c_i64, c_int]),
     "wf_weight_upload": (c_int, [c_i64, c_int, c_vp, c_i64, c_i64, c_int, c_int, P(c_i64)]),
+    "wf_gguf_open": (c_int, [c_char_p, P(c_i64), c_char_p, c_i64]),
+    "wf_gguf_close": (c_int, [c_i64]),
+    "wf_gguf_info": (c_int, [c_i64, P(c_int), P(c_i64), P(c_i64), P(c_i64), P(c_int), P(c_i64)]),
+    "wf_gguf_tensor_name": (c_int, [c_i64, c_i64, c_char_p, c_i64]),
+    "wf_gguf_tensor_info": (c_int, [c_i64, c_char_p, P(c_int), P(c_int), P(c_i64), P(c_i64), P(c_i64)]),
+    "wf_gguf_tensor_data": (c_int, [c_i64, c_char_p, P(c_vp), P(c_i64)]),
+    "wf_gguf_metadata": (c_int, [c_i64, c_i64, c_char_p, c_i64, c_char_p, c_i64]),
+    "wf_gguf_upload": (c_int, [c_i64, c_i64, c_char_p, c_int, c_int, c_int, P(c_i64)]),
     "wf_weight_free": (c_int, [c_i64, c_i64]),
     "wf_weight_info": (c_int, [c_i64, c_i64, P(c_int), P(c_i64), P(c_i64), P(c_i64), P(c_i64)]),
     "wf_dequant_rows": (c_int, [c_i64, c_i64, c_i64, c_i64, c_vp]),
@@ -70,7 +79,8 @@ SIGNATURES = {
 WF_OK = 0
 WF_ERR_INVALID_ARGUMENT, WF_ERR_INVALID_HANDLE, WF_ERR_UNSUPPORTED_TYPE, WF_ERR_SHAPE = -1, -2, -3, -4
 WF_ERR_SHARD, WF_ERR_BUSY, WF_ERR_NO_DEVICE, WF_ERR_NOT_SM100 = -5, -6, -7, -8
-WF_ERR_NCCL_UNAVAILABLE, WF_ERR_DEVICE_WAIT, WF_ERR_TOO_LARGE = -9, -10, -11
+WF_ERR_NCCL_UNAVAILABLE, WF_ERR_DEVICE_WAIT, WF_ERR_TOO_LARGE, WF_ERR_GGUF = -9, -10, -11, -12
+WF_Q4_0_ORDER_REFERENCE, WF_Q4_0_ORDER_GGML = 0, 1
 WF_DTYPE_F32, WF_DTYPE_BF16 = 0, 1
 WF_OP_NEW_X, WF_OP_DEPENDS = 1, 2
 

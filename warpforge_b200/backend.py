@@ -221,6 +221,24 @@ class QuantizedWeight:
         self.row0 = self.rows * shard_rank
         self.shard_rank, self.shard_world = shard_rank, shard_world
 
+    @classmethod
+    def from_gguf(cls, context: "CudaContext", gguf_file, name: str, shard_rank: int = 0, shard_world: int = 1,
+                  q4_0_order: int = N.WF_Q4_0_ORDER_REFERENCE) -> "QuantizedWeight":
+        """Upload the 2-D tensor `name` of an open GGUF file ({k, rows} in file order) straight
+        from the library's mapping of the file (wf_gguf_upload)."""
+        info = gguf_file.tensor_info(name)
+        h = ctypes.c_int64()
+        context._ck("wf_gguf_upload", context._lib.wf_gguf_upload(
+            context.handle, gguf_file.handle, name.encode(), shard_rank, shard_world, q4_0_order, ctypes.byref(h)))
+        self = cls.__new__(cls)
+        self.context, self.qtype = context, QuantizationType.from_ggml(info.ggml_type)
+        self.handle = h.value
+        self.k, self.total_rows = info.shape[0], info.shape[1]
+        self.rows = self.total_rows // shard_world
+        self.row0 = self.rows * shard_rank
+        self.shard_rank, self.shard_world = shard_rank, shard_world
+        return self
+
     def shape(self):
         return (self.rows, self.k)
 
@@ -344,6 +362,14 @@ class NvidiaBackend:
                       shard_world: int = 1) -> QuantizedWeight:
         self._check_not_closed()
         w = QuantizedWeight(self.cuda_context, qtype, blocks, rows, k, shard_rank, shard_world)
+        self._weights.append(w)
+        return w
+
+    def upload_gguf_weight(self, gguf_file, name: str, shard_rank: int = 0, shard_world: int = 1,
+                           q4_0_order: int = N.WF_Q4_0_ORDER_REFERENCE) -> QuantizedWeight:
+        """Linear weight `name` of an open warpforge_b200.gguf.GGUF file, from the file mapping to the device."""
+        self._check_not_closed()
+        w = QuantizedWeight.from_gguf(self.cuda_context, gguf_file, name, shard_rank, shard_world, q4_0_order)
         self._weights.append(w)
         return w
 

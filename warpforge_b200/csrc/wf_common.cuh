@@ -64,6 +64,10 @@ struct Context {
     int64_t h_stage_bytes = 0;
     void* d_stage = nullptr;
     int64_t d_stage_bytes = 0;
+    void* h_upload = nullptr;  // two pinned chunks the weight upload streams a host tensor through
+    void* d_upload = nullptr;  // their landing place on the device, read by the repack kernel
+    int64_t upload_chunk_bytes = 0;
+    cudaEvent_t upload_done[2] = {nullptr, nullptr};
     void* d_x16 = nullptr;  // fp16 copy of the activations for the tensor-core GEMM
     int64_t x16_bytes = 0;
     float* d_gemm_partial = nullptr;       // [sm_count][256][128] pieces of tiles cut by a share boundary
@@ -79,10 +83,13 @@ Context* get_context(int64_t h);
 Weight* get_weight(Context* c, int64_t h);
 cudaStream_t resolve_stream(Context* c, int64_t stream);
 int ensure_stage(Context* c, int64_t host_bytes, int64_t dev_bytes);
+// validated shard upload + repack shared by wf_weight_upload and wf_gguf_upload; takes the context lock
+int weight_upload(Context* c, int qtype, const void* blocks, int64_t n_rows, int64_t k, int shard_rank, int shard_world,
+                  int q4_0_order, int64_t* weight);
 
 // wf_repack.cu
 cudaError_t launch_repack(int qtype, const uint8_t* d_raw, uint8_t* d_tiles, int64_t rows, int64_t k,
-                          cudaStream_t s);
+                          int q4_0_order, cudaStream_t s);
 cudaError_t launch_dequant_rows(const Weight& w, int64_t row0, int64_t nrows, float* d_out, cudaStream_t s);
 
 // wf_gemv.cu

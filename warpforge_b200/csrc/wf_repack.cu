@@ -19,7 +19,7 @@ __device__ __forceinline__ uint16_t ld_u16(const uint8_t* p) { return (uint16_t)
 
 // One thread per (row, 32-k block, element group q).
 __global__ void repack_q4_0_kernel(const uint8_t* __restrict__ raw, uint8_t* __restrict__ tiles, int64_t rows,
-                                   int64_t nblk, int64_t kt) {
+                                   int64_t nblk, int64_t kt, int ggml_order) {
     int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= rows * nblk * 4) return;
     int q = idx & 3;
@@ -28,11 +28,19 @@ __global__ void repack_q4_0_kernel(const uint8_t* __restrict__ raw, uint8_t* __r
     uint8_t* tile = tiles + ((r >> 4) * kt + (bk >> 2)) * Tile<WF_QTYPE_Q4_0>::BYTES;
     int ri = r & 15, j = bk & 3;
     uint32_t nib[8];
+    if (ggml_order) {  // files written by ggml: byte i -> elements i (low), i + 16 (high)
 #pragma unroll
-    for (int i = 0; i < 4; i++) {  // reference order: byte i -> elements 2i (low), 2i+1 (high)
-        uint8_t b = src[2 + 4 * q + i];
-        nib[2 * i] = b & 0xF;
-        nib[2 * i + 1] = b >> 4;
+        for (int i = 0; i < 8; i++) {
+            uint8_t b = src[2 + ((8 * q + i) & 15)];
+            nib[i] = q >= 2 ? (b >> 4) : (b & 0xF);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 4; i++) {  // reference order: byte i -> elements 2i (low), 2i+1 (high)
+            uint8_t b = src[2 + 4 * q + i];
+            nib[2 * i] = b & 0xF;
+            nib[2 * i + 1] = b >> 4;
+        }
     }
     *reinterpret_cast<uint32_t*>(tile + plane_word_off(ri, j, q)) = pack8(nib);
     if (q == 0)
@@ -108,7 +116,7 @@ __global__ void repack_q4_k_kernel(const uint8_t* __restrict__ raw, uint8_t* __r
 }
 
 cudaError_t launch_repack(int qtype, const uint8_t* d_raw, uint8_t* d_tiles, int64_t rows, int64_t k,
-                          cudaStream_t s) {
+                          int q4_0_order, cudaStream_t s) {
     const int threads = 256;
     if (qtype == WF_QTYPE_Q4_K) {
         int64_t nsb = k / 256, n = rows * nsb * 32;
@@ -117,7 +125,7 @@ cudaError_t launch_repack(int qtype, const uint8_t* d_raw, uint8_t* d_tiles, int
         int64_t nblk = k / 32, n = rows * nblk * 4, kt = (k + 127) / 128;
         unsigned grid = (unsigned)((n + threads - 1) / threads);
         if (qtype == WF_QTYPE_Q4_0)
-            repack_q4_0_kernel<<<grid, threads, 0, s>>>(d_raw, d_tiles, rows, nblk, kt);
+            repack_q4_0_kernel<<<grid, threads, 0, s>>>(d_raw, d_tiles, rows, nblk, kt, q4_0_order == WF_Q4_0_ORDER_GGML);
         else
             repack_q8_0_kernel<<<grid, threads, 0, s>>>(d_raw, d_tiles, rows, nblk, kt);
     }

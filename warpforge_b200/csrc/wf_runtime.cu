@@ -8,6 +8,8 @@
 #include <string.h>
 
 #include <algorithm>
+#include <atomic>
+#include <thread>
 #include <unordered_set>
 
 #include "wf_common.cuh"
@@ -67,6 +69,76 @@ int ensure_stage(Context* c, int64_t host_bytes, int64_t dev_bytes) {
         c->d_stage_bytes = dev_bytes;
     }
     return WF_OK;
+}
+
+// Host blocks (pageable memory, e.g. a mapped file) -> tiled device layout as a three-stage pipeline over
+// chunks of whole 16-row tiles: helper threads copy chunk i+1 into one of two pinned buffers while the DMA
+// of chunk i runs and the repack kernel of chunk i-1 writes its tiles.  A plain cudaMemcpyAsync from
+// pageable memory stages through one driver thread and runs several times slower; the scratch on the
+// device is two chunks, not a second copy of the tensor.
+constexpr int64_t UPLOAD_CHUNK = 8 << 20;
+constexpr int UPLOAD_THREADS = 4;
+
+static cudaError_t upload_and_repack(Context* c, int qtype, const uint8_t* src, int64_t rows, int64_t k, int64_t row_bytes,
+                                     uint8_t* d_tiles, int64_t tile_row_bytes, int q4_0_order, cudaStream_t s) {
+    const int64_t chunk_rows = std::max<int64_t>(TILE_ROWS, UPLOAD_CHUNK / row_bytes / TILE_ROWS * TILE_ROWS);
+    const int64_t chunk_bytes = (chunk_rows * row_bytes + 255) & ~255LL;
+    const int nchunks = (int)((rows + chunk_rows - 1) / chunk_rows);
+    cudaError_t e = cudaSuccess;
+    if (chunk_bytes > c->upload_chunk_bytes) {
+        if (c->h_upload) cudaFreeHost(c->h_upload);
+        if (c->d_upload) cudaFree(c->d_upload);
+        c->h_upload = c->d_upload = nullptr;
+        c->upload_chunk_bytes = 0;
+        e = cudaMallocHost(&c->h_upload, (size_t)(2 * chunk_bytes));
+        if (e == cudaSuccess) e = cudaMalloc(&c->d_upload, (size_t)(2 * chunk_bytes));
+        if (e != cudaSuccess) return e;
+        c->upload_chunk_bytes = chunk_bytes;
+    }
+    for (int i = 0; i < 2; i++)
+        if (!c->upload_done[i] && (e = cudaEventCreateWithFlags(&c->upload_done[i], cudaEventDisableTiming)) != cudaSuccess) return e;
+    uint8_t* const pinned = static_cast<uint8_t*>(c->h_upload);
+    auto chunk_size = [&](int i) { return std::min(chunk_rows, rows - i * chunk_rows) * row_bytes; };
+
+    // released: chunks [0, released) may be written into their pinned buffer; filled[i]: helpers done with chunk i
+    const int helpers_n = rows * row_bytes > (1 << 20) ? UPLOAD_THREADS : 0;
+    std::atomic<int> released{2};
+    std::atomic<bool> stop{false};
+    std::vector<std::atomic<int>> filled((size_t)nchunks);
+    for (auto& f : filled) f.store(0);
+    std::vector<std::thread> helpers;
+    for (int t = 0; t < helpers_n; t++)
+        helpers.emplace_back([&, t] {
+            for (int i = 0; i < nchunks; i++) {
+                while (released.load(std::memory_order_acquire) <= i && !stop.load()) std::this_thread::yield();
+                if (stop.load()) return;
+                const int64_t n = chunk_size(i), part = (n / helpers_n + 4095) & ~4095LL;
+                const int64_t lo = std::min(n, t * part), hi = std::min(n, (t + 1) * part);
+                if (hi > lo) memcpy(pinned + (i & 1) * chunk_bytes + lo, src + i * chunk_rows * row_bytes + lo, (size_t)(hi - lo));
+                filled[(size_t)i].fetch_add(1, std::memory_order_release);
+            }
+        });
+    for (int i = 0; i < nchunks && e == cudaSuccess; i++) {
+        const int64_t n = chunk_size(i), r0 = i * chunk_rows;
+        uint8_t* h = pinned + (i & 1) * chunk_bytes;
+        uint8_t* d = static_cast<uint8_t*>(c->d_upload) + (i & 1) * chunk_bytes;
+        if (helpers_n == 0) {
+            if (i >= 2) e = cudaEventSynchronize(c->upload_done[i & 1]);
+            memcpy(h, src + r0 * row_bytes, (size_t)n);
+        } else {
+            while (filled[(size_t)i].load(std::memory_order_acquire) < helpers_n) std::this_thread::yield();
+        }
+        if (e == cudaSuccess) e = cudaMemcpyAsync(d, h, (size_t)n, cudaMemcpyHostToDevice, s);
+        if (e == cudaSuccess) e = cudaEventRecord(c->upload_done[i & 1], s);
+        if (e == cudaSuccess) e = launch_repack(qtype, d, d_tiles + r0 / TILE_ROWS * tile_row_bytes, n / row_bytes, k, q4_0_order, s);
+        if (helpers_n && i >= 1 && e == cudaSuccess) {  // the DMA of chunk i-1 has left its pinned buffer: chunk i+1 may fill it
+            e = cudaEventSynchronize(c->upload_done[(i - 1) & 1]);
+            released.store(i + 2, std::memory_order_release);
+        }
+    }
+    stop.store(e != cudaSuccess);
+    for (std::thread& h : helpers) h.join();
+    return e;
 }
 
 static bool qtype_supported(int qt) { return qt == WF_QTYPE_Q4_0 || qt == WF_QTYPE_Q8_0 || qt == WF_QTYPE_Q4_K; }
@@ -158,6 +230,10 @@ int wf_destroy(int64_t ctx) {
     for (cudaEvent_t ev : c->events) cudaEventDestroy(ev);
     for (cudaStream_t s : c->streams) cudaStreamDestroy(s);
     if (c->h_stage) cudaFreeHost(c->h_stage);
+    if (c->h_upload) cudaFreeHost(c->h_upload);
+    if (c->d_upload) cudaFree(c->d_upload);
+    for (cudaEvent_t e : c->upload_done)
+        if (e) cudaEventDestroy(e);
     if (c->d_stage) cudaFree(c->d_stage);
     if (c->d_x16) cudaFree(c->d_x16);
     if (c->d_gemm_partial) cudaFree(c->d_gemm_partial);
@@ -280,7 +356,19 @@ int wf_memcpy_d2h(int64_t ctx, void* dst, int64_t src, int64_t bytes, int64_t st
 
 int wf_weight_upload(int64_t ctx, int qtype, const void* blocks, int64_t n_rows, int64_t k, int shard_rank,
                      int shard_world, int64_t* weight) {
-    WF_ENTER(ctx);
+    Context* c = get_context(ctx);
+    if (!c) return WF_ERR_INVALID_HANDLE;
+    return weight_upload(c, qtype, blocks, n_rows, k, shard_rank, shard_world, WF_Q4_0_ORDER_REFERENCE, weight);
+}
+
+}  // extern "C"
+
+namespace wf {
+int weight_upload(Context* c, int qtype, const void* blocks, int64_t n_rows, int64_t k, int shard_rank, int shard_world,
+                  int q4_0_order, int64_t* weight) {
+    ScopedLock lock(c);
+    if (!lock.ok) return WF_ERR_BUSY;
+    WF_CUDA(c, cudaSetDevice(c->device));
     if (!blocks || !weight) return set_error(c, WF_ERR_INVALID_ARGUMENT, "null pointer");
     *weight = 0;
     if (!qtype_supported(qtype))
@@ -305,17 +393,12 @@ int wf_weight_upload(int64_t ctx, int qtype, const void* blocks, int64_t n_rows,
     w->g.rt_alloc = (w->g.rt + 7) / 8 * 8;
     w->row0 = row0;
     w->total_rows = n_rows;
-    const int64_t raw_bytes = rows * row_bytes;
-    void* d_raw = nullptr;
     cudaError_t e = cudaMalloc(&w->d_tiles, (size_t)w->g.bytes());
-    if (e == cudaSuccess) e = cudaMalloc(&d_raw, (size_t)raw_bytes);
     if (e == cudaSuccess) e = cudaMemsetAsync(w->d_tiles, 0, (size_t)w->g.bytes(), c->stream);
     if (e == cudaSuccess)
-        e = cudaMemcpyAsync(d_raw, static_cast<const uint8_t*>(blocks) + row0 * row_bytes, (size_t)raw_bytes,
-                            cudaMemcpyHostToDevice, c->stream);
-    if (e == cudaSuccess) e = launch_repack(qtype, static_cast<const uint8_t*>(d_raw), w->d_tiles, rows, k, c->stream);
+        e = upload_and_repack(c, qtype, static_cast<const uint8_t*>(blocks) + row0 * row_bytes, rows, k, row_bytes, w->d_tiles,
+                              w->g.kt * (int64_t)tile_bytes(qtype), q4_0_order, c->stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
-    if (d_raw) cudaFree(d_raw);
     if (e != cudaSuccess) {
         if (w->d_tiles) cudaFree(w->d_tiles);
         delete w;
@@ -326,6 +409,9 @@ int wf_weight_upload(int64_t ctx, int qtype, const void* blocks, int64_t n_rows,
     *weight = reinterpret_cast<int64_t>(w);
     return WF_OK;
 }
+}  // namespace wf
+
+extern "C" {
 
 int wf_weight_free(int64_t ctx, int64_t weight) {
     WF_ENTER(ctx);
@@ -496,6 +582,7 @@ const char* wf_error_string(int status) {
         case WF_ERR_NCCL_UNAVAILABLE: return "WF_ERR_NCCL_UNAVAILABLE";
         case WF_ERR_DEVICE_WAIT: return "WF_ERR_DEVICE_WAIT";
         case WF_ERR_TOO_LARGE: return "WF_ERR_TOO_LARGE";
+        case WF_ERR_GGUF: return "WF_ERR_GGUF";
         default: break;
     }
     if (status >= WF_ERR_NCCL_BASE) return "WF_ERR_NCCL";
