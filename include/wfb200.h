@@ -39,6 +39,7 @@ extern "C" {
 #define WF_ERR_DEVICE_WAIT (-10)     /* a bounded device-side wait ran out (see wf_stream_sync) */
 #define WF_ERR_TOO_LARGE (-11)       /* request exceeds a fixed capacity                 */
 #define WF_ERR_GGUF (-12)            /* not a GGUF file, unsupported version or type, truncated */
+#define WF_ERR_INDEX (-13)           /* an embedding index outside the table (reported by wf_stream_sync) */
 #define WF_ERR_CUDA_BASE 1000
 #define WF_ERR_NCCL_BASE 2000
 
@@ -142,6 +143,31 @@ int wf_gguf_upload(int64_t ctx, int64_t gguf, const char* name, int shard_rank, 
  * block format): fp32 values of shard rows [row0, row0+nrows), bit-identical to the CPU
  * result, written to host memory. */
 int wf_dequant_rows(int64_t ctx, int64_t weight, int64_t row0, int64_t nrows, float* out_host);
+
+/* ---- the fp32 operations between the projections of a decode step ---------------------
+ * Replace the custom_call kernels of CudaCustomCallKernel.execute
+ * (nvidia/ops/CudaCustomCallKernel.java:50-59: "rms_norm", "layer_norm", "softmax", "silu",
+ * "embedding") with the arithmetic of the CPU backend's CustomCallKernel
+ * (warpforge-backend-cpu/.../ops/scalar/CustomCallKernel.java: layer_norm :109-171,
+ * softmax :173-224, silu :262-280, embedding :282-318, rms_norm :368-412).  All pointers are
+ * device pointers to contiguous fp32 (indices: int64), the calls only enqueue on `stream`.
+ * Row operations work on [rows, n] and normalise the last dimension, as the reference does;
+ * gamma / beta may be 0 (not given), as the optional inputs of the reference are.  The
+ * reference takes eps = 1e-5 always (it does not parse the op's attributes); pass that for
+ * parity.  wf_swiglu is silu(gate) * up (the silu custom_call followed by stablehlo.multiply),
+ * wf_add the residual stablehlo.add.  In-place use (y == x) is allowed for all but
+ * wf_embedding.  An embedding index outside [0, vocab) writes a row of zeros and makes the
+ * next wf_stream_sync return WF_ERR_INDEX (the CPU backend throws there). */
+int wf_rms_norm(int64_t ctx, int64_t x_dev, int64_t gamma_dev, int64_t y_dev, int64_t rows, int64_t n, float eps,
+                int64_t stream);
+int wf_layer_norm(int64_t ctx, int64_t x_dev, int64_t gamma_dev, int64_t beta_dev, int64_t y_dev, int64_t rows,
+                  int64_t n, float eps, int64_t stream);
+int wf_softmax(int64_t ctx, int64_t x_dev, int64_t y_dev, int64_t rows, int64_t n, int64_t stream);
+int wf_silu(int64_t ctx, int64_t x_dev, int64_t y_dev, int64_t count, int64_t stream);
+int wf_swiglu(int64_t ctx, int64_t gate_dev, int64_t up_dev, int64_t y_dev, int64_t count, int64_t stream);
+int wf_add(int64_t ctx, int64_t a_dev, int64_t b_dev, int64_t y_dev, int64_t count, int64_t stream);
+int wf_embedding(int64_t ctx, int64_t indices_dev, int64_t table_dev, int64_t y_dev, int64_t count, int64_t vocab,
+                 int64_t dim, int64_t stream);
 
 /* ---- the op -------------------------------------------------------------------------
  * Replaces DotGeneralKernel.execute for `linear`: lhs [m,k] contracting dim 1, rhs [n,k]

@@ -73,6 +73,15 @@ class COracle:
         L.wfo_count_not_close.restype = ctypes.c_int64
         L.wfo_count_not_close.argtypes = [f32p, f32p, ctypes.c_int64, ctypes.c_double, ctypes.c_double]
         L.wfo_max_threads.restype = ctypes.c_int
+        i64 = ctypes.c_int64
+        L.wfo_rms_norm.argtypes = [f32p, f32p, f32p, i64, i64, ctypes.c_float]
+        L.wfo_layer_norm.argtypes = [f32p, f32p, f32p, f32p, i64, i64, ctypes.c_float]
+        L.wfo_softmax.argtypes = [f32p, f32p, i64, i64]
+        L.wfo_silu.argtypes = [f32p, f32p, i64]
+        L.wfo_swiglu.argtypes = [f32p, f32p, f32p, i64]
+        L.wfo_add.argtypes = [f32p, f32p, f32p, i64]
+        L.wfo_embedding.restype = ctypes.c_int
+        L.wfo_embedding.argtypes = [i64p, f32p, f32p, i64, i64, i64]
 
     def max_threads(self) -> int:
         return int(self.lib.wfo_max_threads())
@@ -161,6 +170,61 @@ class COracle:
         if rc != 0:
             raise ValueError(f"wfo_qlinear_rows failed: {rc}")
         return np.ascontiguousarray(y.T)
+
+    # ---- the fp32 operations between the projections (CustomCallKernel.java); x is [rows, n] or flat
+    @staticmethod
+    def _f32(a):
+        return np.ascontiguousarray(a, np.float32)
+
+    def _opt(self, a):
+        return None if a is None else _ptr(self._f32(a), ctypes.c_float)
+
+    def rms_norm(self, x, gamma=None, eps: float = 1e-5) -> np.ndarray:
+        x = self._f32(x)
+        y = np.empty_like(x)
+        self.lib.wfo_rms_norm(_ptr(x, ctypes.c_float), self._opt(gamma), _ptr(y, ctypes.c_float), x.size // x.shape[-1], x.shape[-1], eps)
+        return y
+
+    def layer_norm(self, x, gamma=None, beta=None, eps: float = 1e-5) -> np.ndarray:
+        x = self._f32(x)
+        y = np.empty_like(x)
+        self.lib.wfo_layer_norm(_ptr(x, ctypes.c_float), self._opt(gamma), self._opt(beta), _ptr(y, ctypes.c_float),
+                                x.size // x.shape[-1], x.shape[-1], eps)
+        return y
+
+    def softmax(self, x) -> np.ndarray:
+        x = self._f32(x)
+        y = np.empty_like(x)
+        self.lib.wfo_softmax(_ptr(x, ctypes.c_float), _ptr(y, ctypes.c_float), x.size // x.shape[-1], x.shape[-1])
+        return y
+
+    def silu(self, x) -> np.ndarray:
+        x = self._f32(x)
+        y = np.empty_like(x)
+        self.lib.wfo_silu(_ptr(x, ctypes.c_float), _ptr(y, ctypes.c_float), x.size)
+        return y
+
+    def swiglu(self, gate, up) -> np.ndarray:
+        gate, up = self._f32(gate), self._f32(up)
+        y = np.empty_like(gate)
+        self.lib.wfo_swiglu(_ptr(gate, ctypes.c_float), _ptr(up, ctypes.c_float), _ptr(y, ctypes.c_float), gate.size)
+        return y
+
+    def add(self, a, b) -> np.ndarray:
+        a, b = self._f32(a), self._f32(b)
+        y = np.empty_like(a)
+        self.lib.wfo_add(_ptr(a, ctypes.c_float), _ptr(b, ctypes.c_float), _ptr(y, ctypes.c_float), a.size)
+        return y
+
+    def embedding(self, indices, table) -> np.ndarray:
+        idx = np.ascontiguousarray(indices, np.int64)
+        table = self._f32(table)
+        y = np.empty(idx.shape + (table.shape[1],), np.float32)
+        rc = self.lib.wfo_embedding(_ptr(idx, ctypes.c_int64), _ptr(table, ctypes.c_float), _ptr(y, ctypes.c_float), idx.size,
+                                    table.shape[0], table.shape[1])
+        if rc != 0:
+            raise IndexError("embedding index outside the table")
+        return y
 
     def count_not_close(self, expected, actual, atol=1e-4, rtol=1e-3) -> int:
         e = np.ascontiguousarray(expected, np.float32).ravel()

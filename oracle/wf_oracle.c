@@ -382,6 +382,94 @@ int64_t wfo_count_not_close(const float* expected, const float* actual, int64_t 
     return bad;
 }
 
+/* ---- the fp32 operations between the projections (CPU backend CustomCallKernel.java) --------------
+ * One float accumulator, elements in ascending order, every operation rounded to float as the Java
+ * code's float arithmetic is; Math.exp / Math.sqrt are the double functions, cast back to float. */
+
+/* CustomCallKernel.java:368-412.  gamma may be NULL (the optional second input). */
+void wfo_rms_norm(const float* x, const float* gamma, float* y, int64_t rows, int64_t n, float eps) {
+    for (int64_t b = 0; b < rows; b++) {
+        const float* in = x + b * n;
+        float sum_sq = 0;
+        for (int64_t i = 0; i < n; i++) sum_sq += in[i] * in[i];
+        float rms = (float)sqrt((double)(sum_sq / (float)n + eps));
+        float inv = 1.0f / rms;
+        for (int64_t i = 0; i < n; i++) {
+            float v = in[i] * inv;
+            if (gamma) v *= gamma[i];
+            y[b * n + i] = v;
+        }
+    }
+}
+
+/* CustomCallKernel.java:109-171.  gamma / beta may be NULL. */
+void wfo_layer_norm(const float* x, const float* gamma, const float* beta, float* y, int64_t rows, int64_t n, float eps) {
+    for (int64_t b = 0; b < rows; b++) {
+        const float* in = x + b * n;
+        float sum = 0;
+        for (int64_t i = 0; i < n; i++) sum += in[i];
+        float mean = sum / (float)n;
+        float var_sum = 0;
+        for (int64_t i = 0; i < n; i++) {
+            float d = in[i] - mean;
+            var_sum += d * d;
+        }
+        float var = var_sum / (float)n;
+        float inv = 1.0f / (float)sqrt((double)(var + eps));
+        for (int64_t i = 0; i < n; i++) {
+            float v = (in[i] - mean) * inv;
+            if (gamma) v *= gamma[i];
+            if (beta) v += beta[i];
+            y[b * n + i] = v;
+        }
+    }
+}
+
+/* CustomCallKernel.java:173-224 with the default dimension (the last one, inner size 1). */
+void wfo_softmax(const float* x, float* y, int64_t rows, int64_t n) {
+    for (int64_t b = 0; b < rows; b++) {
+        const float* in = x + b * n;
+        float mx = -INFINITY;
+        for (int64_t i = 0; i < n; i++)
+            if (in[i] > mx) mx = in[i];
+        float sum = 0;
+        for (int64_t i = 0; i < n; i++) sum += (float)exp((double)(in[i] - mx));
+        for (int64_t i = 0; i < n; i++) y[b * n + i] = (float)exp((double)(in[i] - mx)) / sum;
+    }
+}
+
+/* CustomCallKernel.java:262-280 */
+void wfo_silu(const float* x, float* y, int64_t n) {
+    for (int64_t i = 0; i < n; i++) {
+        float sigmoid = 1.0f / (1.0f + (float)exp((double)-x[i]));
+        y[i] = x[i] * sigmoid;
+    }
+}
+
+/* silu custom_call, then stablehlo.multiply (cpu/ops/scalar/MultiplyKernel: a[i] * b[i]) */
+void wfo_swiglu(const float* gate, const float* up, float* y, int64_t n) {
+    for (int64_t i = 0; i < n; i++) {
+        float sigmoid = 1.0f / (1.0f + (float)exp((double)-gate[i]));
+        float s = gate[i] * sigmoid;
+        y[i] = s * up[i];
+    }
+}
+
+/* stablehlo.add (cpu/ops/scalar/AddKernel: a[i] + b[i]) */
+void wfo_add(const float* a, const float* b, float* y, int64_t n) {
+    for (int64_t i = 0; i < n; i++) y[i] = a[i] + b[i];
+}
+
+/* CustomCallKernel.java:282-318; returns -1 at the first index outside the table (Java throws there). */
+int wfo_embedding(const int64_t* indices, const float* table, float* y, int64_t count, int64_t vocab, int64_t dim) {
+    for (int64_t i = 0; i < count; i++) {
+        int64_t idx = (int64_t)(int32_t)indices[i];
+        if (idx < 0 || idx >= vocab) return -1;
+        memcpy(y + i * dim, table + idx * dim, (size_t)dim * sizeof(float));
+    }
+    return 0;
+}
+
 int wfo_max_threads(void) {
     long n = sysconf(_SC_NPROCESSORS_ONLN);
     return n > 0 ? (int)n : 1;

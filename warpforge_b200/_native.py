@@ -36,6 +36,13 @@ SIGNATURES = {
     "wf_memcpy_h2d": (c_int, [c_i64, c_i64, c_vp, c_i64, c_i64, c_int]),
     "wf_memcpy_d2h": (c_int, [c_i64, c_vp, c_i64, c_i64, c_i64, c_int]),
     "wf_weight_upload": (c_int, [c_i64, c_int, c_vp, c_i64, c_i64, c_int, c_int, P(c_i64)]),
+    "wf_rms_norm": (c_int, [c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_f32, c_i64]),
+    "wf_layer_norm": (c_int, [c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_f32, c_i64]),
+    "wf_softmax": (c_int, [c_i64, c_i64, c_i64, c_i64, c_i64, c_i64]),
+    "wf_silu": (c_int, [c_i64, c_i64, c_i64, c_i64, c_i64]),
+    "wf_swiglu": (c_int, [c_i64, c_i64, c_i64, c_i64, c_i64, c_i64]),
+    "wf_add": (c_int, [c_i64, c_i64, c_i64, c_i64, c_i64, c_i64]),
+    "wf_embedding": (c_int, [c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_i64]),
     "wf_gguf_open": (c_int, [c_char_p, P(c_i64), c_char_p, c_i64]),
     "wf_gguf_close": (c_int, [c_i64]),
     "wf_gguf_info": (c_int, [c_i64, P(c_int), P(c_i64), P(c_i64), P(c_i64), P(c_int), P(c_i64)]),
@@ -80,6 +87,7 @@ WF_OK = 0
 WF_ERR_INVALID_ARGUMENT, WF_ERR_INVALID_HANDLE, WF_ERR_UNSUPPORTED_TYPE, WF_ERR_SHAPE = -1, -2, -3, -4
 WF_ERR_SHARD, WF_ERR_BUSY, WF_ERR_NO_DEVICE, WF_ERR_NOT_SM100 = -5, -6, -7, -8
 WF_ERR_NCCL_UNAVAILABLE, WF_ERR_DEVICE_WAIT, WF_ERR_TOO_LARGE, WF_ERR_GGUF = -9, -10, -11, -12
+WF_ERR_INDEX = -13
 WF_Q4_0_ORDER_REFERENCE, WF_Q4_0_ORDER_GGML = 0, 1
 WF_DTYPE_F32, WF_DTYPE_BF16 = 0, 1
 WF_OP_NEW_X, WF_OP_DEPENDS = 1, 2

@@ -329,11 +329,117 @@ class QuantizedLinearKernel(CudaOpKernel):
         return [Tensor(y, "f32")]
 
 
+@dataclass(frozen=True)
+class CustomCallOp:
+    """stablehlo.custom_call: only the target name and the result shape matter to the kernels
+    (the reference's CustomCallOp carries no parsed attributes either, CustomCallKernel.java:414-419)."""
+    call_target: str
+    result_shape: Sequence[int]
+    result_dtype: str = "f32"
+
+
+@dataclass(frozen=True)
+class AddOp:
+    """stablehlo.add on two fp32 tensors of one shape (the residual connection)."""
+    result_shape: Sequence[int]
+
+
+@dataclass(frozen=True)
+class MultiplyOp:
+    """stablehlo.multiply; only the fused form silu(gate) * up exists on the device (``swiglu``)."""
+    result_shape: Sequence[int]
+
+
+DEFAULT_EPS = 1e-5  # CustomCallKernel.java:421
+
+
+class CudaCustomCallKernel(CudaOpKernel):
+    """Mirror of nvidia/ops/CudaCustomCallKernel.java:30-66: dispatch on the call target; host tensors
+    are copied to the device, the kernel runs, the result comes back (as the reference does per call);
+    DeviceTensor inputs stay on the device and the call only enqueues.  Targets: rms_norm, layer_norm,
+    softmax, silu, embedding, plus ``swiglu`` (silu(gate) * up in one pass)."""
+
+    TARGETS = ("rms_norm", "layer_norm", "softmax", "silu", "embedding", "swiglu")
+
+    def __init__(self, context: CudaContext, salt: int = 0, stream: int = 0):
+        self.context, self.salt, self.stream = context, salt, stream
+
+    def get_stream(self) -> int:
+        return self.stream
+
+    def supports(self, op) -> bool:
+        return isinstance(op, (CustomCallOp, AddOp))
+
+    def _to_device(self, t, temps, dtype=np.float32):
+        if isinstance(t, DeviceTensor):
+            return t.ptr
+        a = np.ascontiguousarray(t.data if isinstance(t, Tensor) else t, dtype)
+        p = self.context.allocate(max(a.nbytes, 4))
+        temps.append(p)
+        if a.nbytes:
+            self.context.copy_to_device(p, a, self.stream, sync=True)
+        return p
+
+    def execute(self, op, inputs: List) -> List:
+        ctx, lib, s = self.context, self.context._lib, self.stream
+        target = "add" if isinstance(op, AddOp) else op.call_target
+        if target not in self.TARGETS + ("add",):
+            raise UnsupportedOperationError(f"Unknown custom_call target for CUDA: {target}")
+        on_device = isinstance(inputs[0], DeviceTensor)
+        temps: List[int] = []
+        try:
+            shape = tuple(inputs[0].shape())
+            if target == "embedding":
+                table_shape = tuple(inputs[1].shape())
+                out_shape = shape + (table_shape[1],)
+                count = int(np.prod(shape)) if shape else 1
+                idx = self._to_device(inputs[0], temps, np.int64)
+                table = self._to_device(inputs[1], temps)
+                out = ctx.allocate(max(count * table_shape[1] * 4, 4))
+                ctx._ck("wf_embedding", lib.wf_embedding(ctx.handle, idx, table, out, count, table_shape[0], table_shape[1], s))
+            else:
+                out_shape = shape
+                n = shape[-1] if shape else 1
+                total = int(np.prod(shape)) if shape else 1
+                rows = total // n if n else 0
+                ptrs = [self._to_device(t, temps) for t in inputs]
+                out = ctx.allocate(max(total * 4, 4))
+                opt = lambda i: ptrs[i] if len(ptrs) > i else 0
+                if target == "rms_norm":
+                    rc = lib.wf_rms_norm(ctx.handle, ptrs[0], opt(1), out, rows, n, DEFAULT_EPS, s)
+                elif target == "layer_norm":
+                    rc = lib.wf_layer_norm(ctx.handle, ptrs[0], opt(1), opt(2), out, rows, n, DEFAULT_EPS, s)
+                elif target == "softmax":
+                    rc = lib.wf_softmax(ctx.handle, ptrs[0], out, rows, n, s)
+                elif target == "silu":
+                    rc = lib.wf_silu(ctx.handle, ptrs[0], out, total, s)
+                else:
+                    if len(ptrs) != 2 or tuple(inputs[1].shape()) != shape:
+                        raise ValueError(f"{target} requires 2 inputs of one shape")
+                    fn = lib.wf_swiglu if target == "swiglu" else lib.wf_add
+                    rc = fn(ctx.handle, ptrs[0], ptrs[1], out, total, s)
+                ctx._ck("wf_" + target, rc)
+            if on_device:
+                return [DeviceTensor(out, out_shape, "f32", owner=ctx)]
+            host = np.empty(out_shape, np.float32)
+            try:
+                if host.nbytes:
+                    ctx.copy_to_host(host, out, s, sync=True)
+                ctx.synchronize(s)  # reports an embedding index outside the table
+            finally:
+                ctx.free(out)
+            return [Tensor(host, "f32")]
+        finally:
+            for p in temps:  # wf_free waits for the device, so work that still reads them has finished
+                ctx.free(p)
+
+
 class NvidiaBackend:
     def __init__(self, device_index: int = 0, salt: int = 0):
         self._device_index, self._salt = device_index, salt
         self.cuda_context = CudaContext(device_index)
-        self._kernels = {DotGeneralOp: QuantizedLinearKernel(self.cuda_context, salt)}
+        glue = CudaCustomCallKernel(self.cuda_context, salt)
+        self._kernels = {DotGeneralOp: QuantizedLinearKernel(self.cuda_context, salt), CustomCallOp: glue, AddOp: glue}
         self._closed = False
         self._weights: List[QuantizedWeight] = []
 

@@ -14,7 +14,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libwfb200.so")
-SOURCES = ["wf_runtime.cu", "wf_repack.cu", "wf_gemv.cu", "wf_gemm.cu", "wf_comm.cu", "wf_decode.cu", "wf_gguf.cu"]
+SOURCES = ["wf_runtime.cu", "wf_repack.cu", "wf_gemv.cu", "wf_gemm.cu", "wf_comm.cu", "wf_decode.cu", "wf_gguf.cu", "wf_glue.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler=-Wall",

@@ -21,6 +21,7 @@ constexpr uint32_t COMM_MAGIC = 0x5746434D;    // "WFCM"
 constexpr int STATUS_GEMV_FIXUP_TIMEOUT = 1;
 constexpr int STATUS_GEMM_PIPE_TIMEOUT = 2;
 constexpr int STATUS_PEER_WAIT_TIMEOUT = 4;
+constexpr int STATUS_BAD_INDEX = 8;  // an embedding index outside the table
 
 struct Context;
 

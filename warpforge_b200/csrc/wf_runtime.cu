@@ -293,6 +293,7 @@ int wf_stream_sync(int64_t ctx, int64_t stream) {
     WF_CUDA(c, cudaMemcpy(&st, c->d_status, sizeof st, cudaMemcpyDeviceToHost));
     if (st != 0) {
         WF_CUDA(c, cudaMemset(c->d_status, 0, sizeof st));
+        if (st == STATUS_BAD_INDEX) return set_error(c, WF_ERR_INDEX, "an embedding index was outside the table (its row was written as zeros)");
         return set_error(c, WF_ERR_DEVICE_WAIT, "a device-side bounded wait expired (status bits 0x%x)", st);
     }
     return WF_OK;
@@ -583,6 +584,7 @@ const char* wf_error_string(int status) {
         case WF_ERR_DEVICE_WAIT: return "WF_ERR_DEVICE_WAIT";
         case WF_ERR_TOO_LARGE: return "WF_ERR_TOO_LARGE";
         case WF_ERR_GGUF: return "WF_ERR_GGUF";
+        case WF_ERR_INDEX: return "WF_ERR_INDEX";
         default: break;
     }
     if (status >= WF_ERR_NCCL_BASE) return "WF_ERR_NCCL";
