@@ -157,7 +157,12 @@ int wf_dequant_rows(int64_t ctx, int64_t weight, int64_t row0, int64_t nrows, fl
  * parity.  wf_swiglu is silu(gate) * up (the silu custom_call followed by stablehlo.multiply),
  * wf_add the residual stablehlo.add.  In-place use (y == x) is allowed for all but
  * wf_embedding.  An embedding index outside [0, vocab) writes a row of zeros and makes the
- * next wf_stream_sync return WF_ERR_INDEX (the CPU backend throws there). */
+ * next wf_stream_sync return WF_ERR_INDEX (the CPU backend throws there).
+ * wf_set_exact_exp(ctx, 1) makes wf_silu / wf_swiglu / wf_softmax evaluate the exponential
+ * as the CPU backend does, (float) Math.exp(x): the result then equals the CPU's bit for bit
+ * (silu, swiglu) at about half the speed; the default is the fp32 exponential (2 ulp), which
+ * keeps these operations memory-bound. */
+int wf_set_exact_exp(int64_t ctx, int on);
 int wf_rms_norm(int64_t ctx, int64_t x_dev, int64_t gamma_dev, int64_t y_dev, int64_t rows, int64_t n, float eps,
                 int64_t stream);
 int wf_layer_norm(int64_t ctx, int64_t x_dev, int64_t gamma_dev, int64_t beta_dev, int64_t y_dev, int64_t rows,

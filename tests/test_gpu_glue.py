@@ -2,12 +2,16 @@
 swiglu, add, embedding) through the C ABI against the CPU oracle.
 
 Bars.  Element operations (silu, swiglu, add, embedding) follow the CPU arithmetic operation by
-operation: bit-exact, except that the double exp of the device and of the host libm may round a
-last double bit differently, so silu / swiglu allow 1 ulp on at most one element in 10^5.  Row
+operation.  With wf_set_exact_exp(1) they are bit-exact, except that the double exp of the device and
+of the host libm may round a last bit differently, so silu / swiglu allow 1 ulp on at most one element
+in 10^5.  In the default mode the exponential is the fp32 one (2 ulp): silu / swiglu must stay within
+8 ulp of the oracle where |x| <= 20 (sigmoid not yet rounded into 0 or 1) and meet the reference's rule
+for the target, |d| <= 1e-4 + 1e-3*|expected|, everywhere.  Row
 reductions are summed in another order than the CPU's one-after-another fp32 sum; they must meet the
 reference's own acceptance rule for these targets, |d| <= 1e-4 + 1e-3*|expected| on every element
-(warpforge-core/.../testing/ToleranceConfig.java:47-51), and the tighter max|d| <= 2e-5 * max|expected|
-(the size of the rounding noise of the oracle's own 16384-term fp32 sums)."""
+(warpforge-core/.../testing/ToleranceConfig.java:47-51), and the tighter max|d| <= 1e-4 * max|expected|:
+the oracle's one-accumulator fp32 sum over 16384 terms drops every term below half an ulp of the running sum,
+which biases it by about 2e-5 relative; the device's sums do not lose them."""
 import ctypes
 
 import numpy as np
@@ -46,7 +50,7 @@ def _check_rows(oracle, got, want):
     assert got.shape == want.shape
     assert oracle.count_not_close(want, got, 1e-4, 1e-3) == 0
     scale = float(np.max(np.abs(want))) or 1.0
-    assert float(np.max(np.abs(got.astype(np.float64) - want))) <= 2e-5 * scale
+    assert float(np.max(np.abs(got.astype(np.float64) - want))) <= 1e-4 * scale
 
 
 def _check_elements(got, want):
@@ -55,6 +59,15 @@ def _check_elements(got, want):
     assert np.array_equal(np.isnan(got), nan)
     u = u[~nan]
     assert u.size == 0 or (u.max() <= 1 and np.count_nonzero(u) <= max(1, u.size // 100000)), f"max ulp {u.max()}, {np.count_nonzero(u)} differ"
+
+
+def _check_elements_fp32_exp(oracle, got, want, x):
+    nan = np.isnan(want)
+    assert np.array_equal(np.isnan(got), nan)
+    ok = ~nan & np.isfinite(want)
+    assert oracle.count_not_close(want[ok], got[ok], 1e-4, 1e-3) == 0
+    near = ok & (np.abs(x) <= 20)
+    assert near.sum() == 0 or _ulps(got[near], want[near]).max() <= 8
 
 
 SHAPES = [(1, 4096), (16, 4096), (3, 11008), (512, 4096), (5, 1000), (7, 7), (2, 8192), (2, 16384), (4, 8196), (1, 1), (33, 130)]
@@ -84,9 +97,14 @@ def test_layer_norm(backend, oracle, rows, n):
 def test_softmax(backend, oracle, rows, n):
     rng = np.random.default_rng(rows * 41 + n)
     x = (rng.standard_normal((rows, n)) * 4).astype(np.float32)
-    got = _call(backend, "softmax", x)
-    _check_rows(oracle, got, oracle.softmax(x))
-    assert np.allclose(got.sum(axis=-1), 1.0, atol=1e-5)
+    for exact in (False, True):
+        backend.cuda_context.set_exact_exp(exact)
+        try:
+            got = _call(backend, "softmax", x)
+        finally:
+            backend.cuda_context.set_exact_exp(False)
+        _check_rows(oracle, got, oracle.softmax(x))
+        assert np.allclose(got.sum(axis=-1), 1.0, atol=1e-5)
 
 
 def test_reference_test_cases(backend, oracle):
@@ -96,7 +114,7 @@ def test_reference_test_cases(backend, oracle):
     y = _call(backend, "softmax", np.array([1000, 1001, 1002, 1003], np.float32))
     assert np.all(np.isfinite(y)) and abs(float(y.sum()) - 1) < 1e-5 and y[0] < y[1] < y[2] < y[3]
     y = _call(backend, "silu", np.array([1.0, 2.0, -1.0], np.float32))
-    assert np.array_equal(y, oracle.silu(np.array([1.0, 2.0, -1.0], np.float32)))
+    assert np.allclose(y, oracle.silu(np.array([1.0, 2.0, -1.0], np.float32)), atol=1e-5, rtol=0)  # the reference test's EPSILON
     y = _call(backend, "rms_norm", np.array([[3, 4]], np.float32))
     assert abs(np.sqrt(float(np.sum(y * y)) / 2) - 1) < 1e-5
 
@@ -108,8 +126,14 @@ def test_silu_swiglu_add(backend, oracle, count):
     b = rng.standard_normal(count).astype(np.float32)
     if count >= 16:
         a[:8] = [0.0, -0.0, np.inf, -np.inf, np.nan, 100.0, -100.0, 1e-30]
-    _check_elements(_call(backend, "silu", a), oracle.silu(a))
-    _check_elements(_call(backend, "swiglu", a, b), oracle.swiglu(a, b))
+    _check_elements_fp32_exp(oracle, _call(backend, "silu", a), oracle.silu(a), a)
+    _check_elements_fp32_exp(oracle, _call(backend, "swiglu", a, b), oracle.swiglu(a, b), a)
+    backend.cuda_context.set_exact_exp(True)
+    try:
+        _check_elements(_call(backend, "silu", a), oracle.silu(a))
+        _check_elements(_call(backend, "swiglu", a, b), oracle.swiglu(a, b))
+    finally:
+        backend.cuda_context.set_exact_exp(False)
     got, want = _call(backend, "add", a, b), oracle.add(a, b)
     assert np.array_equal(got.view(np.uint32)[~np.isnan(want)], want.view(np.uint32)[~np.isnan(want)])
 
@@ -161,7 +185,9 @@ def test_device_tensors_in_place_and_odd_alignment(backend, oracle):
         ctx.copy_to_host(y, d_x)
         _check_rows(oracle, y, oracle.rms_norm(x, g))
         ctx.copy_to_device(d_x, x)
+        ctx.set_exact_exp(True)
         assert lib.wf_silu(ctx.handle, d_x, d_x, rows * n, 0) == N.WF_OK
+        ctx.set_exact_exp(False)
         ctx.copy_to_host(y, d_x)
         _check_elements(y, oracle.silu(x))
     ctx.free(buf)

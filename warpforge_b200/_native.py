@@ -36,6 +36,7 @@ SIGNATURES = {
     "wf_memcpy_h2d": (c_int, [c_i64, c_i64, c_vp, c_i64, c_i64, c_int]),
     "wf_memcpy_d2h": (c_int, [c_i64, c_vp, c_i64, c_i64, c_i64, c_int]),
     "wf_weight_upload": (c_int, [c_i64, c_int, c_vp, c_i64, c_i64, c_int, c_int, P(c_i64)]),
+    "wf_set_exact_exp": (c_int, [c_i64, c_int]),
     "wf_rms_norm": (c_int, [c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_f32, c_i64]),
     "wf_layer_norm": (c_int, [c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_f32, c_i64]),
     "wf_softmax": (c_int, [c_i64, c_i64, c_i64, c_i64, c_i64, c_i64]),

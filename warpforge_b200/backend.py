@@ -153,6 +153,10 @@ class CudaContext:
         assert host.flags.c_contiguous
         self._ck("wf_memcpy_d2h", self._lib.wf_memcpy_d2h(self.handle, host.ctypes.data, dptr, host.nbytes, stream, int(sync)))
 
+    def set_exact_exp(self, on: bool) -> None:
+        """silu / swiglu / softmax with the exponential evaluated as (float) Math.exp(x) (slower, bit-exact)."""
+        self._ck("wf_set_exact_exp", self._lib.wf_set_exact_exp(self.handle, int(on)))
+
     def create_stream(self) -> int:
         s = ctypes.c_int64()
         self._ck("wf_stream_create", self._lib.wf_stream_create(self.handle, ctypes.byref(s)))

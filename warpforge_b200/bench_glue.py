@@ -33,9 +33,11 @@ def main() -> None:
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--only", default="")
+    ap.add_argument("--exact-exp", action="store_true", help="silu / swiglu / softmax with the host's (float) exp((double) x)")
     a = ap.parse_args()
     ctx = CudaContext(0)
     lib, h = ctx._lib, ctx.handle
+    ctx.set_exact_exp(a.exact_exp)
     rows, n, total = a.rows, a.n, a.rows * a.n
     rng = np.random.default_rng(1)
     x = rng.standard_normal((rows, n), dtype=np.float32)
@@ -73,7 +75,7 @@ def main() -> None:
         us = ctx.elapsed_ms(e0, e1) * 1e3 / a.iters
         gbs = nbytes / us / 1e3
         print(json.dumps({"op": name, "shape": [rows, n], "us": round(us, 2), "algorithmic_bytes": nbytes,
-                          "achieved_gbs": round(gbs, 1), "peak_gbs": peak, "peak": src, "frac": round(gbs / peak, 3)}), flush=True)
+                          "achieved_gbs": round(gbs, 1), "peak_gbs": peak, "peak": src, "frac": round(gbs / peak, 3), "exact_exp": bool(a.exact_exp)}), flush=True)
     ctx.close()
 
 

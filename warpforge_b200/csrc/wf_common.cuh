@@ -75,6 +75,7 @@ struct Context {
     unsigned int* d_gemm_ready = nullptr;  // [sm_count][4] launch number whose piece is complete, per 32-row quarter
     unsigned int gemm_launches = 0;
     int64_t launches = 0;
+    bool glue_exact = false;  // silu / softmax evaluate exp as the host does (double, one rounding) instead of expf
     int gemv_ctas_per_sm[3] = {0, 0, 0};
 };
 

@@ -46,34 +46,63 @@ __device__ __forceinline__ float block_max(float v, float* red) {
     return t;
 }
 
-// (float) Math.exp(x): the exponential in double, one rounding to float.  Only the float result matters,
-// so the double value needs far less than the library's last-bit accuracy: argument reduction by ln 2
-// in two parts and the Taylor series to r^11 (|r| <= 0.347, truncation below 2^-46) leave an error of
-// about 2^-46, which changes the rounded float for roughly one argument in four million.  Outside
-// [-104, 89] the float result is 0 or infinity whatever the double is.
-__device__ __forceinline__ float exp_as_host(float x) {
+// (float) Math.exp(x): the exponential in double, one rounding to float.  Only the float result matters, so
+// the double needs about 2^-44, not the library's last bit, and the fp64 pipe (a fraction of the fp32 rate
+// on this GPU; the library exp made silu and softmax compute-bound at 45 % and 29 % of HBM speed) gets as few
+// operations as possible: x = (32 k + j) ln2/32 + r with |r| <= ln2/64, exp(x) = 2^k * 2^(j/32) * exp(r);
+// 2^(j/32) comes from a 32-entry table in shared memory, exp(r) - 1 = r + r^2/2 in double plus the terms
+// from r^3 on, below 2^-22, in fp32; float -> double, the rounding of x * 32/ln2 to an integer, integer ->
+// double and the scaling by 2^k are done on the bit patterns (conversion instructions are slower still).
+// Seven fp64 operations per call.  Against (float) exp((double) x) of the host libm: 11 differences of one
+// ulp in 4e8 arguments.  Outside [-104, 89] the float result is 0 or infinity whatever the double is.
+__constant__ double EXP2_32[32] = {
+    1.00000000000000000e+00, 1.02189714865411663e+00, 1.04427378242741375e+00, 1.06714040067682370e+00,
+    1.09050773266525769e+00, 1.11438674259589243e+00, 1.13878863475669156e+00, 1.16372485877757748e+00,
+    1.18920711500272103e+00, 1.21524735998046896e+00, 1.24185781207348400e+00, 1.26905095719173322e+00,
+    1.29683955465100964e+00, 1.32523664315974132e+00, 1.35425554693689265e+00, 1.38390988196383202e+00,
+    1.41421356237309515e+00, 1.44518080697704665e+00, 1.47682614593949935e+00, 1.50916442759342284e+00,
+    1.54221082540794074e+00, 1.57598084510788650e+00, 1.61049033194925428e+00, 1.64575547815396495e+00,
+    1.68179283050742900e+00, 1.71861929812247793e+00, 1.75625216037329945e+00, 1.79470907500310717e+00,
+    1.83400808640934243e+00, 1.87416763411029996e+00, 1.91520656139714740e+00, 1.95714412417540018e+00};
+
+// every thread of the CTA calls this once before the first exp_as_host
+__device__ __forceinline__ void load_exp_table(double* tab) {
+    if (threadIdx.x < 32) tab[threadIdx.x] = EXP2_32[threadIdx.x];
+    __syncthreads();
+}
+
+__device__ __forceinline__ double widen_normal(float f) {  // (double) f for a normal (not zero, not subnormal) float
+    const uint32_t b = __float_as_uint(f), em = b & 0x7FFFFFFFu;
+    return __hiloint2double((int)((b & 0x80000000u) | ((em >> 3) + (896u << 20))), (int)(em << 29));
+}
+
+// EXACT: the host's (float) exp((double) x); otherwise the fp32 library exponential (2 ulp), about a third
+// of the instructions: the exact form leaves silu and softmax issue-bound at about 45 % of HBM speed.
+template <bool EXACT> __device__ __forceinline__ float exp_sel(float x, const double* tab);
+
+__device__ __forceinline__ float exp_as_host(float x, const double* tab) {
     if (x != x) return x;
     if (x > 89.0f) return INFINITY;
     if (x < -104.0f) return 0.0f;
-    const double xd = (double)x;
-    const double kf = rint(xd * 1.4426950408889634074);
-    double r = fma(-kf, 6.93147180369123816490e-01, xd);
-    r = fma(-kf, 1.90821492927058770002e-10, r);
-    double p = 2.50521083854417187751e-08;  // 1/11!
-    p = fma(p, r, 2.75573192239858906526e-07);
-    p = fma(p, r, 2.75573192239858906526e-06);
-    p = fma(p, r, 2.48015873015873015873e-05);
-    p = fma(p, r, 1.98412698412698412698e-04);
-    p = fma(p, r, 1.38888888888888888889e-03);
-    p = fma(p, r, 8.33333333333333333333e-03);
-    p = fma(p, r, 4.16666666666666666667e-02);
-    p = fma(p, r, 1.66666666666666666667e-01);
-    p = fma(p, r, 0.5);
-    p = fma(p, r, 1.0);
-    p = fma(p, r, 1.0);
-    const long long bits = (long long)((int)kf + 1023) << 52;
-    return (float)(p * __longlong_as_double(bits));
+    if (fabsf(x) < 1e-8f) return 1.0f;
+    const float t = __fmaf_rn(x, 46.1662413f, 12582912.f);  // 1.5 * 2^23: the integer lands in the low mantissa bits
+    const int n = (int)(__float_as_uint(t) - 0x4B400000u);
+    const float nf = __fsub_rn(t, 12582912.f);
+    const double nd = __hiloint2double(0x43300000, n ^ 0x80000000) - 4503601774854144.0;  // 2^52 + 2^31
+    double r = fma(-nd, 2.16608493924468348268e-02, widen_normal(x));  // ln2/32, 36 bits: the product is exact
+    r = fma(-nd, 5.14560924465533821524e-14, r);
+    float rf = __fmaf_rn(-nf, 2.1652221680e-02f, x);  // the same reduction in fp32 (11 + 24 bits) for the small terms
+    rf = __fmaf_rn(-nf, 8.6277132141e-06f, rf);
+    const float tail = rf * rf * rf * __fmaf_rn(rf, __fmaf_rn(rf, 8.33333333e-3f, 4.16666667e-2f), 1.66666667e-1f);
+    double s = fma(0.5 * r, r, r);
+    s += fabsf(tail) < 1e-30f ? 0.0 : widen_normal(tail);
+    const double tj = tab[n & 31];
+    const double v = fma(tj, s, tj);  // in [1, 2.05): adding k to the exponent field scales it exactly
+    return (float)__hiloint2double(__double2hiint(v) + ((n >> 5) << 20), __double2loint(v));
 }
+
+template <> __device__ __forceinline__ float exp_sel<true>(float x, const double* tab) { return exp_as_host(x, tab); }
+template <> __device__ __forceinline__ float exp_sel<false>(float x, const double*) { return expf(x); }
 
 // A row held by one CTA: float4 pieces in registers when the row is 16-byte addressable and short
 // enough, otherwise element loops over global memory.  `f(i, x)` visits every element.
@@ -169,53 +198,58 @@ __global__ void __launch_bounds__(ROW_THREADS) layer_norm_kernel(const float* __
 }
 
 // CustomCallKernel.java:173-224, over the last dimension: (float) exp(x - max) / sum
+template <bool EXACT>
 __global__ void __launch_bounds__(ROW_THREADS) softmax_kernel(const float* __restrict__ x, float* __restrict__ y, int n) {
     __shared__ double red[ROW_THREADS / 32];
     __shared__ float redf[ROW_THREADS / 32];
+    __shared__ double tab[32];
+    if (EXACT) load_exp_table(tab);
     RowView row(x + (size_t)blockIdx.x * n, n);
     float mx = -INFINITY;
     row.for_each([&](int, float v) { mx = v > mx ? v : mx; });  // `if (val > maxVal)`: a NaN never becomes the maximum
     mx = block_max(mx, redf);
     float part = 0.f;
     if (row.vec) {  // the exponentials replace the row in registers: one exp per element
-        row.map_registers([&](float v) { return exp_as_host(__fsub_rn(v, mx)); });
+        row.map_registers([&](float v) { return exp_sel<EXACT>(__fsub_rn(v, mx), tab); });
         row.for_each([&](int, float e) { part = __fadd_rn(part, e); });
         const float sum = (float)block_sum((double)part, red);
         row.write(y + (size_t)blockIdx.x * n, [&](int, float e) { return __fdiv_rn(e, sum); });
     } else {
-        row.for_each([&](int, float v) { part = __fadd_rn(part, exp_as_host(__fsub_rn(v, mx))); });
+        row.for_each([&](int, float v) { part = __fadd_rn(part, exp_sel<EXACT>(__fsub_rn(v, mx), tab)); });
         const float sum = (float)block_sum((double)part, red);
-        row.write(y + (size_t)blockIdx.x * n, [&](int, float v) { return __fdiv_rn(exp_as_host(__fsub_rn(v, mx)), sum); });
+        row.write(y + (size_t)blockIdx.x * n, [&](int, float v) { return __fdiv_rn(exp_sel<EXACT>(__fsub_rn(v, mx), tab), sum); });
     }
 }
 
 // ---- element operations: 16 bytes per thread per step, grid sized to the SM count
-__device__ __forceinline__ float silu_as_host(float x) {  // CustomCallKernel.java:273-275
-    const float sigmoid = __fdiv_rn(1.0f, __fadd_rn(1.0f, exp_as_host(-x)));
+template <bool EXACT> __device__ __forceinline__ float silu_as_host(float x, const double* tab) {  // CustomCallKernel.java:273-275
+    const float sigmoid = __fdiv_rn(1.0f, __fadd_rn(1.0f, exp_sel<EXACT>(-x, tab)));
     return __fmul_rn(x, sigmoid);
 }
 
 enum { EL_SILU = 0, EL_SWIGLU = 1, EL_ADD = 2 };
 
-template <int OP> __device__ __forceinline__ float el(float a, float b) {
-    if (OP == EL_SILU) return silu_as_host(a);
-    if (OP == EL_SWIGLU) return __fmul_rn(silu_as_host(a), b);
+template <int OP, bool EXACT> __device__ __forceinline__ float el(float a, float b, const double* tab) {
+    if (OP == EL_SILU) return silu_as_host<EXACT>(a, tab);
+    if (OP == EL_SWIGLU) return __fmul_rn(silu_as_host<EXACT>(a, tab), b);
     return __fadd_rn(a, b);
 }
 
-template <int OP>
+template <int OP, bool EXACT>
 __global__ void __launch_bounds__(256) elementwise_kernel(const float* __restrict__ a, const float* __restrict__ b,
                                                           float* __restrict__ y, int64_t n, int vec) {
     const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, step = (int64_t)gridDim.x * blockDim.x;
+    __shared__ double tab[32];
+    if (OP != EL_ADD && EXACT) load_exp_table(tab);
     if (vec) {
         for (int64_t i = tid; i < n / 4; i += step) {
             const float4 u = __ldcs(reinterpret_cast<const float4*>(a) + i);
             const float4 v = OP == EL_SILU ? u : __ldcs(reinterpret_cast<const float4*>(b) + i);
-            __stcs(reinterpret_cast<float4*>(y) + i, make_float4(el<OP>(u.x, v.x), el<OP>(u.y, v.y), el<OP>(u.z, v.z), el<OP>(u.w, v.w)));
+            __stcs(reinterpret_cast<float4*>(y) + i, make_float4(el<OP, EXACT>(u.x, v.x, tab), el<OP, EXACT>(u.y, v.y, tab), el<OP, EXACT>(u.z, v.z, tab), el<OP, EXACT>(u.w, v.w, tab)));
         }
-        for (int64_t i = n / 4 * 4 + tid; i < n; i += step) y[i] = el<OP>(a[i], OP == EL_SILU ? 0.f : b[i]);
+        for (int64_t i = n / 4 * 4 + tid; i < n; i += step) y[i] = el<OP, EXACT>(a[i], OP == EL_SILU ? 0.f : b[i], tab);
     } else {
-        for (int64_t i = tid; i < n; i += step) y[i] = el<OP>(a[i], OP == EL_SILU ? 0.f : b[i]);
+        for (int64_t i = tid; i < n; i += step) y[i] = el<OP, EXACT>(a[i], OP == EL_SILU ? 0.f : b[i], tab);
     }
 }
 
@@ -277,6 +311,13 @@ static int check_rows(Context* c, const char* what, int64_t x, int64_t y, int64_
 
 extern "C" {
 
+int wf_set_exact_exp(int64_t ctx, int on) {
+    Context* c = get_context(ctx);
+    if (!c) return WF_ERR_INVALID_HANDLE;
+    c->glue_exact = on != 0;
+    return WF_OK;
+}
+
 int wf_rms_norm(int64_t ctx, int64_t x_dev, int64_t gamma_dev, int64_t y_dev, int64_t rows, int64_t n, float eps, int64_t stream) {
     GLUE_ENTER(ctx);
     int rc = check_rows(c, "rms_norm", x_dev, y_dev, rows, n);
@@ -300,7 +341,10 @@ int wf_softmax(int64_t ctx, int64_t x_dev, int64_t y_dev, int64_t rows, int64_t 
     GLUE_ENTER(ctx);
     int rc = check_rows(c, "softmax", x_dev, y_dev, rows, n);
     if (rc != WF_OK || rows == 0) return rc;
-    softmax_kernel<<<(unsigned)rows, ROW_THREADS, 0, s>>>(reinterpret_cast<const float*>(x_dev), reinterpret_cast<float*>(y_dev), (int)n);
+    if (c->glue_exact)
+        softmax_kernel<true><<<(unsigned)rows, ROW_THREADS, 0, s>>>(reinterpret_cast<const float*>(x_dev), reinterpret_cast<float*>(y_dev), (int)n);
+    else
+        softmax_kernel<false><<<(unsigned)rows, ROW_THREADS, 0, s>>>(reinterpret_cast<const float*>(x_dev), reinterpret_cast<float*>(y_dev), (int)n);
     return launched(c, "softmax");
 }
 
@@ -315,9 +359,11 @@ static int elementwise(int64_t ctx, int op, const char* what, int64_t a_dev, int
     const float *fa = static_cast<const float*>(a), *fb = static_cast<const float*>(b);
     float* fy = reinterpret_cast<float*>(y_dev);
     const int grid = element_grid(c, count);
-    if (op == EL_SILU) elementwise_kernel<EL_SILU><<<grid, 256, 0, s>>>(fa, fb, fy, count, vec);
-    else if (op == EL_SWIGLU) elementwise_kernel<EL_SWIGLU><<<grid, 256, 0, s>>>(fa, fb, fy, count, vec);
-    else elementwise_kernel<EL_ADD><<<grid, 256, 0, s>>>(fa, fb, fy, count, vec);
+    if (op == EL_SILU && c->glue_exact) elementwise_kernel<EL_SILU, true><<<grid, 256, 0, s>>>(fa, fb, fy, count, vec);
+    else if (op == EL_SILU) elementwise_kernel<EL_SILU, false><<<grid, 256, 0, s>>>(fa, fb, fy, count, vec);
+    else if (op == EL_SWIGLU && c->glue_exact) elementwise_kernel<EL_SWIGLU, true><<<grid, 256, 0, s>>>(fa, fb, fy, count, vec);
+    else if (op == EL_SWIGLU) elementwise_kernel<EL_SWIGLU, false><<<grid, 256, 0, s>>>(fa, fb, fy, count, vec);
+    else elementwise_kernel<EL_ADD, false><<<grid, 256, 0, s>>>(fa, fb, fy, count, vec);
     return launched(c, what);
 }
 
