@@ -273,13 +273,14 @@ def np_dequant_q4_0(blocks, n: int) -> np.ndarray:
     return (vals * d[:, None]).astype(np.float32).ravel()[:n]
 
 
-def q4_0_ggml_to_reference_order(blocks) -> np.ndarray:
-    """Q4_0 blocks in ggml's nibble order (byte i = elements i and i+16) rewritten in the order the
-    reference's Dequantizer.java:251-279 reads (byte i = elements 2i and 2i+1); scales untouched."""
-    blk = np.asarray(blocks, np.uint8).reshape(-1, 18).copy()
-    qs = blk[:, 2:]
+def q4_0_ggml_to_reference_order(blocks, header: int = 2) -> np.ndarray:
+    """Q4_0 blocks (header 2: the scale) or Q4_1 blocks (header 4: scale and min) in ggml's nibble order
+    (byte i = elements i and i+16) rewritten in the order the reference's Dequantizer.java:251-279 /
+    :304-358 reads (byte i = elements 2i and 2i+1); the header bytes are untouched."""
+    blk = np.asarray(blocks, np.uint8).reshape(-1, header + 16).copy()
+    qs = blk[:, header:]
     elems = np.concatenate([qs & 0x0F, qs >> 4], axis=1)  # [nb, 32] in element order
-    blk[:, 2:] = elems[:, 0::2] | (elems[:, 1::2] << 4)
+    blk[:, header:] = elems[:, 0::2] | (elems[:, 1::2] << 4)
     return blk.ravel()
 
 

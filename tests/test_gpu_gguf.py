@@ -29,7 +29,7 @@ def backend():
 def model_file(tmp_path_factory):
     """A small model-shaped file: one linear weight per quantization type, {k, rows} in file order,
     between tensors of other types so that offsets and alignment padding matter."""
-    specs = {"q4_0": (96, 512), "q8_0": (40, 256), "q4_k": (64, 1024)}
+    specs = {"q4_0": (96, 512), "q8_0": (40, 256), "q4_k": (64, 1024), "q4_1": (48, 384)}
     blocks = {n: Q.synth_weight(QT[n][0], r, k, 300 + r) for n, (r, k) in specs.items()}
     tensors = [("token_embd.weight", (8, 3), 0, np.arange(24, dtype=np.float32).tobytes())]
     for n, (r, k) in specs.items():
@@ -41,7 +41,7 @@ def model_file(tmp_path_factory):
     return p, specs, blocks
 
 
-@pytest.mark.parametrize("name", ["q4_0", "q8_0", "q4_k"])
+@pytest.mark.parametrize("name", ["q4_0", "q8_0", "q4_k", "q4_1"])
 def test_upload_from_file_is_bit_exact(backend, oracle, model_file, name):
     p, specs, blocks = model_file
     rows, k = specs[name]
@@ -55,7 +55,7 @@ def test_upload_from_file_is_bit_exact(backend, oracle, model_file, name):
     w.close()
 
 
-@pytest.mark.parametrize("name", ["q4_0", "q8_0", "q4_k"])
+@pytest.mark.parametrize("name", ["q4_0", "q8_0", "q4_k", "q4_1"])
 def test_sharded_upload_and_linear(backend, oracle, model_file, name):
     from warpforge_b200.backend import Tensor
 
@@ -99,7 +99,8 @@ def test_file_written_by_the_gguf_package(backend, oracle, tmp_path):
     p = tmp_path / "pkg.gguf"
     wr = gguf.GGUFWriter(str(p), "llama")
     q = {}
-    for name, t in (("q4", gguf.GGMLQuantizationType.Q4_0), ("q8", gguf.GGMLQuantizationType.Q8_0)):
+    types = (("q4", gguf.GGMLQuantizationType.Q4_0), ("q8", gguf.GGMLQuantizationType.Q8_0), ("q41", gguf.GGMLQuantizationType.Q4_1))
+    for name, t in types:
         q[name] = gguf.quants.quantize(dense, t)
         wr.add_tensor(f"{name}.weight", q[name], raw_dtype=t)
     wr.write_header_to_file()
@@ -107,12 +108,23 @@ def test_file_written_by_the_gguf_package(backend, oracle, tmp_path):
     wr.write_tensors_to_file()
     wr.close()
     with GGUF.open(p) as g:
-        for name, t in (("q4", gguf.GGMLQuantizationType.Q4_0), ("q8", gguf.GGMLQuantizationType.Q8_0)):
+        for name, t in types:
             w = g.upload(backend.cuda_context, f"{name}.weight", q4_0_order=N.WF_Q4_0_ORDER_GGML)
             assert (w.rows, w.k) == (48, 256)
             want = gguf.quants.dequantize(q[name], t).astype(np.float32)
             assert np.array_equal(w.dequantize_to_array().view(np.uint32), want.view(np.uint32))
             w.close()
+
+
+def test_q4_1_in_ggml_order(backend, oracle, model_file):
+    p, specs, blocks = model_file
+    rows, k = specs["q4_1"]
+    with GGUF.open(p) as g:
+        w = g.upload(backend.cuda_context, "blk.0.q4_1.weight", q4_0_order=N.WF_Q4_0_ORDER_GGML)
+    got = w.dequantize_to_array()
+    w.close()
+    want = oracle.dequant(O.Q4_1, O.q4_0_ggml_to_reference_order(blocks["q4_1"], header=4), rows * k).reshape(rows, k)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
 
 
 def test_upload_errors(backend, model_file):

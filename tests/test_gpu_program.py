@@ -44,6 +44,40 @@ def test_program_equals_per_op_kernels(oracle, tokens):
         ctx.close()
 
 
+@pytest.mark.parametrize("qname", ["Q4_0", "Q4_1", "Q8_0", "Q4_K"])
+@pytest.mark.parametrize("tokens", [1, 5])
+def test_program_every_quantization_type(oracle, qname, tokens):
+    """A small two-layer stack per type: the program's outputs equal the per-projection kernels' bit for bit
+    and the oracle within the matmul tolerance (1 token: the single-column kernel, 5: the eight-column one)."""
+    from warpforge_b200.backend import CudaContext
+    from warpforge_b200.decode import ProjectionStack, StackSpec
+
+    qt = Q.QuantizationType[qname]
+    oq = {"Q4_0": O.Q4_0, "Q4_1": O.Q4_1, "Q8_0": O.Q8_0, "Q4_K": O.Q4_K}[qname]
+    spec = StackSpec("small " + qname, qt, 2, (("wq", 512, 512), ("wk", 512, 512), ("wo", 512, 512), ("wgate", 1280, 512),
+                                                ("wup", 1280, 512), ("wdown", 512, 1280)), 0)
+    ctx = CudaContext(0)
+    try:
+        st = ProjectionStack(ctx, spec, tokens=tokens)
+        st._issue()
+        ctx.synchronize()
+        ref = {n: st.read_output(n) for n, _, _ in st.spec.projections}
+        for n, ptr in st.y_dev.items():
+            ctx.copy_to_device(ptr, np.zeros_like(ref[n]))
+        st.build_program()
+        for _ in range(2):
+            st.run_program()
+        ctx.synchronize()
+        for name, rows, k in st.spec.projections:
+            got = st.read_output(name)
+            assert np.array_equal(got.view(np.uint32), ref[name].view(np.uint32)), name
+            want = oracle.qlinear(oq, st.blocks[name], rows, k, Q.bf16_bits_to_float(st.x_host[k]), nthreads=oracle.max_threads())
+            assert np.max(np.abs(got - want)) <= 1e-3 * np.max(np.abs(want)), name
+        st.close()
+    finally:
+        ctx.close()
+
+
 def test_program_rejects_bad_arguments():
     import ctypes
 

@@ -236,3 +236,16 @@ def test_q4_0_ggml_order_against_gguf_package(oracle):
     got = oracle.dequant(O.Q4_0, O.q4_0_ggml_to_reference_order(w), 8 * 256)
     assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
     assert np.array_equal(O.np_dequant_q4_0_ggml(w, 8 * 256).view(np.uint32), want.view(np.uint32))
+
+
+def test_q4_1_ggml_order_against_gguf_package(oracle):
+    """Q4_1 (Dequantizer.java:304-358 has no block test in the reference): ggml-ordered blocks rewritten to
+    the reference's order dequantize to what the gguf package makes of them, up to the package's fused
+    d * q + m (it computes in fp32 numpy: product and sum rounded separately, as the reference does)."""
+    gguf = pytest.importorskip("gguf")
+    from gguf import quants
+
+    w = Q.synth_q4_1(8, 256, 12)
+    want = quants.dequantize(w.reshape(-1, 20), gguf.GGMLQuantizationType.Q4_1).astype(np.float32).ravel()
+    got = oracle.dequant(O.Q4_1, O.q4_0_ggml_to_reference_order(w, header=4), 8 * 256)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))

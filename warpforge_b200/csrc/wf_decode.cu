@@ -445,9 +445,9 @@ int wf_program_run(int64_t ctx, int64_t program, int64_t stream) {
     const int qt = pr->qtype;
     cudaError_t e;
     if (pr->m == 1)
-        e = qt == WF_QTYPE_Q4_0 ? program_launch<WF_QTYPE_Q4_0, 1>(*pr, s) : qt == WF_QTYPE_Q8_0 ? program_launch<WF_QTYPE_Q8_0, 1>(*pr, s) : program_launch<WF_QTYPE_Q4_K, 1>(*pr, s);
+        e = qt == WF_QTYPE_Q4_0 ? program_launch<WF_QTYPE_Q4_0, 1>(*pr, s) : qt == WF_QTYPE_Q4_1 ? program_launch<WF_QTYPE_Q4_1, 1>(*pr, s) : qt == WF_QTYPE_Q8_0 ? program_launch<WF_QTYPE_Q8_0, 1>(*pr, s) : program_launch<WF_QTYPE_Q4_K, 1>(*pr, s);
     else
-        e = qt == WF_QTYPE_Q4_0 ? program_launch<WF_QTYPE_Q4_0, 8>(*pr, s) : qt == WF_QTYPE_Q8_0 ? program_launch<WF_QTYPE_Q8_0, 8>(*pr, s) : program_launch<WF_QTYPE_Q4_K, 8>(*pr, s);
+        e = qt == WF_QTYPE_Q4_0 ? program_launch<WF_QTYPE_Q4_0, 8>(*pr, s) : qt == WF_QTYPE_Q4_1 ? program_launch<WF_QTYPE_Q4_1, 8>(*pr, s) : qt == WF_QTYPE_Q8_0 ? program_launch<WF_QTYPE_Q8_0, 8>(*pr, s) : program_launch<WF_QTYPE_Q4_K, 8>(*pr, s);
     if (e != cudaSuccess) return cuda_status(c, e, "program launch");
     c->launches++;
     return WF_OK;

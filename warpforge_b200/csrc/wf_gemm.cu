@@ -271,6 +271,36 @@ template <> struct DequantRegs<WF_QTYPE_Q4_0> {
     }
 };
 
+template <> struct DequantRegs<WF_QTYPE_Q4_1> {
+    uint4 c[2];
+    uint2 sc[2], mn[2];
+    __device__ __forceinline__ void load(const uint8_t* tile, int kb, int lane) {
+        (void)kb;
+        using T = Tile<WF_QTYPE_Q4_1>;
+        const int g = lane >> 2;
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            c[h] = __ldg(reinterpret_cast<const uint4*>(tile + h * 512 + lane * 16));
+            sc[h] = __ldg(reinterpret_cast<const uint2*>(tile + T::SCALE_OFF + g * 16 + h * 8));
+            mn[h] = __ldg(reinterpret_cast<const uint2*>(tile + T::MIN_OFF + g * 16 + h * 8));
+        }
+    }
+    __device__ __forceinline__ void store(uint8_t* a_stage, int rt16, int lane) const {
+        const int g = lane >> 2, q = lane & 3;
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const float2 s01 = __half22float2(as_half2(sc[h].x)), s23 = __half22float2(as_half2(sc[h].y));
+            const float2 m01 = __half22float2(as_half2(mn[h].x)), m23 = __half22float2(as_half2(mn[h].y));
+            const float a[4] = {s01.x, s01.y, s23.x, s23.y}, b[4] = {m01.x, m01.y, m23.x, m23.y};
+            const uint32_t w[4] = {c[h].x, c[h].y, c[h].z, c[h].w};
+            const int r = rt16 * 16 + g + 8 * h;
+#pragma unroll
+            for (int j = 0; j < 4; j++)  // value = scale * code + min in fp32, rounded once to fp16
+                *reinterpret_cast<uint4*>(a_stage + a_chunk_off(r, j * 4 + q)) = word_to_half8(w[j], a[j], b[j]);
+        }
+    }
+};
+
 template <> struct DequantRegs<WF_QTYPE_Q8_0> {
     uint4 ch[2], cl[2];
     uint2 sc[2];
@@ -708,6 +738,7 @@ int gemm_launch(Context* c, const GemvCall& call, cudaStream_t s) {
     p.launch = c->gemm_launches;
     const size_t smem = 1024 + (size_t)p.stages * stage_bytes;
     cudaError_t e = qt == WF_QTYPE_Q4_0   ? gemm_launch_one<WF_QTYPE_Q4_0>(p, map, grid, smem, s)
+                    : qt == WF_QTYPE_Q4_1 ? gemm_launch_one<WF_QTYPE_Q4_1>(p, map, grid, smem, s)
                     : qt == WF_QTYPE_Q8_0 ? gemm_launch_one<WF_QTYPE_Q8_0>(p, map, grid, smem, s)
                                           : gemm_launch_one<WF_QTYPE_Q4_K>(p, map, grid, smem, s);
     if (e != cudaSuccess) return cuda_status(c, e, "gemm launch");

@@ -187,6 +187,7 @@ static cudaError_t launch_one(const GemvParams& p, int grid, size_t smem, cudaSt
 template <int XC>
 static cudaError_t launch_qt(int qt, const GemvParams& p, int grid, size_t smem, cudaStream_t s) {
     return qt == WF_QTYPE_Q4_0   ? launch_one<WF_QTYPE_Q4_0, XC>(p, grid, smem, s)
+           : qt == WF_QTYPE_Q4_1 ? launch_one<WF_QTYPE_Q4_1, XC>(p, grid, smem, s)
            : qt == WF_QTYPE_Q8_0 ? launch_one<WF_QTYPE_Q8_0, XC>(p, grid, smem, s)
                                  : launch_one<WF_QTYPE_Q4_K, XC>(p, grid, smem, s);
 }

@@ -260,6 +260,48 @@ template <> struct TileRegs<WF_QTYPE_Q4_0> {
     }
 };
 
+template <> struct TileRegs<WF_QTYPE_Q4_1> {
+    static constexpr float BETA = -16.f;  // (16 + code) - 16 = code; the min term is (-min / 16) * (start value)
+    uint4 c[2], s, mn;
+    __device__ __forceinline__ void load(uint32_t t, int lane) {
+        using T = Tile<WF_QTYPE_Q4_1>;
+        c[0] = lds128(t);
+        c[1] = lds128(t + 512);
+        s = lds128(t - lane * 16 + T::SCALE_OFF + (lane >> 2) * 16);
+        mn = lds128(t - lane * 16 + T::MIN_OFF + (lane >> 2) * 16);
+    }
+    template <int XC>
+    __device__ __forceinline__ void compute(float (&acc)[4], uint32_t xaddr, uint32_t caddr, uint32_t live) const {
+        const float2 s0 = half2_bits_to_float2(s.x), s1 = half2_bits_to_float2(s.y);  // row g, blocks 0..3
+        const float2 s2 = half2_bits_to_float2(s.z), s3 = half2_bits_to_float2(s.w);  // row g + 8
+        const float2 m0 = half2_bits_to_float2(mn.x), m1 = half2_bits_to_float2(mn.y);
+        const float2 m2 = half2_bits_to_float2(mn.z), m3 = half2_bits_to_float2(mn.w);
+        const float sg[4] = {s0.x, s0.y, s1.x, s1.y}, sh[4] = {s2.x, s2.y, s3.x, s3.y};
+        const float mg[4] = {m0.x * -0.0625f, m0.y * -0.0625f, m1.x * -0.0625f, m1.y * -0.0625f};
+        const float mh[4] = {m2.x * -0.0625f, m2.y * -0.0625f, m3.x * -0.0625f, m3.y * -0.0625f};
+        uint4 xb = make_uint4(0u, 0u, 0u, 0u);
+        float4 ci;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            fetch_block<XC>(xaddr + j * 64, caddr + j * cinit_block_bytes<XC>(), live, xb, ci);
+            float d[4];
+            if (XC == 1) {
+                block_mma(d, word_of(c[0], j), word_of(c[1], j), xb, MAGIC_16, 0.f, 0.f, 0.f, 0.f);
+                d[0] += ci.x;
+                d[2] += ci.z;
+            } else {
+                block_mma(d, word_of(c[0], j), word_of(c[1], j), xb, MAGIC_16, ci.x, ci.y, ci.z, ci.w);
+            }
+            acc[0] = fmaf(sg[j], d[0], fmaf(mg[j], ci.x, acc[0]));
+            acc[2] = fmaf(sh[j], d[2], fmaf(mh[j], ci.z, acc[2]));
+            if (XC > 1) {
+                acc[1] = fmaf(sg[j], d[1], fmaf(mg[j], ci.y, acc[1]));
+                acc[3] = fmaf(sh[j], d[3], fmaf(mh[j], ci.w, acc[3]));
+            }
+        }
+    }
+};
+
 template <> struct TileRegs<WF_QTYPE_Q8_0> {
     static constexpr float BETA = -400.f;  // (256 + 16 hi) + (16 + lo) - 400 = 16 (hi - 8) + lo
     uint4 c[4], s;                         // c[0..1] high plane rows g / g+8, c[2..3] low plane

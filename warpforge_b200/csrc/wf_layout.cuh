@@ -19,6 +19,8 @@
 //
 //   Q4_0  tile = 128 k : plane (codes 0..15, value = code - 8)          1024
 //                        fp16 scales [g][row g: blocks 0..3 | row g+8: blocks 0..3]  128
+//   Q4_1  tile = 128 k : plane (codes 0..15, value = code * scale + min)  1024
+//                        fp16 scales as for Q4_0   128;  fp16 mins, same shape   128
 //   Q8_0  tile = 128 k : plane H (high nibble of byte ^ 0x80), plane L (low nibble)  2048
 //                        fp16 scales as above                                          128
 //   Q4_K  tile = 256 k : plane for sub-blocks 0..3, plane for sub-blocks 4..7         2048
@@ -31,6 +33,7 @@
 #include <stdint.h>
 
 #define WF_QTYPE_Q4_0 2
+#define WF_QTYPE_Q4_1 3
 #define WF_QTYPE_Q8_0 8
 #define WF_QTYPE_Q4_K 14
 
@@ -51,6 +54,10 @@ template <> struct Tile<WF_QTYPE_Q4_0> {
     static constexpr int K = 128, BYTES = 1152, PLANES = 1, BLOCK_K = 32, BLOCK_BYTES = 18;
     static constexpr int SCALE_OFF = 1024;
 };
+template <> struct Tile<WF_QTYPE_Q4_1> {
+    static constexpr int K = 128, BYTES = 1280, PLANES = 1, BLOCK_K = 32, BLOCK_BYTES = 20;
+    static constexpr int SCALE_OFF = 1024, MIN_OFF = 1152;
+};
 template <> struct Tile<WF_QTYPE_Q8_0> {
     static constexpr int K = 128, BYTES = 2176, PLANES = 2, BLOCK_K = 32, BLOCK_BYTES = 34;
     static constexpr int SCALE_OFF = 2048;
@@ -61,9 +68,9 @@ template <> struct Tile<WF_QTYPE_Q4_K> {
 };
 
 WF_HD int tile_k(int qt) { return qt == WF_QTYPE_Q4_K ? 256 : 128; }
-WF_HD int tile_bytes(int qt) { return qt == WF_QTYPE_Q4_0 ? 1152 : qt == WF_QTYPE_Q8_0 ? 2176 : 2368; }
+WF_HD int tile_bytes(int qt) { return qt == WF_QTYPE_Q4_0 ? 1152 : qt == WF_QTYPE_Q4_1 ? 1280 : qt == WF_QTYPE_Q8_0 ? 2176 : 2368; }
 WF_HD int block_k(int qt) { return qt == WF_QTYPE_Q4_K ? 256 : 32; }
-WF_HD int block_bytes(int qt) { return qt == WF_QTYPE_Q4_0 ? 18 : qt == WF_QTYPE_Q8_0 ? 34 : 144; }
+WF_HD int block_bytes(int qt) { return qt == WF_QTYPE_Q4_0 ? 18 : qt == WF_QTYPE_Q4_1 ? 20 : qt == WF_QTYPE_Q8_0 ? 34 : 144; }
 
 // Nibble position of element e (0..7) inside its 32-bit word.
 WF_HD int nibble_pos(int e) { return (e >> 1) | ((e & 1) << 2); }

@@ -48,6 +48,40 @@ __global__ void repack_q4_0_kernel(const uint8_t* __restrict__ raw, uint8_t* __r
             ld_u16(src);
 }
 
+// Q4_1 (Dequantizer.java:304-358): fp16 scale, fp16 min, 16 code bytes in the same two nibble orders.
+__global__ void repack_q4_1_kernel(const uint8_t* __restrict__ raw, uint8_t* __restrict__ tiles, int64_t rows,
+                                   int64_t nblk, int64_t kt, int ggml_order) {
+    using T = Tile<WF_QTYPE_Q4_1>;
+    int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= rows * nblk * 4) return;
+    int q = idx & 3;
+    int64_t bk = (idx >> 2) % nblk, r = (idx >> 2) / nblk;
+    const uint8_t* src = raw + (r * nblk + bk) * 20;
+    uint8_t* tile = tiles + ((r >> 4) * kt + (bk >> 2)) * T::BYTES;
+    int ri = r & 15, j = bk & 3;
+    uint32_t nib[8];
+    if (ggml_order) {
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            uint8_t b = src[4 + ((8 * q + i) & 15)];
+            nib[i] = q >= 2 ? (b >> 4) : (b & 0xF);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            uint8_t b = src[4 + 4 * q + i];
+            nib[2 * i] = b & 0xF;
+            nib[2 * i + 1] = b >> 4;
+        }
+    }
+    *reinterpret_cast<uint32_t*>(tile + plane_word_off(ri, j, q)) = pack8(nib);
+    if (q == 0) {
+        const int so = (ri & 7) * 16 + (ri >> 3) * 8 + j * 2;
+        *reinterpret_cast<uint16_t*>(tile + T::SCALE_OFF + so) = ld_u16(src);
+        *reinterpret_cast<uint16_t*>(tile + T::MIN_OFF + so) = ld_u16(src + 2);
+    }
+}
+
 __global__ void repack_q8_0_kernel(const uint8_t* __restrict__ raw, uint8_t* __restrict__ tiles, int64_t rows,
                                    int64_t nblk, int64_t kt) {
     int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -126,6 +160,8 @@ cudaError_t launch_repack(int qtype, const uint8_t* d_raw, uint8_t* d_tiles, int
         unsigned grid = (unsigned)((n + threads - 1) / threads);
         if (qtype == WF_QTYPE_Q4_0)
             repack_q4_0_kernel<<<grid, threads, 0, s>>>(d_raw, d_tiles, rows, nblk, kt, q4_0_order == WF_Q4_0_ORDER_GGML);
+        else if (qtype == WF_QTYPE_Q4_1)
+            repack_q4_1_kernel<<<grid, threads, 0, s>>>(d_raw, d_tiles, rows, nblk, kt, q4_0_order == WF_Q4_0_ORDER_GGML);
         else
             repack_q8_0_kernel<<<grid, threads, 0, s>>>(d_raw, d_tiles, rows, nblk, kt);
     }
@@ -161,6 +197,13 @@ __device__ __forceinline__ float sub_host(float a, float b) {
     return (r != r) ? __uint_as_float(0xFFC00000u) : r;
 }
 
+__device__ __forceinline__ float add_host(float a, float b) {
+    if (a != a) return a;
+    if (b != b) return b;
+    float r = __fadd_rn(a, b);
+    return (r != r) ? __uint_as_float(0xFFC00000u) : r;
+}
+
 // One thread per output element; multiply and subtract rounded separately, never fused.
 __global__ void dequant_rows_kernel(const uint8_t* __restrict__ tiles, int qtype, int64_t kt, int64_t k,
                                     int64_t row0, int64_t nrows, float* __restrict__ out) {
@@ -186,6 +229,13 @@ __global__ void dequant_rows_kernel(const uint8_t* __restrict__ tiles, int qtype
         int so = (ri & 7) * 16 + (ri >> 3) * 8 + j * 2;
         int qv;
         float scale;
+        if (qtype == WF_QTYPE_Q4_1) {  // q * scale + min, product and sum rounded separately
+            using T = Tile<WF_QTYPE_Q4_1>;
+            scale = half_bits_to_float(*reinterpret_cast<const uint16_t*>(tile + T::SCALE_OFF + so));
+            const float mn = half_bits_to_float(*reinterpret_cast<const uint16_t*>(tile + T::MIN_OFF + so));
+            out[idx] = add_host(mul_host((float)tile_nibble(tile, ri, j, e), scale), mn);
+            return;
+        }
         if (qtype == WF_QTYPE_Q4_0) {
             qv = (int)tile_nibble(tile, ri, j, e) - 8;
             scale = half_bits_to_float(*reinterpret_cast<const uint16_t*>(tile + Tile<WF_QTYPE_Q4_0>::SCALE_OFF + so));

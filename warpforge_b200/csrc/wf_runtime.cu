@@ -141,7 +141,7 @@ static cudaError_t upload_and_repack(Context* c, int qtype, const uint8_t* src, 
     return e;
 }
 
-static bool qtype_supported(int qt) { return qt == WF_QTYPE_Q4_0 || qt == WF_QTYPE_Q8_0 || qt == WF_QTYPE_Q4_K; }
+static bool qtype_supported(int qt) { return qt == WF_QTYPE_Q4_0 || qt == WF_QTYPE_Q4_1 || qt == WF_QTYPE_Q8_0 || qt == WF_QTYPE_Q4_K; }
 
 }  // namespace wf
 
