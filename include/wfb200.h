@@ -129,7 +129,7 @@ int wf_gguf_metadata(int64_t gguf, int64_t index, char* key, int64_t key_len, ch
 
 /* wf_weight_upload straight from the mapping: the 2-D tensor `name` ({k, n_rows} in the
  * file) becomes a device-resident row shard without the bytes passing through the caller.
- * q4_0_order says how a Q4_0 block's 16 quant bytes map to its 32 elements:
+ * q4_0_order says how the 16 quant bytes of a Q4_0 or Q4_1 block map to its 32 elements:
  * WF_Q4_0_ORDER_REFERENCE is the order Dequantizer.java:251-279 reads (byte i holds
  * elements 2i and 2i+1), WF_Q4_0_ORDER_GGML the order ggml writes (byte i holds elements i
  * and i+16).  The device layout is the same either way, so the choice costs nothing at
