@@ -633,8 +633,58 @@ __device__ __forceinline__ uint32_t pack_bf16_trunc(float a, float b) {
     return (__float_as_uint(a) >> 16) | (__float_as_uint(b) & 0xFFFF0000u);
 }
 
+// bf16 activations: the copy is verbatim.  Token by token (no index division), four 16-byte loads in
+// flight per thread, one block sum per four consecutive lanes.
+static __device__ void stage_x_bf16(const GemvParams& p, uint8_t* xs, float* cinit, int kp, float beta, int nthreads, bool one_col) {
+    const int groups = kp >> 3, padded = (groups + 31) & ~31, kgroups = p.k >> 3;
+    constexpr int U = 4;
+    for (int t = 0; t < p.m; t++) {
+        const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.x) + (size_t)t * p.ldx);
+        uint8_t* dst = xs + (size_t)t * p.sx;
+        float* col = one_col ? cinit : cinit + (t >> 1) * 4 + (t & 1);  // [block][q][4]: entries (t&1) and (t&1)+2 of quad t>>1
+        for (int c0 = threadIdx.x; c0 < padded; c0 += nthreads * U) {   // warp-uniform trip counts
+            uint4 pre[U];
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+                const int c8 = c0 + u * nthreads;
+                pre[u] = make_uint4(0, 0, 0, 0);
+                if (c8 < kgroups) pre[u] = __ldcg(src + c8);
+            }
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+                const int c8 = c0 + u * nthreads;
+                if ((c8 & ~31) >= padded) break;  // warp-uniform
+                const uint4 v = pre[u];
+                if (c8 < groups) *reinterpret_cast<uint4*>(dst + c8 * 16) = v;
+                const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+                float sum = 0.f;
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    sum += __uint_as_float(w[i] << 16);
+                    sum += __uint_as_float(w[i] & 0xFFFF0000u);
+                }
+                sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
+                sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
+                if (c8 < groups && (threadIdx.x & 3) == 0) {
+                    const float v0 = beta * sum;
+                    if (one_col) {
+                        col[c8 >> 2] = v0;
+                    } else {
+                        col[(c8 >> 2) * 16] = v0;
+                        col[(c8 >> 2) * 16 + 2] = v0;
+                    }
+                }
+            }
+        }
+    }
+}
+
 // one_col: write the start values as one float per block (column 0 only) instead of [4] float4
 static __device__ void stage_x(const GemvParams& p, uint8_t* xs, float* cinit, int kp, float beta, int nthreads, bool one_col) {
+    if (!p.x_f32) {
+        stage_x_bf16(p, xs, cinit, kp, beta, nthreads, one_col);
+        return;
+    }
     const int groups = kp >> 3;  // 8 elements per thread step
     const int total = p.m * groups;
     constexpr int U = 4;  // bf16 path: four independent loads in flight per thread
