@@ -71,7 +71,7 @@ struct Context {
     cudaEvent_t upload_done[2] = {nullptr, nullptr};
     void* d_x16 = nullptr;  // fp16 copy of the activations for the tensor-core GEMM
     int64_t x16_bytes = 0;
-    float* d_gemm_partial = nullptr;       // [sm_count][256][128] pieces of tiles cut by a share boundary
+    float* d_gemm_partial = nullptr;       // [sm_count][512][128] pieces of tiles cut by a share boundary
     unsigned int* d_gemm_ready = nullptr;  // [sm_count][4] launch number whose piece is complete, per 32-row quarter
     unsigned int gemm_launches = 0;
     int64_t launches = 0;

@@ -15,17 +15,25 @@
 //   warps 2,3,8-13  dequant: read the quantized tiles straight from global memory (coalesced 16-byte
 //               loads, the layout is already fragment-ordered), unpack 4-bit codes, apply the block
 //               scale and write fp16 rows into the swizzled A stage; one 16-row tile per warp and stage
-// Stages hold BK = 128 k: A = 128 rows x 128 k fp16 (two 64-k swizzle spans, 32 KB), B = BM x 128 k bf16.
+// Stages hold BK = 128 k: A = 128 rows x 128 k fp16 (two 64-k swizzle spans, 32 KB), B = BM x 128 k fp16.
 // The accumulator is double buffered in TMEM (2 x BM columns <= 512) so the epilogue of one tile
-// overlaps the main loop of the next.
+// overlaps the main loop of the next.  A dequant warp converts its registers to fp16 BEFORE it waits
+// for the stage to be released, so only the shared-memory stores lie between "stage released" and
+// "stage full again".
+//
+// Above 512 tokens a token tile is two halves of 256 tokens (TMEM columns 0 and 256, one accumulator each)
+// that share every dequantized weight stage, and a stage holds 64 k (A 16 KB, B 2 x 32 KB): the weight
+// loads and conversions per MMA halve.  The two halves have their own full / empty barriers, so the
+// epilogue drains the first half while the MMAs of the second still run.
 //
 // Work split ("stream-K"): all (tile, k-block) steps form one sequence in tile order, cut into
 // equal contiguous shares, one per CTA, so every SM does the same number of MMA steps whatever the
 // tile count.  A tile cut by a share boundary is finished by the CTA that holds its first
 // k-block: the CTAs holding the rest reach their piece first (it is the head of their share),
-// write it to a scratch buffer and publish the launch number; the owner reaches the tile last,
-// adds the pieces in CTA order (deterministic) and writes y.  The owner's wait is bounded.  Every wait is bounded; on expiry the CTA sets a status bit,
-// stops issuing work and still frees its TMEM.
+// write it to a scratch buffer and publish the launch number; the owner reaches the tile last --
+// it is the last thing in its share, so all its warps are free by then: twelve of them (three per
+// TMEM lane quarter) add the pieces in CTA order (deterministic) and write y.  Every wait is bounded;
+// on expiry the CTA sets a status bit, stops issuing work and still frees its TMEM.
 //
 // Weights are rounded once to fp16 (relative 2^-12) after the exact fp32 dequantization; products
 // and sums are fp32 in the tensor core.  Replaces the host transpose + batch_matmul_f32 of
@@ -33,15 +41,32 @@
 #include <cuda.h>
 #include <cuda_fp16.h>
 
+#include <type_traits>
+
 #include "wf_common.cuh"
 
 namespace wf {
 
 constexpr int GEMM_BN = 128;        // weight rows per tile (UMMA M)
 constexpr int GEMM_BK = 128;        // k per stage
-constexpr int GEMM_THREADS = 448;   // 14 warps: TMA, MMA, 4 epilogue, 8 dequant
+// Build-time choices, measured on one B200 against each other (config: Q4_K [14336 x 4096], 512 / 2048 tokens):
+// 8 dequant warps 77.9 / 254.6 us, 16 dequant warps 84.0 / 278.3 us; token tiles of 2 x 256 above 512 tokens
+// 254.6 us against 263.6 us without them at 2048 tokens ([8192 x 8192]: 278.4 against 311.4 us).
+#ifndef WF_GEMM_DQ_WARPS
+#define WF_GEMM_DQ_WARPS 8
+#endif
+#ifndef WF_GEMM_WIDE_MIN
+#define WF_GEMM_WIDE_MIN 512  // token counts above this use the 2 x 256 token tiles
+#endif
+constexpr int GEMM_DEQUANT_WARPS = WF_GEMM_DQ_WARPS;  // 8: a 16-row weight tile each; 16: one row half (8 rows) each
+constexpr int GEMM_DQ_HALVES = 16 / GEMM_DEQUANT_WARPS;   // row halves a dequant warp converts per step
+constexpr int GEMM_THREADS = (6 + GEMM_DEQUANT_WARPS) * 32;  // TMA, MMA, 4 epilogue, dequant warps
 constexpr int GEMM_WAIT_SPINS = 1 << 26;
 constexpr int GEMM_A_BYTES = GEMM_BN * GEMM_BK * 2;  // 32 KB
+constexpr int GEMM_WIDE_BK = 64;                     // k per stage when a token tile is 2 x 256 tokens
+constexpr int GEMM_WIDE_A_BYTES = GEMM_BN * GEMM_WIDE_BK * 2;  // 16 KB
+constexpr int GEMM_WIDE_B_HALF = 256 * GEMM_WIDE_BK * 2;       // 32 KB: 256 tokens x 64 k
+constexpr int GEMM_PIECE_TOKENS = 512;               // tokens a stream-K piece can hold
 
 struct GemmParams {
     const uint8_t* tiles;
@@ -51,13 +76,15 @@ struct GemmParams {
     int64_t ldy, col0;
     int rows, k, kt_w;   // kt_w: weight k-tiles per row-tile stripe (tile_k of the format)
     int m;               // tokens
-    int bm;              // tokens per tile (multiple of 16, <= 256)
-    int n_tiles, m_tiles, k_blocks;  // k_blocks = ceil(k / 128)
+    int bm;              // tokens per MMA (UMMA N: multiple of 16, <= 256)
+    int halves;          // 1: token tiles of bm, 128-k stages, accumulator double buffered;
+                         // 2: token tiles of 2 x 256 sharing each dequantized weight stage, 64-k stages
+    int n_tiles, m_tiles, k_blocks;  // k_blocks = ceil(k / k per stage)
     int stages;
     uint32_t idesc;
     // stream-K: the (tile, k-block) units form one sequence, CTA b owns units [b*q + min(b,r), ...)
     int unit_q, unit_r;
-    float* partial;        // [ctas][bm][128] fp32: a CTA's piece of a tile that begins in an earlier CTA
+    float* partial;        // [ctas][GEMM_PIECE_TOKENS][128] fp32: a CTA's piece of a tile that begins in an earlier CTA
     unsigned int* ready;   // [ctas][4] launch number whose piece (per 32-row quarter) is complete in `partial`
     unsigned int launch;   // this launch's number (never 0)
 };
@@ -168,6 +195,67 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// The same load without the wait, and the wait as a statement that owns the registers: arithmetic on r[]
+// cannot be scheduled before it.  Used to keep the load of the next 32 columns in flight while the current
+// ones are stored.
+__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[32]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]),
+                   "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]),
+                   "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]),
+                   "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+                 :
+                 : "memory");
+}
+
+// ---------------------------------------------------------------- epilogue pieces (one lane = one weight row)
+// r[j] = accumulator of (token m0 + j, weight row n).  Rows of y are ldy floats apart; a warp writes 32
+// consecutive floats of one token row per store.  m0 is a multiple of 32, so the row scales load as float4.
+__device__ __forceinline__ void store_chunk(float* __restrict__ y, int64_t ldy, int64_t col0, const float* __restrict__ unscale,
+                                            const uint32_t (&r)[32], int m0, int m, int n, int rows) {
+    if (n >= rows || m0 >= m) return;
+    float* yp = y + (int64_t)m0 * ldy + col0 + n;
+    if (m0 + 32 <= m) {
+        float sc[32];
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const float4 v = __ldg(reinterpret_cast<const float4*>(unscale + m0) + i);
+            sc[4 * i] = v.x, sc[4 * i + 1] = v.y, sc[4 * i + 2] = v.z, sc[4 * i + 3] = v.w;
+        }
+#pragma unroll
+        for (int j = 0; j < 32; j++) yp[(int64_t)j * ldy] = __uint_as_float(r[j]) * sc[j];
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; j++)
+            if (m0 + j < m) yp[(int64_t)j * ldy] = __uint_as_float(r[j]) * __ldg(unscale + m0 + j);
+    }
+}
+// A stream-K piece is token-major, 128 weight rows contiguous per token.
+__device__ __forceinline__ void write_piece_chunk(float* __restrict__ piece, const uint32_t (&r)[32], int tok, int row) {
+    float* pp = piece + (size_t)tok * GEMM_BN + row;
+#pragma unroll
+    for (int j = 0; j < 32; j++) pp[j * GEMM_BN] = __uint_as_float(r[j]);
+}
+__device__ __forceinline__ void add_piece_chunk(const float* __restrict__ piece, uint32_t (&r)[32], int tok, int row) {
+    const float* pp = piece + (size_t)tok * GEMM_BN + row;
+    float v[32];
+#pragma unroll
+    for (int j = 0; j < 32; j++) v[j] = __ldcg(pp + j * GEMM_BN);  // 32 independent loads in flight
+#pragma unroll
+    for (int j = 0; j < 32; j++) r[j] = __float_as_uint(__uint_as_float(r[j]) + v[j]);
+}
+
 // ---------------------------------------------------------------- dequantization to fp16
 // A plane word holds the codes of 8 consecutive elements: rotated back by PLANE_ROT, nibble p of the
 // low half is element 2p and nibble p of the high half element 2p + 1.  As fp16 bit patterns
@@ -245,116 +333,222 @@ __device__ __forceinline__ uint32_t a_chunk_off(int r, int c) {
 template <int QT> struct DequantRegs;
 
 template <> struct DequantRegs<WF_QTYPE_Q4_0> {
-    uint4 c[2];
-    uint2 sc[2];
-    __device__ __forceinline__ void load(const uint8_t* tile, int kb, int lane) {
+    uint4 c[1];
+    uint2 sc[1];
+    __device__ __forceinline__ void load(const uint8_t* tile, int kb, int lane, int hsel) {
         (void)kb;
         const int g = lane >> 2;
-#pragma unroll
-        for (int h = 0; h < 2; h++) {
-            c[h] = __ldg(reinterpret_cast<const uint4*>(tile + h * 512 + lane * 16));
-            sc[h] = __ldg(reinterpret_cast<const uint2*>(tile + Tile<WF_QTYPE_Q4_0>::SCALE_OFF + g * 16 + h * 8));
+        {
+            const int h = hsel;
+            c[0] = __ldg(reinterpret_cast<const uint4*>(tile + h * 512 + lane * 16));
+            sc[0] = __ldg(reinterpret_cast<const uint2*>(tile + Tile<WF_QTYPE_Q4_0>::SCALE_OFF + g * 16 + h * 8));
         }
     }
-    __device__ __forceinline__ void store(uint8_t* a_stage, int rt16, int lane) const {
-        const int g = lane >> 2, q = lane & 3;
-#pragma unroll
-        for (int h = 0; h < 2; h++) {
-            const __half2 s01 = as_half2(sc[h].x), s23 = as_half2(sc[h].y);  // block scales 0..3 of this row, fp16
+    template <class F>
+    __device__ __forceinline__ void convert(int lane, int hsel, F&& f) const {  // f(row half, 16-byte chunk, 8 fp16 values)
+        (void)lane;
+        {
+            const int h = hsel;
+            const __half2 s01 = as_half2(sc[0].x), s23 = as_half2(sc[0].y);  // block scales 0..3 of this row, fp16
             const __half2 s[4] = {__low2half2(s01), __high2half2(s01), __low2half2(s23), __high2half2(s23)};
-            const uint32_t w[4] = {c[h].x, c[h].y, c[h].z, c[h].w};
-            const int r = rt16 * 16 + g + 8 * h;
+            const uint32_t w[4] = {c[0].x, c[0].y, c[0].z, c[0].w};
 #pragma unroll
             for (int j = 0; j < 4; j++)  // value = s * (code - 8)
-                *reinterpret_cast<uint4*>(a_stage + a_chunk_off(r, j * 4 + q)) = word_to_half8_q4_0(w[j], s[j]);
+                f(h, j, word_to_half8_q4_0(w[j], s[j]));
         }
     }
 };
 
 template <> struct DequantRegs<WF_QTYPE_Q4_1> {
-    uint4 c[2];
-    uint2 sc[2], mn[2];
-    __device__ __forceinline__ void load(const uint8_t* tile, int kb, int lane) {
+    uint4 c[1];
+    uint2 sc[1], mn[1];
+    __device__ __forceinline__ void load(const uint8_t* tile, int kb, int lane, int hsel) {
         (void)kb;
         using T = Tile<WF_QTYPE_Q4_1>;
         const int g = lane >> 2;
-#pragma unroll
-        for (int h = 0; h < 2; h++) {
-            c[h] = __ldg(reinterpret_cast<const uint4*>(tile + h * 512 + lane * 16));
-            sc[h] = __ldg(reinterpret_cast<const uint2*>(tile + T::SCALE_OFF + g * 16 + h * 8));
-            mn[h] = __ldg(reinterpret_cast<const uint2*>(tile + T::MIN_OFF + g * 16 + h * 8));
+        {
+            const int h = hsel;
+            c[0] = __ldg(reinterpret_cast<const uint4*>(tile + h * 512 + lane * 16));
+            sc[0] = __ldg(reinterpret_cast<const uint2*>(tile + T::SCALE_OFF + g * 16 + h * 8));
+            mn[0] = __ldg(reinterpret_cast<const uint2*>(tile + T::MIN_OFF + g * 16 + h * 8));
         }
     }
-    __device__ __forceinline__ void store(uint8_t* a_stage, int rt16, int lane) const {
-        const int g = lane >> 2, q = lane & 3;
-#pragma unroll
-        for (int h = 0; h < 2; h++) {
-            const float2 s01 = __half22float2(as_half2(sc[h].x)), s23 = __half22float2(as_half2(sc[h].y));
-            const float2 m01 = __half22float2(as_half2(mn[h].x)), m23 = __half22float2(as_half2(mn[h].y));
+    template <class F>
+    __device__ __forceinline__ void convert(int lane, int hsel, F&& f) const {  // f(row half, 16-byte chunk, 8 fp16 values)
+        (void)lane;
+        {
+            const int h = hsel;
+            const float2 s01 = __half22float2(as_half2(sc[0].x)), s23 = __half22float2(as_half2(sc[0].y));
+            const float2 m01 = __half22float2(as_half2(mn[0].x)), m23 = __half22float2(as_half2(mn[0].y));
             const float a[4] = {s01.x, s01.y, s23.x, s23.y}, b[4] = {m01.x, m01.y, m23.x, m23.y};
-            const uint32_t w[4] = {c[h].x, c[h].y, c[h].z, c[h].w};
-            const int r = rt16 * 16 + g + 8 * h;
+            const uint32_t w[4] = {c[0].x, c[0].y, c[0].z, c[0].w};
 #pragma unroll
             for (int j = 0; j < 4; j++)  // value = scale * code + min in fp32, rounded once to fp16
-                *reinterpret_cast<uint4*>(a_stage + a_chunk_off(r, j * 4 + q)) = word_to_half8(w[j], a[j], b[j]);
+                f(h, j, word_to_half8(w[j], a[j], b[j]));
         }
     }
 };
 
 template <> struct DequantRegs<WF_QTYPE_Q8_0> {
-    uint4 ch[2], cl[2];
-    uint2 sc[2];
-    __device__ __forceinline__ void load(const uint8_t* tile, int kb, int lane) {
+    uint4 ch[1], cl[1];
+    uint2 sc[1];
+    __device__ __forceinline__ void load(const uint8_t* tile, int kb, int lane, int hsel) {
         (void)kb;
         const int g = lane >> 2;
-#pragma unroll
-        for (int h = 0; h < 2; h++) {
-            ch[h] = __ldg(reinterpret_cast<const uint4*>(tile + h * 512 + lane * 16));
-            cl[h] = __ldg(reinterpret_cast<const uint4*>(tile + PLANE_BYTES + h * 512 + lane * 16));
-            sc[h] = __ldg(reinterpret_cast<const uint2*>(tile + Tile<WF_QTYPE_Q8_0>::SCALE_OFF + g * 16 + h * 8));
+        {
+            const int h = hsel;
+            ch[0] = __ldg(reinterpret_cast<const uint4*>(tile + h * 512 + lane * 16));
+            cl[0] = __ldg(reinterpret_cast<const uint4*>(tile + PLANE_BYTES + h * 512 + lane * 16));
+            sc[0] = __ldg(reinterpret_cast<const uint2*>(tile + Tile<WF_QTYPE_Q8_0>::SCALE_OFF + g * 16 + h * 8));
         }
     }
-    __device__ __forceinline__ void store(uint8_t* a_stage, int rt16, int lane) const {
-        const int g = lane >> 2, q = lane & 3;
-#pragma unroll
-        for (int h = 0; h < 2; h++) {
-            const __half2 s01 = as_half2(sc[h].x), s23 = as_half2(sc[h].y);
+    template <class F>
+    __device__ __forceinline__ void convert(int lane, int hsel, F&& f) const {  // f(row half, 16-byte chunk, 8 fp16 values)
+        (void)lane;
+        {
+            const int h = hsel;
+            const __half2 s01 = as_half2(sc[0].x), s23 = as_half2(sc[0].y);
             const __half2 s[4] = {__low2half2(s01), __high2half2(s01), __low2half2(s23), __high2half2(s23)};
-            const uint32_t wh[4] = {ch[h].x, ch[h].y, ch[h].z, ch[h].w}, wl[4] = {cl[h].x, cl[h].y, cl[h].z, cl[h].w};
-            const int r = rt16 * 16 + g + 8 * h;
+            const uint32_t wh[4] = {ch[0].x, ch[0].y, ch[0].z, ch[0].w}, wl[4] = {cl[0].x, cl[0].y, cl[0].z, cl[0].w};
 #pragma unroll
             for (int j = 0; j < 4; j++)
-                *reinterpret_cast<uint4*>(a_stage + a_chunk_off(r, j * 4 + q)) = words_to_half8_q8(wh[j], wl[j], s[j]);
+                f(h, j, words_to_half8_q8(wh[j], wl[j], s[j]));
         }
     }
 };
 
 template <> struct DequantRegs<WF_QTYPE_Q4_K> {  // the stage is one half (plane kb & 1) of a 256-k tile
-    uint4 c[2];
-    uint32_t dd[2], scw[2], mnw[2];
-    __device__ __forceinline__ void load(const uint8_t* tile, int kb, int lane) {
+    uint4 c[1];
+    uint32_t dd[1], scw[1], mnw[1];
+    __device__ __forceinline__ void load(const uint8_t* tile, int kb, int lane, int hsel) {
         using T = Tile<WF_QTYPE_Q4_K>;
         const int g = lane >> 2, pl = kb & 1;
-#pragma unroll
-        for (int h = 0; h < 2; h++) {
-            c[h] = __ldg(reinterpret_cast<const uint4*>(tile + pl * PLANE_BYTES + h * 512 + lane * 16));
-            dd[h] = __ldg(reinterpret_cast<const uint32_t*>(tile + T::D_OFF + g * 8 + h * 4));
-            scw[h] = __ldg(reinterpret_cast<const uint32_t*>(tile + T::SC_OFF + g * 16 + h * 8 + pl * 4));
-            mnw[h] = __ldg(reinterpret_cast<const uint32_t*>(tile + T::MN_OFF + g * 16 + h * 8 + pl * 4));
+        {
+            const int h = hsel;
+            c[0] = __ldg(reinterpret_cast<const uint4*>(tile + pl * PLANE_BYTES + h * 512 + lane * 16));
+            dd[0] = __ldg(reinterpret_cast<const uint32_t*>(tile + T::D_OFF + g * 8 + h * 4));
+            scw[0] = __ldg(reinterpret_cast<const uint32_t*>(tile + T::SC_OFF + g * 16 + h * 8 + pl * 4));
+            mnw[0] = __ldg(reinterpret_cast<const uint32_t*>(tile + T::MN_OFF + g * 16 + h * 8 + pl * 4));
         }
     }
-    __device__ __forceinline__ void store(uint8_t* a_stage, int rt16, int lane) const {
-        const int g = lane >> 2, q = lane & 3;
-#pragma unroll
-        for (int h = 0; h < 2; h++) {
-            const float2 d = __half22float2(as_half2(dd[h]));  // (d, dmin)
-            const uint32_t w[4] = {c[h].x, c[h].y, c[h].z, c[h].w};
-            const int r = rt16 * 16 + g + 8 * h;
+    template <class F>
+    __device__ __forceinline__ void convert(int lane, int hsel, F&& f) const {  // f(row half, 16-byte chunk, 8 fp16 values)
+        (void)lane;
+        {
+            const int h = hsel;
+            const float2 d = __half22float2(as_half2(dd[0]));  // (d, dmin)
+            const uint32_t w[4] = {c[0].x, c[0].y, c[0].z, c[0].w};
 #pragma unroll
             for (int j = 0; j < 4; j++) {  // value = (d * sc) * code - dmin * m
-                const float a = d.x * (float)((scw[h] >> (8 * j)) & 0xFF), b = -(d.y * (float)((mnw[h] >> (8 * j)) & 0xFF));
-                *reinterpret_cast<uint4*>(a_stage + a_chunk_off(r, j * 4 + q)) = word_to_half8(w[j], a, b);
+                const float a = d.x * (float)((scw[0] >> (8 * j)) & 0xFF), b = -(d.y * (float)((mnw[0] >> (8 * j)) & 0xFF));
+                f(h, j, word_to_half8(w[j], a, b));
             }
+        }
+    }
+};
+
+// 64-k stages (token tiles of 512): a warp converts 16 rows x 64 k of a weight tile per stage, i.e. the
+// two words (32-k blocks) 2*sub and 2*sub + 1 of every lane's 16-byte piece.  `sub` counts 64-k pieces
+// inside the weight tile: 0..1 for the 128-k formats, 0..3 for Q4_K (plane = sub / 2).
+template <int QT> struct DequantHalf;
+
+template <> struct DequantHalf<WF_QTYPE_Q4_0> {
+    uint2 c[1];
+    uint32_t sc[1];
+    __device__ __forceinline__ void load(const uint8_t* tile, int sub, int lane, int hsel) {
+        const int g = lane >> 2;
+        {
+            const int h = hsel;
+            c[0] = __ldg(reinterpret_cast<const uint2*>(tile + h * 512 + lane * 16 + sub * 8));
+            sc[0] = __ldg(reinterpret_cast<const uint32_t*>(tile + Tile<WF_QTYPE_Q4_0>::SCALE_OFF + g * 16 + h * 8 + sub * 4));
+        }
+    }
+    template <class F>
+    __device__ __forceinline__ void convert(int lane, int hsel, F&& f) const {  // f(row half, 16-byte chunk, 8 fp16 values)
+        (void)lane;
+        {
+            const int h = hsel;
+            const __half2 s01 = as_half2(sc[0]);
+            f(h, 0, word_to_half8_q4_0(c[0].x, __low2half2(s01)));
+            f(h, 1, word_to_half8_q4_0(c[0].y, __high2half2(s01)));
+        }
+    }
+};
+
+template <> struct DequantHalf<WF_QTYPE_Q4_1> {
+    uint2 c[1];
+    uint32_t sc[1], mn[1];
+    __device__ __forceinline__ void load(const uint8_t* tile, int sub, int lane, int hsel) {
+        using T = Tile<WF_QTYPE_Q4_1>;
+        const int g = lane >> 2;
+        {
+            const int h = hsel;
+            c[0] = __ldg(reinterpret_cast<const uint2*>(tile + h * 512 + lane * 16 + sub * 8));
+            sc[0] = __ldg(reinterpret_cast<const uint32_t*>(tile + T::SCALE_OFF + g * 16 + h * 8 + sub * 4));
+            mn[0] = __ldg(reinterpret_cast<const uint32_t*>(tile + T::MIN_OFF + g * 16 + h * 8 + sub * 4));
+        }
+    }
+    template <class F>
+    __device__ __forceinline__ void convert(int lane, int hsel, F&& f) const {  // f(row half, 16-byte chunk, 8 fp16 values)
+        (void)lane;
+        {
+            const int h = hsel;
+            const float2 s = __half22float2(as_half2(sc[0])), m = __half22float2(as_half2(mn[0]));
+            f(h, 0, word_to_half8(c[0].x, s.x, m.x));
+            f(h, 1, word_to_half8(c[0].y, s.y, m.y));
+        }
+    }
+};
+
+template <> struct DequantHalf<WF_QTYPE_Q8_0> {
+    uint2 ch[1], cl[1];
+    uint32_t sc[1];
+    __device__ __forceinline__ void load(const uint8_t* tile, int sub, int lane, int hsel) {
+        const int g = lane >> 2;
+        {
+            const int h = hsel;
+            ch[0] = __ldg(reinterpret_cast<const uint2*>(tile + h * 512 + lane * 16 + sub * 8));
+            cl[0] = __ldg(reinterpret_cast<const uint2*>(tile + PLANE_BYTES + h * 512 + lane * 16 + sub * 8));
+            sc[0] = __ldg(reinterpret_cast<const uint32_t*>(tile + Tile<WF_QTYPE_Q8_0>::SCALE_OFF + g * 16 + h * 8 + sub * 4));
+        }
+    }
+    template <class F>
+    __device__ __forceinline__ void convert(int lane, int hsel, F&& f) const {  // f(row half, 16-byte chunk, 8 fp16 values)
+        (void)lane;
+        {
+            const int h = hsel;
+            const __half2 s01 = as_half2(sc[0]);
+            f(h, 0, words_to_half8_q8(ch[0].x, cl[0].x, __low2half2(s01)));
+            f(h, 1, words_to_half8_q8(ch[0].y, cl[0].y, __high2half2(s01)));
+        }
+    }
+};
+
+template <> struct DequantHalf<WF_QTYPE_Q4_K> {
+    uint2 c[1];
+    uint32_t dd[1];
+    uint16_t scw[1], mnw[1];  // the two 8-bit sub-block scales / mins of this 64-k piece
+    __device__ __forceinline__ void load(const uint8_t* tile, int sub, int lane, int hsel) {
+        using T = Tile<WF_QTYPE_Q4_K>;
+        const int g = lane >> 2;
+        {
+            const int h = hsel;
+            c[0] = __ldg(reinterpret_cast<const uint2*>(tile + (sub >> 1) * PLANE_BYTES + h * 512 + lane * 16 + (sub & 1) * 8));
+            dd[0] = __ldg(reinterpret_cast<const uint32_t*>(tile + T::D_OFF + g * 8 + h * 4));
+            scw[0] = __ldg(reinterpret_cast<const uint16_t*>(tile + T::SC_OFF + g * 16 + h * 8 + sub * 2));
+            mnw[0] = __ldg(reinterpret_cast<const uint16_t*>(tile + T::MN_OFF + g * 16 + h * 8 + sub * 2));
+        }
+    }
+    template <class F>
+    __device__ __forceinline__ void convert(int lane, int hsel, F&& f) const {  // f(row half, 16-byte chunk, 8 fp16 values)
+        (void)lane;
+        {
+            const int h = hsel;
+            const float2 d = __half22float2(as_half2(dd[0]));  // (d, dmin)
+            const float a0 = d.x * (float)(scw[0] & 0xFF), b0 = -(d.y * (float)(mnw[0] & 0xFF));
+            const float a1 = d.x * (float)(scw[0] >> 8), b1 = -(d.y * (float)(mnw[0] >> 8));
+            f(h, 0, word_to_half8(c[0].x, a0, b0));
+            f(h, 1, word_to_half8(c[0].y, a1, b1));
         }
     }
 };
@@ -431,8 +625,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmParams 
     uint64_t* acc_empty = acc_full + 2;                          // [2]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    const uint32_t b_bytes = (uint32_t)p.bm * 256;
-    const uint32_t stage_bytes = GEMM_A_BYTES + b_bytes;
+    const bool wide = p.halves == 2;
+    const uint32_t a_bytes = wide ? GEMM_WIDE_A_BYTES : GEMM_A_BYTES;
+    const uint32_t b_bytes = wide ? 2u * GEMM_WIDE_B_HALF : (uint32_t)p.bm * 256;
+    const uint32_t stage_bytes = a_bytes + b_bytes;
     uint8_t* stage0 = smem + 1024;
 
     const int warp = __shfl_sync(0xFFFFFFFFu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
@@ -445,7 +641,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmParams 
     if (threadIdx.x == 0) {
         for (int s = 0; s < stages; s++) {
             g_mbar_init(&b_full[s], 1);
-            g_mbar_init(&a_full[s], 8);   // eight dequant warps
+            g_mbar_init(&a_full[s], GEMM_DEQUANT_WARPS);
             g_mbar_init(&s_empty[s], 1);
         }
         for (int b = 0; b < 2; b++) {
@@ -473,20 +669,67 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmParams 
             for (int u = u0; u < u1 && !*abort_flag;) {
                 const GemmSegment g = segment_at(p, u, u1);
                 const int mt = g.tile % p.m_tiles;
+                const int nh = (wide && p.m - mt * 512 > 256) ? 2 : 1;  // 256-token halves of this tile that hold tokens
                 for (int kb = g.kb0; kb < g.kb1; kb++, it++) {
                     const int s = it % stages;
                     if (it >= stages && !g_mbar_wait(&s_empty[s], ((it / stages) - 1) & 1)) { fail(); break; }
-                    uint8_t* b_stage = stage0 + (size_t)s * stage_bytes + GEMM_A_BYTES;
-                    g_mbar_expect_tx(&b_full[s], b_bytes);
-                    tma_load_2d(b_stage, &xmap, kb * GEMM_BK, mt * p.bm, &b_full[s]);
-                    tma_load_2d(b_stage + b_bytes / 2, &xmap, kb * GEMM_BK + 64, mt * p.bm, &b_full[s]);
+                    uint8_t* b_stage = stage0 + (size_t)s * stage_bytes + a_bytes;
+                    if (wide) {  // one 64-k span per 256-token half
+                        g_mbar_expect_tx(&b_full[s], (uint32_t)nh * GEMM_WIDE_B_HALF);
+                        for (int h = 0; h < nh; h++)
+                            tma_load_2d(b_stage + h * GEMM_WIDE_B_HALF, &xmap, kb * GEMM_WIDE_BK, mt * 512 + h * 256, &b_full[s]);
+                    } else {
+                        g_mbar_expect_tx(&b_full[s], b_bytes);
+                        tma_load_2d(b_stage, &xmap, kb * GEMM_BK, mt * p.bm, &b_full[s]);
+                        tma_load_2d(b_stage + b_bytes / 2, &xmap, kb * GEMM_BK + 64, mt * p.bm, &b_full[s]);
+                    }
                 }
                 u += g.kb1 - g.kb0;
             }
         }
     } else if (warp == 1) {
         // ------------------------------------------------ MMA issuer
-        if (lane == 0) {
+        if (lane == 0 && wide) {
+            // Token tile = two halves of 256 tokens, each with its own accumulator (TMEM columns 0 and 256) and its
+            // own full / empty barrier; both halves consume the same dequantized weight stage.  used[h] counts
+            // the tiles that have used half h (a tile's second half is skipped when it holds no tokens).
+            int it = 0, used[2] = {0, 0};
+            for (int u = u0; u < u1 && !*abort_flag;) {
+                const GemmSegment g = segment_at(p, u, u1);
+                const int mt = g.tile % p.m_tiles;
+                const int nh = (p.m - mt * 512 > 256) ? 2 : 1;
+                bool ok = true;
+                for (int kb = g.kb0; kb < g.kb1 && ok; kb++, it++) {
+                    const int s = it % stages;
+                    const uint32_t ph = (it / stages) & 1;
+                    if (!g_mbar_wait(&b_full[s], ph) || !g_mbar_wait(&a_full[s], ph)) { fail(); ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = g_smem_u32(stage0 + (size_t)s * stage_bytes);
+                    const uint32_t b_addr = a_addr + GEMM_WIDE_A_BYTES;
+                    for (int h = 0; h < nh; h++) {
+                        if (kb == g.kb0 && used[h] >= 1) {  // the epilogue must have drained this half's previous tile
+                            if (!g_mbar_wait(&acc_empty[h], (used[h] - 1) & 1)) { fail(); ok = false; break; }
+                            tc_fence_after();
+                        }
+                        const uint32_t d_tmem = tmem_base + (uint32_t)(h * 256);
+#pragma unroll
+                        for (int kk = 0; kk < 4; kk++) {  // 4 x K16 per 64-k stage
+                            const uint64_t ad = smem_desc_sw128(a_addr + kk * 32);
+                            const uint64_t bd = smem_desc_sw128(b_addr + h * GEMM_WIDE_B_HALF + kk * 32);
+                            tc_mma_f16(d_tmem, ad, bd, p.idesc, ((kb - g.kb0) | kk) != 0);
+                        }
+                        if (kb == g.kb1 - 1) {
+                            tc_commit(&acc_full[h]);
+                            used[h]++;
+                        }
+                    }
+                    if (!ok) break;
+                    tc_commit(&s_empty[s]);
+                }
+                if (!ok) break;
+                u += g.kb1 - g.kb0;
+            }
+        } else if (lane == 0) {
             int it = 0, local = 0;
             for (int u = u0; u < u1 && !*abort_flag; local++) {
                 const GemmSegment g = segment_at(p, u, u1);
@@ -517,104 +760,181 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmParams 
         }
     } else if (warp >= 4 && warp < 8) {
         // ------------------------------------------------ epilogue (TMEM lane quarter = warp % 4)
+        // Handles every segment except the tile this CTA owns the beginning of and shares with the following
+        // CTAs: that one is always the last segment of the share and is finished by all warps together below.
         const int quarter = warp & 3;
         const int row = quarter * 32 + lane;  // weight row inside the 128-row block
-        int local = 0;
-        for (int u = u0; u < u1 && !*abort_flag; local++) {
+        int local = 0, used[2] = {0, 0};
+        bool dead = false;
+        float* mine = p.partial + (size_t)blockIdx.x * GEMM_PIECE_TOKENS * GEMM_BN;
+        for (int u = u0; u < u1 && !*abort_flag && !dead; local++) {
             const GemmSegment g = segment_at(p, u, u1);
-            const int buf = local & 1;
             const int nt = g.tile / p.m_tiles, mt = g.tile % p.m_tiles;
-            if (!g_mbar_wait(&acc_full[buf], (local >> 1) & 1)) { if (lane == 0) fail(); break; }
-            tc_fence_after();
             const int n = nt * GEMM_BN + row;
             const bool starts = g.kb0 == 0, ends = g.kb1 == p.k_blocks;
-            // Owner of a tile that continues in the following CTAs: their pieces must be complete.
-            // They were computed at the head of those CTAs' shares, long before this tail of mine.
-            int last_cta = (int)blockIdx.x;
-            if (starts && !ends) {
-                const int tile_end = (g.tile + 1) * p.k_blocks;
-                bool gave_up = false;
-                for (int c = (int)blockIdx.x + 1; c < (int)gridDim.x; c++) {
-                    int c0, c1;
-                    cta_units(p, c, c0, c1);
-                    if (c0 >= tile_end) break;
-                    if (c0 == c1) continue;
-                    last_cta = c;
-                    int spins = 0;  // the same quarter of the other CTA wrote the rows this warp is going to add
-                    while (ld_acquire_u32(p.ready + c * 4 + quarter) != p.launch && ++spins < GEMM_WAIT_SPINS) __nanosleep(64);
-                    if (spins >= GEMM_WAIT_SPINS) gave_up = true;
+            if (starts && !ends) break;
+            // The tile's accumulators: one (double buffered, `local & 1`) or one per 256-token half.
+            const int parts = wide ? ((p.m - mt * 512 > 256) ? 2 : 1) : 1;
+            for (int h = 0; h < parts; h++) {
+                const int acc = wide ? h : (local & 1);
+                const uint32_t parity = wide ? (uint32_t)(used[h] & 1) : (uint32_t)((local >> 1) & 1);
+                const int col_base = wide ? h * 256 : acc * p.bm;   // TMEM column of the accumulator
+                const int tok_base = wide ? mt * 512 + h * 256 : mt * p.bm;
+                const int piece_base = wide ? h * 256 : 0;          // token offset inside a stream-K piece
+                const int ncols = wide ? 256 : p.bm;
+                if (!g_mbar_wait(&acc_full[acc], parity)) { if (lane == 0) fail(); dead = true; break; }
+                tc_fence_after();
+                used[h]++;
+                // 32 columns at a time (also past a BM that is not a multiple of 32)
+                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)col_base;
+                auto emit = [&](const uint32_t (&r)[32], int c) {
+                    if (!starts) write_piece_chunk(mine, r, piece_base + c, row);  // my piece of a tile owned by an earlier CTA
+                    else store_chunk(p.y, p.ldy, p.col0, p.row_unscale, r, tok_base + c, p.m, n, p.rows);
+                };
+                for (int c = 0; c < ncols; c += 32) {
+                    uint32_t r[32];
+                    tmem_ld32(taddr + (uint32_t)c, r);
+                    emit(r, c);
                 }
-                if (gave_up) { if (lane == 0) fail(); break; }
+                tc_fence_before();  // the accumulator has been read: the MMA issuer may overwrite it
+                __syncwarp();
+                if (lane == 0) g_mbar_arrive(&acc_empty[acc]);
             }
-            // room for 256 tokens per CTA: columns are moved 32 at a time, also past a BM that is not a multiple of 32
-            float* mine = p.partial + (size_t)blockIdx.x * 256 * GEMM_BN;
-            for (int c = 0; c < p.bm; c += 32) {
-                uint32_t r[32];
-                tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * p.bm + c), r);
-                const int m0 = mt * p.bm + c;
-                if (!starts) {  // my piece of a tile owned by an earlier CTA: token-major, 128 rows contiguous
-#pragma unroll
-                    for (int j = 0; j < 32; j++) mine[(size_t)(c + j) * GEMM_BN + row] = __uint_as_float(r[j]);
-                    continue;
-                }
-                for (int cc = (int)blockIdx.x + 1; cc <= last_cta; cc++) {  // pieces in CTA order
-                    int c0, c1;
-                    cta_units(p, cc, c0, c1);
-                    if (c0 == c1) continue;
-                    const float* piece = p.partial + (size_t)cc * 256 * GEMM_BN;
-#pragma unroll
-                    for (int j = 0; j < 32; j++)
-                        r[j] = __float_as_uint(__uint_as_float(r[j]) + __ldcg(piece + (size_t)(c + j) * GEMM_BN + row));
-                }
-                if (n < p.rows) {
-#pragma unroll
-                    for (int j = 0; j < 32; j++)
-                        if (m0 + j < p.m)
-                            p.y[(int64_t)(m0 + j) * p.ldy + p.col0 + n] = __uint_as_float(r[j]) * __ldg(p.row_unscale + m0 + j);
-                }
-            }
-            tc_fence_before();
+            if (dead) break;
             if (!starts) {  // publish this warp's 32 rows of the piece
                 __threadfence();
                 __syncwarp();
                 if (lane == 0) st_release_u32(p.ready + blockIdx.x * 4 + quarter, p.launch);
             }
-            __syncwarp();
-            if (lane == 0) g_mbar_arrive(&acc_empty[buf]);
             u += g.kb1 - g.kb0;
         }
     } else {
-        // ------------------------------------------------ dequant warps 2, 3, 8..13: one 16-row tile each per stage
-        const int dq = (warp < 4) ? warp - 2 : warp - 6;  // 0..7 = 16-row tile inside the 128-row block
-        // weight tile of unit u (tile-major, k-block minor), this warp's 16-row tile of the 128-row block
-        auto weight_tile = [&](int u) {
-            const int tile = u / p.k_blocks, kb = u - tile * p.k_blocks;
-            const int64_t wrt = (int64_t)(tile / p.m_tiles) * (GEMM_BN / 16) + dq;
-            return p.tiles + (wrt * p.kt_w + kb / KB_PER_WTILE) * (int64_t)TILE_BYTES;
-        };
-        // one step: wait for the stage, convert the registers loaded one step ago, hand the stage over
-        auto finish_step = [&](const DequantRegs<QT>& regs, int it) {
+        // ------------------------------------------------ dequant warps 2, 3, 8..: one 16-row tile (or half of one) each per stage
+        const int dw = (warp < 4) ? warp - 2 : warp - 6;  // 0 .. GEMM_DEQUANT_WARPS - 1
+        // 16-row tile inside the 128-row block, and the first row half (rows g or g + 8) this warp converts
+        const int dq = GEMM_DQ_HALVES == 2 ? dw : dw >> 1, hsel0 = GEMM_DQ_HALVES == 2 ? 0 : dw & 1;
+        // One step: convert the registers loaded earlier into fp16 rows (still in registers), wait for the stage,
+        // store them and hand the stage over.  Converting before the wait keeps the arithmetic off the path
+        // between "the MMAs have released the stage" and "the stage is full again".
+        const int dg = lane >> 2, dq4 = lane & 3;
+        auto finish_step = [&](const auto& regs, int it) {  // regs[GEMM_DQ_HALVES]
             const int s = it % stages;
+            uint4 out[GEMM_DQ_HALVES][4];
+#pragma unroll
+            for (int hh = 0; hh < GEMM_DQ_HALVES; hh++)
+                regs[hh].convert(lane, hsel0 + hh, [&](int, int j, uint4 v) { out[hh][j] = v; });
             if (it >= stages && !g_mbar_wait(&s_empty[s], ((it / stages) - 1) & 1)) {
                 if (lane == 0) fail();
                 return false;
             }
-            regs.store(stage0 + (size_t)s * stage_bytes, dq, lane);
+            uint8_t* a_stage = stage0 + (size_t)s * stage_bytes;
+            const int nj = wide ? 2 : 4;  // 16-byte chunks per row half and lane: 64 k or 128 k per stage
+#pragma unroll
+            for (int hh = 0; hh < GEMM_DQ_HALVES; hh++)
+#pragma unroll
+                for (int j = 0; j < 4; j++)
+                    if (j < nj)
+                        *reinterpret_cast<uint4*>(a_stage + a_chunk_off(dq * 16 + dg + 8 * (hsel0 + hh), j * 4 + dq4)) = out[hh][j];
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the tensor core
             __syncwarp();
             if (lane == 0) g_mbar_arrive(&a_full[s]);
             return true;
         };
-        // two register sets in turn: the loads of step u + 1 are in flight while step u is converted
-        DequantRegs<QT> ra, rb;
-        int it = 0;
-        if (u0 < u1) ra.load(weight_tile(u0), u0 % p.k_blocks, lane);
-        for (int u = u0; u < u1 && !*abort_flag; u += 2, it += 2) {
-            if (u + 1 < u1) rb.load(weight_tile(u + 1), (u + 1) % p.k_blocks, lane);
-            if (!finish_step(ra, it)) break;
-            if (u + 1 >= u1) break;
-            if (u + 2 < u1) ra.load(weight_tile(u + 2), (u + 2) % p.k_blocks, lane);
-            if (!finish_step(rb, it + 1)) break;
+        // DEPTH register sets in turn: the loads of steps u + 1 .. u + DEPTH - 1 are in flight while step u is
+        // converted.  Two sets for the 128-k steps (four measured 9 % slower: the unrolled loop is four
+        // conversions long), four for the 64-k steps, which are half as long and half as large.
+        auto run = [&](auto& r, auto kbw_tag, auto depth_tag) {
+            constexpr int DEPTH = decltype(depth_tag)::value, KBW = decltype(kbw_tag)::value;  // KBW: stage-sized pieces per weight k-tile
+            // weight tile of unit u (tile-major, k-block minor), this warp's rows of the 128-row block, and the
+            // piece of it the k-block covers
+            auto load = [&](auto& regs, int u) {
+                const int tile = u / p.k_blocks, kb = u - tile * p.k_blocks;
+                const int64_t wrt = (int64_t)(tile / p.m_tiles) * (GEMM_BN / 16) + dq;
+#pragma unroll
+                for (int hh = 0; hh < GEMM_DQ_HALVES; hh++)
+                    regs[hh].load(p.tiles + (wrt * p.kt_w + kb / KBW) * (int64_t)TILE_BYTES, kb % KBW, lane, hsel0 + hh);
+            };
+#pragma unroll
+            for (int d = 0; d < DEPTH - 1; d++)
+                if (u0 + d < u1) load(r[d], u0 + d);
+            bool ok = true;
+            for (int u = u0, it = 0; u < u1 && ok && !*abort_flag; u += DEPTH) {
+#pragma unroll
+                for (int d = 0; d < DEPTH; d++) {  // r[d] holds step u + d; refill the set that was converted last
+                    if (u + d >= u1) break;
+                    if (u + d + DEPTH - 1 < u1) load(r[(d + DEPTH - 1) % DEPTH], u + d + DEPTH - 1);
+                    if (!finish_step(r[d], it++)) { ok = false; break; }
+                }
+            }
+        };
+        if (wide) {
+            DequantHalf<QT> r[4][GEMM_DQ_HALVES];
+            run(r, std::integral_constant<int, Tile<QT>::K / GEMM_WIDE_BK>{}, std::integral_constant<int, 4>{});
+        } else {
+            DequantRegs<QT> r[2][GEMM_DQ_HALVES];
+            run(r, std::integral_constant<int, KB_PER_WTILE>{}, std::integral_constant<int, 2>{});
+        }
+    }
+
+    // ------------------------------------------------ the tile whose beginning this CTA owns and whose rest lies in the
+    // following CTAs.  It is the last segment of the share, so every role has run out of work: twelve warps
+    // (three per TMEM lane quarter, each taking every third group of 32 tokens) add the followers' pieces in CTA
+    // order and write y.  The pieces were computed at the head of the followers' shares, long before this tail.
+    if (u0 < u1 && warp < 12) {
+        const int tile = (u1 - 1) / p.k_blocks;
+        const int kb0 = max(u0, tile * p.k_blocks) - tile * p.k_blocks, kb1 = u1 - tile * p.k_blocks;
+        if (kb0 == 0 && kb1 < p.k_blocks) {
+            const int quarter = warp & 3, slice = warp >> 2;
+            const int row = quarter * 32 + lane;
+            const int nt = tile / p.m_tiles, mt = tile % p.m_tiles;
+            const int n = nt * GEMM_BN + row;
+            // accumulator bookkeeping of the segments before this one (what the epilogue warps counted)
+            int local = 0, used[2] = {0, 0};
+            for (int u = u0; u < u1;) {
+                const GemmSegment g = segment_at(p, u, u1);
+                if (g.tile == tile) break;
+                used[0]++;
+                if (wide && p.m - (g.tile % p.m_tiles) * 512 > 256) used[1]++;
+                local++;
+                u += g.kb1 - g.kb0;
+            }
+            // followers: the CTAs holding the rest of the tile; this quarter's rows of their pieces must be complete
+            int last_cta = (int)blockIdx.x;
+            bool ok = !*abort_flag;
+            const int tile_end = (tile + 1) * p.k_blocks;
+            for (int c = (int)blockIdx.x + 1; c < (int)gridDim.x && ok; c++) {
+                int c0, c1;
+                cta_units(p, c, c0, c1);
+                if (c0 >= tile_end) break;
+                if (c0 == c1) continue;
+                last_cta = c;
+                int spins = 0;
+                while (ld_acquire_u32(p.ready + c * 4 + quarter) != p.launch && ++spins < GEMM_WAIT_SPINS) __nanosleep(64);
+                if (spins >= GEMM_WAIT_SPINS) ok = false;
+            }
+            if (!ok && lane == 0) fail();
+            const int parts = wide ? ((p.m - mt * 512 > 256) ? 2 : 1) : 1;
+            for (int h = 0; h < parts && ok; h++) {
+                const int acc = wide ? h : (local & 1);
+                const uint32_t parity = wide ? (uint32_t)(used[h] & 1) : (uint32_t)((local >> 1) & 1);
+                const int col_base = wide ? h * 256 : acc * p.bm;
+                const int tok_base = wide ? mt * 512 + h * 256 : mt * p.bm;
+                const int piece_base = wide ? h * 256 : 0;
+                const int ncols = wide ? 256 : p.bm;
+                if (!g_mbar_wait(&acc_full[acc], parity)) { if (lane == 0) fail(); break; }
+                tc_fence_after();
+                for (int c = slice * 32; c < ncols; c += 96) {
+                    uint32_t r[32];
+                    tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(col_base + c), r);
+                    for (int cc = (int)blockIdx.x + 1; cc <= last_cta; cc++) {  // pieces in CTA order
+                        int c0, c1;
+                        cta_units(p, cc, c0, c1);
+                        if (c0 == c1) continue;
+                        add_piece_chunk(p.partial + (size_t)cc * GEMM_PIECE_TOKENS * GEMM_BN, r, piece_base + c, row);
+                    }
+                    store_chunk(p.y, p.ldy, p.col0, p.row_unscale, r, tok_base + c, p.m, n, p.rows);
+                }
+            }
         }
     }
 
@@ -682,11 +1002,16 @@ int gemm_launch(Context* c, const GemvCall& call, cudaStream_t s) {
     p.k = (int)w.g.k;
     p.kt_w = (int)w.g.kt;
     p.m = (int)call.m;
+    // More than 512 tokens: token tiles of 2 x 256 that share every dequantized weight stage (half the weight
+    // loads and conversions per MMA; 4 - 10 % faster at 2048 tokens, equal at 512).  Otherwise one MMA column
+    // block per tile and a double-buffered accumulator.
+    p.halves = call.m > WF_GEMM_WIDE_MIN ? 2 : 1;
     p.bm = call.m >= 256 ? 256 : (int)((call.m + 15) / 16 * 16);
+    const int tile_tokens = p.bm * p.halves, bk = p.halves == 2 ? GEMM_WIDE_BK : GEMM_BK;
     p.n_tiles = (int)((w.g.rows + GEMM_BN - 1) / GEMM_BN);
-    p.m_tiles = (int)((call.m + p.bm - 1) / p.bm);
-    p.k_blocks = (int)((w.g.k + GEMM_BK - 1) / GEMM_BK);
-    const size_t stage_bytes = GEMM_A_BYTES + (size_t)p.bm * 256;
+    p.m_tiles = (int)((call.m + tile_tokens - 1) / tile_tokens);
+    p.k_blocks = (int)((w.g.k + bk - 1) / bk);
+    const size_t stage_bytes = p.halves == 2 ? (size_t)GEMM_WIDE_A_BYTES + 2 * GEMM_WIDE_B_HALF : GEMM_A_BYTES + (size_t)p.bm * 256;
     p.stages = (int)std::min<size_t>((GEMM_SMEM_LIMIT - 1024) / stage_bytes, 8);
     // A = fp16 weights, B = fp16 activations, D = fp32; both operands K-major
     p.idesc = (1u << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(p.bm >> 3) << 17) | ((uint32_t)(GEMM_BN >> 4) << 24);
@@ -728,7 +1053,7 @@ int gemm_launch(Context* c, const GemvCall& call, cudaStream_t s) {
     p.unit_q = (int)(units / grid);
     p.unit_r = (int)(units % grid);
     if (!c->d_gemm_partial) {
-        WF_CUDA(c, cudaMalloc(&c->d_gemm_partial, (size_t)c->sm_count * 256 * GEMM_BN * sizeof(float)));
+        WF_CUDA(c, cudaMalloc(&c->d_gemm_partial, (size_t)c->sm_count * GEMM_PIECE_TOKENS * GEMM_BN * sizeof(float)));
         WF_CUDA(c, cudaMalloc(&c->d_gemm_ready, (size_t)c->sm_count * 4 * sizeof(unsigned int)));
         WF_CUDA(c, cudaMemset(c->d_gemm_ready, 0, (size_t)c->sm_count * 4 * sizeof(unsigned int)));
     }
