@@ -625,8 +625,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmParams 
     uint64_t* acc_empty = acc_full + 2;                          // [2]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    const bool wide = p.halves == 2;
-    const uint32_t a_bytes = wide ? GEMM_WIDE_A_BYTES : GEMM_A_BYTES;
+    const bool wide = p.halves == 2, k64 = wide;  // 64-k stages go with the two-half token tiles (alone they measured 25 % slower)
+    const uint32_t a_bytes = k64 ? GEMM_WIDE_A_BYTES : GEMM_A_BYTES;
     const uint32_t b_bytes = wide ? 2u * GEMM_WIDE_B_HALF : (uint32_t)p.bm * 256;
     const uint32_t stage_bytes = a_bytes + b_bytes;
     uint8_t* stage0 = smem + 1024;
@@ -744,7 +744,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmParams 
                     if (!g_mbar_wait(&b_full[s], ph) || !g_mbar_wait(&a_full[s], ph)) { fail(); ok = false; break; }
                     tc_fence_after();
                     const uint32_t a_addr = g_smem_u32(stage0 + (size_t)s * stage_bytes);
-                    const uint32_t b_addr = a_addr + GEMM_A_BYTES;
+                    const uint32_t b_addr = a_addr + a_bytes;
 #pragma unroll
                     for (int kk = 0; kk < 8; kk++) {  // 8 x K16 per stage; spans of 64 k are 16 KB (A) / bm*128 B (B) apart
                         const uint64_t ad = smem_desc_sw128(a_addr + (kk >> 2) * (GEMM_BN * 128) + (kk & 3) * 32);
@@ -817,6 +817,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmParams 
         // store them and hand the stage over.  Converting before the wait keeps the arithmetic off the path
         // between "the MMAs have released the stage" and "the stage is full again".
         const int dg = lane >> 2, dq4 = lane & 3;
+        const bool odd_row = (dg & 1) != 0;
         auto finish_step = [&](const auto& regs, int it) {  // regs[GEMM_DQ_HALVES]
             const int s = it % stages;
             uint4 out[GEMM_DQ_HALVES][4];
@@ -828,13 +829,19 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmParams 
                 return false;
             }
             uint8_t* a_stage = stage0 + (size_t)s * stage_bytes;
-            const int nj = wide ? 2 : 4;  // 16-byte chunks per row half and lane: 64 k or 128 k per stage
+            const int nj = k64 ? 2 : 4;  // 16-byte chunks per row half and lane: 64 k or 128 k per stage
+            // A 16-byte store is served eight lanes at a time, i.e. two consecutive rows x four chunks.  Under the
+            // 128-byte swizzle chunks 4j .. 4j + 3 of both rows fall into the same 64-byte half of their rows, a
+            // two-way bank conflict; so the odd row of each pair stores its chunks of block j ^ 1 in that slot.
 #pragma unroll
             for (int hh = 0; hh < GEMM_DQ_HALVES; hh++)
 #pragma unroll
                 for (int j = 0; j < 4; j++)
-                    if (j < nj)
-                        *reinterpret_cast<uint4*>(a_stage + a_chunk_off(dq * 16 + dg + 8 * (hsel0 + hh), j * 4 + dq4)) = out[hh][j];
+                    if (j < nj) {
+                        const uint4 e = out[hh][j], o = out[hh][j ^ 1];
+                        const uint4 v = odd_row ? o : e;
+                        *reinterpret_cast<uint4*>(a_stage + a_chunk_off(dq * 16 + dg + 8 * (hsel0 + hh), ((j ^ (int)odd_row) * 4 + dq4))) = v;
+                    }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the tensor core
             __syncwarp();
             if (lane == 0) g_mbar_arrive(&a_full[s]);
@@ -867,7 +874,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmParams 
                 }
             }
         };
-        if (wide) {
+        if (k64) {
             DequantHalf<QT> r[4][GEMM_DQ_HALVES];
             run(r, std::integral_constant<int, Tile<QT>::K / GEMM_WIDE_BK>{}, std::integral_constant<int, 4>{});
         } else {
