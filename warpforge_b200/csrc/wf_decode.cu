@@ -193,12 +193,13 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_program_kernel(const Pro
         if (threadIdx.x == 0) {
             const unsigned long long want = idx * gridDim.x;
             int spins = 0;
-            __threadfence();
-            atomicAdd(&P.sync->arrive, 1ULL);
-            while (ld_relaxed_gpu(&P.sync->arrive) < want && ++spins < PROG_BARRIER_SPINS) {
+            // one release-add (no value comes back, the poll starts at once) and acquire loads: the y rows this
+            // CTA wrote before the bar.sync above are ordered before the add, the reads after the barrier after
+            // the load that saw the last arrival
+            asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(&P.sync->arrive), "l"(1ULL) : "memory");
+            while (ld_acquire_gpu(&P.sync->arrive) < want && ++spins < PROG_BARRIER_SPINS) {
             }
             if (spins >= PROG_BARRIER_SPINS) atomicOr(P.status, STATUS_PEER_WAIT_TIMEOUT);
-            __threadfence();
         }
         barriers++;
         consumers_sync();
