@@ -1,0 +1,100 @@
+"""Times one rank's shard of benchmark config 5 (70B-shape projection set, Q4_K, 8 row shards) on one GPU.
+
+    python -m warpforge_b200.bench_config5 [--world 8] [--layers 5] [--iters 3]
+
+Every rank of the row-sharded run does exactly this work between two gathers, so one GPU is enough to
+measure it: rows / world of each of the seven projections of a layer, `--layers` distinct copies of each
+(the weights of `--layers` layers, > 2 x L2, so every call reads its weights from HBM), walked in layer order.
+Two legs: (i) batch-16 decode (16 bf16 tokens through `wf_qlinear`, which routes more than 8 tokens to the
+tensor-core kernel) against the HBM roofline, (ii) a 2048-token prefill against the tensor roofline.
+The per-layer time times 80 layers is the per-rank step time of the full configuration (stated as an
+extrapolation in the output).  Events on the launching stream, three warm-up walks.  One JSON line per leg.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+from . import _native as N
+from . import quant as Q
+from .backend import CudaContext, QuantizedWeight
+from .decode import LLAMA_70B_Q4_K
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return float(d["hbm_gbs"]), float(d["bf16_tflops"]), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--world", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=5, help="distinct layers resident (the step is extrapolated to 80)")
+    ap.add_argument("--iters", type=int, default=3)
+    a = ap.parse_args()
+    spec = LLAMA_70B_Q4_K
+    ctx = CudaContext(0)
+    lib, h = ctx._lib, ctx.handle
+    qt = spec.qtype
+    weights, shard_bytes, shard_macs = [], 0, 0
+    for layer in range(a.layers):
+        row = []
+        for i, (name, rows, k) in enumerate(spec.projections):
+            r = rows // a.world
+            blocks = Q.synth_weight(qt, r, k, Q.config_seed(5, layer * len(spec.projections) + i))
+            row.append((name, r, k, QuantizedWeight(ctx, qt, blocks, r, k)))
+            if layer == 0:
+                shard_bytes += r * qt.row_bytes(k)
+                shard_macs += r * k
+        weights.append(row)
+    kmax = max(k for _, _, k in spec.projections)
+    rmax = max(r // a.world for _, r, _ in spec.projections)
+    hbm, tf, src = peaks()
+    e0, e1 = ctx.create_event(), ctx.create_event()
+    for leg, m in (("decode_batch16", 16), ("prefill_2048", 2048)):
+        x = Q.synth_activation_bf16(m, kmax, 5)
+        dx = ctx.allocate(x.nbytes)
+        ctx.copy_to_device(dx, x)
+        dy = ctx.allocate(m * rmax * 4)
+
+        def walk():
+            for row in weights:
+                for name, r, k, w in row:
+                    # the activation buffer is read as [m, k] (row stride k): same bytes for every projection
+                    N.check(name, lib.wf_qlinear(h, w.handle, dx, N.WF_DTYPE_BF16, 1, m, dy, 1, 0), h)
+
+        for _ in range(3):
+            walk()
+        ctx.synchronize()
+        ctx.record_event(e0)
+        for _ in range(a.iters):
+            walk()
+        ctx.record_event(e1)
+        ctx.synchronize()
+        us_layer = ctx.elapsed_ms(e0, e1) * 1e3 / a.iters / a.layers
+        out = {"leg": leg, "tokens": m, "world": a.world, "layers_resident": a.layers, "us_per_layer": round(us_layer, 1),
+               "ms_per_step_80_layers_extrapolated": round(us_layer * spec.layers / 1e3, 2),
+               "weight_bytes_per_layer_per_rank": shard_bytes}
+        if m <= 16:
+            gbs = shard_bytes / us_layer / 1e3
+            out.update({"bound": "hbm", "achieved_gbs": round(gbs, 1), "peak_gbs": hbm, "frac": round(gbs / hbm, 3), "peak": src})
+        else:
+            tfs = 2.0 * m * shard_macs / us_layer / 1e6
+            out.update({"bound": "tensor", "achieved_tflops": round(tfs, 1), "peak_tflops": tf, "frac": round(tfs / tf, 3), "peak": src})
+        print(json.dumps(out), flush=True)
+        ctx.free(dx)
+        ctx.free(dy)
+    for row in weights:
+        for _, _, _, w in row:
+            w.close()
+    ctx.close()
+
+
+if __name__ == "__main__":
+    main()

@@ -38,8 +38,8 @@ struct ProgOp {
     int n_total, pad2;
     int64_t ldy, col0;
     int rows, k, kt, rt;
-    int chunk_q, chunk_r;
-    int flags, pad;
+    int chunk_q, chunk_r;      // CTA b < ctas owns tiles [b*q + min(b,r), (b+1)*q + min(b+1,r)); the others none
+    int flags, ctas;
 };
 
 struct ProgSync {                     // device memory owned by the program
@@ -125,7 +125,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_program_kernel(const Pro
             for (int o = 0; o < P.n_ops && !*abort_flag; o++) {
                 const ProgOp& op = P.ops[o];
                 const int t0 = bx * op.chunk_q + min(bx, op.chunk_r);
-                const int t1 = t0 + op.chunk_q + (bx < op.chunk_r ? 1 : 0);
+                const int t1 = bx < op.ctas ? t0 + op.chunk_q + (bx < op.chunk_r ? 1 : 0) : t0;
                 produce_share<QT>(op.tiles, t0, t1, smem_u32(ring), bar, stages, pos, abort_flag);
             }
         }
@@ -210,7 +210,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_program_kernel(const Pro
         const int flags = op.flags;
         const int kt = op.kt;
         const int t0 = bx * op.chunk_q + min(bx, op.chunk_r);
-        const int t1 = t0 + op.chunk_q + (bx < op.chunk_r ? 1 : 0);
+        const int t1 = bx < op.ctas ? t0 + op.chunk_q + (bx < op.chunk_r ? 1 : 0) : t0;
         uint2* slots = P.scratch + (size_t)(o & 1) * gridDim.x * 128;
 
         stamp();  // op start (4 stamps per op: start, after barrier, after staging, after compute)
@@ -365,8 +365,9 @@ int wf_program_create(int64_t ctx, int n_ops, const int64_t* weights, const int6
         op.k = (int)w->g.k;
         op.kt = (int)w->g.kt;
         op.rt = (int)w->g.rt;
-        op.chunk_q = (int)(total / grid);
-        op.chunk_r = (int)(total % grid);
+        op.ctas = std::min(grid, gemv_ctas(c->sm_count, total));  // the split gemv_kernel uses: same sums, same bits
+        op.chunk_q = (int)(total / op.ctas);
+        op.chunk_r = (int)(total % op.ctas);
         op.flags = (o == 0 ? (flags[o] | OP_NEW_X) : flags[o]) & (OP_NEW_X | OP_DEPENDS);
         if ((op.flags & OP_DEPENDS) && !(op.flags & OP_NEW_X)) op.flags |= OP_NEW_X;
         if (o == 0) op.flags &= ~OP_DEPENDS;  // nothing of this run precedes the first op

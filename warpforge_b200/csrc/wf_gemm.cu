@@ -1012,7 +1012,10 @@ int gemm_launch(Context* c, const GemvCall& call, cudaStream_t s) {
     // More than 512 tokens: token tiles of 2 x 256 that share every dequantized weight stage (half the weight
     // loads and conversions per MMA; 4 - 10 % faster at 2048 tokens, equal at 512).  Otherwise one MMA column
     // block per tile and a double-buffered accumulator.
-    p.halves = call.m > WF_GEMM_WIDE_MIN ? 2 : 1;
+    // The two-half tiles make stream-K pieces of 256 KB: only when there are enough tiles that a tile is cut at most
+    // about twice.
+    const int64_t wide_tiles = ((w.g.rows + GEMM_BN - 1) / GEMM_BN) * ((call.m + 511) / 512);
+    p.halves = (call.m > WF_GEMM_WIDE_MIN && wide_tiles >= c->sm_count / 2) ? 2 : 1;
     p.bm = call.m >= 256 ? 256 : (int)((call.m + 15) / 16 * 16);
     const int tile_tokens = p.bm * p.halves, bk = p.halves == 2 ? GEMM_WIDE_BK : GEMM_BK;
     p.n_tiles = (int)((w.g.rows + GEMM_BN - 1) / GEMM_BN);
@@ -1056,7 +1059,11 @@ int gemm_launch(Context* c, const GemvCall& call, cudaStream_t s) {
     // stream-K shares and the scratch the CTAs hand pieces of cut tiles through
     const int64_t units = (int64_t)p.n_tiles * p.m_tiles * p.k_blocks;
     if (units >= (1LL << 31)) return set_error(c, WF_ERR_TOO_LARGE, "GEMM has too many tile steps");
-    const int grid = (int)std::min<int64_t>(c->sm_count, units);
+    // A tile of U k-blocks shared by S CTAs costs about U / S steps plus S - 1 pieces added by its owner, a piece
+    // costing about two steps: no share is shorter than sqrt(2 U) steps, which bounds S for weights with few tiles.
+    int min_units = 1;
+    while ((int64_t)min_units * min_units < 2 * (int64_t)p.k_blocks) min_units++;
+    const int grid = (int)std::min<int64_t>(c->sm_count, std::max<int64_t>(1, units / min_units));
     p.unit_q = (int)(units / grid);
     p.unit_r = (int)(units % grid);
     if (!c->d_gemm_partial) {

@@ -215,8 +215,7 @@ static int launch_passes(Context* c, const GemvCall& call, cudaStream_t s, uint2
     const int kp = (int)w.g.kt * tile_k(qt);
     const int per_pass = gemv_max_tokens_per_pass(w, call.x_dtype);
     const int64_t total = w.g.rt * w.g.kt;
-    int grid = c->sm_count;
-    if ((int64_t)grid > total) grid = (int)total;
+    const int grid = gemv_ctas(c->sm_count, total);
     const size_t esz = call.x_dtype == WF_DTYPE_F32 ? 4 : 2;
     int max_rounds = (int)((total / grid + 1 + GEMV_WARPS - 1) / GEMV_WARPS);
     for (int64_t m0 = 0; m0 < call.m; m0 += per_pass) {

@@ -26,6 +26,13 @@ constexpr int GEMV_XCOLS = 8;  // columns of one mma n-tile
 constexpr int GEMV_FIXUP_SPINS = 1 << 22;
 constexpr int GEMV_SLOT_SPINS = 1 << 24;
 constexpr int GEMV_MAX_SLOTS = 8;  // partial-sum slots a CTA rotates through
+// CTAs that share a weight of `tiles` tiles: one per SM, but never fewer than two ring rounds of tiles per CTA -- a
+// small weight cut into 148 shares would spend its time in the fix-up between the CTAs that share a row-tile,
+// not in reading its bytes.
+inline int gemv_ctas(int sm_count, int64_t tiles) {
+    const int64_t by_work = tiles / (2 * GEMV_WARPS);
+    return (int)std::min<int64_t>(sm_count, std::max<int64_t>(1, by_work));
+}
 // control block: abort flag | full[MAX_STAGES] | empty[MAX_STAGES] | done[MAX_SLOTS] | vacant[MAX_SLOTS]
 constexpr int GEMV_CTRL_BYTES = 128 + (2 * GEMV_MAX_STAGES + 2 * GEMV_MAX_SLOTS) * 8;
 // XC = 1: one live column; XC = 8: up to 8.  N partial-sum slots of [GEMV_WARPS][ELEMS] floats.
@@ -505,23 +512,29 @@ __device__ __forceinline__ void collect_pieces(uint2* slots, float (&v)[(ELEMS +
         const int c0 = c * chunk_q + min(c, chunk_r), c1 = c0 + chunk_q + (c < chunk_r ? 1 : 0);
         if (c0 >= row_end) break;
         if (c0 == c1) continue;
+        // all of this lane's elements of the piece are requested at once; those not yet published are polled
+        constexpr int PER_LANE = (ELEMS + 31) / 32;
+        uint2 e[PER_LANE];
 #pragma unroll
-        for (int u = 0; u < (ELEMS + 31) / 32; u++) {
+        for (int u = 0; u < PER_LANE; u++) {
+            const int i = lane + 32 * u;
+            e[u] = i < ELEMS ? ld_slot(slots + (size_t)c * 128 + i) : make_uint2(0u, 1u);
+        }
+#pragma unroll
+        for (int u = 0; u < PER_LANE; u++) {
             const int i = lane + 32 * u;
             if (i >= ELEMS) continue;
             uint2* sp = slots + (size_t)c * 128 + i;
-            uint2 e;
             int spins = 0;
-            do {
-                e = ld_slot(sp);
-                if (e.y != 0u) break;
+            while (e[u].y == 0u && ++spins < GEMV_FIXUP_SPINS) {
                 __nanosleep(32);
-            } while (++spins < GEMV_FIXUP_SPINS);
-            if (e.y == 0u) {
+                e[u] = ld_slot(sp);
+            }
+            if (e[u].y == 0u) {
                 atomicOr(status, STATUS_GEMV_FIXUP_TIMEOUT);
                 gave_up = true;
             } else {
-                v[u] += __uint_as_float(e.x);
+                v[u] += __uint_as_float(e[u].x);
                 st_slot(sp, make_uint2(0u, 0u));
             }
         }
