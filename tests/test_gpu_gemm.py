@@ -39,7 +39,9 @@ def _check(got, want):
 
 @pytest.mark.parametrize("name", ["q4_0", "q8_0", "q4_k", "q4_1"])
 @pytest.mark.parametrize("rows,k,m", [(128, 256, 16), (256, 1024, 64), (1000, 2048, 300), (136, 512, 9), (4096, 4096, 33),
-                                      (256, 1024, 513), (384, 1280, 700), (2048, 512, 1024)])
+                                      (256, 1024, 513), (384, 1280, 700), (2048, 512, 1024),
+                                      # enough tiles for the token tiles of 2 x 256: a last tile with one half, rows not a multiple of 128
+                                      (4800, 256, 513), (4864, 512, 700)])
 def test_gemm_matches_oracle(backend, oracle, name, rows, k, m):
     qt, oq = QT[name]
     blocks = Q.synth_weight(qt, rows, k, 77 + rows + m)
