@@ -562,6 +562,7 @@ constexpr int XPRE_THREADS = 256, XPRE_KEEP = 4;
 __global__ void __launch_bounds__(XPRE_THREADS) x_to_f16_kernel(const uint16_t* __restrict__ x, __half* __restrict__ x16,
                                                                 float* __restrict__ unscale, int k) {
     __shared__ int s_emax;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the GEMM may set itself up while the rows are converted
     const uint4* row = reinterpret_cast<const uint4*>(x + (size_t)blockIdx.x * k);  // k is a multiple of 8
     uint4* out = reinterpret_cast<uint4*>(x16 + (size_t)blockIdx.x * k);
     const int pieces = k >> 3;
@@ -665,6 +666,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmParams 
     if (warp == 0) {
         // ------------------------------------------------ TMA producer (activations)
         if (lane == 0) {
+            asm volatile("griddepcontrol.wait;" ::: "memory");  // the fp16 activations are the pre-pass kernel's output
             int it = 0;
             for (int u = u0; u < u1 && !*abort_flag;) {
                 const GemmSegment g = segment_at(p, u, u1);
@@ -766,6 +768,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmParams 
         const int row = quarter * 32 + lane;  // weight row inside the 128-row block
         int local = 0, used[2] = {0, 0};
         bool dead = false;
+        asm volatile("griddepcontrol.wait;" ::: "memory");  // the row scales are the pre-pass kernel's output
         float* mine = p.partial + (size_t)blockIdx.x * GEMM_PIECE_TOKENS * GEMM_BN;
         for (int u = u0; u < u1 && !*abort_flag && !dead; local++) {
             const GemmSegment g = segment_at(p, u, u1);
@@ -888,6 +891,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmParams 
     // (three per TMEM lane quarter, each taking every third group of 32 tokens) add the followers' pieces in CTA
     // order and write y.  The pieces were computed at the head of the followers' shares, long before this tail.
     if (u0 < u1 && warp < 12) {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
         const int tile = (u1 - 1) / p.k_blocks;
         const int kb0 = max(u0, tile * p.k_blocks) - tile * p.k_blocks, kb1 = u1 - tile * p.k_blocks;
         if (kb0 == 0 && kb1 < p.k_blocks) {
@@ -992,8 +996,20 @@ static cudaError_t gemm_launch_one(const GemmParams& p, const CUtensorMap& map, 
         if (e != cudaSuccess) return e;
         attr_set[dev] = true;
     }
-    gemm_kernel<QT><<<grid, GEMM_THREADS, smem, s>>>(p, map);
-    return cudaGetLastError();
+    // Programmatic stream serialization: this kernel may start while the activation pre-pass (the previous launch of
+    // the stream) is still running; what reads the pre-pass's output waits with griddepcontrol.wait, the rest
+    // (barrier set-up, TMEM allocation, the first weight loads and conversions) runs under it.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, gemm_kernel<QT>, p, map);
 }
 
 int gemm_launch(Context* c, const GemvCall& call, cudaStream_t s) {
@@ -1059,10 +1075,12 @@ int gemm_launch(Context* c, const GemvCall& call, cudaStream_t s) {
     // stream-K shares and the scratch the CTAs hand pieces of cut tiles through
     const int64_t units = (int64_t)p.n_tiles * p.m_tiles * p.k_blocks;
     if (units >= (1LL << 31)) return set_error(c, WF_ERR_TOO_LARGE, "GEMM has too many tile steps");
-    // A tile of U k-blocks shared by S CTAs costs about U / S steps plus S - 1 pieces added by its owner, a piece
-    // costing about two steps: no share is shorter than sqrt(2 U) steps, which bounds S for weights with few tiles.
+    // A tile of U k-blocks shared by S CTAs costs about U / S steps plus S - 1 pieces added by its owner, a piece of
+    // 256 tokens costing about two steps (smaller ones in proportion, 0.3 at least): no share is shorter than
+    // sqrt(c U) steps, which bounds S for weights with few tiles.
+    const double piece_steps = std::max(0.3, 2.0 * tile_tokens / 256.0);
     int min_units = 1;
-    while ((int64_t)min_units * min_units < 2 * (int64_t)p.k_blocks) min_units++;
+    while ((double)min_units * min_units < piece_steps * (double)p.k_blocks) min_units++;
     const int grid = (int)std::min<int64_t>(c->sm_count, std::max<int64_t>(1, units / min_units));
     p.unit_q = (int)(units / grid);
     p.unit_r = (int)(units % grid);
