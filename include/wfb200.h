@@ -46,6 +46,7 @@ extern "C" {
 /* ---- enums (ggml type ids, as in GGUF.java:294-305) ------------------------------- */
 #define WF_QTYPE_Q4_0 2
 #define WF_QTYPE_Q4_1 3
+#define WF_QTYPE_Q5_0 6 /* GGUF.java:332-351 knows its size only; held on the device in the Q8_0 layout */
 #define WF_QTYPE_Q8_0 8
 #define WF_QTYPE_Q4_K 14
 

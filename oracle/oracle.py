@@ -27,9 +27,9 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libwforacle.so")
 
-Q4_0, Q4_1, Q8_0, Q4_K = 2, 3, 8, 14  # ggml type ids, GGUF.java:297-305
-BLOCK_ELEMS = {Q4_0: 32, Q4_1: 32, Q8_0: 32, Q4_K: 256}
-BLOCK_BYTES = {Q4_0: 18, Q4_1: 20, Q8_0: 34, Q4_K: 144}
+Q4_0, Q4_1, Q8_0, Q4_K, Q5_0 = 2, 3, 8, 14, 6  # ggml type ids, GGUF.java:297-305
+BLOCK_ELEMS = {Q4_0: 32, Q4_1: 32, Q8_0: 32, Q4_K: 256, Q5_0: 32}
+BLOCK_BYTES = {Q4_0: 18, Q4_1: 20, Q8_0: 34, Q4_K: 144, Q5_0: 22}
 
 
 def build(force: bool = False) -> str:
@@ -312,8 +312,21 @@ def np_dequant_q4_k(blocks, n: int) -> np.ndarray:
     return ((dl[:, :, None] * q).astype(np.float32) - ml[:, :, None]).astype(np.float32).ravel()[:n]
 
 
+def np_dequant_q5_0(blocks, n: int) -> np.ndarray:
+    """Q5_0 (public GGUF format): d fp16, 32 high bits, 16 code bytes; element i < 16 = low nibble of byte i,
+    element i + 16 = high nibble of byte i; w = d * ((nibble | bit << 4) - 16)."""
+    blk = np.asarray(blocks, np.uint8).reshape(-1, 22)
+    d = np_half_to_float(blk[:, :2].copy().view(np.uint16)[:, 0])
+    qh = blk[:, 2:6].copy().view("<u4")[:, 0]
+    qs = blk[:, 6:]
+    nib = np.concatenate([qs & 0x0F, qs >> 4], axis=1).astype(np.int32)
+    bits = ((qh[:, None] >> np.arange(32, dtype=np.uint32)[None, :]) & 1).astype(np.int32)
+    q = (nib | (bits << 4)) - 16
+    return (q.astype(np.float32) * d[:, None]).astype(np.float32).ravel()[:n]
+
+
 def np_dequant(qtype: int, blocks, n: int) -> np.ndarray:
-    return {Q8_0: np_dequant_q8_0, Q4_0: np_dequant_q4_0, Q4_K: np_dequant_q4_k}[qtype](blocks, n)
+    return {Q8_0: np_dequant_q8_0, Q4_0: np_dequant_q4_0, Q4_K: np_dequant_q4_k, Q5_0: np_dequant_q5_0}[qtype](blocks, n)
 
 
 def np_linear_sequential(x: np.ndarray, w: np.ndarray) -> np.ndarray:

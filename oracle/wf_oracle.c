@@ -20,7 +20,9 @@
  * Dequantizer.java:58-71; only the geometry 256 elements / 144 bytes is fixed at
  * warpforge-data/.../format/GGUF.java:345-346).  wfo_dequant_q4_k restates the public GGUF
  * Q4_K super-block format; its parity is UNPINNED by the reference and is cross-checked
- * only against the third-party gguf Python package used as a black box.
+ * only against the third-party gguf Python package used as a black box.  The same holds for
+ * Q5_0 (22 bytes / 32 elements, sized at GGUF.java:332-351, never dequantized by the reference):
+ * wfo_dequant_q5_0 restates the public block format, parity UNPINNED, cross-checked against gguf.
  *
  * Java evaluates `sum += a * b` on floats as a separately rounded multiply and add, in
  * ascending k, with one accumulator.  Build with -ffp-contract=off so gcc does the same.
@@ -37,6 +39,7 @@
 #define WFO_Q4_0 2
 #define WFO_Q4_1 3
 #define WFO_Q4_K 14
+#define WFO_Q5_0 6
 
 static inline float bits_to_float(uint32_t u) {
     float f;
@@ -117,6 +120,29 @@ void wfo_dequant_q4_1(const uint8_t* in, float* out, int64_t n) {
 }
 
 /*
+ * Q5_0 block, 22 bytes / 32 elements (public GGUF format; the reference only knows its size,
+ * GGUF.java:332-351): [0:2) d fp16, [2:6) 32 high bits (little-endian word, bit e = element e),
+ * [6:22) 16 code bytes: element i < 16 = low nibble of byte i, element i + 16 = high nibble of byte i.
+ * w = d * ((nibble | bit << 4) - 16).
+ */
+void wfo_dequant_q5_0(const uint8_t* in, float* out, int64_t n) {
+    int64_t nblocks = (n + 31) / 32;
+    for (int64_t b = 0; b < nblocks; b++) {
+        const uint8_t* blk = in + b * 22;
+        float d = wfo_half_to_float(load_u16(blk));
+        uint32_t qh = (uint32_t)blk[2] | ((uint32_t)blk[3] << 8) | ((uint32_t)blk[4] << 16) | ((uint32_t)blk[5] << 24);
+        for (int e = 0; e < 32; e++) {
+            int64_t o = b * 32 + e;
+            if (o >= n) break;
+            uint8_t byte = blk[6 + (e & 15)];
+            int nib = e < 16 ? (byte & 0x0F) : (byte >> 4);
+            int q = (nib | (int)(((qh >> e) & 1u) << 4)) - 16;
+            out[o] = (float)q * d;
+        }
+    }
+}
+
+/*
  * Q4_K super-block, 144 bytes / 256 elements (public GGUF format; NOT in the reference):
  *   [0:2) d fp16, [2:4) dmin fp16, [4:16) eight 6-bit scales + eight 6-bit mins, [16:144) codes.
  * Sub-block j < 4: sc = s[j] & 63, m = s[j+4] & 63;
@@ -167,6 +193,7 @@ int64_t wfo_block_bytes(int qtype) {
         case WFO_Q4_0: return 18;
         case WFO_Q4_1: return 20;
         case WFO_Q4_K: return 144;
+        case WFO_Q5_0: return 22;
         default: return -1;
     }
 }
@@ -177,6 +204,7 @@ int wfo_dequant(int qtype, const uint8_t* in, float* out, int64_t n) {
         case WFO_Q4_0: wfo_dequant_q4_0(in, out, n); return 0;
         case WFO_Q4_1: wfo_dequant_q4_1(in, out, n); return 0;
         case WFO_Q4_K: wfo_dequant_q4_k(in, out, n); return 0;
+        case WFO_Q5_0: wfo_dequant_q5_0(in, out, n); return 0;
         default: return -1; /* Dequantizer.forType: "Dequantization not yet implemented" */
     }
 }

@@ -12,7 +12,8 @@ from warpforge_b200 import quant as Q
 pytestmark = pytest.mark.gpu
 
 QT = {"q4_0": (Q.QuantizationType.Q4_0, O.Q4_0), "q8_0": (Q.QuantizationType.Q8_0, O.Q8_0),
-      "q4_k": (Q.QuantizationType.Q4_K, O.Q4_K), "q4_1": (Q.QuantizationType.Q4_1, O.Q4_1)}
+      "q4_k": (Q.QuantizationType.Q4_K, O.Q4_K), "q4_1": (Q.QuantizationType.Q4_1, O.Q4_1),
+      "q5_0": (Q.QuantizationType.Q5_0, O.Q5_0)}
 
 
 @pytest.fixture(scope="module")
@@ -37,7 +38,7 @@ def _check(got, want):
     assert rel_max <= 1e-3 and rel_rms <= 3e-4, f"max err / max|y| = {rel_max:.3e}, rms err / rms y = {rel_rms:.3e}"
 
 
-@pytest.mark.parametrize("name", ["q4_0", "q8_0", "q4_k", "q4_1"])
+@pytest.mark.parametrize("name", ["q4_0", "q8_0", "q4_k", "q4_1", "q5_0"])
 @pytest.mark.parametrize("rows,k,m", [(128, 256, 16), (256, 1024, 64), (1000, 2048, 300), (136, 512, 9), (4096, 4096, 33),
                                       (256, 1024, 513), (384, 1280, 700), (2048, 512, 1024),
                                       # enough tiles for the token tiles of 2 x 256: a last tile with one half, rows not a multiple of 128

@@ -29,7 +29,7 @@ def backend():
 def model_file(tmp_path_factory):
     """A small model-shaped file: one linear weight per quantization type, {k, rows} in file order,
     between tensors of other types so that offsets and alignment padding matter."""
-    specs = {"q4_0": (96, 512), "q8_0": (40, 256), "q4_k": (64, 1024), "q4_1": (48, 384)}
+    specs = {"q4_0": (96, 512), "q8_0": (40, 256), "q4_k": (64, 1024), "q4_1": (48, 384), "q5_0": (32, 640)}
     blocks = {n: Q.synth_weight(QT[n][0], r, k, 300 + r) for n, (r, k) in specs.items()}
     tensors = [("token_embd.weight", (8, 3), 0, np.arange(24, dtype=np.float32).tobytes())]
     for n, (r, k) in specs.items():
@@ -41,7 +41,7 @@ def model_file(tmp_path_factory):
     return p, specs, blocks
 
 
-@pytest.mark.parametrize("name", ["q4_0", "q8_0", "q4_k", "q4_1"])
+@pytest.mark.parametrize("name", ["q4_0", "q8_0", "q4_k", "q4_1", "q5_0"])
 def test_upload_from_file_is_bit_exact(backend, oracle, model_file, name):
     p, specs, blocks = model_file
     rows, k = specs[name]
@@ -55,7 +55,7 @@ def test_upload_from_file_is_bit_exact(backend, oracle, model_file, name):
     w.close()
 
 
-@pytest.mark.parametrize("name", ["q4_0", "q8_0", "q4_k", "q4_1"])
+@pytest.mark.parametrize("name", ["q4_0", "q8_0", "q4_k", "q4_1", "q5_0"])
 def test_sharded_upload_and_linear(backend, oracle, model_file, name):
     from warpforge_b200.backend import Tensor
 

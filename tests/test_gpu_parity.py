@@ -12,7 +12,8 @@ from warpforge_b200 import quant as Q
 pytestmark = pytest.mark.gpu
 
 QT = {"q4_0": (Q.QuantizationType.Q4_0, O.Q4_0), "q8_0": (Q.QuantizationType.Q8_0, O.Q8_0),
-      "q4_k": (Q.QuantizationType.Q4_K, O.Q4_K), "q4_1": (Q.QuantizationType.Q4_1, O.Q4_1)}
+      "q4_k": (Q.QuantizationType.Q4_K, O.Q4_K), "q4_1": (Q.QuantizationType.Q4_1, O.Q4_1),
+      "q5_0": (Q.QuantizationType.Q5_0, O.Q5_0)}
 ATOL, RTOL, MAXREL = 1e-4, 1e-3, 1e-3
 
 
@@ -60,7 +61,7 @@ def _linear(backend, w, x_tensor):
     return backend.execute(DotGeneralOp(LINEAR_DIMS, (m, w.rows)), [x_tensor, w])[0].data
 
 
-@pytest.mark.parametrize("name", ["q4_0", "q8_0", "q4_k", "q4_1"])
+@pytest.mark.parametrize("name", ["q4_0", "q8_0", "q4_k", "q4_1", "q5_0"])
 @pytest.mark.parametrize("rows,k", [(16, 256), (48, 1024), (100, 512), (7, 256), (33, 4096)])
 def test_dequant_bit_exact(backend, oracle, name, rows, k):
     qt, oq = QT[name]
@@ -100,7 +101,7 @@ def test_dequant_edge_scales(backend, oracle):
     assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
 
 
-@pytest.mark.parametrize("name", ["q4_0", "q8_0", "q4_k", "q4_1"])
+@pytest.mark.parametrize("name", ["q4_0", "q8_0", "q4_k", "q4_1", "q5_0"])
 @pytest.mark.parametrize("m", [1, 2, 4, 8])
 @pytest.mark.parametrize("rows,k", [(64, 1024), (1000, 2048), (37, 512), (4096, 4096)])
 def test_qlinear_bf16_matches_oracle(backend, oracle, name, m, rows, k):
@@ -118,7 +119,7 @@ def test_qlinear_bf16_matches_oracle(backend, oracle, name, m, rows, k):
     w.close()
 
 
-@pytest.mark.parametrize("name", ["q4_0", "q8_0", "q4_k", "q4_1"])
+@pytest.mark.parametrize("name", ["q4_0", "q8_0", "q4_k", "q4_1", "q5_0"])
 @pytest.mark.parametrize("m", [1, 2, 3, 5])
 def test_qlinear_f32_activations(backend, oracle, name, m):
     from warpforge_b200.backend import Tensor

@@ -44,7 +44,7 @@ def test_program_equals_per_op_kernels(oracle, tokens):
         ctx.close()
 
 
-@pytest.mark.parametrize("qname", ["Q4_0", "Q4_1", "Q8_0", "Q4_K"])
+@pytest.mark.parametrize("qname", ["Q4_0", "Q4_1", "Q8_0", "Q4_K", "Q5_0"])
 @pytest.mark.parametrize("tokens", [1, 5])
 def test_program_every_quantization_type(oracle, qname, tokens):
     """A small two-layer stack per type: the program's outputs equal the per-projection kernels' bit for bit
@@ -53,7 +53,7 @@ def test_program_every_quantization_type(oracle, qname, tokens):
     from warpforge_b200.decode import ProjectionStack, StackSpec
 
     qt = Q.QuantizationType[qname]
-    oq = {"Q4_0": O.Q4_0, "Q4_1": O.Q4_1, "Q8_0": O.Q8_0, "Q4_K": O.Q4_K}[qname]
+    oq = {"Q4_0": O.Q4_0, "Q4_1": O.Q4_1, "Q8_0": O.Q8_0, "Q4_K": O.Q4_K, "Q5_0": O.Q5_0}[qname]
     spec = StackSpec("small " + qname, qt, 2, (("wq", 512, 512), ("wk", 512, 512), ("wo", 512, 512), ("wgate", 1280, 512),
                                                 ("wup", 1280, 512), ("wdown", 512, 1280)), 0)
     ctx = CudaContext(0)

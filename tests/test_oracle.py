@@ -249,3 +249,18 @@ def test_q4_1_ggml_order_against_gguf_package(oracle):
     want = quants.dequantize(w.reshape(-1, 20), gguf.GGMLQuantizationType.Q4_1).astype(np.float32).ravel()
     got = oracle.dequant(O.Q4_1, O.q4_0_ggml_to_reference_order(w, header=4), 8 * 256)
     assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+def test_q5_0_against_gguf_package(oracle):
+    """Q5_0 is a format the reference can only size (GGUF.java:332-351): the restatement of the public block
+    format (C and numpy) is checked against the independent implementation in the gguf package, bit for bit.
+    Parity with the reference itself is unpinned for this type: the reference has no dequantizer for it."""
+    gguf = pytest.importorskip("gguf")
+    from gguf import quants
+
+    w = Q.synth_q5_0(8, 256, 13)
+    want = quants.dequantize(w.reshape(-1, 22), gguf.GGMLQuantizationType.Q5_0).astype(np.float32).ravel()
+    got = oracle.dequant(O.Q5_0, w, 8 * 256)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    assert np.array_equal(O.np_dequant_q5_0(w, 8 * 256).view(np.uint32), want.view(np.uint32))
+    assert Q.QuantizationType.Q5_0.tensor_bytes(8 * 256) == 8 * 8 * 22 and O.BLOCK_BYTES[O.Q5_0] == 22

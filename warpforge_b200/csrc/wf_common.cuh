@@ -28,7 +28,8 @@ struct Context;
 struct Weight {
     uint32_t magic = WEIGHT_MAGIC;
     Context* ctx = nullptr;
-    WeightGeom g{};
+    WeightGeom g{};          // g.qtype is the DEVICE format (device_qtype of the file's type)
+    int file_qtype = 0;      // ggml type of the blocks that were uploaded
     int64_t row0 = 0;        // first global row of this shard
     int64_t total_rows = 0;  // rows of the unsharded tensor
     uint8_t* d_tiles = nullptr;

@@ -23,6 +23,7 @@
 //                        fp16 scales as for Q4_0   128;  fp16 mins, same shape   128
 //   Q8_0  tile = 128 k : plane H (high nibble of byte ^ 0x80), plane L (low nibble)  2048
 //                        fp16 scales as above                                          128
+//   Q5_0  held as Q8_0 tiles (q = code - 16 as the 8-bit integer)
 //   Q4_K  tile = 256 k : plane for sub-blocks 0..3, plane for sub-blocks 4..7         2048
 //                        (d, dmin) fp16 pairs [g][row g | row g+8]                      64
 //                        8-bit sub-block scales [g][row g: 0..7 | row g+8: 0..7]       128
@@ -34,6 +35,7 @@
 
 #define WF_QTYPE_Q4_0 2
 #define WF_QTYPE_Q4_1 3
+#define WF_QTYPE_Q5_0 6
 #define WF_QTYPE_Q8_0 8
 #define WF_QTYPE_Q4_K 14
 
@@ -70,7 +72,10 @@ template <> struct Tile<WF_QTYPE_Q4_K> {
 WF_HD int tile_k(int qt) { return qt == WF_QTYPE_Q4_K ? 256 : 128; }
 WF_HD int tile_bytes(int qt) { return qt == WF_QTYPE_Q4_0 ? 1152 : qt == WF_QTYPE_Q4_1 ? 1280 : qt == WF_QTYPE_Q8_0 ? 2176 : 2368; }
 WF_HD int block_k(int qt) { return qt == WF_QTYPE_Q4_K ? 256 : 32; }
-WF_HD int block_bytes(int qt) { return qt == WF_QTYPE_Q4_0 ? 18 : qt == WF_QTYPE_Q4_1 ? 20 : qt == WF_QTYPE_Q8_0 ? 34 : 144; }
+WF_HD int block_bytes(int qt) { return qt == WF_QTYPE_Q4_0 ? 18 : qt == WF_QTYPE_Q4_1 ? 20 : qt == WF_QTYPE_Q5_0 ? 22 : qt == WF_QTYPE_Q8_0 ? 34 : 144; }
+// The format a file type is held in on the device: Q5_0 (value = d * (q5 - 16), an integer in [-16, 15]) is expanded
+// into the two 4-bit planes of Q8_0 with the same fp16 scale and runs on the Q8_0 kernels (8 bits per weight in HBM).
+WF_HD int device_qtype(int qt) { return qt == WF_QTYPE_Q5_0 ? WF_QTYPE_Q8_0 : qt; }
 
 // Nibble position of element e (0..7) inside its 32-bit word.
 WF_HD int nibble_pos(int e) { return (e >> 1) | ((e & 1) << 2); }

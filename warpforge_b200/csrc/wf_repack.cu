@@ -106,6 +106,38 @@ __global__ void repack_q8_0_kernel(const uint8_t* __restrict__ raw, uint8_t* __r
             ld_u16(src);
 }
 
+// Q5_0 (22 bytes: fp16 scale, 32 high bits, 16 nibble bytes; element i < 16 = low nibble of byte i, element
+// i + 16 = high nibble of byte i) into Q8_0 tiles: q = (nibble | bit << 4) - 16 is stored as the 8-bit integer
+// the Q8_0 kernels expect (nibbles of q ^ 0x80), with the block's own fp16 scale.
+__global__ void repack_q5_0_kernel(const uint8_t* __restrict__ raw, uint8_t* __restrict__ tiles, int64_t rows,
+                                   int64_t nblk, int64_t kt) {
+    int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= rows * nblk * 4) return;
+    int q = idx & 3;
+    int64_t bk = (idx >> 2) % nblk, r = (idx >> 2) / nblk;
+    const uint8_t* src = raw + (r * nblk + bk) * 22;
+    uint8_t* tile = tiles + ((r >> 4) * kt + (bk >> 2)) * Tile<WF_QTYPE_Q8_0>::BYTES;
+    int ri = r & 15, j = bk & 3;
+    const uint32_t qh = (uint32_t)src[2] | ((uint32_t)src[3] << 8) | ((uint32_t)src[4] << 16) | ((uint32_t)src[5] << 24);
+    uint32_t hi[8], lo[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int e = 8 * q + i;
+        const uint8_t byte = src[6 + (e & 15)];
+        const int nib = e < 16 ? (byte & 0xF) : (byte >> 4);
+        const int v = (nib | (int)(((qh >> e) & 1u) << 4)) - 16;
+        const uint8_t u = (uint8_t)v ^ 0x80;
+        hi[i] = u >> 4;
+        lo[i] = u & 0xF;
+    }
+    int off = plane_word_off(ri, j, q);
+    *reinterpret_cast<uint32_t*>(tile + off) = pack8(hi);
+    *reinterpret_cast<uint32_t*>(tile + PLANE_BYTES + off) = pack8(lo);
+    if (q == 0)
+        *reinterpret_cast<uint16_t*>(tile + Tile<WF_QTYPE_Q8_0>::SCALE_OFF + (ri & 7) * 16 + (ri >> 3) * 8 + j * 2) =
+            ld_u16(src);
+}
+
 __device__ __forceinline__ void q4k_scale_min(const uint8_t* s, int j, uint32_t& sc, uint32_t& m) {
     if (j < 4) {
         sc = s[j] & 63;
@@ -162,6 +194,8 @@ cudaError_t launch_repack(int qtype, const uint8_t* d_raw, uint8_t* d_tiles, int
             repack_q4_0_kernel<<<grid, threads, 0, s>>>(d_raw, d_tiles, rows, nblk, kt, q4_0_order == WF_Q4_0_ORDER_GGML);
         else if (qtype == WF_QTYPE_Q4_1)
             repack_q4_1_kernel<<<grid, threads, 0, s>>>(d_raw, d_tiles, rows, nblk, kt, q4_0_order == WF_Q4_0_ORDER_GGML);
+        else if (qtype == WF_QTYPE_Q5_0)
+            repack_q5_0_kernel<<<grid, threads, 0, s>>>(d_raw, d_tiles, rows, nblk, kt);
         else
             repack_q8_0_kernel<<<grid, threads, 0, s>>>(d_raw, d_tiles, rows, nblk, kt);
     }

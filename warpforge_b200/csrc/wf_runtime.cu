@@ -141,7 +141,9 @@ static cudaError_t upload_and_repack(Context* c, int qtype, const uint8_t* src, 
     return e;
 }
 
-static bool qtype_supported(int qt) { return qt == WF_QTYPE_Q4_0 || qt == WF_QTYPE_Q4_1 || qt == WF_QTYPE_Q8_0 || qt == WF_QTYPE_Q4_K; }
+static bool qtype_supported(int qt) {
+    return qt == WF_QTYPE_Q4_0 || qt == WF_QTYPE_Q4_1 || qt == WF_QTYPE_Q5_0 || qt == WF_QTYPE_Q8_0 || qt == WF_QTYPE_Q4_K;
+}
 
 }  // namespace wf
 
@@ -386,11 +388,12 @@ int weight_upload(Context* c, int qtype, const void* blocks, int64_t n_rows, int
     const int64_t row_bytes = k / block_k(qtype) * block_bytes(qtype);
     Weight* w = new Weight();
     w->ctx = c;
-    w->g.qtype = qtype;
+    w->g.qtype = device_qtype(qtype);  // the kernels see the device format; `qtype` is the file's
+    w->file_qtype = qtype;
     w->g.rows = rows;
     w->g.k = k;
     w->g.rt = (rows + TILE_ROWS - 1) / TILE_ROWS;
-    w->g.kt = (k + tile_k(qtype) - 1) / tile_k(qtype);
+    w->g.kt = (k + tile_k(w->g.qtype) - 1) / tile_k(w->g.qtype);
     w->g.rt_alloc = (w->g.rt + 7) / 8 * 8;
     w->row0 = row0;
     w->total_rows = n_rows;
@@ -398,7 +401,7 @@ int weight_upload(Context* c, int qtype, const void* blocks, int64_t n_rows, int
     if (e == cudaSuccess) e = cudaMemsetAsync(w->d_tiles, 0, (size_t)w->g.bytes(), c->stream);
     if (e == cudaSuccess)
         e = upload_and_repack(c, qtype, static_cast<const uint8_t*>(blocks) + row0 * row_bytes, rows, k, row_bytes, w->d_tiles,
-                              w->g.kt * (int64_t)tile_bytes(qtype), q4_0_order, c->stream);
+                              w->g.kt * (int64_t)tile_bytes(w->g.qtype), q4_0_order, c->stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
     if (e != cudaSuccess) {
         if (w->d_tiles) cudaFree(w->d_tiles);
@@ -431,7 +434,7 @@ int wf_weight_info(int64_t ctx, int64_t weight, int* qtype, int64_t* rows, int64
     WF_ENTER(ctx);
     Weight* w = get_weight(c, weight);
     if (!w) return WF_ERR_INVALID_HANDLE;
-    if (qtype) *qtype = w->g.qtype;
+    if (qtype) *qtype = w->file_qtype;
     if (rows) *rows = w->g.rows;
     if (k) *k = w->g.k;
     if (row0) *row0 = w->row0;

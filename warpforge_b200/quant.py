@@ -22,6 +22,7 @@ class QuantizationType(enum.Enum):
 
     Q4_0 = (2, 4, 32, 18)
     Q4_1 = (3, 4, 32, 20)
+    Q5_0 = (6, 5, 32, 22)
     Q8_0 = (8, 8, 32, 34)
     Q4_K = (14, 4, 256, 144)
 
@@ -115,6 +116,17 @@ def synth_q4_1(n_rows: int, k: int, seed: int, scale: float = 0.02) -> np.ndarra
     return out.reshape(n_rows, -1)
 
 
+def synth_q5_0(n_rows: int, k: int, seed: int, scale: float = 0.02) -> np.ndarray:
+    """5-bit codes uniform 0..31 (value = (code - 16) * scale): fp16 scale |N(0,1)|*scale, 32 high bits and
+    16 nibble bytes per block of 32, in the file's own (ggml) element order."""
+    rng = np.random.Generator(np.random.PCG64(seed))
+    nb = n_rows * k // 32
+    out = np.empty((nb, 22), np.uint8)
+    out[:, 0:2] = _fp16_scales(rng, nb, scale).view(np.uint8).reshape(nb, 2)
+    out[:, 2:] = rng.integers(0, 256, size=(nb, 20), dtype=np.uint8)
+    return out.reshape(n_rows, -1)
+
+
 def pack_q4k_scales(sc: np.ndarray, m: np.ndarray) -> np.ndarray:
     """[nb, 8] 6-bit scales and mins -> the 12-byte field of a Q4_K super-block."""
     sc = sc.astype(np.uint8)
@@ -145,7 +157,8 @@ def synth_weight(qtype: QuantizationType, n_rows: int, k: int, seed: int) -> np.
     """Returns uint8 [n_rows, row_bytes] of GGUF blocks (blocks run along K inside a row)."""
     qtype.row_bytes(k)
     return {QuantizationType.Q8_0: synth_q8_0, QuantizationType.Q4_0: synth_q4_0,
-            QuantizationType.Q4_1: synth_q4_1, QuantizationType.Q4_K: synth_q4_k}[qtype](n_rows, k, seed)
+            QuantizationType.Q4_1: synth_q4_1, QuantizationType.Q4_K: synth_q4_k,
+            QuantizationType.Q5_0: synth_q5_0}[qtype](n_rows, k, seed)
 
 
 def synth_activation_f32(m: int, k: int, seed: int) -> np.ndarray:
