@@ -212,7 +212,12 @@ def run_ours(args) -> None:
     comm = None
     spec = LLAMA_7B_Q4_0
     mode = args.mode if args.mode != "auto" else "program"
-    if mode == "program":
+    replicas = mode == "replicas"  # every rank decodes its own token stream on the whole model: no exchange at all
+    if replicas:
+        stack = ProjectionStack(ctx, spec, tokens=1, layers=args.layers or None)
+        stack.build_program(None)
+        stack.mode = "program"
+    elif mode == "program":
         # one persistent kernel per token and rank; the row-shard gather is fused into the GEMV
         # epilogue (peer stores), so no communicator is needed
         stack = ProjectionStack(ctx, spec, tokens=1, rank=rank, world=world, layers=args.layers or None)
@@ -281,27 +286,29 @@ def run_ours(args) -> None:
     if rank == 0:
         hbm_peak, peak_src = measured_peaks()
         ms_step = ms / args.steps
-        tok_s = 1e3 / ms_step
+        tok_s = 1e3 / ms_step * (world if replicas else 1)
         alg_bytes = stack.algorithmic_bytes_per_step()          # this rank's shard
-        n_launch = 1 if mode == "program" else stack.layers * len(spec.projections)
+        n_launch = 1 if mode in ("program", "replicas") else stack.layers * len(spec.projections)
         gbs = alg_bytes / (ms_step * 1e-3) / 1e9
         h2d = sum(v.nbytes for v in stack.x_host.values())
         line = {
             "metric": METRIC, "value": tok_s, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak" if replicas else "strong", "vs_baseline": None,
             "dtype": "bf16 activations x 4-bit codes, fp32 accumulate", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "parallelism": f"row-sharded tp{world}" if world > 1 else "single GPU",
+            "config": {"workload": WORKLOAD,
+                       "parallelism": (f"{world} independent replicas, one token stream each" if replicas
+                                       else f"row-sharded tp{world}" if world > 1 else "single GPU"),
                        "execution": ("one persistent kernel per token, gather fused into the GEMV epilogue (peer stores)"
-                                     if mode == "program" else "CUDA graph of one GEMV kernel per projection"
+                                     if mode == "program" else "one persistent kernel per token and replica" if replicas else "CUDA graph of one GEMV kernel per projection"
                                      + (" + NCCL all-gather" if world > 1 else "")),
                        "l2": "inputs larger than L2: 3.64 GB of distinct weights per step", "bytes_per_token": spec.bytes_per_token()},
-            "e2e": {"value": 1e3 / (e2e_ms / args.steps), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": int(y_out.nbytes)},
+            "e2e": {"value": 1e3 / (e2e_ms / args.steps) * (world if replicas else 1), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": int(y_out.nbytes)},
             "gpu_launches": int(launches),
             "clocks": clocks,
-            "roofline": {"bound": "hbm", "kernel": ("gemv_program_kernel" if mode == "program" else "gemv_kernel") + "<Q4_0, 1 column>", "achieved": gbs, "peak": hbm_peak, "unit": "GB/s",
+            "roofline": {"bound": "hbm", "kernel": ("gemv_program_kernel" if mode in ("program", "replicas") else "gemv_kernel") + "<Q4_0, 1 column>", "achieved": gbs, "peak": hbm_peak, "unit": "GB/s",
                          "frac": gbs / hbm_peak, "frac_of_8TBs_nominal": gbs / 8000.0, "peak_source": peak_src,
                          "bytes_per_launch": alg_bytes / n_launch, "us_per_launch": ms_step * 1e3 / n_launch,
-                         "traffic": NCU_TRAFFIC_BYTES_PER_LAYER * stack.layers / world / n_launch,
+                         "traffic": NCU_TRAFFIC_BYTES_PER_LAYER * stack.layers / (1 if replicas else world) / n_launch,
                          "traffic_source": "ncu dram bytes of a 2-layer capture, scaled by layers (and 1 / ranks)"},
         }
         if stack.layers != spec.layers:
@@ -336,8 +343,9 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--mode", default="auto", choices=["auto", "graph", "program"],
-                    help="program: one persistent kernel per token (default); graph: one kernel per projection in a CUDA graph")
+    ap.add_argument("--mode", default="auto", choices=["auto", "graph", "program", "replicas"],
+                    help="program: one persistent kernel per token (default); graph: one kernel per projection in a CUDA graph; "
+                         "replicas: N > 1 ranks each decode their own stream on the whole model (weak scaling, no exchange)")
     ap.add_argument("--layers", type=int, default=0,
                     help="profiling aid: run only this many of the 32 layers (the line is then marked partial and is not a bench value)")
     ap.add_argument("--kernel-only", action="store_true",
