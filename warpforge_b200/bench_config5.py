@@ -9,12 +9,18 @@ Two legs: (i) batch-16 decode (16 bf16 tokens through `wf_qlinear`, which routes
 tensor-core kernel) against the HBM roofline, (ii) a 2048-token prefill against the tensor roofline.
 The per-layer time times 80 layers is the per-rank step time of the full configuration (stated as an
 extrapolation in the output).  Events on the launching stream, three warm-up walks.  One JSON line per leg.
+
+Under `python -m torch.distributed.run --nproc-per-node N -m warpforge_b200.bench_config5 --world N` the N ranks run
+the configuration as it is specified: every projection row-sharded N ways, each followed by the NCCL all-gather of
+`wf_qlinear_allgather`, so that every rank holds all rows; the time is the maximum over the ranks.
 """
 from __future__ import annotations
 
 import argparse
 import json
 import os
+
+import numpy as np
 
 from . import _native as N
 from . import quant as Q
@@ -39,7 +45,21 @@ def main() -> None:
     ap.add_argument("--iters", type=int, default=3)
     a = ap.parse_args()
     spec = LLAMA_70B_Q4_K
-    ctx = CudaContext(0)
+    rank, nranks = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    gather = nranks > 1
+    dist = comm = None
+    ctx = CudaContext(int(os.environ.get("LOCAL_RANK", "0")))
+    if gather:
+        import torch.distributed as dist  # control plane only: id exchange, barrier, max over ranks
+
+        from .decode import Communicator
+
+        if a.world != nranks:
+            raise SystemExit(f"--world {a.world} must equal the number of ranks {nranks}")
+        dist.init_process_group("gloo", rank=rank, world_size=nranks)
+        ids = [Communicator.create_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(ids, src=0)
+        comm = Communicator(ctx, ids[0], rank, nranks)
     lib, h = ctx._lib, ctx.handle
     qt = spec.qtype
     weights, shard_bytes, shard_macs = [], 0, 0
@@ -47,8 +67,15 @@ def main() -> None:
         row = []
         for i, (name, rows, k) in enumerate(spec.projections):
             r = rows // a.world
-            blocks = Q.synth_weight(qt, r, k, Q.config_seed(5, layer * len(spec.projections) + i))
-            row.append((name, r, k, QuantizedWeight(ctx, qt, blocks, r, k)))
+            blocks = Q.synth_weight(qt, r, k, Q.config_seed(5, layer * len(spec.projections) + i) + 7919 * rank)
+            if gather:  # the upload reads this rank's rows out of the whole tensor: only those rows are filled in
+                full = np.empty((rows, qt.row_bytes(k)), np.uint8)
+                full[rank * r:(rank + 1) * r] = blocks
+                w = QuantizedWeight(ctx, qt, full, rows, k, rank, nranks)
+                del full
+            else:
+                w = QuantizedWeight(ctx, qt, blocks, r, k)
+            row.append((name, r, k, w))
             if layer == 0:
                 shard_bytes += r * qt.row_bytes(k)
                 shard_macs += r * k
@@ -61,23 +88,35 @@ def main() -> None:
         x = Q.synth_activation_bf16(m, kmax, 5)
         dx = ctx.allocate(x.nbytes)
         ctx.copy_to_device(dx, x)
-        dy = ctx.allocate(m * rmax * 4)
+        dy = ctx.allocate(m * rmax * 4 * (nranks if gather else 1))
 
         def walk():
             for row in weights:
                 for name, r, k, w in row:
                     # the activation buffer is read as [m, k] (row stride k): same bytes for every projection
-                    N.check(name, lib.wf_qlinear(h, w.handle, dx, N.WF_DTYPE_BF16, 1, m, dy, 1, 0), h)
+                    if gather:
+                        N.check(name, lib.wf_qlinear_allgather(h, comm.handle, w.handle, dx, N.WF_DTYPE_BF16, m, dy, 0), h)
+                    else:
+                        N.check(name, lib.wf_qlinear(h, w.handle, dx, N.WF_DTYPE_BF16, 1, m, dy, 1, 0), h)
 
         for _ in range(3):
             walk()
         ctx.synchronize()
+        if gather:
+            dist.barrier()
         ctx.record_event(e0)
         for _ in range(a.iters):
             walk()
         ctx.record_event(e1)
         ctx.synchronize()
-        us_layer = ctx.elapsed_ms(e0, e1) * 1e3 / a.iters / a.layers
+        ms = ctx.elapsed_ms(e0, e1)
+        if gather:
+            import torch
+
+            t = torch.tensor([ms], dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t[0])
+        us_layer = ms * 1e3 / a.iters / a.layers
         out = {"leg": leg, "tokens": m, "world": a.world, "layers_resident": a.layers, "us_per_layer": round(us_layer, 1),
                "ms_per_step_80_layers_extrapolated": round(us_layer * spec.layers / 1e3, 2),
                "weight_bytes_per_layer_per_rank": shard_bytes}
@@ -87,13 +126,21 @@ def main() -> None:
         else:
             tfs = 2.0 * m * shard_macs / us_layer / 1e6
             out.update({"bound": "tensor", "achieved_tflops": round(tfs, 1), "peak_tflops": tf, "frac": round(tfs / tf, 3), "peak": src})
-        print(json.dumps(out), flush=True)
+        if gather:
+            out["execution"] = f"{nranks} ranks, NCCL all-gather after every projection, max over ranks"
+        if rank == 0:
+            print(json.dumps(out), flush=True)
         ctx.free(dx)
         ctx.free(dy)
     for row in weights:
         for _, _, _, w in row:
             w.close()
+    if comm is not None:
+        comm.close()
     ctx.close()
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":
