@@ -21,12 +21,13 @@
 // warpforge-backend-nvidia/src/main/java/io/surfworks/warpforge/backend/nvidia/ops/DotGeneralKernel.java:263-283.
 #include <string.h>
 
-#include "wf_gemv_core.cuh"
+#include "wf_gemv_stream.cuh"
 
 namespace wf {
 
 constexpr int PROG_MAX_WORLD = 8;
 constexpr int PROG_BARRIER_SPINS = 1 << 24;
+constexpr int PROG_ONE_TOKEN_STAGES = 4;  // copies in flight per warp of the one-token program kernel
 constexpr int OP_NEW_X = 1;    // stage activations before this op (otherwise it reuses the staged ones)
 constexpr int OP_DEPENDS = 2;  // the activations were produced by earlier ops: grid (and rank) barrier first
 
@@ -35,7 +36,8 @@ struct ProgOp {
     const void* x;
     float* y;                  // this rank's plain fp32 output [m, n_total]
     uint2* ll[PROG_MAX_WORLD]; // every rank's landing buffer for this op [m, n_total] {value, tag}; own at [rank]
-    int n_total, pad2;
+    int n_total;
+    int aligned;               // one-token kernel: chunk_q / chunk_r count whole row-tiles
     int64_t ldy, col0;
     int rows, k, kt, rt;
     int chunk_q, chunk_r;      // CTA b < ctas owns tiles [b*q + min(b,r), (b+1)*q + min(b+1,r)); the others none
@@ -94,7 +96,106 @@ __device__ __forceinline__ uint2 ld_slot_sys(const uint2* p) {
     return make_uint2((uint32_t)w, (uint32_t)(w >> 32));
 }
 
-// Shared memory: ctrl | partial sums | cinit (kp_max) | staged x | ring.
+// What the consumer threads of both program kernels share: the landing of the other ranks' rows, the grid
+// barrier and the way out.  A wait that ran out anywhere in this CTA, or a failure another CTA or an earlier
+// kernel reported through the status word, is latched in shared memory (`failed`): from then on no landing
+// poll and no barrier spin is started, so that a program whose peer has gone ends within about one
+// timeout instead of one timeout per projection.
+struct ProgRun {
+    const ProgParams& P;
+    volatile int* failed;  // CTA-wide latch in shared memory
+    unsigned long long epoch;
+    int barriers = 0, land_from = 0;
+
+    __device__ __forceinline__ void consumers_sync() const { asm volatile("bar.sync 1, %0;" ::"n"(GEMV_CONSUMERS) : "memory"); }
+    __device__ __forceinline__ unsigned int tag() const { return (unsigned int)(epoch + (unsigned long long)barriers + 1); }
+
+    // Wait for the other ranks' rows of ops [first, last) and copy them into y.  The CTAs split the elements;
+    // each element is polled until it carries this barrier's tag.
+    __device__ __forceinline__ void land(int first, int last, unsigned int want_tag) {
+        if (P.world == 1 || *failed) return;
+        for (int o2 = first; o2 < last; o2++) {
+            const ProgOp& op2 = P.ops[o2];
+            const int total = P.m * op2.n_total;
+            const uint2* mine = op2.ll[P.rank];
+            for (int e = (int)blockIdx.x * GEMV_CONSUMERS + threadIdx.x; e < total; e += gridDim.x * GEMV_CONSUMERS) {
+                const int col = e % op2.n_total;
+                if (col >= (int)op2.col0 && col < (int)op2.col0 + op2.rows) continue;  // my own rows are already in y
+                uint2 v;
+                int spins = 0;
+                do {
+                    v = ld_slot_sys(mine + e);
+                    if (v.y == want_tag) break;
+                    __nanosleep(20);
+                } while (++spins < GEMV_FIXUP_SPINS && !*failed);
+                if (v.y != want_tag) {
+                    atomicOr(P.status, STATUS_PEER_WAIT_TIMEOUT);
+                    *failed = 1;
+                    return;
+                }
+                op2.y[e] = __uint_as_float(v.x);
+            }
+        }
+    }
+
+    // Grid barrier number `barriers` of this run; with several ranks the landing comes first, so that after the
+    // barrier every rank's y holds all rows.
+    __device__ __forceinline__ void grid_barrier(int o_now) {
+        consumers_sync();  // every warp of this CTA has written its y values and finished its row-tiles
+        const unsigned long long idx = epoch + (unsigned long long)barriers + 1;  // 1-based barrier number
+        land(land_from, o_now, (unsigned int)idx);
+        land_from = o_now;
+        if (P.world > 1) consumers_sync();
+        if (threadIdx.x == 0) {
+            // a failure reported by another CTA, another rank's stalled store or an earlier kernel: stop waiting
+            int st;
+            asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(st) : "l"(P.status) : "memory");
+            if (st != 0) *failed = 1;
+            const unsigned long long want = idx * gridDim.x;
+            int spins = 0;
+            // one release-add (no value comes back, the poll starts at once) and acquire loads: the y rows this
+            // CTA wrote before the bar.sync above are ordered before the add, the reads after the barrier after
+            // the load that saw the last arrival
+            asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(&P.sync->arrive), "l"(1ULL) : "memory");
+            // a short pause between polls: 148 pollers reading the line back to back slow the arrivals down
+            if (!*failed) {
+                while (ld_acquire_gpu(&P.sync->arrive) < want && ++spins < PROG_BARRIER_SPINS) __nanosleep(50);
+                if (spins >= PROG_BARRIER_SPINS) {
+                    atomicOr(P.status, STATUS_PEER_WAIT_TIMEOUT);
+                    *failed = 1;
+                }
+            }
+        }
+        barriers++;
+        consumers_sync();
+    }
+
+    // The rows of the last ops land before the kernel ends (tag of the barrier that never comes); the last CTA
+    // out advances the epoch for the next run.
+    __device__ __forceinline__ void leave() {
+        consumers_sync();
+        land(land_from, P.n_ops, tag());
+        consumers_sync();
+        if (threadIdx.x == 0) {
+            __threadfence();
+            const unsigned int d = atomicAdd(&P.sync->done_ctas, 1u);
+            if (d == gridDim.x - 1) {
+                P.sync->done_ctas = 0;
+                // CTAs that skipped barriers after a failure would leave `arrive` short: resynchronise it
+                P.sync->arrive = (epoch + (unsigned long long)P.n_barriers + 1) * gridDim.x;
+                __threadfence();
+                st_release_gpu(&P.sync->epoch, epoch + (unsigned long long)P.n_barriers + 1);  // +1: the final landing's tag
+            }
+        }
+    }
+};
+
+// This CTA's share of op `o`.
+__device__ __forceinline__ void prog_share(const ProgOp& op, int bx, int& t0, int& t1) {
+    ws_cta_share(bx, op.ctas, op.chunk_q, op.chunk_r, op.aligned, op.kt, t0, t1);
+}
+
+// Several tokens (2..8).  Shared memory: ctrl | partial sums | cinit (kp_max) | staged x | ring.
 template <int QT, int XC>
 __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_program_kernel(const ProgParams P) {
     using T = Tile<QT>;
@@ -114,6 +215,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_program_kernel(const Pro
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
+        reinterpret_cast<volatile int*>(smem)[1] = 0;
         barrier_set_init<XC>(bar, stages);
     }
     __syncthreads();
@@ -124,8 +226,8 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_program_kernel(const Pro
             WalkState pos;
             for (int o = 0; o < P.n_ops && !*abort_flag; o++) {
                 const ProgOp& op = P.ops[o];
-                const int t0 = bx * op.chunk_q + min(bx, op.chunk_r);
-                const int t1 = bx < op.ctas ? t0 + op.chunk_q + (bx < op.chunk_r ? 1 : 0) : t0;
+                int t0, t1;
+                prog_share(op, bx, t0, t1);
                 produce_share<QT>(op.tiles, t0, t1, smem_u32(ring), bar, stages, pos, abort_flag);
             }
         }
@@ -133,14 +235,12 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_program_kernel(const Pro
     }
 
     // ---------------------------------------------------- consumers
-    const unsigned long long epoch = ld_acquire_gpu(&P.sync->epoch);
+    ProgRun run{P, reinterpret_cast<volatile int*>(smem) + 1, ld_acquire_gpu(&P.sync->epoch)};
     const uint8_t* xrow = xs + (size_t)(g < P.m ? g : P.m - 1) * P.sx;
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     WalkState st;
-    int barriers = 0;
     bool failed = false;
-    const uint32_t x32 = smem_u32(xrow) + q * 16, c32 = smem_u32(cinit) + (XC == 1 ? 0 : q * 16);
-    const uint32_t live = (XC == 1) ? (uint32_t)(g == 0) : 1u;
+    const uint32_t x32 = smem_u32(xrow) + q * 16, c32 = smem_u32(cinit) + q * 16;
 
     int stamp_i = 0;
     auto stamp = [&]() {
@@ -152,72 +252,19 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_program_kernel(const Pro
         stamp_i++;
     };
     stamp();
-    auto consumers_sync = [&]() { asm volatile("bar.sync 1, %0;" ::"n"(GEMV_CONSUMERS) : "memory"); };
-
-    // Landing: wait for the other ranks' rows of ops [first, last) and copy them into y.
-    // The CTAs split the elements; each element is polled until it carries this barrier's tag.
-    int land_from = 0;
-    auto land = [&](int first, int last, unsigned int tag) {
-        if (P.world == 1) return;
-        for (int o2 = first; o2 < last; o2++) {
-            const ProgOp& op2 = P.ops[o2];
-            const int total = P.m * op2.n_total;
-            const uint2* mine = op2.ll[P.rank];
-            for (int e = bx * GEMV_CONSUMERS + threadIdx.x; e < total; e += gridDim.x * GEMV_CONSUMERS) {
-                const int col = e % op2.n_total;
-                if (col >= (int)op2.col0 && col < (int)op2.col0 + op2.rows) continue;  // my own rows are already in y
-                uint2 v;
-                int spins = 0;
-                do {
-                    v = ld_slot_sys(mine + e);
-                    if (v.y == tag) break;
-                    __nanosleep(20);
-                } while (++spins < GEMV_FIXUP_SPINS);
-                if (v.y != tag) {
-                    atomicOr(P.status, STATUS_PEER_WAIT_TIMEOUT);
-                    break;
-                }
-                op2.y[e] = __uint_as_float(v.x);
-            }
-        }
-    };
-
-    // Grid barrier number `barriers` of this run; with several ranks the landing comes first, so
-    // that after the barrier every rank's y holds all rows.
-    auto grid_barrier = [&](int o_now) {
-        consumers_sync();  // every warp of this CTA has written its y values and passed its reductions
-        const unsigned long long idx = epoch + (unsigned long long)barriers + 1;  // 1-based barrier number
-        land(land_from, o_now, (unsigned int)idx);
-        land_from = o_now;
-        if (P.world > 1) consumers_sync();
-        if (threadIdx.x == 0) {
-            const unsigned long long want = idx * gridDim.x;
-            int spins = 0;
-            // one release-add (no value comes back, the poll starts at once) and acquire loads: the y rows this
-            // CTA wrote before the bar.sync above are ordered before the add, the reads after the barrier after
-            // the load that saw the last arrival
-            asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(&P.sync->arrive), "l"(1ULL) : "memory");
-            // a short pause between polls: 148 pollers reading the line back to back slow the arrivals down
-            // (measured 731 -> 736 tok/s with 50 ns, no gain with 250 ns; four staggered pollers per CTA: 706)
-            while (ld_acquire_gpu(&P.sync->arrive) < want && ++spins < PROG_BARRIER_SPINS) __nanosleep(50);
-            if (spins >= PROG_BARRIER_SPINS) atomicOr(P.status, STATUS_PEER_WAIT_TIMEOUT);
-        }
-        barriers++;
-        consumers_sync();
-    };
 
     for (int o = 0; o < P.n_ops && !failed; o++) {
         const ProgOp& op = P.ops[o];
         const int flags = op.flags;
         const int kt = op.kt;
-        const int t0 = bx * op.chunk_q + min(bx, op.chunk_r);
-        const int t1 = bx < op.ctas ? t0 + op.chunk_q + (bx < op.chunk_r ? 1 : 0) : t0;
+        int t0, t1;
+        prog_share(op, bx, t0, t1);
         uint2* slots = P.scratch + (size_t)(o & 1) * gridDim.x * 128;
 
         stamp();  // op start (4 stamps per op: start, after barrier, after staging, after compute)
         if (flags & OP_NEW_X) {
-            if (flags & OP_DEPENDS) grid_barrier(o);
-            else consumers_sync();  // the staged activations are about to be replaced
+            if (flags & OP_DEPENDS) run.grid_barrier(o);
+            else run.consumers_sync();  // the staged activations are about to be replaced
             stamp();
             GemvParams sp{};
             sp.x = op.x;
@@ -226,8 +273,8 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_program_kernel(const Pro
             sp.ldx = op.k;
             sp.x_f32 = 0;
             sp.sx = P.sx;
-            stage_x(sp, xs, reinterpret_cast<float*>(cinit), kt * T::K, R::BETA, GEMV_CONSUMERS, XC == 1);
-            consumers_sync();
+            stage_x(sp, xs, reinterpret_cast<float*>(cinit), kt * T::K, R::BETA, GEMV_CONSUMERS);
+            run.consumers_sync();
             stamp();
         } else {
             stamp();
@@ -242,39 +289,117 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_program_kernel(const Pro
                     const int64_t off = (int64_t)col * op.ldy + op.col0 + n;
                     const float v = buf[i];
                     op.y[off] = v;
-                    const uint2 word = make_uint2(__float_as_uint(v), (unsigned int)(epoch + (unsigned long long)barriers + 1));
+                    const uint2 word = make_uint2(__float_as_uint(v), run.tag());
                     for (int r = 0; r < P.world; r++)
                         if (r != P.rank) st_slot_sys(op.ll[r] + off, word);
                 }
             }
         };
         consume_share<QT, XC>(t0, t1, kt, op.chunk_q, op.chunk_r, warp, lane, smem_u32(ring), bar, partial, stages, st, x32, c32,
-                              live, slots, P.status, smem_u32(const_cast<int*>(abort_flag)), acc, emit);
+                              slots, P.status, smem_u32(const_cast<int*>(abort_flag)), acc, emit);
         if (*abort_flag) failed = true;
         stamp();
     }
     if (failed) {
         if (lane == 0) atomicOr(P.status, STATUS_GEMV_FIXUP_TIMEOUT);
+        *run.failed = 1;
         drain_after_abort();
     }
+    run.leave();
+}
 
-    // ---- the rows of the last ops land before the kernel ends (tag of the barrier that never comes)
-    consumers_sync();
-    if (!failed) land(land_from, P.n_ops, (unsigned int)(epoch + (unsigned long long)barriers + 1));
+// One token.  Shared memory: control | pieces | block records | digits | rings (wf_gemv_stream.cuh); all 512
+// threads are consumers, every warp requests its own copies and runs ahead over the following projections.
+template <int QT>
+__global__ void __launch_bounds__(GEMV_CONSUMERS, 1) gemv1_program_kernel(const ProgParams P) {
+    using T = Tile<QT>;
+    using R = TileRegs<QT>;
+    using G = WsGeom<QT>;
+    extern __shared__ __align__(128) uint8_t smem[];
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem);
+    WsPiece* pieces = reinterpret_cast<WsPiece*>(smem + WS_CTRL_BYTES);
+    uint8_t* recs = smem + WS_CTRL_BYTES + WS_PIECE_BYTES;
+    uint8_t* xd = recs + (size_t)(P.kp_max >> 5) * 32;
+    uint8_t* ring = smem + (((size_t)(xd - smem) + (size_t)P.kp_max * 4 + 64 + 127) & ~(size_t)127);
 
-    // ---- leave: the last CTA out advances the epoch for the next run
-    consumers_sync();
+    const int warp = __shfl_sync(0xFFFFFFFFu, (int)(threadIdx.x >> 5), 0);
+    const int lane = threadIdx.x & 31;
+    const int bx = blockIdx.x, stages = P.stages;
     if (threadIdx.x == 0) {
-        __threadfence();
-        const unsigned int d = atomicAdd(&P.sync->done_ctas, 1u);
-        if (d == gridDim.x - 1) {
-            P.sync->done_ctas = 0;
-            // CTAs that skipped barriers after a failure would leave `arrive` short: resynchronise it
-            P.sync->arrive = (epoch + (unsigned long long)P.n_barriers + 1) * gridDim.x;
-            __threadfence();
-            st_release_gpu(&P.sync->epoch, epoch + (unsigned long long)P.n_barriers + 1);  // +1: the final landing's tag
-        }
+        *abort_flag = 0;
+        reinterpret_cast<volatile int*>(smem)[1] = 0;
+        ws_bars_init(smem, stages);
     }
+    __syncthreads();
+
+    const WsBars bar = ws_bars(smem, warp);
+    auto share_of = [&](int o) {
+        const ProgOp& op = P.ops[o];
+        WsShare sh;
+        sh.tiles = op.tiles;
+        prog_share(op, bx, sh.t0, sh.t1);
+        return sh;
+    };
+    WsStream ss;
+    const uint32_t ring_w = smem_u32(ring) + (uint32_t)warp * (uint32_t)stages * G::STAGE_BYTES;
+    // the weights depend on nothing: request the first copies of this warp's stream at once
+    for (int s = 0; s < stages; s++) ws_issue<QT>(ss, share_of, P.n_ops, warp, lane, ring_w, bar.full_w, stages);
+
+    ProgRun run{P, reinterpret_cast<volatile int*>(smem) + 1, ld_acquire_gpu(&P.sync->epoch)};
+    bool failed = false;
+    int stamp_i = 0;
+    auto stamp = [&]() {
+        if (P.timing != nullptr && threadIdx.x == 0 && stamp_i < 64) {
+            unsigned long long tm;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tm));
+            P.timing[(size_t)bx * 64 + stamp_i] = tm;
+        }
+        stamp_i++;
+    };
+    stamp();
+
+    for (int o = 0; o < P.n_ops && !failed; o++) {
+        const ProgOp& op = P.ops[o];
+        const int flags = op.flags;
+        const int kt = op.kt;
+        const WsShare sh = share_of(o);
+        uint2* slots = P.scratch + (size_t)(o & 1) * gridDim.x * 128;
+
+        stamp();  // op start (4 stamps per op: start, after barrier, after staging, after compute)
+        if (flags & OP_NEW_X) {
+            if (flags & OP_DEPENDS) run.grid_barrier(o);
+            else run.consumers_sync();  // the staged activations are about to be replaced
+            stamp();
+            stage_x_q8<R::BETA_INT>(op.x, op.k, xd, recs, kt * T::K, GEMV_CONSUMERS);
+            run.consumers_sync();
+            stamp();
+        } else {
+            stamp();
+            stamp();
+        }
+
+        // y goes to every rank's buffer: the row-shard gather happens here
+        auto emit_row = [&](int n, float v) {
+            if (n < op.rows) {
+                const int64_t off = op.col0 + n;
+                op.y[off] = v;
+                const uint2 word = make_uint2(__float_as_uint(v), run.tag());
+                for (int r = 0; r < P.world; r++)
+                    if (r != P.rank) st_slot_sys(op.ll[r] + off, word);
+            }
+        };
+        ws_consume<QT>(sh, kt, op.chunk_q, op.chunk_r, warp, lane, ring_w, bar, pieces, stages, ss, smem_u32(xd), smem_u32(recs),
+                       smem_u32(recs) + (uint32_t)((kt * T::K) >> 5) * 16, slots, P.status, smem_u32(const_cast<int*>(abort_flag)),
+                       share_of, P.n_ops, emit_row);
+        if (*abort_flag) failed = true;
+        stamp();
+    }
+    if (failed) {
+        if (lane == 0) atomicOr(P.status, STATUS_GEMV_FIXUP_TIMEOUT);
+        *run.failed = 1;
+        drain_after_abort();
+    }
+    run.leave();
 }
 
 // ---------------------------------------------------------------- host side
@@ -300,6 +425,20 @@ static Program* get_program(Context* c, int64_t h) {
     if (!p || std::find(g_programs.begin(), g_programs.end(), p) == g_programs.end() || p->magic != 0x57465047 || p->ctx != c)
         return nullptr;
     return p;
+}
+
+template <int QT>
+static cudaError_t program_launch_one_token(const Program& pr, cudaStream_t s) {
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 64 && !attr_set[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(gemv1_program_kernel<QT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (e != cudaSuccess) return e;
+        attr_set[dev] = true;
+    }
+    gemv1_program_kernel<QT><<<pr.grid, GEMV_CONSUMERS, pr.smem, s>>>(pr.params);
+    return cudaGetLastError();
 }
 
 template <int QT, int XC>
@@ -366,25 +505,46 @@ int wf_program_create(int64_t ctx, int n_ops, const int64_t* weights, const int6
         op.k = (int)w->g.k;
         op.kt = (int)w->g.kt;
         op.rt = (int)w->g.rt;
-        op.ctas = std::min(grid, gemv_ctas(c->sm_count, total));  // the split gemv_kernel uses: same sums, same bits
-        op.chunk_q = (int)(total / op.ctas);
-        op.chunk_r = (int)(total % op.ctas);
+        // the split the per-projection kernel uses: same sums, same bits
+        if (m == 1) {
+            const WsSplit sp = ws_split(c->sm_count, w->g.rt, w->g.kt);
+            op.ctas = sp.ctas;
+            op.aligned = sp.aligned;
+            op.chunk_q = sp.chunk_q;
+            op.chunk_r = sp.chunk_r;
+        } else {
+            op.ctas = std::min(grid, gemv_ctas(c->sm_count, total));
+            op.aligned = 0;
+            op.chunk_q = (int)(total / op.ctas);
+            op.chunk_r = (int)(total % op.ctas);
+        }
         op.flags = (o == 0 ? (flags[o] | OP_NEW_X) : flags[o]) & (OP_NEW_X | OP_DEPENDS);
         if ((op.flags & OP_DEPENDS) && !(op.flags & OP_NEW_X)) op.flags |= OP_NEW_X;
         if (o == 0) op.flags &= ~OP_DEPENDS;  // nothing of this run precedes the first op
         if (op.flags & OP_DEPENDS) n_barriers++;
         kp_max = std::max(kp_max, op.kt * tile_k(qt));
     }
-    // shared memory: ctrl + partial + cinit + x + ring
+    // shared memory: one token -- the streaming layout (wf_gemv_stream.cuh); several -- ctrl + partial + cinit + x + ring
     const int xc = (m == 1) ? 1 : 8;
-    const int nslot = xc == 1 ? Slots<1>::N : Slots<8>::N, elems = 16 * xc;
-    const int sx = kp_max * 2 + 64;
-    size_t fixed = GEMV_CTRL_BYTES + (size_t)nslot * GEMV_WARPS * elems * 4 + (size_t)(kp_max / 32) * 64 + (size_t)m * sx;
-    fixed = (fixed + 127) & ~(size_t)127;
-    const size_t stage = (size_t)GEMV_WARPS * tile_bytes(qt);
-    if (fixed + 2 * stage > 227 * 1024) return set_error(c, WF_ERR_TOO_LARGE, "K=%d with %lld tokens does not fit one SM's shared memory", kp_max, (long long)m);
-    // the ring also carries the next projections' weights across barriers: a little deeper than the single-op kernel's
-    const int stages = (int)std::min<size_t>((227 * 1024 - fixed) / stage, GEMV_USE_STAGES + 2);
+    size_t fixed, stage;
+    int stages, sx = 0;
+    if (xc == 1) {
+        int want = PROG_ONE_TOKEN_STAGES;
+        if (const char* e = getenv("WF_PROG_STAGES")) want = std::max(2, std::min(atoi(e), WS_MAX_STAGES));
+        fixed = ws_fixed_smem(kp_max);
+        stage = (size_t)GEMV_WARPS * (tile_bytes(qt) <= 1280 ? 2 : 1) * tile_bytes(qt);
+        stages = ws_stages(qt, kp_max, want);
+        if (stages < 2) return set_error(c, WF_ERR_TOO_LARGE, "K=%d does not fit one SM's shared memory", kp_max);
+    } else {
+        const int nslot = Slots<8>::N, elems = 16 * xc;
+        sx = kp_max * 2 + 64;
+        fixed = GEMV_CTRL_BYTES + (size_t)nslot * GEMV_WARPS * elems * 4 + (size_t)(kp_max / 32) * 64 + (size_t)m * sx;
+        fixed = (fixed + 127) & ~(size_t)127;
+        stage = (size_t)GEMV_WARPS * tile_bytes(qt);
+        if (fixed + 2 * stage > 227 * 1024) return set_error(c, WF_ERR_TOO_LARGE, "K=%d with %lld tokens does not fit one SM's shared memory", kp_max, (long long)m);
+        // the ring also carries the next projections' weights across barriers: a little deeper than the single-op kernel's
+        stages = (int)std::min<size_t>((227 * 1024 - fixed) / stage, GEMV_USE_STAGES + 2);
+    }
 
     Program* pr = new Program();
     pr->ctx = c;
@@ -448,7 +608,7 @@ int wf_program_run(int64_t ctx, int64_t program, int64_t stream) {
     const int qt = pr->qtype;
     cudaError_t e;
     if (pr->m == 1)
-        e = qt == WF_QTYPE_Q4_0 ? program_launch<WF_QTYPE_Q4_0, 1>(*pr, s) : qt == WF_QTYPE_Q4_1 ? program_launch<WF_QTYPE_Q4_1, 1>(*pr, s) : qt == WF_QTYPE_Q8_0 ? program_launch<WF_QTYPE_Q8_0, 1>(*pr, s) : program_launch<WF_QTYPE_Q4_K, 1>(*pr, s);
+        e = qt == WF_QTYPE_Q4_0 ? program_launch_one_token<WF_QTYPE_Q4_0>(*pr, s) : qt == WF_QTYPE_Q4_1 ? program_launch_one_token<WF_QTYPE_Q4_1>(*pr, s) : qt == WF_QTYPE_Q8_0 ? program_launch_one_token<WF_QTYPE_Q8_0>(*pr, s) : program_launch_one_token<WF_QTYPE_Q4_K>(*pr, s);
     else
         e = qt == WF_QTYPE_Q4_0 ? program_launch<WF_QTYPE_Q4_0, 8>(*pr, s) : qt == WF_QTYPE_Q4_1 ? program_launch<WF_QTYPE_Q4_1, 8>(*pr, s) : qt == WF_QTYPE_Q8_0 ? program_launch<WF_QTYPE_Q8_0, 8>(*pr, s) : program_launch<WF_QTYPE_Q4_K, 8>(*pr, s);
     if (e != cudaSuccess) return cuda_status(c, e, "program launch");

@@ -28,7 +28,7 @@
 // Replaces the fp32 batch_matmul_f32 launch of
 // warpforge-backend-nvidia/src/main/java/io/surfworks/warpforge/backend/nvidia/ops/DotGeneralKernel.java:263-281
 // (PTX at .../nvidia/cuda/CudaKernels.java:4423-4585) for quantized right-hand sides.
-#include "wf_gemv_core.cuh"
+#include "wf_gemv_stream.cuh"
 
 namespace wf {
 
@@ -90,7 +90,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvParams 
     asm volatile("griddepcontrol.wait;" ::: "memory");
     stamp(0);
     // cinit entries of dead columns stay uninitialised: they only feed dead columns
-    stage_x(p, xs, reinterpret_cast<float*>(cinit), kp, R::BETA, GEMV_CONSUMERS, XC == 1);
+    stage_x(p, xs, reinterpret_cast<float*>(cinit), kp, R::BETA, GEMV_CONSUMERS);
     asm volatile("bar.sync 1, %0;" ::"n"(GEMV_CONSUMERS) : "memory");
     stamp(1);
 
@@ -115,12 +115,74 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvParams 
         }
     };
 
-    const uint32_t x32 = smem_u32(xrow) + q * 16, c32 = smem_u32(cinit) + (XC == 1 ? 0 : q * 16);
-    const uint32_t live = (XC == 1) ? (uint32_t)(g == 0) : 1u;
+    const uint32_t x32 = smem_u32(xrow) + q * 16, c32 = smem_u32(cinit) + q * 16;
     stamp(2);
     WalkState st;
     consume_share<QT, XC>(t0, t1, p.kt, p.chunk_q, p.chunk_r, warp, lane, smem_u32(ring), bar, partial, stages, st, x32, c32,
-                          live, p.scratch, p.status, smem_u32(const_cast<int*>(abort_flag)), acc, emit);
+                          p.scratch, p.status, smem_u32(const_cast<int*>(abort_flag)), acc, emit);
+    stamp(4);
+    if (*abort_flag) {  // a wait ran out somewhere in this CTA
+        if (lane == 0) atomicOr(p.status, STATUS_GEMV_FIXUP_TIMEOUT);
+        drain_after_abort();
+    }
+    stamp(5);
+}
+
+// ---------------------------------------------------------------- one bf16 token
+// Integer MMAs on exact base-256 digits of the activations, every warp streaming its own run of tiles
+// (wf_gemv_stream.cuh).  512 threads, all of them consumers: each warp issues its own bulk copies.
+template <int QT>
+__global__ void __launch_bounds__(GEMV_CONSUMERS, 1) gemv1_kernel(const GemvParams p) {
+    using T = Tile<QT>;
+    using R = TileRegs<QT>;
+    using G = WsGeom<QT>;
+    extern __shared__ __align__(128) uint8_t smem[];
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem);
+    WsPiece* pieces = reinterpret_cast<WsPiece*>(smem + WS_CTRL_BYTES);
+    uint8_t* recs = smem + WS_CTRL_BYTES + WS_PIECE_BYTES;
+    const int kp = p.kt * T::K;
+    uint8_t* xd = recs + (size_t)(kp >> 5) * 32;
+    uint8_t* ring = smem + (((size_t)(xd - smem) + (size_t)kp * 4 + 64 + 127) & ~(size_t)127);
+
+    const int warp = __shfl_sync(0xFFFFFFFFu, (int)(threadIdx.x >> 5), 0);
+    const int lane = threadIdx.x & 31;
+    const int bx = blockIdx.x, stages = p.stages;
+    int t0, t1;
+    ws_cta_share(bx, (int)gridDim.x, p.chunk_q, p.chunk_r, p.aligned, p.kt, t0, t1);
+    auto stamp = [&](int i) {
+        if (p.timing != nullptr && threadIdx.x == 0) {
+            unsigned long long tm;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tm));
+            p.timing[(size_t)blockIdx.x * 8 + i] = tm;
+        }
+    };
+    // Programmatic stream serialization: see gemv_kernel.  The weights depend on nothing, so every warp
+    // requests the first copies of its run before waiting for the previous grid.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        ws_bars_init(smem, stages);
+    }
+    __syncthreads();
+    const WsBars bar = ws_bars(smem, warp);
+    const WsShare share{p.tiles, t0, t1};
+    auto share_of = [&](int) { return share; };
+    WsStream ss;
+    const uint32_t ring_w = smem_u32(ring) + (uint32_t)warp * (uint32_t)stages * G::STAGE_BYTES;
+    for (int s = 0; s < stages; s++) ws_issue<QT>(ss, share_of, 1, warp, lane, ring_w, bar.full_w, stages);
+
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    stamp(0);
+    stage_x_q8<R::BETA_INT>(p.x, p.k, xd, recs, kp, GEMV_CONSUMERS);
+    __syncthreads();
+    stamp(1);
+    auto emit_row = [&](int n, float v) {
+        if (n < p.rows) p.y[p.col0 + n] = v;
+    };
+    stamp(2);
+    ws_consume<QT>(share, p.kt, p.chunk_q, p.chunk_r, warp, lane, ring_w, bar, pieces, stages, ss, smem_u32(xd), smem_u32(recs),
+                   smem_u32(recs) + (uint32_t)(kp >> 5) * 16, p.scratch, p.status, smem_u32(const_cast<int*>(abort_flag)), share_of, 1,
+                   emit_row);
     stamp(4);
     if (*abort_flag) {  // a wait ran out somewhere in this CTA
         if (lane == 0) atomicOr(p.status, STATUS_GEMV_FIXUP_TIMEOUT);
@@ -139,6 +201,7 @@ static size_t gemv_fixed_smem(int kp, int xcols, int* sx_out) {
 }
 
 constexpr size_t GEMV_SMEM_LIMIT = 227 * 1024;
+constexpr int GEMV_ONE_TOKEN_STAGES = 4;  // copies in flight per warp of the one-token kernel
 
 // Ring depth that fits beside the staged activations (0 = does not fit at all).
 template <int XC>
@@ -156,7 +219,7 @@ int gemv_max_tokens_per_pass(const Weight& w, int x_dtype) {
     int best = 0;
     for (int m = 1; m * per_tok <= GEMV_XCOLS; m++)
         if (gemv_stages<8>(w.g.qtype, kp, m * per_tok) >= 2) best = m;
-    if (best == 0 && per_tok == 1 && gemv_stages<1>(w.g.qtype, kp, 1) >= 1) best = 1;
+    if (best == 0 && per_tok == 1 && ws_stages(w.g.qtype, kp, 2) >= 2) best = 1;  // only the one-token kernel fits
     return best;
 }
 
@@ -182,6 +245,36 @@ static cudaError_t launch_one(const GemvParams& p, int grid, size_t smem, cudaSt
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, gemv_kernel<QT, XC>, p);
+}
+
+template <int QT>
+static cudaError_t launch_one_token(const GemvParams& p, int grid, size_t smem, cudaStream_t s) {
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 64 && !attr_set[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(gemv1_kernel<QT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMV_SMEM_LIMIT);
+        if (e != cudaSuccess) return e;
+        attr_set[dev] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(GEMV_CONSUMERS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, gemv1_kernel<QT>, p);
+}
+
+static cudaError_t launch_qt_one_token(int qt, const GemvParams& p, int grid, size_t smem, cudaStream_t s) {
+    return qt == WF_QTYPE_Q4_0   ? launch_one_token<WF_QTYPE_Q4_0>(p, grid, smem, s)
+           : qt == WF_QTYPE_Q4_1 ? launch_one_token<WF_QTYPE_Q4_1>(p, grid, smem, s)
+           : qt == WF_QTYPE_Q8_0 ? launch_one_token<WF_QTYPE_Q8_0>(p, grid, smem, s)
+                                 : launch_one_token<WF_QTYPE_Q4_K>(p, grid, smem, s);
 }
 
 template <int XC>
@@ -215,9 +308,10 @@ static int launch_passes(Context* c, const GemvCall& call, cudaStream_t s, uint2
     const int kp = (int)w.g.kt * tile_k(qt);
     const int per_pass = gemv_max_tokens_per_pass(w, call.x_dtype);
     const int64_t total = w.g.rt * w.g.kt;
-    const int grid = gemv_ctas(c->sm_count, total);
+    const int grid_several = gemv_ctas(c->sm_count, total);
+    const WsSplit one = ws_split(c->sm_count, w.g.rt, w.g.kt);  // the one-token kernel's cut
     const size_t esz = call.x_dtype == WF_DTYPE_F32 ? 4 : 2;
-    int max_rounds = (int)((total / grid + 1 + GEMV_WARPS - 1) / GEMV_WARPS);
+    int max_rounds = (int)((total / grid_several + 1 + GEMV_WARPS - 1) / GEMV_WARPS);
     for (int64_t m0 = 0; m0 < call.m; m0 += per_pass) {
         GemvParams p{};
         p.tiles = w.d_tiles;
@@ -233,17 +327,22 @@ static int launch_passes(Context* c, const GemvCall& call, cudaStream_t s, uint2
         p.k = (int)w.g.k;
         p.kt = (int)w.g.kt;
         p.rt = (int)w.g.rt;
-        p.chunk_q = (int)(total / grid);
-        p.chunk_r = (int)(total % grid);
         p.m = (int)((call.m - m0) < per_pass ? (call.m - m0) : per_pass);
         p.x_f32 = call.x_dtype == WF_DTYPE_F32;
         const int xcols = p.x_f32 ? 3 * p.m : p.m;
+        const bool one_token = xcols == 1 && ws_stages(qt, kp, 2) >= 2;
+        const int grid = one_token ? one.ctas : grid_several;
+        p.chunk_q = one_token ? one.chunk_q : (int)(total / grid);
+        p.chunk_r = one_token ? one.chunk_r : (int)(total % grid);
+        p.aligned = one_token ? one.aligned : 0;
         const size_t stage = (size_t)GEMV_WARPS * tile_bytes(qt);
         if (clear_slots) WF_CUDA(c, cudaMemsetAsync(slots, 0, (size_t)grid * 128 * sizeof(uint2), s));
         cudaError_t e;
-        if (xcols == 1) {
-            p.stages = std::min(gemv_stages<1>(qt, kp, xcols), std::max(max_rounds, 1));
-            e = launch_qt<1>(qt, p, grid, gemv_fixed_smem<1>(kp, xcols, &p.sx) + p.stages * stage, s);
+        if (one_token) {  // one bf16 token: the integer path, every warp streaming its own run
+            const int chunk = tile_bytes(qt) <= 1280 ? 2 : 1;
+            const int my_chunks = (int)((total / grid + GEMV_WARPS) / GEMV_WARPS + chunk - 1) / chunk;
+            p.stages = std::min(ws_stages(qt, kp, GEMV_ONE_TOKEN_STAGES), std::max(my_chunks, 2));
+            e = launch_qt_one_token(qt, p, grid, ws_fixed_smem(kp) + (size_t)p.stages * GEMV_WARPS * chunk * tile_bytes(qt), s);
         } else {
             p.stages = std::min(gemv_stages<8>(qt, kp, xcols), std::max(max_rounds, 1));
             e = launch_qt<8>(qt, p, grid, gemv_fixed_smem<8>(kp, xcols, &p.sx) + p.stages * stage, s);

@@ -52,6 +52,7 @@ struct GemvParams {
     int sx;       // shared-memory row stride of staged x, in bytes
     int stages;   // ring depth, each stage holds GEMV_WARPS tiles
     int chunk_q, chunk_r;  // CTA b owns tiles [b*q + min(b,r), (b+1)*q + min(b+1,r))
+    int aligned;           // one-token kernel: 1 = chunk_q / chunk_r count whole row-tiles (no row-tile is cut between CTAs)
     unsigned long long* timing;  // optional [ctas][8] globaltimer stamps (instrumented launches only)
 };
 
@@ -67,31 +68,34 @@ __device__ __forceinline__ uint2 lds64(uint32_t a) {
     asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
     return v;
 }
-// Per 32-k block: the B fragment (8 activations of this lane's column) and the accumulator start.
-//   XC = 8: every lane loads its own column (16 bytes) and its float4 of start values.
-//   XC = 1: only column 0 is live.  The four lanes that own it (g == 0) load the activations --
-//           a predicated load touches one quarter-warp instead of four -- and the start value is a
-//           single float read by all lanes at one address (a broadcast).  Dead columns compute on
-//           whatever the registers hold; their results are never stored.
+__device__ __forceinline__ uint32_t lds32(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds16(uint32_t a) {
+    uint32_t v;
+    asm volatile("{\n\t.reg .b16 h;\n\tld.shared.u16 h, [%1];\n\tcvt.u32.u16 %0, h;\n\t}" : "=r"(v) : "r"(a));
+    return v;
+}
+// 16-byte load by the lanes whose `pred` is non-zero; the other lanes keep what `v` held.
+__device__ __forceinline__ void lds128_if(uint4& v, uint32_t a, uint32_t pred) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %5, 0;\n\t@p ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n\t}"
+        : "+r"(v.x), "+r"(v.y), "+r"(v.z), "+r"(v.w)
+        : "r"(a), "r"(pred));
+}
+// Several tokens (XC = 8): per 32-k block the B fragment (8 activations of this lane's column, 16 bytes)
+// and the lane's float4 of accumulator start values.
 template <int XC>
 __device__ __forceinline__ void fetch_block(uint32_t xaddr, uint32_t caddr, uint32_t live, uint4& xb, float4& ci) {
-    if (XC == 1) {
-        asm volatile(
-            "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %5, 0;\n\t@p ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n\t}"
-            : "+r"(xb.x), "+r"(xb.y), "+r"(xb.z), "+r"(xb.w)
-            : "r"(xaddr), "r"(live));
-        // the start value is added after the MMA (the MMA's C operand would need it in four registers)
-        float c;
-        asm volatile("ld.shared.f32 %0, [%1];" : "=f"(c) : "r"(caddr));
-        ci = make_float4(c, 0.f, c, 0.f);
-    } else {
-        xb = lds128(xaddr);
-        const uint4 t = lds128(caddr);
-        ci = make_float4(__uint_as_float(t.x), __uint_as_float(t.y), __uint_as_float(t.z), __uint_as_float(t.w));
-    }
+    (void)live;
+    xb = lds128(xaddr);
+    const uint4 t = lds128(caddr);
+    ci = make_float4(__uint_as_float(t.x), __uint_as_float(t.y), __uint_as_float(t.z), __uint_as_float(t.w));
 }
-// Offsets of block `blk` inside the start-value table: one float (XC = 1) or [4] float4 (XC = 8).
-template <int XC> __device__ __forceinline__ constexpr int cinit_block_bytes() { return XC == 1 ? 4 : 64; }
+// Bytes per block in the start-value table of the several-token path: [4] float4.
+template <int XC> __device__ __forceinline__ constexpr int cinit_block_bytes() { return 64; }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 // Barriers are addressed by their 32-bit shared-memory address throughout: no generic-pointer
@@ -209,6 +213,90 @@ __device__ __forceinline__ void block_mma(float (&d)[4], uint32_t wg, uint32_t w
           "r"(0x00780078u), "r"(magic));
 }
 
+// ---- one token: integer MMAs, the eight accumulator columns = two blocks x four activation digits
+// With a single bf16 token seven of the eight columns of the B operand would be idle, and turning 4-bit
+// codes into bf16 operands costs seven half-rate integer instructions per word of eight codes.  The
+// one-token path therefore runs on mma.m16n8k32.s32.u8.s8:
+//   * A operand: a plane word AND 0x78787878 is four bytes 8 * code (nibble positions 0, 2, 4, 6 of the
+//     rotated word sit in bits 3..6 of the four bytes); a rotation by 4 bits gives the other four codes.
+//     Three integer instructions per word, no layout change.
+//   * B operand: the activations of a 32-k block are written as x = X * 2^e with one exponent per block
+//     and X an integer below 2^30, and X as four signed base-256 digits (exact for every element within
+//     2^-22 of the block's largest; smaller ones are cut at 2^-30 of it).  The 32 k-slots of an MMA belong to
+//     two different blocks (slots 0..15 / 16..31) and column n = 4 * h + digit holds digit `digit` of
+//     block h in that block's slots and zeros elsewhere, so column n of the int32 accumulator is the
+//     exact sum over one block and one digit.
+//   * After the two MMAs of a block pair lane (g, q) holds, for rows g and g+8, digits 2(q&1), 2(q&1)+1
+//     of block (q >> 1) of the pair: D = 256 * D_even + D_odd in integers, one conversion to float, one
+//     product with weight scale x block exponent, one FMA into the row's accumulator.
+// The constant offset of the codes (8 * (code - 8) wanted, 8 * code multiplied) enters as the int32
+// start value -64 * (sum of the block's digits), prepared with the digits.
+//
+// Staged form of one token, per 128 k (a "unit" = four blocks j = 0..3, block pairs A = (0, 2) and
+// B = (1, 3)): 512 bytes of digits, lane L = 4 g + q reads 16 bytes at L * 16 holding digit (g & 3) of elements
+// 8q..8q+7 of block 2 (g >> 2) [pair A] and of block 2 (g >> 2) + 1 [pair B], each as the byte
+// quadruples of the first MMA (elements 0, 4, 1, 5) and of the second (2, 6, 3, 7).  A lane is a live
+// source for the low k-slots (its block is the pair's first) when g < 4 and for the high k-slots
+// otherwise; the registers of the other half stay zero for the whole kernel (predicated loads), so only
+// half a warp touches shared memory per load.
+// Per unit and lane quad position q = 2 h + p a 16-byte record {W, f, W', f'} for blocks 2h and 2h+1 and
+// digit pair p: W = int32 correction beta * (256 * sum of digit 2p + sum of digit 2p+1) that cancels the
+// codes' offset, f = 2^e * 256^(2 - 2p) / 8 the factor that turns the integer block sum into the block's
+// value; and 8 bytes {sum of x, sum of x'} for p = 0, zeros for p = 1 (formats with a per-block minimum).
+
+constexpr uint32_t CODE8_MASK = 0x78787878u;
+
+// d += (8 * codes) x digits over one block pair: w00 / w10 = rows g / g+8 of the pair's first block,
+// w01 / w11 = of its second block; bl = digit bytes for the low k-slots (first MMA, second MMA),
+// bh = for the high k-slots.
+__device__ __forceinline__ void pair_imma(int (&d)[4], uint32_t w00, uint32_t w10, uint32_t w01, uint32_t w11,
+                                          uint32_t bl1, uint32_t bl2, uint32_t bh1, uint32_t bh2) {
+    asm(
+        "{\n\t"
+        ".reg .b32 a0, a1, a2, a3, r0, r1, r2, r3;\n\t"
+        "and.b32 a0, %4, %12;\n\t"
+        "and.b32 a1, %5, %12;\n\t"
+        "and.b32 a2, %6, %12;\n\t"
+        "and.b32 a3, %7, %12;\n\t"
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {a0,a1,a2,a3}, {%8,%10}, {%0,%1,%2,%3};\n\t"
+        "shf.r.wrap.b32 r0, %4, %4, 4;\n\t"
+        "shf.r.wrap.b32 r1, %5, %5, 4;\n\t"
+        "shf.r.wrap.b32 r2, %6, %6, 4;\n\t"
+        "shf.r.wrap.b32 r3, %7, %7, 4;\n\t"
+        "and.b32 a0, r0, %12;\n\t"
+        "and.b32 a1, r1, %12;\n\t"
+        "and.b32 a2, r2, %12;\n\t"
+        "and.b32 a3, r3, %12;\n\t"
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {a0,a1,a2,a3}, {%9,%11}, {%0,%1,%2,%3};\n\t"
+        "}\n"
+        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+        : "r"(w00), "r"(w10), "r"(w01), "r"(w11), "r"(bl1), "r"(bl2), "r"(bh1), "r"(bh2), "r"(CODE8_MASK));
+}
+
+// Lane-specific shared addresses of the staged token for the tile at hand.
+struct Q8Addr {
+    uint32_t x;    // this lane's 16 digit bytes of the tile's first unit
+    uint32_t rec;  // this lane's record of the tile's first unit
+    uint32_t sx;   // this lane's pair of activation sums
+};
+// The B registers of a warp: `lo` feeds the low k-slots and is loaded by lanes 0..15, `hi` the high k-slots by
+// lanes 16..31; the other half of each stays zero from construction on.
+struct Q8Digits {
+    uint4 lo = make_uint4(0u, 0u, 0u, 0u), hi = make_uint4(0u, 0u, 0u, 0u);
+    __device__ __forceinline__ void load(uint32_t a, uint32_t is_lo) {
+        lds128_if(lo, a, is_lo);
+        lds128_if(hi, a, is_lo ^ 1u);
+    }
+};
+
+// 256 D_even + D_odd as a float (|D| < 2^20 for the 4-bit formats, so the integer is exact and the conversion rounds once)
+__device__ __forceinline__ float digits_to_float(int de, int dodd) { return (float)(de * 256 + dodd); }
+// the same for sums up to 2^24 (Q8_0: two planes combined), where 256 D would leave 32 bits; w = the offset correction,
+// split so that both summands stay below 2^24 and convert exactly (one rounding in the FMA)
+__device__ __forceinline__ float wide_digits_to_float(int de, int dodd, int w) {
+    return fmaf((float)(de + (w >> 8)), 256.f, (float)(dodd + (w & 255)));
+}
+
 __device__ __forceinline__ uint32_t word_of(const uint4& v, int j) {
     return j == 0 ? v.x : j == 1 ? v.y : j == 2 ? v.z : v.w;
 }
@@ -220,12 +308,36 @@ template <int QT> struct TileRegs;
 
 template <> struct TileRegs<WF_QTYPE_Q4_0> {
     static constexpr float BETA = -24.f;  // (16 + code) - 24 = code - 8
+    static constexpr int BETA_INT = -64;   // one token: 8 * code - 64 = 8 * (code - 8)
     uint4 c[2], s;
+    uint32_t sg2, sh2;  // one token: fp16 scales of blocks 2h, 2h+1 (h = q >> 1) for row g / row g+8
     // t = shared address of the tile + lane * 16
+    template <int XC>
     __device__ __forceinline__ void load(uint32_t t, int lane) {
         c[0] = lds128(t);
         c[1] = lds128(t + 512);
-        s = lds128(t - lane * 16 + Tile<WF_QTYPE_Q4_0>::SCALE_OFF + (lane >> 2) * 16);
+        const uint32_t sb = t - lane * 16 + Tile<WF_QTYPE_Q4_0>::SCALE_OFF + (lane >> 2) * 16;
+        if (XC == 1) {
+            sg2 = lds32(sb + (lane & 2) * 2);
+            sh2 = lds32(sb + 8 + (lane & 2) * 2);
+        } else {
+            s = lds128(sb);
+        }
+    }
+    // One token: lane (g, q) adds its share of rows g (acc[0]) and g+8 (acc[2]); the four lanes of a quad
+    // hold different digit pairs / blocks of the same rows and are summed when the row-tile is flushed.
+    __device__ __forceinline__ void compute_q8(float (&acc)[4], const Q8Addr& a, Q8Digits& dg, uint32_t is_lo) const {
+        dg.load(a.x, is_lo);
+        const uint4 r = lds128(a.rec);  // {W, f, W', f'}: the odd digit's accumulator starts at the offset correction
+        int da[4] = {0, (int)r.x, 0, (int)r.x}, db[4] = {0, (int)r.z, 0, (int)r.z};
+        pair_imma(da, c[0].x, c[1].x, c[0].z, c[1].z, dg.lo.x, dg.lo.y, dg.hi.x, dg.hi.y);
+        pair_imma(db, c[0].y, c[1].y, c[0].w, c[1].w, dg.lo.z, dg.lo.w, dg.hi.z, dg.hi.w);
+        const float2 sg = half2_bits_to_float2(sg2), sh = half2_bits_to_float2(sh2);
+        const float ea = __uint_as_float(r.y), eb = __uint_as_float(r.w);
+        acc[0] = fmaf(sg.x * ea, digits_to_float(da[0], da[1]), acc[0]);
+        acc[2] = fmaf(sh.x * ea, digits_to_float(da[2], da[3]), acc[2]);
+        acc[0] = fmaf(sg.y * eb, digits_to_float(db[0], db[1]), acc[0]);
+        acc[2] = fmaf(sh.y * eb, digits_to_float(db[2], db[3]), acc[2]);
     }
     template <int XC>
     // xaddr: shared address of this lane's activations for k = kbase (row + q * 16 bytes);
@@ -234,48 +346,60 @@ template <> struct TileRegs<WF_QTYPE_Q4_0> {
         const float2 s0 = half2_bits_to_float2(s.x), s1 = half2_bits_to_float2(s.y);  // row g, blocks 0..3
         const float2 s2 = half2_bits_to_float2(s.z), s3 = half2_bits_to_float2(s.w);  // row g + 8
         const float sg[4] = {s0.x, s0.y, s1.x, s1.y}, sh[4] = {s2.x, s2.y, s3.x, s3.y};
-        if (XC == 1) {
-            // All lanes load (the lanes of the dead columns read the live column's activations: their MMA
-            // columns are never read).  One 16-byte load of the four start values.
-            uint4 xb[4];
-            (void)live;
+        uint4 xb;
+        float4 ci;
 #pragma unroll
-            for (int j = 0; j < 4; j++) xb[j] = lds128(xaddr + j * 64);
-            const uint4 t = lds128(caddr);
-            const float ci[4] = {__uint_as_float(t.x), __uint_as_float(t.y), __uint_as_float(t.z), __uint_as_float(t.w)};
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-                float d[4];
-                block_mma(d, word_of(c[0], j), word_of(c[1], j), xb[j], MAGIC_16, 0.f, 0.f, 0.f, 0.f);
-                acc[0] = fmaf(sg[j], d[0] + ci[j], acc[0]);
-                acc[2] = fmaf(sh[j], d[2] + ci[j], acc[2]);
-            }
-        } else {
-            uint4 xb;
-            float4 ci;
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-                fetch_block<XC>(xaddr + j * 64, caddr + j * cinit_block_bytes<XC>(), live, xb, ci);
-                float d[4];
-                block_mma(d, word_of(c[0], j), word_of(c[1], j), xb, MAGIC_16, ci.x, ci.y, ci.z, ci.w);
-                acc[0] = fmaf(sg[j], d[0], acc[0]);
-                acc[2] = fmaf(sh[j], d[2], acc[2]);
-                acc[1] = fmaf(sg[j], d[1], acc[1]);
-                acc[3] = fmaf(sh[j], d[3], acc[3]);
-            }
+        for (int j = 0; j < 4; j++) {
+            fetch_block<XC>(xaddr + j * 64, caddr + j * cinit_block_bytes<XC>(), live, xb, ci);
+            float d[4];
+            block_mma(d, word_of(c[0], j), word_of(c[1], j), xb, MAGIC_16, ci.x, ci.y, ci.z, ci.w);
+            acc[0] = fmaf(sg[j], d[0], acc[0]);
+            acc[2] = fmaf(sh[j], d[2], acc[2]);
+            acc[1] = fmaf(sg[j], d[1], acc[1]);
+            acc[3] = fmaf(sh[j], d[3], acc[3]);
         }
     }
 };
 
 template <> struct TileRegs<WF_QTYPE_Q4_1> {
     static constexpr float BETA = -16.f;  // (16 + code) - 16 = code; the min term is (-min / 16) * (start value)
+    static constexpr int BETA_INT = 0;    // one token: codes are unsigned, nothing to cancel
     uint4 c[2], s, mn;
+    uint32_t sg2, sh2, mg2, mh2;  // one token: fp16 scales and mins of blocks 2h, 2h+1 (h = q >> 1) for row g / row g+8
+    template <int XC>
     __device__ __forceinline__ void load(uint32_t t, int lane) {
         using T = Tile<WF_QTYPE_Q4_1>;
         c[0] = lds128(t);
         c[1] = lds128(t + 512);
-        s = lds128(t - lane * 16 + T::SCALE_OFF + (lane >> 2) * 16);
-        mn = lds128(t - lane * 16 + T::MIN_OFF + (lane >> 2) * 16);
+        const uint32_t sb = t - lane * 16 + T::SCALE_OFF + (lane >> 2) * 16;
+        const uint32_t mb = t - lane * 16 + T::MIN_OFF + (lane >> 2) * 16;
+        if (XC == 1) {
+            sg2 = lds32(sb + (lane & 2) * 2);
+            sh2 = lds32(sb + 8 + (lane & 2) * 2);
+            mg2 = lds32(mb + (lane & 2) * 2);
+            mh2 = lds32(mb + 8 + (lane & 2) * 2);
+        } else {
+            s = lds128(sb);
+            mn = lds128(mb);
+        }
+    }
+    // One token: 8 * code enters the MMA as is (no offset); the min term is min * (sum of the block's
+    // activations), which only the lanes of the first digit pair carry (the others read zeros).
+    __device__ __forceinline__ void compute_q8(float (&acc)[4], const Q8Addr& a, Q8Digits& dg, uint32_t is_lo) const {
+        dg.load(a.x, is_lo);
+        const uint4 r = lds128(a.rec);
+        const uint2 sx = lds64(a.sx);
+        int da[4] = {0, 0, 0, 0}, db[4] = {0, 0, 0, 0};
+        pair_imma(da, c[0].x, c[1].x, c[0].z, c[1].z, dg.lo.x, dg.lo.y, dg.hi.x, dg.hi.y);
+        pair_imma(db, c[0].y, c[1].y, c[0].w, c[1].w, dg.lo.z, dg.lo.w, dg.hi.z, dg.hi.w);
+        const float2 sg = half2_bits_to_float2(sg2), sh = half2_bits_to_float2(sh2);
+        const float2 mg = half2_bits_to_float2(mg2), mh = half2_bits_to_float2(mh2);
+        const float ea = __uint_as_float(r.y), eb = __uint_as_float(r.w);
+        const float xa = __uint_as_float(sx.x), xb = __uint_as_float(sx.y);
+        acc[0] = fmaf(sg.x * ea, digits_to_float(da[0], da[1]), fmaf(mg.x, xa, acc[0]));
+        acc[2] = fmaf(sh.x * ea, digits_to_float(da[2], da[3]), fmaf(mh.x, xa, acc[2]));
+        acc[0] = fmaf(sg.y * eb, digits_to_float(db[0], db[1]), fmaf(mg.y, xb, acc[0]));
+        acc[2] = fmaf(sh.y * eb, digits_to_float(db[2], db[3]), fmaf(mh.y, xb, acc[2]));
     }
     template <int XC>
     __device__ __forceinline__ void compute(float (&acc)[4], uint32_t xaddr, uint32_t caddr, uint32_t live) const {
@@ -286,64 +410,73 @@ template <> struct TileRegs<WF_QTYPE_Q4_1> {
         const float sg[4] = {s0.x, s0.y, s1.x, s1.y}, sh[4] = {s2.x, s2.y, s3.x, s3.y};
         const float mg[4] = {m0.x * -0.0625f, m0.y * -0.0625f, m1.x * -0.0625f, m1.y * -0.0625f};
         const float mh[4] = {m2.x * -0.0625f, m2.y * -0.0625f, m3.x * -0.0625f, m3.y * -0.0625f};
-        uint4 xb = make_uint4(0u, 0u, 0u, 0u);
+        uint4 xb;
         float4 ci;
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             fetch_block<XC>(xaddr + j * 64, caddr + j * cinit_block_bytes<XC>(), live, xb, ci);
             float d[4];
-            if (XC == 1) {
-                block_mma(d, word_of(c[0], j), word_of(c[1], j), xb, MAGIC_16, 0.f, 0.f, 0.f, 0.f);
-                d[0] += ci.x;
-                d[2] += ci.z;
-            } else {
-                block_mma(d, word_of(c[0], j), word_of(c[1], j), xb, MAGIC_16, ci.x, ci.y, ci.z, ci.w);
-            }
+            block_mma(d, word_of(c[0], j), word_of(c[1], j), xb, MAGIC_16, ci.x, ci.y, ci.z, ci.w);
             acc[0] = fmaf(sg[j], d[0], fmaf(mg[j], ci.x, acc[0]));
             acc[2] = fmaf(sh[j], d[2], fmaf(mh[j], ci.z, acc[2]));
-            if (XC > 1) {
-                acc[1] = fmaf(sg[j], d[1], fmaf(mg[j], ci.y, acc[1]));
-                acc[3] = fmaf(sh[j], d[3], fmaf(mh[j], ci.w, acc[3]));
-            }
+            acc[1] = fmaf(sg[j], d[1], fmaf(mg[j], ci.y, acc[1]));
+            acc[3] = fmaf(sh[j], d[3], fmaf(mh[j], ci.w, acc[3]));
         }
     }
 };
 
 template <> struct TileRegs<WF_QTYPE_Q8_0> {
     static constexpr float BETA = -400.f;  // (256 + 16 hi) + (16 + lo) - 400 = 16 (hi - 8) + lo
+    static constexpr int BETA_INT = -1024;  // one token: 16 * (8 hi) + (8 lo) - 1024 = 8 * (16 (hi - 8) + lo)
     uint4 c[4], s;                         // c[0..1] high plane rows g / g+8, c[2..3] low plane
+    uint32_t sg2, sh2;
+    template <int XC>
     __device__ __forceinline__ void load(uint32_t t, int lane) {
 #pragma unroll
         for (int i = 0; i < 4; i++) c[i] = lds128(t + i * 512);
-        s = lds128(t - lane * 16 + Tile<WF_QTYPE_Q8_0>::SCALE_OFF + (lane >> 2) * 16);
+        const uint32_t sb = t - lane * 16 + Tile<WF_QTYPE_Q8_0>::SCALE_OFF + (lane >> 2) * 16;
+        if (XC == 1) {
+            sg2 = lds32(sb + (lane & 2) * 2);
+            sh2 = lds32(sb + 8 + (lane & 2) * 2);
+        } else {
+            s = lds128(sb);
+        }
+    }
+    // One token: value = 16 (hi - 8) + lo; the two planes accumulate separately and combine as integers.
+    __device__ __forceinline__ void compute_q8(float (&acc)[4], const Q8Addr& a, Q8Digits& dg, uint32_t is_lo) const {
+        dg.load(a.x, is_lo);
+        const uint4 r = lds128(a.rec);
+        int la[4] = {0, 0, 0, 0}, lb[4] = {0, 0, 0, 0}, ha[4] = {0, 0, 0, 0}, hb[4] = {0, 0, 0, 0};
+        pair_imma(ha, c[0].x, c[1].x, c[0].z, c[1].z, dg.lo.x, dg.lo.y, dg.hi.x, dg.hi.y);
+        pair_imma(la, c[2].x, c[3].x, c[2].z, c[3].z, dg.lo.x, dg.lo.y, dg.hi.x, dg.hi.y);
+        pair_imma(hb, c[0].y, c[1].y, c[0].w, c[1].w, dg.lo.z, dg.lo.w, dg.hi.z, dg.hi.w);
+        pair_imma(lb, c[2].y, c[3].y, c[2].w, c[3].w, dg.lo.z, dg.lo.w, dg.hi.z, dg.hi.w);
+        const float2 sg = half2_bits_to_float2(sg2), sh = half2_bits_to_float2(sh2);
+        const float ea = __uint_as_float(r.y), eb = __uint_as_float(r.w);
+        const int wa = (int)r.x, wb = (int)r.z;
+        acc[0] = fmaf(sg.x * ea, wide_digits_to_float(16 * ha[0] + la[0], 16 * ha[1] + la[1], wa), acc[0]);
+        acc[2] = fmaf(sh.x * ea, wide_digits_to_float(16 * ha[2] + la[2], 16 * ha[3] + la[3], wa), acc[2]);
+        acc[0] = fmaf(sg.y * eb, wide_digits_to_float(16 * hb[0] + lb[0], 16 * hb[1] + lb[1], wb), acc[0]);
+        acc[2] = fmaf(sh.y * eb, wide_digits_to_float(16 * hb[2] + lb[2], 16 * hb[3] + lb[3], wb), acc[2]);
     }
     template <int XC>
     // xaddr: shared address of this lane's activations for k = kbase (row + q * 16 bytes);
     // caddr: shared address of the start value(s) of block kbase / 32; live: lane owns a live column
     __device__ __forceinline__ void compute(float (&acc)[4], uint32_t xaddr, uint32_t caddr, uint32_t live) const {
-        uint4 xb = make_uint4(0u, 0u, 0u, 0u);
+        uint4 xb;
         float4 ci;
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             fetch_block<XC>(xaddr + j * 64, caddr + j * cinit_block_bytes<XC>(), live, xb, ci);
             float d[4];
-            if (XC == 1)
-                block_mma(d, word_of(c[0], j), word_of(c[1], j), xb, MAGIC_256, 0.f, 0.f, 0.f, 0.f);
-            else
-                block_mma(d, word_of(c[0], j), word_of(c[1], j), xb, MAGIC_256, ci.x, ci.y, ci.z, ci.w);
+            block_mma(d, word_of(c[0], j), word_of(c[1], j), xb, MAGIC_256, ci.x, ci.y, ci.z, ci.w);
             block_mma(d, word_of(c[2], j), word_of(c[3], j), xb, MAGIC_16, d[0], d[1], d[2], d[3]);
-            if (XC == 1) {
-                d[0] += ci.x;
-                d[2] += ci.z;
-            }
             const float2 dg = half2_bits_to_float2(j < 2 ? s.x : s.y), dh = half2_bits_to_float2(j < 2 ? s.z : s.w);
             const float sg = (j & 1) ? dg.y : dg.x, sh = (j & 1) ? dh.y : dh.x;
             acc[0] = fmaf(sg, d[0], acc[0]);
             acc[2] = fmaf(sh, d[2], acc[2]);
-            if (XC > 1) {
-                acc[1] = fmaf(sg, d[1], acc[1]);
-                acc[3] = fmaf(sh, d[3], acc[3]);
-            }
+            acc[1] = fmaf(sg, d[1], acc[1]);
+            acc[3] = fmaf(sh, d[3], acc[3]);
         }
     }
 };
@@ -356,22 +489,64 @@ __device__ __forceinline__ float byte_times(uint32_t w, int i, float d, float ne
 
 template <> struct TileRegs<WF_QTYPE_Q4_K> {
     static constexpr float BETA = -16.f;  // (16 + code) - 16 = code
+    static constexpr int BETA_INT = 0;    // one token: codes are unsigned, nothing to cancel
     uint4 c[4], sc, mn;                   // c[0..1] sub-blocks 0..3 rows g / g+8, c[2..3] sub-blocks 4..7
     uint2 dd;                             // (d, dmin) of row g, of row g+8
+    uint32_t scg[2], sch[2], mng[2], mnh[2];  // one token, per unit u: scale / min bytes of sub-blocks 4u+2h, 4u+2h+1 (h = q >> 1), rows g / g+8
+    template <int XC>
     __device__ __forceinline__ void load(uint32_t t, int lane) {
         using T = Tile<WF_QTYPE_Q4_K>;
 #pragma unroll
         for (int i = 0; i < 4; i++) c[i] = lds128(t + i * 512);
         const uint32_t base = t - lane * 16;
         dd = lds64(base + T::D_OFF + (lane >> 2) * 8);
-        sc = lds128(base + T::SC_OFF + (lane >> 2) * 16);
-        mn = lds128(base + T::MN_OFF + (lane >> 2) * 16);
+        if (XC == 1) {
+            const uint32_t so = (lane >> 2) * 16 + (lane & 2);  // row g: bytes 2h, 2h+1; +4: sub-blocks 4+2h, 5+2h; +8: row g+8
+#pragma unroll
+            for (int u = 0; u < 2; u++) {
+                scg[u] = lds16(base + T::SC_OFF + so + 4 * u);
+                sch[u] = lds16(base + T::SC_OFF + so + 8 + 4 * u);
+                mng[u] = lds16(base + T::MN_OFF + so + 4 * u);
+                mnh[u] = lds16(base + T::MN_OFF + so + 8 + 4 * u);
+            }
+        } else {
+            sc = lds128(base + T::SC_OFF + (lane >> 2) * 16);
+            mn = lds128(base + T::MN_OFF + (lane >> 2) * 16);
+        }
+    }
+    // One token: the tile is two units of 128 k (sub-blocks 0..3 and 4..7).  8 * code enters the MMA as is;
+    // the min term is (dmin * m) * (sum of the sub-block's activations), carried by the lanes of the first digit pair.
+    __device__ __forceinline__ void compute_q8(float (&acc)[4], const Q8Addr& a, Q8Digits& dg, uint32_t is_lo) const {
+        const float2 g = half2_bits_to_float2(dd.x), h = half2_bits_to_float2(dd.y);  // (d, dmin) of rows g / g+8
+        const float BIG = 8388608.f;
+        const float ngd = -BIG * g.x, ngm = BIG * g.y, nhd = -BIG * h.x, nhm = BIG * h.y;
+#pragma unroll
+        for (int u = 0; u < 2; u++) {
+            dg.load(a.x + u * 512, is_lo);
+            const uint4 r = lds128(a.rec + u * 64);
+            const uint2 sx = lds64(a.sx + u * 32);
+            int da[4] = {0, 0, 0, 0}, db[4] = {0, 0, 0, 0};
+            pair_imma(da, c[2 * u].x, c[2 * u + 1].x, c[2 * u].z, c[2 * u + 1].z, dg.lo.x, dg.lo.y, dg.hi.x, dg.hi.y);
+            pair_imma(db, c[2 * u].y, c[2 * u + 1].y, c[2 * u].w, c[2 * u + 1].w, dg.lo.z, dg.lo.w, dg.hi.z, dg.hi.w);
+            const uint32_t wsg = scg[u], wsh = sch[u], wmg = mng[u], wmh = mnh[u];
+            const float ea = __uint_as_float(r.y), eb = __uint_as_float(r.w);
+            const float xa = __uint_as_float(sx.x), xb = __uint_as_float(sx.y);
+            // d * sc and -(dmin * m), exact
+            acc[0] = fmaf(byte_times(wsg, 0, g.x, ngd) * ea, digits_to_float(da[0], da[1]),
+                          fmaf(byte_times(wmg, 0, -g.y, ngm), xa, acc[0]));
+            acc[2] = fmaf(byte_times(wsh, 0, h.x, nhd) * ea, digits_to_float(da[2], da[3]),
+                          fmaf(byte_times(wmh, 0, -h.y, nhm), xa, acc[2]));
+            acc[0] = fmaf(byte_times(wsg, 1, g.x, ngd) * eb, digits_to_float(db[0], db[1]),
+                          fmaf(byte_times(wmg, 1, -g.y, ngm), xb, acc[0]));
+            acc[2] = fmaf(byte_times(wsh, 1, h.x, nhd) * eb, digits_to_float(db[2], db[3]),
+                          fmaf(byte_times(wmh, 1, -h.y, nhm), xb, acc[2]));
+        }
     }
     template <int XC>
     // xaddr: shared address of this lane's activations for k = kbase (row + q * 16 bytes);
     // caddr: shared address of the start value(s) of block kbase / 32; live: lane owns a live column
     __device__ __forceinline__ void compute(float (&acc)[4], uint32_t xaddr, uint32_t caddr, uint32_t live) const {
-        uint4 xb = make_uint4(0u, 0u, 0u, 0u);
+        uint4 xb;
         float4 ci;
         const float2 g = half2_bits_to_float2(dd.x), h = half2_bits_to_float2(dd.y);  // (d, dmin)
         const float BIG = 8388608.f;
@@ -382,25 +557,16 @@ template <> struct TileRegs<WF_QTYPE_Q4_K> {
         for (int jj = 0; jj < 8; jj++) {
             fetch_block<XC>(xaddr + jj * 64, caddr + jj * cinit_block_bytes<XC>(), live, xb, ci);
             float d[4];
-            if (XC == 1) {
-                block_mma(d, word_of(c[(jj >> 2) * 2], jj & 3), word_of(c[(jj >> 2) * 2 + 1], jj & 3), xb, MAGIC_16, 0.f, 0.f,
-                          0.f, 0.f);
-                d[0] += ci.x;
-                d[2] += ci.z;
-            } else {
-                block_mma(d, word_of(c[(jj >> 2) * 2], jj & 3), word_of(c[(jj >> 2) * 2 + 1], jj & 3), xb, MAGIC_16, ci.x,
-                          ci.y, ci.z, ci.w);
-            }
+            block_mma(d, word_of(c[(jj >> 2) * 2], jj & 3), word_of(c[(jj >> 2) * 2 + 1], jj & 3), xb, MAGIC_16, ci.x,
+                      ci.y, ci.z, ci.w);
             const float ag = byte_times(jj < 4 ? sc.x : sc.y, jj & 3, g.x, ngd);  // d * sc, exact
             const float ah = byte_times(jj < 4 ? sc.z : sc.w, jj & 3, h.x, nhd);
             const float cg = byte_times(jj < 4 ? mn.x : mn.y, jj & 3, gm, ngm);  // dmin * m / 16, exact
             const float ch = byte_times(jj < 4 ? mn.z : mn.w, jj & 3, hm, nhm);
             acc[0] = fmaf(ag, d[0], fmaf(cg, ci.x, acc[0]));
             acc[2] = fmaf(ah, d[2], fmaf(ch, ci.z, acc[2]));
-            if (XC > 1) {
-                acc[1] = fmaf(ag, d[1], fmaf(cg, ci.y, acc[1]));
-                acc[3] = fmaf(ah, d[3], fmaf(ch, ci.w, acc[3]));
-            }
+            acc[1] = fmaf(ag, d[1], fmaf(cg, ci.y, acc[1]));
+            acc[3] = fmaf(ah, d[3], fmaf(ch, ci.w, acc[3]));
         }
     }
 };
@@ -548,7 +714,7 @@ __device__ __forceinline__ void collect_pieces(uint2* slots, float (&v)[(ELEMS +
 template <int QT, int XC, class Emit>
 __device__ __forceinline__ void consume_share(int t0, int t1, int kt, int chunk_q, int chunk_r, int warp, int lane,
                                               uint32_t ring32, const BarrierSet& bar, float* partial, int stages,
-                                              WalkState& st, uint32_t x32, uint32_t c32, uint32_t live, uint2* slots,
+                                              WalkState& st, uint32_t x32, uint32_t c32, uint2* slots,
                                               int* status, uint32_t abort32, float (&acc)[4], Emit&& emit) {
     using T = Tile<QT>;
     using R = TileRegs<QT>;
@@ -599,10 +765,10 @@ __device__ __forceinline__ void consume_share(int t0, int t1, int kt, int chunk_
         for (; t < seg_end; t += GEMV_WARPS) {  // my tiles below seg_end
             mbar_wait_or_abort(bar.full + st.s * 8, st.lap & 1, abort32);
             R regs;
-            regs.load(my_tile + st.s * STAGE_BYTES, lane);
+            regs.template load<XC>(my_tile + st.s * STAGE_BYTES, lane);
             __syncwarp();
             mbar_arrive_if(bar.empty + st.s * 8, lane_is_0);
-            regs.template compute<XC>(acc, xa, ca, live);
+            regs.template compute<XC>(acc, xa, ca, 1u);
             xa += GEMV_WARPS * T::K * 2;
             ca += GEMV_WARPS * (T::K >> 5) * cinit_block_bytes<XC>();
             st.advance(stages);
@@ -648,13 +814,13 @@ __device__ __forceinline__ uint32_t pack_bf16_trunc(float a, float b) {
 
 // bf16 activations: the copy is verbatim.  Token by token (no index division), four 16-byte loads in
 // flight per thread, one block sum per four consecutive lanes.
-static __device__ void stage_x_bf16(const GemvParams& p, uint8_t* xs, float* cinit, int kp, float beta, int nthreads, bool one_col) {
+static __device__ void stage_x_bf16(const GemvParams& p, uint8_t* xs, float* cinit, int kp, float beta, int nthreads) {
     const int groups = kp >> 3, padded = (groups + 31) & ~31, kgroups = p.k >> 3;
     constexpr int U = 4;
     for (int t = 0; t < p.m; t++) {
         const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.x) + (size_t)t * p.ldx);
         uint8_t* dst = xs + (size_t)t * p.sx;
-        float* col = one_col ? cinit : cinit + (t >> 1) * 4 + (t & 1);  // [block][q][4]: entries (t&1) and (t&1)+2 of quad t>>1
+        float* col = cinit + (t >> 1) * 4 + (t & 1);  // [block][q][4]: entries (t&1) and (t&1)+2 of quad t>>1
         for (int c0 = threadIdx.x; c0 < padded; c0 += nthreads * U) {   // warp-uniform trip counts
             uint4 pre[U];
 #pragma unroll
@@ -680,22 +846,120 @@ static __device__ void stage_x_bf16(const GemvParams& p, uint8_t* xs, float* cin
                 sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
                 if (c8 < groups && (threadIdx.x & 3) == 0) {
                     const float v0 = beta * sum;
-                    if (one_col) {
-                        col[c8 >> 2] = v0;
-                    } else {
-                        col[(c8 >> 2) * 16] = v0;
-                        col[(c8 >> 2) * 16 + 2] = v0;
-                    }
+                    col[(c8 >> 2) * 16] = v0;
+                    col[(c8 >> 2) * 16 + 2] = v0;
                 }
             }
         }
     }
 }
 
-// one_col: write the start values as one float per block (column 0 only) instead of [4] float4
-static __device__ void stage_x(const GemvParams& p, uint8_t* xs, float* cinit, int kp, float beta, int nthreads, bool one_col) {
+// One bf16 token for the integer path (layout and arithmetic: see pair_imma).  Per 32-k block the four
+// threads that hold it find the largest magnitude, whose exponent field e (at least 40, so that every factor
+// below is a normal float) fixes the block's scale: X = trunc(x * 2^(156 - e)) is an integer below 2^30,
+// exact for every element within 2^-22 of the block's largest.  (X + 0x808080) XOR 0x808080 holds, byte by
+// byte, the four signed base-256 digits of X.  A block holding Inf (and no NaN) is staged as signs only with
+// an infinite factor, one holding a NaN with a NaN factor.  recs: 16 bytes per block of records followed by 8
+// bytes per block of activation sums.
+template <int BETA_INT>
+static __device__ void stage_x_q8(const void* x, int k, uint8_t* xd, uint8_t* recs, int kp, int nthreads) {
+    const int groups = kp >> 3, padded = (groups + 31) & ~31, kgroups = k >> 3;
+    const uint4* src = static_cast<const uint4*>(x);
+    uint8_t* sums = recs + (size_t)(kp >> 5) * 16;  // the activation sums follow the records
+    constexpr int U = 3;  // loads in flight per thread
+    for (int c0 = threadIdx.x; c0 < padded; c0 += nthreads * U) {  // warp-uniform trip counts
+        uint4 pre[U];
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const int c8 = c0 + u * nthreads;
+            pre[u] = make_uint4(0u, 0u, 0u, 0u);
+            if (c8 < kgroups) pre[u] = __ldcg(src + c8);
+        }
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const int c8 = c0 + u * nthreads;
+            if ((c8 & ~31) >= padded) break;  // warp-uniform
+            const uint4 v = pre[u];
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+            float f[8];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                f[2 * i] = __uint_as_float(w[i] << 16);
+                f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+            }
+            float sum = ((f[0] + f[1]) + (f[2] + f[3])) + ((f[4] + f[5]) + (f[6] + f[7]));
+            float amax = fmaxf(fmaxf(fmaxf(fabsf(f[0]), fabsf(f[1])), fmaxf(fabsf(f[2]), fabsf(f[3]))),
+                               fmaxf(fmaxf(fabsf(f[4]), fabsf(f[5])), fmaxf(fabsf(f[6]), fabsf(f[7]))));
+            amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+            amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
+            sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
+            sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
+            const int eeff = max((int)(__float_as_uint(amax) >> 23), 40);
+            const bool special = eeff == 0xFF || sum != sum;  // an Inf or a NaN in the block (a NaN makes the sum a NaN)
+            const float scale = __uint_as_float((uint32_t)(283 - eeff) << 23);  // 2^(156 - e)
+            uint32_t z[8];  // per element the four signed digit bytes, least significant digit in byte 0
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                int X = __float2int_rz(f[i] * scale);
+                if (special) X = (fabsf(f[i]) == __uint_as_float(0x7F800000u)) ? (f[i] < 0.f ? -1 : 1) : 0;
+                z[i] = ((uint32_t)X + 0x00808080u) ^ 0x00808080u;
+            }
+            // transpose to digit-major byte quadruples in the element order of the two MMAs: (0, 4, 1, 5) and (2, 6, 3, 7)
+            uint32_t t1[4], t2[4];
+            {
+                const uint32_t P = __byte_perm(z[0], z[4], 0x5140), Q = __byte_perm(z[0], z[4], 0x7362);
+                const uint32_t R = __byte_perm(z[1], z[5], 0x5140), S = __byte_perm(z[1], z[5], 0x7362);
+                t1[0] = __byte_perm(P, R, 0x5410); t1[1] = __byte_perm(P, R, 0x7632);
+                t1[2] = __byte_perm(Q, S, 0x5410); t1[3] = __byte_perm(Q, S, 0x7632);
+            }
+            {
+                const uint32_t P = __byte_perm(z[2], z[6], 0x5140), Q = __byte_perm(z[2], z[6], 0x7362);
+                const uint32_t R = __byte_perm(z[3], z[7], 0x5140), S = __byte_perm(z[3], z[7], 0x7362);
+                t2[0] = __byte_perm(P, R, 0x5410); t2[1] = __byte_perm(P, R, 0x7632);
+                t2[2] = __byte_perm(Q, S, 0x5410); t2[3] = __byte_perm(Q, S, 0x7632);
+            }
+            int dsum[4];
+#pragma unroll
+            for (int t = 0; t < 4; t++) {
+                dsum[t] = BETA_INT == 0 ? 0 : __dp4a((int)t1[t], 0x01010101, __dp4a((int)t2[t], 0x01010101, 0));
+                if (BETA_INT != 0) {
+                    dsum[t] += __shfl_xor_sync(0xFFFFFFFFu, dsum[t], 1);
+                    dsum[t] += __shfl_xor_sync(0xFFFFFFFFu, dsum[t], 2);
+                }
+            }
+            if (c8 < groups) {
+                const int b = c8 >> 2, q = c8 & 3, unit = b >> 2, j = b & 3, pair = j & 1, hcol = j >> 1;
+                uint8_t* base = xd + (size_t)unit * 512 + pair * 8 + q * 16;
+#pragma unroll
+                for (int t = 0; t < 4; t++)  // digit t has weight 256^t; column digit index = 3 - t (most significant first)
+                    *reinterpret_cast<uint2*>(base + (4 * hcol + (3 - t)) * 64) = make_uint2(t1[t], t2[t]);
+                if (q == 0) {
+                    // x = X * 2^(e - 156); the MMA multiplies 8 * code; the lanes of the first digit pair hold
+                    // 256^3 D + 256^2 D' = 2^16 (256 D + D')
+                    float f_hi = __uint_as_float((uint32_t)(eeff - 156 - 3 + 16 + 127) << 23);
+                    float f_lo = __uint_as_float((uint32_t)(eeff - 156 - 3 + 127) << 23);
+                    if (special) {
+                        // a NaN sum: a NaN element, or Infs of both signs (which the CPU's sum of products turns into NaN as well)
+                        const bool nan = sum != sum;
+                        f_hi = nan ? __uint_as_float(0x7FC00000u) : 0.f;
+                        f_lo = nan ? __uint_as_float(0x7FC00000u) : __uint_as_float(0x7F800000u);
+                    }
+                    // block j of the unit is block (j & 1) of lane position h = j >> 1; digit pair p: record at (2 h + p) * 16
+                    uint8_t* rec = recs + (size_t)unit * 64 + (size_t)(j >> 1) * 32 + (size_t)(j & 1) * 8;
+                    *reinterpret_cast<uint2*>(rec) = make_uint2((uint32_t)(BETA_INT * (256 * dsum[3] + dsum[2])), __float_as_uint(f_hi));
+                    *reinterpret_cast<uint2*>(rec + 16) = make_uint2((uint32_t)(BETA_INT * (256 * dsum[1] + dsum[0])), __float_as_uint(f_lo));
+                    float* sp = reinterpret_cast<float*>(sums + (size_t)unit * 32 + (size_t)(j >> 1) * 16 + (size_t)(j & 1) * 4);
+                    sp[0] = sum;
+                    sp[2] = 0.f;
+                }
+            }
+        }
+    }
+}
+
+static __device__ void stage_x(const GemvParams& p, uint8_t* xs, float* cinit, int kp, float beta, int nthreads) {
     if (!p.x_f32) {
-        stage_x_bf16(p, xs, cinit, kp, beta, nthreads, one_col);
+        stage_x_bf16(p, xs, cinit, kp, beta, nthreads);
         return;
     }
     const int groups = kp >> 3;  // 8 elements per thread step
@@ -768,10 +1032,6 @@ static __device__ void stage_x(const GemvParams& p, uint8_t* xs, float* cinit, i
             sum[s] += __shfl_xor_sync(0xFFFFFFFFu, sum[s], 2);
         }
         if (live && (threadIdx.x & 3) == 0) {
-            if (one_col) {
-                cinit[c8 >> 2] = beta * sum[0];
-                continue;
-            }
             float* blk = cinit + (size_t)(c8 >> 2) * 16;  // [q][4]
             const int parts = p.x_f32 ? 3 : 1;
             for (int s = 0; s < parts; s++) {
