@@ -1,7 +1,11 @@
-"""The decode step as one persistent kernel (wf_program_*): its outputs must equal, bit for
-bit, those of the same projections run one kernel at a time (same arithmetic, same work
-split), and both must match the CPU oracle.  A two-rank variant (row-sharded, gather fused
-into the epilogue over peer memory) runs when two GPUs are visible."""
+"""The decode step as one persistent kernel (wf_program_*): its outputs must agree with those of
+the same projections run one kernel at a time and with the CPU oracle.  With several tokens the
+program uses the per-projection work split, so the results are the same bits.  With one token the
+program cuts projections that share their activations (Wq / Wk / Wv, Wgate / Wup) as one list of
+row-tiles, so a row's k-range may be summed in different pieces: the same exact integer block sums,
+a different order of the final fp32 additions -- equal to 1e-5 of the output scale, and the same
+bits from run to run.  A two-rank variant (row-sharded, gather fused into the epilogue over peer
+memory) runs when two GPUs are visible."""
 import os
 import subprocess
 import sys
@@ -15,6 +19,14 @@ from warpforge_b200 import quant as Q
 pytestmark = pytest.mark.gpu
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _same_as_per_op(got, ref, tokens, name):
+    if tokens > 1:
+        assert np.array_equal(got.view(np.uint32), ref.view(np.uint32)), name
+    else:
+        assert np.max(np.abs(got - ref)) <= 1e-5 * np.max(np.abs(ref)), name
+
 
 
 @pytest.mark.parametrize("tokens", [1, 3])
@@ -31,12 +43,15 @@ def test_program_equals_per_op_kernels(oracle, tokens):
         for n, ptr in st.y_dev.items():
             ctx.copy_to_device(ptr, np.zeros_like(ref[n]))
         st.build_program()
-        for _ in range(2):  # twice: the second run starts from the state the first one left
-            st.run_program()
+        st.run_program()
+        ctx.synchronize()
+        first = {n: st.read_output(n) for n, _, _ in st.spec.projections}
+        st.run_program()  # twice: the second run starts from the state the first one left
         ctx.synchronize()  # also reports a bounded wait that ran out
         for name, rows, k in st.spec.projections:
             got = st.read_output(name)
-            assert np.array_equal(got.view(np.uint32), ref[name].view(np.uint32)), name
+            assert np.array_equal(got.view(np.uint32), first[name].view(np.uint32)), name + ": not the same bits from run to run"
+            _same_as_per_op(got, ref[name], tokens, name)
             want = oracle.qlinear(O.Q4_0, st.blocks[name], rows, k, Q.bf16_bits_to_float(st.x_host[k]), nthreads=oracle.max_threads())
             assert np.max(np.abs(got - want)) <= 1e-3 * np.max(np.abs(want))
         st.close()
@@ -47,8 +62,9 @@ def test_program_equals_per_op_kernels(oracle, tokens):
 @pytest.mark.parametrize("qname", ["Q4_0", "Q4_1", "Q8_0", "Q4_K", "Q5_0"])
 @pytest.mark.parametrize("tokens", [1, 5])
 def test_program_every_quantization_type(oracle, qname, tokens):
-    """A small two-layer stack per type: the program's outputs equal the per-projection kernels' bit for bit
-    and the oracle within the matmul tolerance (1 token: the single-column kernel, 5: the eight-column one)."""
+    """A small two-layer stack per type: the program's outputs equal the per-projection kernels' (bit for bit with
+    several tokens) and the oracle within the matmul tolerance (1 token: the integer one-token kernel, 5: the
+    eight-column one)."""
     from warpforge_b200.backend import CudaContext
     from warpforge_b200.decode import ProjectionStack, StackSpec
 
@@ -70,7 +86,7 @@ def test_program_every_quantization_type(oracle, qname, tokens):
         ctx.synchronize()
         for name, rows, k in st.spec.projections:
             got = st.read_output(name)
-            assert np.array_equal(got.view(np.uint32), ref[name].view(np.uint32)), name
+            _same_as_per_op(got, ref[name], tokens, name)
             want = oracle.qlinear(oq, st.blocks[name], rows, k, Q.bf16_bits_to_float(st.x_host[k]), nthreads=oracle.max_threads())
             assert np.max(np.abs(got - want)) <= 1e-3 * np.max(np.abs(want)), name
         st.close()

@@ -27,7 +27,6 @@ namespace wf {
 
 constexpr int PROG_MAX_WORLD = 8;
 constexpr int PROG_BARRIER_SPINS = 1 << 24;
-constexpr int PROG_ONE_TOKEN_STAGES = 4;  // copies in flight per warp of the one-token program kernel
 constexpr int OP_NEW_X = 1;    // stage activations before this op (otherwise it reuses the staged ones)
 constexpr int OP_DEPENDS = 2;  // the activations were produced by earlier ops: grid (and rank) barrier first
 
@@ -62,6 +61,7 @@ struct ProgParams {
     int stages, sx, kp_max;
     int n_barriers;
     unsigned long long* timing;  // optional [ctas][64]: globaltimer at op boundaries of the first ops (salt 2)
+    const int2* shares;          // one-token kernel: [n_ops][ctas] tiles {t0, t1} of every CTA's share of every op
 };
 
 __device__ __forceinline__ unsigned long long ld_acquire_gpu(const unsigned long long* p) {
@@ -190,6 +190,14 @@ struct ProgRun {
     }
 };
 
+// The row-shard gather of the one-token kernel: one output value to every other rank's landing buffer, tagged with
+// the barrier it belongs to.  Out of line: the tile loop stores rows in several places and stays small this way.
+static __device__ __noinline__ void emit_to_peers(uint2* const* ll, int world, int rank, int64_t off, float v, unsigned int tag) {
+    const uint2 word = make_uint2(__float_as_uint(v), tag);
+    for (int r = 0; r < world; r++)
+        if (r != rank) st_slot_sys(ll[r] + off, word);
+}
+
 // This CTA's share of op `o`.
 __device__ __forceinline__ void prog_share(const ProgOp& op, int bx, int& t0, int& t1) {
     ws_cta_share(bx, op.ctas, op.chunk_q, op.chunk_r, op.aligned, op.kt, t0, t1);
@@ -308,45 +316,55 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_program_kernel(const Pro
     run.leave();
 }
 
-// One token.  Shared memory: control | pieces | block records | digits | rings (wf_gemv_stream.cuh); all 512
-// threads are consumers, every warp requests its own copies and runs ahead over the following projections.
+// One token.  Shared memory: control | pieces | share table | block records | digits (wf_gemv_stream.cuh); all 512
+// threads are consumers, every warp loads its own tiles into registers and runs ahead over the following projections.
 template <int QT>
 __global__ void __launch_bounds__(GEMV_CONSUMERS, 1) gemv1_program_kernel(const ProgParams P) {
     using T = Tile<QT>;
     using R = TileRegs<QT>;
-    using G = WsGeom<QT>;
     extern __shared__ __align__(128) uint8_t smem[];
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem);
     WsPiece* pieces = reinterpret_cast<WsPiece*>(smem + WS_CTRL_BYTES);
-    uint8_t* recs = smem + WS_CTRL_BYTES + WS_PIECE_BYTES;
+    WsShare* table = reinterpret_cast<WsShare*>(smem + WS_CTRL_BYTES + WS_PIECE_BYTES);
+    const int n_table = min(P.n_ops, WS_TABLE_OPS);
+    uint8_t* recs = reinterpret_cast<uint8_t*>(table + n_table);
     uint8_t* xd = recs + (size_t)(P.kp_max >> 5) * 32;
-    uint8_t* ring = smem + (((size_t)(xd - smem) + (size_t)P.kp_max * 4 + 64 + 127) & ~(size_t)127);
 
     const int warp = __shfl_sync(0xFFFFFFFFu, (int)(threadIdx.x >> 5), 0);
     const int lane = threadIdx.x & 31;
-    const int bx = blockIdx.x, stages = P.stages;
+    const int bx = blockIdx.x;
     if (threadIdx.x == 0) {
         *abort_flag = 0;
         reinterpret_cast<volatile int*>(smem)[1] = 0;
-        ws_bars_init(smem, stages);
+        ws_bars_init(smem);
     }
-    __syncthreads();
-
-    const WsBars bar = ws_bars(smem, warp);
-    auto share_of = [&](int o) {
+    // this CTA's share of every projection, once, into shared memory: the load requests that run ahead and the
+    // consumers read it from there instead of chasing descriptors in global memory inside the tile loop
+    auto share_from_global = [&](int o) {
         const ProgOp& op = P.ops[o];
         WsShare sh;
         sh.tiles = op.tiles;
-        prog_share(op, bx, sh.t0, sh.t1);
+        const int2 t = P.shares[(size_t)o * gridDim.x + bx];
+        sh.t0 = t.x;
+        sh.t1 = t.y;
+        sh.kt = op.kt;
+        sh.flags = op.flags;
+        sh.pad[0] = sh.pad[1] = 0;
         return sh;
     };
-    WsStream ss;
-    const uint32_t ring_w = smem_u32(ring) + (uint32_t)warp * (uint32_t)stages * G::STAGE_BYTES;
-    // the weights depend on nothing: request the first copies of this warp's stream at once
-    for (int s = 0; s < stages; s++) ws_issue<QT>(ss, share_of, P.n_ops, warp, lane, ring_w, bar.full_w, stages);
+    for (int o = threadIdx.x; o < n_table; o += GEMV_CONSUMERS) table[o] = share_from_global(o);
+    __syncthreads();
+
+    const WsBars bar = ws_bars(smem);
+    auto share_of = [&](int o) { return o < n_table ? table[o] : share_from_global(o); };
+    // the weights depend on nothing: request the first tiles of this warp's stream at once
+    R slots[WsGeom<QT>::DEPTH];
+    WsCursor cur, pf;
+    ws_prime<QT>(slots, cur, pf, share_of, P.n_ops, warp, lane);
 
     ProgRun run{P, reinterpret_cast<volatile int*>(smem) + 1, ld_acquire_gpu(&P.sync->epoch)};
     bool failed = false;
+    uint32_t seq = 0;
     int stamp_i = 0;
     auto stamp = [&]() {
         if (P.timing != nullptr && threadIdx.x == 0 && stamp_i < 64) {
@@ -360,10 +378,13 @@ __global__ void __launch_bounds__(GEMV_CONSUMERS, 1) gemv1_program_kernel(const 
 
     for (int o = 0; o < P.n_ops && !failed; o++) {
         const ProgOp& op = P.ops[o];
-        const int flags = op.flags;
-        const int kt = op.kt;
         const WsShare sh = share_of(o);
-        uint2* slots = P.scratch + (size_t)(o & 1) * gridDim.x * 128;
+        const int flags = sh.flags, kt = sh.kt;
+        // what the row stores need, fetched before the tiles are walked
+        float* const y = op.y;
+        const int rows = op.rows;
+        const int64_t col0 = op.col0;
+        uint2* slots_g = P.scratch + (size_t)(o & 1) * gridDim.x * 128;
 
         stamp();  // op start (4 stamps per op: start, after barrier, after staging, after compute)
         if (flags & OP_NEW_X) {
@@ -380,16 +401,14 @@ __global__ void __launch_bounds__(GEMV_CONSUMERS, 1) gemv1_program_kernel(const 
 
         // y goes to every rank's buffer: the row-shard gather happens here
         auto emit_row = [&](int n, float v) {
-            if (n < op.rows) {
-                const int64_t off = op.col0 + n;
-                op.y[off] = v;
-                const uint2 word = make_uint2(__float_as_uint(v), run.tag());
-                for (int r = 0; r < P.world; r++)
-                    if (r != P.rank) st_slot_sys(op.ll[r] + off, word);
+            if (n < rows) {
+                const int64_t off = col0 + n;
+                y[off] = v;
+                if (P.world > 1) emit_to_peers(op.ll, P.world, P.rank, off, v, run.tag());
             }
         };
-        ws_consume<QT>(sh, kt, op.chunk_q, op.chunk_r, warp, lane, ring_w, bar, pieces, stages, ss, smem_u32(xd), smem_u32(recs),
-                       smem_u32(recs) + (uint32_t)((kt * T::K) >> 5) * 16, slots, P.status, smem_u32(const_cast<int*>(abort_flag)),
+        ws_consume<QT>(sh, op.chunk_q, op.chunk_r, warp, lane, slots, cur, pf, bar, pieces, seq, smem_u32(xd), smem_u32(recs),
+                       smem_u32(recs) + (uint32_t)((kt * T::K) >> 5) * 16, slots_g, P.status, smem_u32(const_cast<int*>(abort_flag)),
                        share_of, P.n_ops, emit_row);
         if (*abort_flag) failed = true;
         stamp();
@@ -397,7 +416,6 @@ __global__ void __launch_bounds__(GEMV_CONSUMERS, 1) gemv1_program_kernel(const 
     if (failed) {
         if (lane == 0) atomicOr(P.status, STATUS_GEMV_FIXUP_TIMEOUT);
         *run.failed = 1;
-        drain_after_abort();
     }
     run.leave();
 }
@@ -410,6 +428,7 @@ struct Program {
     ProgOp* d_ops = nullptr;
     ProgSync* d_sync = nullptr;
     uint2* d_scratch = nullptr;
+    int2* d_shares = nullptr;
     unsigned long long* d_timing = nullptr;
     ProgParams params{};
     size_t smem = 0;
@@ -524,17 +543,54 @@ int wf_program_create(int64_t ctx, int n_ops, const int64_t* weights, const int6
         if (op.flags & OP_DEPENDS) n_barriers++;
         kp_max = std::max(kp_max, op.kt * tile_k(qt));
     }
+    // One token: every CTA's share of every op, as tiles.  Consecutive projections that read the same staged
+    // activations (no new input between them) and have the same K are cut as ONE list of row-tiles: a CTA then has
+    // work in one or two of them instead of a short run in each, and pays the per-projection hand-over once.
+    std::vector<int2> shares;
+    if (m == 1) {
+        shares.assign((size_t)n_ops * grid, make_int2(0, 0));
+        for (int i = 0; i < n_ops;) {
+            int j = i + 1;
+            while (j < n_ops && !(ops[j].flags & OP_NEW_X) && ops[j].kt == ops[i].kt) j++;
+            if (j - i > 1) {
+                int64_t rt_all = 0;
+                for (int k = i; k < j; k++) rt_all += ops[k].rt;
+                const int ctas = (int)std::max<int64_t>(1, std::min<int64_t>(grid, rt_all));
+                const int64_t q = rt_all / ctas, r = rt_all % ctas;
+                for (int cta = 0; cta < ctas; cta++) {
+                    const int64_t u0 = cta * q + std::min<int64_t>(cta, r), u1 = u0 + q + (cta < r ? 1 : 0);
+                    int64_t base = 0;
+                    for (int k = i; k < j; k++) {
+                        const int64_t lo = std::max(u0, base) - base, hi = std::min(u1, base + ops[k].rt) - base;
+                        if (lo < hi) shares[(size_t)k * grid + cta] = make_int2((int)(lo * ops[k].kt), (int)(hi * ops[k].kt));
+                        base += ops[k].rt;
+                    }
+                }
+                for (int k = i; k < j; k++) {  // whole row-tiles: nothing is finished between CTAs
+                    ops[k].ctas = ctas;
+                    ops[k].aligned = 1;
+                    ops[k].chunk_q = ops[k].chunk_r = 0;
+                }
+            } else {
+                for (int cta = 0; cta < grid; cta++) {
+                    int t0, t1;
+                    ws_cta_share(cta, ops[i].ctas, ops[i].chunk_q, ops[i].chunk_r, ops[i].aligned, ops[i].kt, t0, t1);
+                    shares[(size_t)i * grid + cta] = make_int2(t0, t1);
+                }
+            }
+            i = j;
+        }
+    }
     // shared memory: one token -- the streaming layout (wf_gemv_stream.cuh); several -- ctrl + partial + cinit + x + ring
     const int xc = (m == 1) ? 1 : 8;
     size_t fixed, stage;
     int stages, sx = 0;
     if (xc == 1) {
-        int want = PROG_ONE_TOKEN_STAGES;
-        if (const char* e = getenv("WF_PROG_STAGES")) want = std::max(2, std::min(atoi(e), WS_MAX_STAGES));
-        fixed = ws_fixed_smem(kp_max);
-        stage = (size_t)GEMV_WARPS * (tile_bytes(qt) <= 1280 ? 2 : 1) * tile_bytes(qt);
-        stages = ws_stages(qt, kp_max, want);
-        if (stages < 2) return set_error(c, WF_ERR_TOO_LARGE, "K=%d does not fit one SM's shared memory", kp_max);
+        const int table_ops = std::min(n_ops, WS_TABLE_OPS);
+        if (!ws_fits(kp_max, table_ops)) return set_error(c, WF_ERR_TOO_LARGE, "K=%d does not fit one SM's shared memory", kp_max);
+        fixed = ws_smem(kp_max, table_ops);
+        stage = 0;
+        stages = 0;
     } else {
         const int nslot = Slots<8>::N, elems = 16 * xc;
         sx = kp_max * 2 + 64;
@@ -558,6 +614,8 @@ int wf_program_create(int64_t ctx, int n_ops, const int64_t* weights, const int6
     cudaError_t e = cudaMalloc(&pr->d_ops, sizeof(ProgOp) * (size_t)n_ops);
     if (e == cudaSuccess) e = cudaMalloc(&pr->d_sync, sizeof(ProgSync));
     if (e == cudaSuccess) e = cudaMalloc(&pr->d_scratch, (size_t)2 * grid * 128 * sizeof(uint2));
+    if (e == cudaSuccess && !shares.empty()) e = cudaMalloc(&pr->d_shares, shares.size() * sizeof(int2));
+    if (e == cudaSuccess && !shares.empty()) e = cudaMemcpy(pr->d_shares, shares.data(), shares.size() * sizeof(int2), cudaMemcpyHostToDevice);
     if (e == cudaSuccess) e = cudaMemcpy(pr->d_ops, ops.data(), sizeof(ProgOp) * (size_t)n_ops, cudaMemcpyHostToDevice);
     if (e == cudaSuccess) e = cudaMemset(pr->d_sync, 0, sizeof(ProgSync));
     if (e == cudaSuccess) e = cudaMemset(pr->d_scratch, 0, (size_t)2 * grid * 128 * sizeof(uint2));
@@ -565,6 +623,7 @@ int wf_program_create(int64_t ctx, int n_ops, const int64_t* weights, const int6
         cudaFree(pr->d_ops);
         cudaFree(pr->d_sync);
         cudaFree(pr->d_scratch);
+        cudaFree(pr->d_shares);
         delete pr;
         return cuda_status(c, e, "program allocation");
     }
@@ -573,6 +632,7 @@ int wf_program_create(int64_t ctx, int n_ops, const int64_t* weights, const int6
     P.n_ops = n_ops;
     P.m = (int)m;
     P.scratch = pr->d_scratch;
+    P.shares = pr->d_shares;
     P.status = c->d_status;
     P.sync = pr->d_sync;
     P.world = world;
@@ -646,6 +706,7 @@ int wf_program_destroy(int64_t ctx, int64_t program) {
     cudaFree(pr->d_ops);
     cudaFree(pr->d_sync);
     cudaFree(pr->d_scratch);
+    cudaFree(pr->d_shares);
     if (pr->d_timing) cudaFree(pr->d_timing);
     pr->magic = 0;
     delete pr;

@@ -129,24 +129,22 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvParams 
 }
 
 // ---------------------------------------------------------------- one bf16 token
-// Integer MMAs on exact base-256 digits of the activations, every warp streaming its own run of tiles
-// (wf_gemv_stream.cuh).  512 threads, all of them consumers: each warp issues its own bulk copies.
+// Integer MMAs on exact base-256 digits of the activations, every warp streaming its own run of tiles from
+// global memory into registers (wf_gemv_stream.cuh).  512 threads, all of them consumers.
 template <int QT>
 __global__ void __launch_bounds__(GEMV_CONSUMERS, 1) gemv1_kernel(const GemvParams p) {
     using T = Tile<QT>;
     using R = TileRegs<QT>;
-    using G = WsGeom<QT>;
     extern __shared__ __align__(128) uint8_t smem[];
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem);
     WsPiece* pieces = reinterpret_cast<WsPiece*>(smem + WS_CTRL_BYTES);
     uint8_t* recs = smem + WS_CTRL_BYTES + WS_PIECE_BYTES;
     const int kp = p.kt * T::K;
     uint8_t* xd = recs + (size_t)(kp >> 5) * 32;
-    uint8_t* ring = smem + (((size_t)(xd - smem) + (size_t)kp * 4 + 64 + 127) & ~(size_t)127);
 
     const int warp = __shfl_sync(0xFFFFFFFFu, (int)(threadIdx.x >> 5), 0);
     const int lane = threadIdx.x & 31;
-    const int bx = blockIdx.x, stages = p.stages;
+    const int bx = blockIdx.x;
     int t0, t1;
     ws_cta_share(bx, (int)gridDim.x, p.chunk_q, p.chunk_r, p.aligned, p.kt, t0, t1);
     auto stamp = [&](int i) {
@@ -157,19 +155,19 @@ __global__ void __launch_bounds__(GEMV_CONSUMERS, 1) gemv1_kernel(const GemvPara
         }
     };
     // Programmatic stream serialization: see gemv_kernel.  The weights depend on nothing, so every warp
-    // requests the first copies of its run before waiting for the previous grid.
+    // requests the first tiles of its run before waiting for the previous grid.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const WsShare share{p.tiles, t0, t1, p.kt, 0, {0, 0}};
+    auto share_of = [&](int) { return share; };
+    R slots[WsGeom<QT>::DEPTH];
+    WsCursor cur, pf;
+    ws_prime<QT>(slots, cur, pf, share_of, 1, warp, lane);
     if (threadIdx.x == 0) {
         *abort_flag = 0;
-        ws_bars_init(smem, stages);
+        ws_bars_init(smem);
     }
     __syncthreads();
-    const WsBars bar = ws_bars(smem, warp);
-    const WsShare share{p.tiles, t0, t1};
-    auto share_of = [&](int) { return share; };
-    WsStream ss;
-    const uint32_t ring_w = smem_u32(ring) + (uint32_t)warp * (uint32_t)stages * G::STAGE_BYTES;
-    for (int s = 0; s < stages; s++) ws_issue<QT>(ss, share_of, 1, warp, lane, ring_w, bar.full_w, stages);
+    const WsBars bar = ws_bars(smem);
 
     asm volatile("griddepcontrol.wait;" ::: "memory");
     stamp(0);
@@ -180,13 +178,13 @@ __global__ void __launch_bounds__(GEMV_CONSUMERS, 1) gemv1_kernel(const GemvPara
         if (n < p.rows) p.y[p.col0 + n] = v;
     };
     stamp(2);
-    ws_consume<QT>(share, p.kt, p.chunk_q, p.chunk_r, warp, lane, ring_w, bar, pieces, stages, ss, smem_u32(xd), smem_u32(recs),
+    uint32_t seq = 0;
+    ws_consume<QT>(share, p.chunk_q, p.chunk_r, warp, lane, slots, cur, pf, bar, pieces, seq, smem_u32(xd), smem_u32(recs),
                    smem_u32(recs) + (uint32_t)(kp >> 5) * 16, p.scratch, p.status, smem_u32(const_cast<int*>(abort_flag)), share_of, 1,
                    emit_row);
     stamp(4);
     if (*abort_flag) {  // a wait ran out somewhere in this CTA
         if (lane == 0) atomicOr(p.status, STATUS_GEMV_FIXUP_TIMEOUT);
-        drain_after_abort();
     }
     stamp(5);
 }
@@ -201,7 +199,6 @@ static size_t gemv_fixed_smem(int kp, int xcols, int* sx_out) {
 }
 
 constexpr size_t GEMV_SMEM_LIMIT = 227 * 1024;
-constexpr int GEMV_ONE_TOKEN_STAGES = 4;  // copies in flight per warp of the one-token kernel
 
 // Ring depth that fits beside the staged activations (0 = does not fit at all).
 template <int XC>
@@ -219,7 +216,7 @@ int gemv_max_tokens_per_pass(const Weight& w, int x_dtype) {
     int best = 0;
     for (int m = 1; m * per_tok <= GEMV_XCOLS; m++)
         if (gemv_stages<8>(w.g.qtype, kp, m * per_tok) >= 2) best = m;
-    if (best == 0 && per_tok == 1 && ws_stages(w.g.qtype, kp, 2) >= 2) best = 1;  // only the one-token kernel fits
+    if (best == 0 && per_tok == 1 && ws_fits(kp, 0)) best = 1;  // only the one-token kernel fits
     return best;
 }
 
@@ -330,7 +327,7 @@ static int launch_passes(Context* c, const GemvCall& call, cudaStream_t s, uint2
         p.m = (int)((call.m - m0) < per_pass ? (call.m - m0) : per_pass);
         p.x_f32 = call.x_dtype == WF_DTYPE_F32;
         const int xcols = p.x_f32 ? 3 * p.m : p.m;
-        const bool one_token = xcols == 1 && ws_stages(qt, kp, 2) >= 2;
+        const bool one_token = xcols == 1 && ws_fits(kp, 0);
         const int grid = one_token ? one.ctas : grid_several;
         p.chunk_q = one_token ? one.chunk_q : (int)(total / grid);
         p.chunk_r = one_token ? one.chunk_r : (int)(total % grid);
@@ -339,10 +336,7 @@ static int launch_passes(Context* c, const GemvCall& call, cudaStream_t s, uint2
         if (clear_slots) WF_CUDA(c, cudaMemsetAsync(slots, 0, (size_t)grid * 128 * sizeof(uint2), s));
         cudaError_t e;
         if (one_token) {  // one bf16 token: the integer path, every warp streaming its own run
-            const int chunk = tile_bytes(qt) <= 1280 ? 2 : 1;
-            const int my_chunks = (int)((total / grid + GEMV_WARPS) / GEMV_WARPS + chunk - 1) / chunk;
-            p.stages = std::min(ws_stages(qt, kp, GEMV_ONE_TOKEN_STAGES), std::max(my_chunks, 2));
-            e = launch_qt_one_token(qt, p, grid, ws_fixed_smem(kp) + (size_t)p.stages * GEMV_WARPS * chunk * tile_bytes(qt), s);
+            e = launch_qt_one_token(qt, p, grid, ws_smem(kp, 0), s);
         } else {
             p.stages = std::min(gemv_stages<8>(qt, kp, xcols), std::max(max_rounds, 1));
             e = launch_qt<8>(qt, p, grid, gemv_fixed_smem<8>(kp, xcols, &p.sx) + p.stages * stage, s);

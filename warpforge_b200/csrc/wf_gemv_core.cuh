@@ -78,6 +78,28 @@ __device__ __forceinline__ uint32_t lds16(uint32_t a) {
     asm volatile("{\n\t.reg .b16 h;\n\tld.shared.u16 h, [%1];\n\tcvt.u32.u16 %0, h;\n\t}" : "=r"(v) : "r"(a));
     return v;
 }
+// Streaming loads of weight tiles straight from global memory (read-only for the kernel's lifetime, no reuse:
+// not kept in L1).  A warp's 16-byte loads of a plane half cover 512 contiguous bytes.
+__device__ __forceinline__ uint4 ldg128_stream(const uint8_t* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint2 ldg64_stream(const uint8_t* p) {
+    uint2 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint32_t ldg32_stream(const uint8_t* p) {
+    uint32_t v;
+    asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint32_t ldg16_stream(const uint8_t* p) {
+    uint32_t v;
+    asm volatile("{\n\t.reg .b16 h;\n\tld.global.nc.L1::no_allocate.u16 h, [%1];\n\tcvt.u32.u16 %0, h;\n\t}" : "=r"(v) : "l"(p));
+    return v;
+}
 // 16-byte load by the lanes whose `pred` is non-zero; the other lanes keep what `v` held.
 __device__ __forceinline__ void lds128_if(uint4& v, uint32_t a, uint32_t pred) {
     asm volatile(
@@ -250,27 +272,36 @@ constexpr uint32_t CODE8_MASK = 0x78787878u;
 // w01 / w11 = of its second block; bl = digit bytes for the low k-slots (first MMA, second MMA),
 // bh = for the high k-slots.
 __device__ __forceinline__ void pair_imma(int (&d)[4], uint32_t w00, uint32_t w10, uint32_t w01, uint32_t w11,
-                                          uint32_t bl1, uint32_t bl2, uint32_t bh1, uint32_t bh2) {
+                                          uint32_t bl1, uint32_t bl2, uint32_t bh1, uint32_t bh2, uint32_t mul28) {
+    // The rotation by four bits for the second MMA goes through the multiplier (w * 2^28 as a 64-bit product:
+    // low word w << 28, high word w >> 4) and one three-input logic op ((lo | hi) & mask), which leaves two
+    // instead of three instructions per word on the half-rate integer pipe.  mul28 = 2^28, kept in a register the
+    // compiler cannot see through (a constant factor would be turned back into shifts).
     asm(
         "{\n\t"
-        ".reg .b32 a0, a1, a2, a3, r0, r1, r2, r3;\n\t"
+        ".reg .b32 a0, a1, a2, a3, l0, l1, l2, l3, h0, h1, h2, h3;\n\t"
+        ".reg .b64 p0, p1, p2, p3;\n\t"
         "and.b32 a0, %4, %12;\n\t"
         "and.b32 a1, %5, %12;\n\t"
         "and.b32 a2, %6, %12;\n\t"
         "and.b32 a3, %7, %12;\n\t"
+        "mul.wide.u32 p0, %4, %13;\n\t"
+        "mul.wide.u32 p1, %5, %13;\n\t"
+        "mul.wide.u32 p2, %6, %13;\n\t"
+        "mul.wide.u32 p3, %7, %13;\n\t"
         "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {a0,a1,a2,a3}, {%8,%10}, {%0,%1,%2,%3};\n\t"
-        "shf.r.wrap.b32 r0, %4, %4, 4;\n\t"
-        "shf.r.wrap.b32 r1, %5, %5, 4;\n\t"
-        "shf.r.wrap.b32 r2, %6, %6, 4;\n\t"
-        "shf.r.wrap.b32 r3, %7, %7, 4;\n\t"
-        "and.b32 a0, r0, %12;\n\t"
-        "and.b32 a1, r1, %12;\n\t"
-        "and.b32 a2, r2, %12;\n\t"
-        "and.b32 a3, r3, %12;\n\t"
+        "mov.b64 {l0, h0}, p0;\n\t"
+        "mov.b64 {l1, h1}, p1;\n\t"
+        "mov.b64 {l2, h2}, p2;\n\t"
+        "mov.b64 {l3, h3}, p3;\n\t"
+        "lop3.b32 a0, l0, h0, %12, 0xA8;\n\t"
+        "lop3.b32 a1, l1, h1, %12, 0xA8;\n\t"
+        "lop3.b32 a2, l2, h2, %12, 0xA8;\n\t"
+        "lop3.b32 a3, l3, h3, %12, 0xA8;\n\t"
         "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {a0,a1,a2,a3}, {%9,%11}, {%0,%1,%2,%3};\n\t"
         "}\n"
         : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
-        : "r"(w00), "r"(w10), "r"(w01), "r"(w11), "r"(bl1), "r"(bl2), "r"(bh1), "r"(bh2), "r"(CODE8_MASK));
+        : "r"(w00), "r"(w10), "r"(w01), "r"(w11), "r"(bl1), "r"(bl2), "r"(bh1), "r"(bh2), "r"(CODE8_MASK), "r"(mul28));
 }
 
 // Lane-specific shared addresses of the staged token for the tile at hand.
@@ -283,6 +314,7 @@ struct Q8Addr {
 // lanes 16..31; the other half of each stays zero from construction on.
 struct Q8Digits {
     uint4 lo = make_uint4(0u, 0u, 0u, 0u), hi = make_uint4(0u, 0u, 0u, 0u);
+    uint32_t mul28 = 0x10000000u | (gridDim.y >> 16);  // 2^28 (a grid has fewer than 2^16 CTAs in y), opaque to the compiler
     __device__ __forceinline__ void load(uint32_t a, uint32_t is_lo) {
         lds128_if(lo, a, is_lo);
         lds128_if(hi, a, is_lo ^ 1u);
@@ -324,14 +356,22 @@ template <> struct TileRegs<WF_QTYPE_Q4_0> {
             s = lds128(sb);
         }
     }
+    // one token: the tile straight from global memory into registers
+    __device__ __forceinline__ void load_global(const uint8_t* tile, int lane) {
+        c[0] = ldg128_stream(tile + lane * 16);
+        c[1] = ldg128_stream(tile + 512 + lane * 16);
+        const uint8_t* sb = tile + Tile<WF_QTYPE_Q4_0>::SCALE_OFF + (lane >> 2) * 16 + (lane & 2) * 2;
+        sg2 = ldg32_stream(sb);
+        sh2 = ldg32_stream(sb + 8);
+    }
     // One token: lane (g, q) adds its share of rows g (acc[0]) and g+8 (acc[2]); the four lanes of a quad
     // hold different digit pairs / blocks of the same rows and are summed when the row-tile is flushed.
     __device__ __forceinline__ void compute_q8(float (&acc)[4], const Q8Addr& a, Q8Digits& dg, uint32_t is_lo) const {
         dg.load(a.x, is_lo);
         const uint4 r = lds128(a.rec);  // {W, f, W', f'}: the odd digit's accumulator starts at the offset correction
         int da[4] = {0, (int)r.x, 0, (int)r.x}, db[4] = {0, (int)r.z, 0, (int)r.z};
-        pair_imma(da, c[0].x, c[1].x, c[0].z, c[1].z, dg.lo.x, dg.lo.y, dg.hi.x, dg.hi.y);
-        pair_imma(db, c[0].y, c[1].y, c[0].w, c[1].w, dg.lo.z, dg.lo.w, dg.hi.z, dg.hi.w);
+        pair_imma(da, c[0].x, c[1].x, c[0].z, c[1].z, dg.lo.x, dg.lo.y, dg.hi.x, dg.hi.y, dg.mul28);
+        pair_imma(db, c[0].y, c[1].y, c[0].w, c[1].w, dg.lo.z, dg.lo.w, dg.hi.z, dg.hi.w, dg.mul28);
         const float2 sg = half2_bits_to_float2(sg2), sh = half2_bits_to_float2(sh2);
         const float ea = __uint_as_float(r.y), eb = __uint_as_float(r.w);
         acc[0] = fmaf(sg.x * ea, digits_to_float(da[0], da[1]), acc[0]);
@@ -383,6 +423,17 @@ template <> struct TileRegs<WF_QTYPE_Q4_1> {
             mn = lds128(mb);
         }
     }
+    // one token: the tile straight from global memory into registers
+    __device__ __forceinline__ void load_global(const uint8_t* tile, int lane) {
+        using T = Tile<WF_QTYPE_Q4_1>;
+        c[0] = ldg128_stream(tile + lane * 16);
+        c[1] = ldg128_stream(tile + 512 + lane * 16);
+        const int so = (lane >> 2) * 16 + (lane & 2) * 2;
+        sg2 = ldg32_stream(tile + T::SCALE_OFF + so);
+        sh2 = ldg32_stream(tile + T::SCALE_OFF + so + 8);
+        mg2 = ldg32_stream(tile + T::MIN_OFF + so);
+        mh2 = ldg32_stream(tile + T::MIN_OFF + so + 8);
+    }
     // One token: 8 * code enters the MMA as is (no offset); the min term is min * (sum of the block's
     // activations), which only the lanes of the first digit pair carry (the others read zeros).
     __device__ __forceinline__ void compute_q8(float (&acc)[4], const Q8Addr& a, Q8Digits& dg, uint32_t is_lo) const {
@@ -390,8 +441,8 @@ template <> struct TileRegs<WF_QTYPE_Q4_1> {
         const uint4 r = lds128(a.rec);
         const uint2 sx = lds64(a.sx);
         int da[4] = {0, 0, 0, 0}, db[4] = {0, 0, 0, 0};
-        pair_imma(da, c[0].x, c[1].x, c[0].z, c[1].z, dg.lo.x, dg.lo.y, dg.hi.x, dg.hi.y);
-        pair_imma(db, c[0].y, c[1].y, c[0].w, c[1].w, dg.lo.z, dg.lo.w, dg.hi.z, dg.hi.w);
+        pair_imma(da, c[0].x, c[1].x, c[0].z, c[1].z, dg.lo.x, dg.lo.y, dg.hi.x, dg.hi.y, dg.mul28);
+        pair_imma(db, c[0].y, c[1].y, c[0].w, c[1].w, dg.lo.z, dg.lo.w, dg.hi.z, dg.hi.w, dg.mul28);
         const float2 sg = half2_bits_to_float2(sg2), sh = half2_bits_to_float2(sh2);
         const float2 mg = half2_bits_to_float2(mg2), mh = half2_bits_to_float2(mh2);
         const float ea = __uint_as_float(r.y), eb = __uint_as_float(r.w);
@@ -442,15 +493,23 @@ template <> struct TileRegs<WF_QTYPE_Q8_0> {
             s = lds128(sb);
         }
     }
+    // one token: the tile straight from global memory into registers
+    __device__ __forceinline__ void load_global(const uint8_t* tile, int lane) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) c[i] = ldg128_stream(tile + i * 512 + lane * 16);
+        const uint8_t* sb = tile + Tile<WF_QTYPE_Q8_0>::SCALE_OFF + (lane >> 2) * 16 + (lane & 2) * 2;
+        sg2 = ldg32_stream(sb);
+        sh2 = ldg32_stream(sb + 8);
+    }
     // One token: value = 16 (hi - 8) + lo; the two planes accumulate separately and combine as integers.
     __device__ __forceinline__ void compute_q8(float (&acc)[4], const Q8Addr& a, Q8Digits& dg, uint32_t is_lo) const {
         dg.load(a.x, is_lo);
         const uint4 r = lds128(a.rec);
         int la[4] = {0, 0, 0, 0}, lb[4] = {0, 0, 0, 0}, ha[4] = {0, 0, 0, 0}, hb[4] = {0, 0, 0, 0};
-        pair_imma(ha, c[0].x, c[1].x, c[0].z, c[1].z, dg.lo.x, dg.lo.y, dg.hi.x, dg.hi.y);
-        pair_imma(la, c[2].x, c[3].x, c[2].z, c[3].z, dg.lo.x, dg.lo.y, dg.hi.x, dg.hi.y);
-        pair_imma(hb, c[0].y, c[1].y, c[0].w, c[1].w, dg.lo.z, dg.lo.w, dg.hi.z, dg.hi.w);
-        pair_imma(lb, c[2].y, c[3].y, c[2].w, c[3].w, dg.lo.z, dg.lo.w, dg.hi.z, dg.hi.w);
+        pair_imma(ha, c[0].x, c[1].x, c[0].z, c[1].z, dg.lo.x, dg.lo.y, dg.hi.x, dg.hi.y, dg.mul28);
+        pair_imma(la, c[2].x, c[3].x, c[2].z, c[3].z, dg.lo.x, dg.lo.y, dg.hi.x, dg.hi.y, dg.mul28);
+        pair_imma(hb, c[0].y, c[1].y, c[0].w, c[1].w, dg.lo.z, dg.lo.w, dg.hi.z, dg.hi.w, dg.mul28);
+        pair_imma(lb, c[2].y, c[3].y, c[2].w, c[3].w, dg.lo.z, dg.lo.w, dg.hi.z, dg.hi.w, dg.mul28);
         const float2 sg = half2_bits_to_float2(sg2), sh = half2_bits_to_float2(sh2);
         const float ea = __uint_as_float(r.y), eb = __uint_as_float(r.w);
         const int wa = (int)r.x, wb = (int)r.z;
@@ -514,6 +573,21 @@ template <> struct TileRegs<WF_QTYPE_Q4_K> {
             mn = lds128(base + T::MN_OFF + (lane >> 2) * 16);
         }
     }
+    // one token: the tile straight from global memory into registers
+    __device__ __forceinline__ void load_global(const uint8_t* tile, int lane) {
+        using T = Tile<WF_QTYPE_Q4_K>;
+#pragma unroll
+        for (int i = 0; i < 4; i++) c[i] = ldg128_stream(tile + i * 512 + lane * 16);
+        dd = ldg64_stream(tile + T::D_OFF + (lane >> 2) * 8);
+        const int so = (lane >> 2) * 16 + (lane & 2);  // row g: bytes 2h, 2h+1; +4: sub-blocks 4+2h, 5+2h; +8: row g+8
+#pragma unroll
+        for (int u = 0; u < 2; u++) {
+            scg[u] = ldg16_stream(tile + T::SC_OFF + so + 4 * u);
+            sch[u] = ldg16_stream(tile + T::SC_OFF + so + 8 + 4 * u);
+            mng[u] = ldg16_stream(tile + T::MN_OFF + so + 4 * u);
+            mnh[u] = ldg16_stream(tile + T::MN_OFF + so + 8 + 4 * u);
+        }
+    }
     // One token: the tile is two units of 128 k (sub-blocks 0..3 and 4..7).  8 * code enters the MMA as is;
     // the min term is (dmin * m) * (sum of the sub-block's activations), carried by the lanes of the first digit pair.
     __device__ __forceinline__ void compute_q8(float (&acc)[4], const Q8Addr& a, Q8Digits& dg, uint32_t is_lo) const {
@@ -526,8 +600,8 @@ template <> struct TileRegs<WF_QTYPE_Q4_K> {
             const uint4 r = lds128(a.rec + u * 64);
             const uint2 sx = lds64(a.sx + u * 32);
             int da[4] = {0, 0, 0, 0}, db[4] = {0, 0, 0, 0};
-            pair_imma(da, c[2 * u].x, c[2 * u + 1].x, c[2 * u].z, c[2 * u + 1].z, dg.lo.x, dg.lo.y, dg.hi.x, dg.hi.y);
-            pair_imma(db, c[2 * u].y, c[2 * u + 1].y, c[2 * u].w, c[2 * u + 1].w, dg.lo.z, dg.lo.w, dg.hi.z, dg.hi.w);
+            pair_imma(da, c[2 * u].x, c[2 * u + 1].x, c[2 * u].z, c[2 * u + 1].z, dg.lo.x, dg.lo.y, dg.hi.x, dg.hi.y, dg.mul28);
+            pair_imma(db, c[2 * u].y, c[2 * u + 1].y, c[2 * u].w, c[2 * u + 1].w, dg.lo.z, dg.lo.w, dg.hi.z, dg.hi.w, dg.mul28);
             const uint32_t wsg = scg[u], wsh = sch[u], wmg = mng[u], wmh = mnh[u];
             const float ea = __uint_as_float(r.y), eb = __uint_as_float(r.w);
             const float xa = __uint_as_float(sx.x), xb = __uint_as_float(sx.y);
@@ -862,7 +936,7 @@ static __device__ void stage_x_bf16(const GemvParams& p, uint8_t* xs, float* cin
 // an infinite factor, one holding a NaN with a NaN factor.  recs: 16 bytes per block of records followed by 8
 // bytes per block of activation sums.
 template <int BETA_INT>
-static __device__ void stage_x_q8(const void* x, int k, uint8_t* xd, uint8_t* recs, int kp, int nthreads) {
+static __device__ __noinline__ void stage_x_q8(const void* x, int k, uint8_t* xd, uint8_t* recs, int kp, int nthreads) {
     const int groups = kp >> 3, padded = (groups + 31) & ~31, kgroups = k >> 3;
     const uint4* src = static_cast<const uint4*>(x);
     uint8_t* sums = recs + (size_t)(kp >> 5) * 16;  // the activation sums follow the records

@@ -1,27 +1,30 @@
-// One-token decode GEMV: every warp streams its own run of tiles.
+// One-token decode GEMV: every warp streams its own run of tiles, from global memory straight into registers.
 //
-// A CTA's share of a weight (a contiguous range of tiles, row-tile major / k-tile minor, the same
-// "stream-K" cut as the several-token kernel) is cut once more into sixteen contiguous runs, one per warp.
-// A warp copies its run into a ring of its own with bulk asynchronous copies it issues itself (one or two
-// tiles per copy, a few copies in flight), waits on its own mbarriers and keeps the sums of the row-tile it
-// is walking in registers, so inside a run nothing is exchanged between warps: no per-tile release, no
-// parking of partial sums per row-tile.  The copies of a warp run ahead over the following weights of a
-// multi-op program as far as its ring is deep, so HBM keeps streaming across grid barriers.
+// A CTA's share of a weight (a contiguous range of tiles, row-tile major / k-tile minor) is cut once more into
+// sixteen contiguous runs, one per warp.  The tile layout is already in MMA fragment order -- the sixteen bytes
+// a lane needs of a plane half are contiguous and a warp's load covers 512 contiguous bytes -- so a warp loads
+// its tiles with plain 16-byte global loads into registers, a few tiles ahead of the one it is multiplying
+// (software pipeline over DEPTH register sets).  The weights never pass through shared memory, whose bandwidth
+// is left to the activation digits; measured on a ring-of-bulk-copies form of this kernel, tile loads and
+// copy writes alone took 19 of the 24 shared-memory cycles a tile cost, more than the integer pipe.
+// The load requests of a warp run ahead over the following weights of a multi-op program (the first tiles of
+// the next projection are in flight while the grid barrier and the activation staging run).
 //
-// Where a run starts or ends inside a row-tile the warp writes the piece (sixteen sums) to shared memory;
-// once per weight the warps meet on an mbarrier and the first holder of every cut row-tile adds the pieces
-// in warp order.  A row-tile cut by the CTA's share boundary is then finished between CTAs exactly as in
-// the several-token kernel (publish / collect through tagged scratch slots, bounded waits).
+// Inside a run nothing is exchanged between warps: the sums of the row-tile being walked stay in registers.
+// Where a run starts or ends inside a row-tile the warp writes the piece (sixteen sums) to shared memory; once
+// per weight the warps meet on an mbarrier and the first holder of every cut row-tile adds the pieces in warp
+// order.  A row-tile cut by the CTA's share boundary is then finished between CTAs exactly as in the
+// several-token kernel (publish / collect through tagged scratch slots, bounded waits).
 #pragma once
 #include "wf_gemv_core.cuh"
 
 namespace wf {
 
-constexpr int WS_MAX_STAGES = 8;  // copies in flight per warp, at most
-constexpr int WS_SLOTS = 4;       // hand-over generations (weights) whose pieces may be alive at once
-// control block: abort word | full[GEMV_WARPS][WS_MAX_STAGES] | done[WS_SLOTS] | vacant[WS_SLOTS]
-constexpr int WS_CTRL_BYTES = 1280;
-static_assert(128 + (GEMV_WARPS * WS_MAX_STAGES + 2 * WS_SLOTS) * 8 <= WS_CTRL_BYTES, "control block");
+constexpr int WS_SLOTS = 4;         // hand-over generations (weights) whose pieces may be alive at once
+constexpr int WS_TABLE_OPS = 256;   // weights of a program whose shares are kept in shared memory
+// control block: abort word | failure latch | done[WS_SLOTS] | vacant[WS_SLOTS]
+constexpr int WS_CTRL_BYTES = 256;
+static_assert(128 + 2 * WS_SLOTS * 8 <= WS_CTRL_BYTES, "control block");
 
 struct WsPiece {  // the sums of one cut row-tile as far as one warp's run covers it
     float v[16];
@@ -29,22 +32,16 @@ struct WsPiece {  // the sums of one cut row-tile as far as one warp's run cover
 constexpr int WS_PIECE_BYTES = WS_SLOTS * GEMV_WARPS * 2 * (int)sizeof(WsPiece);
 
 template <int QT> struct WsGeom {
-    static constexpr int CHUNK = Tile<QT>::BYTES <= 1280 ? 2 : 1;  // tiles per bulk copy
-    static constexpr uint32_t STAGE_BYTES = CHUNK * Tile<QT>::BYTES;
+    static constexpr int DEPTH = Tile<QT>::BYTES <= 1280 ? 4 : 2;  // tiles a warp holds in registers
 };
 
 // Shared memory of the one-token kernels:
-//   control | pieces | block records and sums (32 bytes per 32 k) | digits (4 bytes per k) | rings [warp][stage]
-inline size_t ws_fixed_smem(int kp) {
-    size_t b = WS_CTRL_BYTES + WS_PIECE_BYTES + (size_t)(kp / 32) * 32 + (size_t)kp * 4 + 64;
+//   control | pieces | share table (32 bytes per weight) | block records and sums (32 bytes per 32 k) | digits (4 bytes per k)
+inline size_t ws_smem(int kp, int table_ops) {
+    size_t b = WS_CTRL_BYTES + WS_PIECE_BYTES + (size_t)table_ops * 32 + (size_t)(kp / 32) * 32 + (size_t)kp * 4 + 64;
     return (b + 127) & ~(size_t)127;
 }
-inline int ws_stages(int qt, int kp, int want) {
-    const size_t fixed = ws_fixed_smem(kp), limit = 227 * 1024;
-    const size_t stage = (size_t)GEMV_WARPS * (tile_bytes(qt) <= 1280 ? 2 : 1) * tile_bytes(qt);
-    if (fixed + 2 * stage > limit) return 0;
-    return (int)std::min<size_t>((limit - fixed) / stage, (size_t)std::min(want, WS_MAX_STAGES));
-}
+inline bool ws_fits(int kp, int table_ops) { return ws_smem(kp, table_ops) <= 227 * 1024; }
 
 // How a weight of rt row-tiles x kt k-tiles is cut over the CTAs.  Stream-K (equal numbers of tiles, row-tiles
 // cut wherever a share ends) balances perfectly, but every cut row-tile is finished between two CTAs through
@@ -85,19 +82,12 @@ WF_HD void ws_cta_share(int bx, int ctas, int chunk_q, int chunk_r, int aligned,
     t1 = aligned ? u1 * kt : u1;
 }
 
-struct WsShare {  // a CTA's share of one weight
+struct WsShare {  // a CTA's share of one weight (32 bytes: the entry of the share table)
     const uint8_t* tiles;
-    int t0, t1;
-};
-
-struct WsStream {       // one warp's ring position; carries over from weight to weight
-    int p_op = -1;      // producer: weight whose tiles are being requested
-    int p_t = 0, p_end = 0;
-    const uint8_t* p_tiles = nullptr;
-    int p_stage = 0;
-    int c_stage = 0;    // consumer
-    uint32_t c_lap = 0;
-    uint32_t seq = 0;   // weights handed over so far
+    int t0, t1;  // tiles
+    int kt;
+    int flags;
+    int pad[2];
 };
 
 // This warp's run [a, b) of the share [t0, t1).
@@ -107,76 +97,103 @@ __device__ __forceinline__ void ws_run(int t0, int t1, int warp, int& a, int& b)
     b = a + q + (warp < r ? 1 : 0);
 }
 
-// Request the next copy of this warp's stream into the stage the producer side points at (which the caller
-// knows to be free).  All lanes keep the position; lane 0 issues.  Returns without a copy once the program is
-// exhausted.
+// Where this warp's load requests stand in the program.  A warp's stream is the sequence of its runs, weight after
+// weight, cut into groups of DEPTH tiles that never straddle two weights.
+struct WsCursor {
+    int op = -1;
+    int t = 0, end = 0;
+    const uint8_t* tiles = nullptr;
+};
+// The next group to request: address of its first tile and its number of tiles (0 once the program is exhausted).
 template <int QT, class ShareFn>
-__device__ __forceinline__ void ws_issue(WsStream& ss, ShareFn& share_of, int n_ops, int warp, int lane, uint32_t ring_w,
-                                         uint32_t full_w, int stages) {
-    using G = WsGeom<QT>;
-    while (ss.p_t >= ss.p_end) {
-        if (ss.p_op + 1 >= n_ops) {
-            ss.p_op = n_ops;
+__device__ __forceinline__ void ws_next_group(WsCursor& c, ShareFn& share_of, int n_ops, int warp, const uint8_t*& base, int& cnt) {
+    while (c.t >= c.end) {
+        if (c.op + 1 >= n_ops) {
+            c.op = n_ops;
+            base = nullptr;
+            cnt = 0;
             return;
         }
-        ss.p_op++;
-        const WsShare sh = share_of(ss.p_op);
-        ws_run(sh.t0, sh.t1, warp, ss.p_t, ss.p_end);
-        ss.p_tiles = sh.tiles;
+        c.op++;
+        const WsShare sh = share_of(c.op);
+        ws_run(sh.t0, sh.t1, warp, c.t, c.end);
+        c.tiles = sh.tiles;
     }
-    const int cnt = min(G::CHUNK, ss.p_end - ss.p_t);
-    if (lane == 0) {
-        const uint32_t bytes = (uint32_t)cnt * Tile<QT>::BYTES, bar = full_w + ss.p_stage * 8;
-        mbar_expect_tx(bar, bytes);
-        bulk_load(ring_w + ss.p_stage * G::STAGE_BYTES, ss.p_tiles + (size_t)ss.p_t * Tile<QT>::BYTES, bytes, bar);
-    }
-    ss.p_t += cnt;
-    ss.p_stage = ss.p_stage + 1 == stages ? 0 : ss.p_stage + 1;
+    cnt = min(WsGeom<QT>::DEPTH, c.end - c.t);
+    base = c.tiles + (size_t)c.t * Tile<QT>::BYTES;
+    c.t += cnt;
+}
+// The register pipeline is only a group deep (and the loads of a group are requested one by one as its slots
+// free up), which covers the latency of L2 but not of HBM.  A second cursor therefore runs WS_PREFETCH_GROUPS
+// groups ahead of the loads and asks for each group to be brought into L2 with one bulk prefetch (a group is
+// contiguous: at most DEPTH tiles of one weight).
+#ifndef WF_WS_PREFETCH_GROUPS
+#define WF_WS_PREFETCH_GROUPS 0
+#endif
+constexpr int WS_PREFETCH_GROUPS = WF_WS_PREFETCH_GROUPS;
+__device__ __forceinline__ void ws_prefetch_l2(const uint8_t* p, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+template <int QT, class ShareFn>
+__device__ __forceinline__ void ws_prefetch_group(WsCursor& pf, ShareFn& share_of, int n_ops, int warp, int lane) {
+    const uint8_t* base;
+    int cnt;
+    ws_next_group<QT>(pf, share_of, n_ops, warp, base, cnt);
+    if (cnt > 0 && lane == 0) ws_prefetch_l2(base, (uint32_t)cnt * Tile<QT>::BYTES);
+}
+// Request the first group of the stream and the prefetches ahead of it (the weights depend on nothing, so this
+// comes before any wait).
+template <int QT, class ShareFn>
+__device__ __forceinline__ void ws_prime(TileRegs<QT> (&slots)[WsGeom<QT>::DEPTH], WsCursor& c, WsCursor& pf, ShareFn& share_of,
+                                         int n_ops, int warp, int lane) {
+    const uint8_t* base;
+    int cnt;
+    ws_next_group<QT>(c, share_of, n_ops, warp, base, cnt);
+#pragma unroll
+    for (int j = 0; j < WsGeom<QT>::DEPTH; j++)
+        if (j < cnt) slots[j].load_global(base + (size_t)j * Tile<QT>::BYTES, lane);
+    pf = c;
+    for (int i = 0; i < WS_PREFETCH_GROUPS; i++) ws_prefetch_group<QT>(pf, share_of, n_ops, warp, lane);
 }
 
 struct WsBars {  // 32-bit shared addresses
-    uint32_t full_w;  // this warp's full[stage]
-    uint32_t done, vacant;
+    uint32_t done, vacant;  // [WS_SLOTS]: every warp has written its pieces / is through with the weight
 };
-__device__ __forceinline__ WsBars ws_bars(uint8_t* smem, int warp) {
+__device__ __forceinline__ WsBars ws_bars(uint8_t* smem) {
     WsBars b;
-    b.full_w = smem_u32(smem + 128) + warp * WS_MAX_STAGES * 8;
-    b.done = smem_u32(smem + 128) + GEMV_WARPS * WS_MAX_STAGES * 8;
+    b.done = smem_u32(smem + 128);
     b.vacant = b.done + WS_SLOTS * 8;
     return b;
 }
-__device__ __forceinline__ void ws_bars_init(uint8_t* smem, int stages) {
-    const uint32_t full = smem_u32(smem + 128);
-    for (int w = 0; w < GEMV_WARPS; w++)
-        for (int s = 0; s < stages; s++) mbar_init(full + (w * WS_MAX_STAGES + s) * 8, 1);
-    const uint32_t done = full + GEMV_WARPS * WS_MAX_STAGES * 8;
-    for (int s = 0; s < WS_SLOTS; s++) {
-        mbar_init(done + s * 8, GEMV_WARPS);
-        mbar_init(done + (WS_SLOTS + s) * 8, GEMV_WARPS);
-    }
+__device__ __forceinline__ void ws_bars_init(uint8_t* smem) {
+    const uint32_t done = smem_u32(smem + 128);
+    for (int s = 0; s < 2 * WS_SLOTS; s++) mbar_init(done + s * 8, GEMV_WARPS);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
 
 // One weight, one warp: walk the run, hand the cut pieces over, finish the row-tiles this warp is first to hold.
+//   slots: the register sets holding the first group of this run (requested earlier); cur / pf: the load and the
+//   prefetch cursor;
 //   x32 / c32 / s32: shared addresses of the staged digits, the block records and the activation sums;
 //   emit_row(n, value): store output row n of this weight (called by one lane per row);
-//   share_of(o): the CTA's share of weight o of the program (the producer side runs ahead of `op`).
+//   share_of(o): the CTA's share of weight o of the program.
 template <int QT, class EmitRow, class ShareFn>
-__device__ __forceinline__ void ws_consume(const WsShare& sh, int kt, int chunk_q, int chunk_r, int warp, int lane,
-                                           uint32_t ring_w, const WsBars& bar, WsPiece* pieces, int stages, WsStream& ss,
-                                           uint32_t x32, uint32_t c32, uint32_t s32, uint2* slots, int* status,
-                                           uint32_t abort32, ShareFn& share_of, int n_ops, EmitRow&& emit_row) {
+__device__ __forceinline__ void ws_consume(const WsShare& sh, int chunk_q, int chunk_r, int warp, int lane,
+                                           TileRegs<QT> (&slots)[WsGeom<QT>::DEPTH], WsCursor& cur, WsCursor& pf, const WsBars& bar,
+                                           WsPiece* pieces, uint32_t& seq, uint32_t x32, uint32_t c32, uint32_t s32,
+                                           uint2* slots_g, int* status, uint32_t abort32, ShareFn& share_of, int n_ops,
+                                           EmitRow&& emit_row) {
     using T = Tile<QT>;
-    using R = TileRegs<QT>;
-    using G = WsGeom<QT>;
+    constexpr int DEPTH = WsGeom<QT>::DEPTH;
     constexpr uint32_t XSTEP = T::K * 4, RSTEP = (T::K >> 5) * 16, SSTEP = (T::K >> 5) * 8;  // staged bytes per tile
-    const int g = lane >> 2, q = lane & 3;
+    const int g = lane >> 2, q = lane & 3, kt = sh.kt;
     const uint32_t lane_is_0 = lane == 0;
     int a, b;
     ws_run(sh.t0, sh.t1, warp, a, b);
+    const int len = b - a;
 
-    const int slot = (int)(ss.seq % WS_SLOTS);
-    const uint32_t gen = ss.seq / WS_SLOTS;
+    const int slot = (int)(seq % WS_SLOTS);
+    const uint32_t gen = seq / WS_SLOTS;
     WsPiece* mine = pieces + ((size_t)slot * GEMV_WARPS + warp) * 2;
     // the pieces of the weight that used this slot last must have been read by everybody
     if (gen > 0) mbar_wait_or_abort(bar.vacant + slot * 8, (gen - 1) & 1, abort32);
@@ -184,8 +201,16 @@ __device__ __forceinline__ void ws_consume(const WsShare& sh, int kt, int chunk_
     // pieces this warp writes: row-tile and whether this warp is the first of the CTA to hold it
     int npieces = 0, rtag0 = 0, rtag1 = 0;
     bool first0 = false, first1 = false;
-    if (a < b) {
-        int rt = a / kt, kk = a - rt * kt;
+    if (len > 0) {
+        int rt = __float2int_rz(__fdividef((float)a, (float)kt)), kk = a - rt * kt;  // a / kt without the integer division
+        while (kk < 0) {  // the float quotient is off by one at most for tile counts below 2^24; loops cover the rest
+            rt--;
+            kk += kt;
+        }
+        while (kk >= kt) {
+            rt++;
+            kk -= kt;
+        }
         bool starts_here = kk == 0;  // the row-tile being walked began inside this run
         const uint32_t is_lo = lane < 16 ? 1u : 0u;  // this lane feeds the low k-slots of the MMAs
         const uint32_t x0 = x32 + lane * 16, rec0 = c32 + q * 16, sx0 = s32 + q * 8;
@@ -226,20 +251,17 @@ __device__ __forceinline__ void ws_consume(const WsShare& sh, int kt, int chunk_
             acc[0] = acc[2] = 0.f;
         };
 
-        for (int t = a; t < b;) {
-            const int cnt = min(G::CHUNK, b - t);
-            mbar_wait_or_abort(bar.full_w + ss.c_stage * 8, ss.c_lap & 1, abort32);
-            const uint32_t stage32 = ring_w + ss.c_stage * G::STAGE_BYTES + lane * 16;
+        for (int g0 = 0; g0 < len; g0 += DEPTH) {
+            // the group after this one in the warp's stream (maybe of a later weight): requested slot by slot as
+            // the slots of this group are used up
+            const uint8_t* nbase;
+            int ncnt;
+            ws_next_group<QT>(cur, share_of, n_ops, warp, nbase, ncnt);
+            ws_prefetch_group<QT>(pf, share_of, n_ops, warp, lane);
 #pragma unroll
-            for (int i = 0; i < G::CHUNK; i++) {
-                if (i < cnt) {
-                    R regs;
-                    regs.template load<1>(stage32 + i * T::BYTES, lane);
-                    if (i == cnt - 1) {  // the stage is free once its last tile sits in registers: request the next copy into it
-                        __syncwarp();
-                        ws_issue<QT>(ss, share_of, n_ops, warp, lane, ring_w, bar.full_w, stages);
-                    }
-                    regs.compute_q8(acc, qa, dg, is_lo);
+            for (int j = 0; j < DEPTH; j++) {
+                if (g0 + j < len) {
+                    slots[j].compute_q8(acc, qa, dg, is_lo);
                     if (++kk == kt) {
                         flush(true);
                         kk = 0;
@@ -254,11 +276,7 @@ __device__ __forceinline__ void ws_consume(const WsShare& sh, int kt, int chunk_
                         qa.sx += SSTEP;
                     }
                 }
-            }
-            t += cnt;
-            if (++ss.c_stage == stages) {
-                ss.c_stage = 0;
-                ss.c_lap++;
+                if (j < ncnt) slots[j].load_global(nbase + (size_t)j * T::BYTES, lane);
             }
         }
         if (kk != 0) flush(false);
@@ -275,26 +293,31 @@ __device__ __forceinline__ void ws_consume(const WsShare& sh, int kt, int chunk_
             if (!(pi == 0 ? first0 : first1)) continue;  // an earlier warp holds this row-tile first
             const int r = pi == 0 ? rtag0 : rtag1;
             const int row_end = min((r + 1) * kt, sh.t1);
-            float v[1];
-            v[0] = lane < 16 ? mine[pi].v[lane] : 0.f;
-            // the following warps whose runs begin inside the row-tile hold its next pieces, each as its first piece
-            for (int w2 = warp + 1; w2 < GEMV_WARPS; w2++) {
-                const int a2 = sh.t0 + w2 * rq + min(w2, rr);
-                if (a2 >= row_end || (w2 >= rr && rq == 0)) break;  // beyond the row-tile, or a warp without tiles
-                if (lane < 16) v[0] += all[w2 * 2].v[lane];
+            // the following warps whose runs begin inside the row-tile hold its next pieces, each as its first piece:
+            // all loads first (they do not depend on each other), then the additions in warp order
+            float pc[GEMV_WARPS];
+            const int li = lane & 15;
+#pragma unroll
+            for (int d = 1; d < GEMV_WARPS; d++) {
+                const int w2 = warp + d, a2 = sh.t0 + w2 * rq + min(w2, rr);
+                pc[d] = (w2 < GEMV_WARPS && a2 < row_end) ? all[w2 * 2].v[li] : 0.f;
             }
+            float v[1];
+            v[0] = mine[pi].v[li];
+#pragma unroll
+            for (int d = 1; d < GEMV_WARPS; d++) v[0] += pc[d];
             const bool starts = r * kt >= sh.t0, ends = (r + 1) * kt <= sh.t1;
             if (!starts) {
-                publish_piece<16>(slots + (size_t)blockIdx.x * 128, v, lane, status);
+                publish_piece<16>(slots_g + (size_t)blockIdx.x * 128, v, lane, status);
             } else {
-                if (!ends) collect_pieces<16>(slots, v, lane, (r + 1) * kt, chunk_q, chunk_r, status);
+                if (!ends) collect_pieces<16>(slots_g, v, lane, (r + 1) * kt, chunk_q, chunk_r, status);
                 if (lane < 16) emit_row(r * 16 + lane, v[0]);
             }
         }
     }
     __syncwarp();
     mbar_arrive_if(bar.vacant + slot * 8, lane_is_0);
-    ss.seq++;
+    seq++;
 }
 
 }  // namespace wf
