@@ -41,10 +41,20 @@ WORKLOAD = ("benchmark config 4: 7B-shape Llama decode, 224 Q4_0 projections (32
             "{4x[4096x4096], 2x[11008x4096], [4096x11008]}), batch 1, bf16 activations, fp32 out")
 
 
-# DRAM traffic of the decode kernels, from an ncu capture of two layers of this workload
-# (dram__bytes_read.sum + dram__bytes_write.sum = 231.63 MB for 2 layers);
-# traffic grows in proportion to the layers run and splits evenly over row shards.
-NCU_TRAFFIC_BYTES_PER_LAYER = 231.63e6 / 2
+# DRAM traffic of the decode kernel, from the ncu capture summarised in profiles/gemv_program_q4_0_decode_7b.md
+# (dram__bytes_read.sum + dram__bytes_write.sum of one launch over two layers of this workload);
+# traffic grows in proportion to the layers run and splits evenly over row shards.  To be re-captured whenever the
+# kernel changes.
+NCU_TRAFFIC_BYTES_PER_LAYER = 232.6e6 / 2
+
+
+def tensor_peaks():
+    """(burst, sustained) dense bf16 TFLOP/s."""
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return float(p["bf16_tflops"]), float(p.get("bf16_tflops_sustained", p["bf16_tflops"])), "measured (MEASURED_PEAKS.json, cuBLAS bf16)"
+    return 1590.0, 1400.0, "fallback (no MEASURED_PEAKS.json)"
 
 
 def measured_peaks():
@@ -52,7 +62,7 @@ def measured_peaks():
     if os.path.exists(path):
         p = json.load(open(path))
         return float(p["hbm_gbs"]), "measured (MEASURED_PEAKS.json, stream copy)"
-    return 6650.0, "fallback (earlier measurement on this pool)"
+    return 6650.0, "fallback (no MEASURED_PEAKS.json)"
 
 
 class ClockSampler:
@@ -137,8 +147,11 @@ def run_reference(args) -> None:
     t_layer = float(np.mean(times))
     tok_s = 1.0 / (t_layer * spec.layers)
     sample = f"1 of {spec.layers} layers per step (7 projections, 114 MB of Q4_0 blocks), x{spec.layers} for a token"
+    # ms_per_step is what a step really took (the one-layer sample), so that steps x ms_per_step is this run's wall time;
+    # `value` is the token rate that follows for the 32 identical layers
     line = {"impl": "reference", "metric": METRIC, "value": tok_s, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": t_layer * spec.layers * 1e3, "higher_is_better": True, "scaling": "strong",
+            "warmup": args.warmup, "ms_per_step": t_layer * 1e3, "ms_per_token_extrapolated": t_layer * spec.layers * 1e3,
+            "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": WORKLOAD, "timed": sample},
             "cpu_baseline": {"value": tok_s, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
@@ -192,6 +205,157 @@ def gemv_sweep(ctx, hbm_peak: float) -> list:
     return out
 
 
+def parity_stats(orc, want, got) -> dict:
+    """The three error measures of the path: the reference's elementwise rule (count of failures), the largest
+    error against the largest output, and against each output floored at 1 % of the output RMS."""
+    d = np.abs(got.astype(np.float64) - want.astype(np.float64))
+    rms = float(np.sqrt(np.mean(want.astype(np.float64) ** 2)))
+    return {"elements": int(want.size),
+            "rule_failures": int(orc.count_not_close(want, got, 1e-4, 1e-3)),
+            "max_rel": float(np.max(d) / max(float(np.max(np.abs(want))), 1e-30)),
+            "max_rel_floored": float(np.max(d / np.maximum(np.abs(want), max(0.01 * rms, 1e-30))))}
+
+
+def step_parity(stack, rank: int, world: int, dist) -> dict:
+    """After a step every rank holds all rows of every projection: compare the gathered outputs of a [4096]-wide and
+    an [11008]-wide projection with the CPU oracle on rows sampled from EVERY rank's row range."""
+    from oracle import oracle as O
+    from warpforge_b200 import quant as Q
+
+    orc = O.COracle()
+    spec = stack.spec
+    per_rank = max(8, 64 // world)
+    out = {"checked": True, "rows_sampled_per_output": per_rank * world, "outputs": [], "max_rel": 0.0, "rule_failures": 0,
+           "elements": 0}
+    for name in ("wq", "wgate"):
+        rows, k = next((r, kk) for n, r, kk in spec.projections if n == name)
+        got = stack.read_output(name)
+        rng = np.random.default_rng(1000 + rows)
+        shard = rows // world
+        sample = np.sort(np.concatenate([r * shard + rng.choice(shard, per_rank, replace=False) for r in range(world)]))
+        want = orc.qlinear_rows(O.Q4_0, stack.blocks[name], k, Q.bf16_bits_to_float(stack.x_host[k]), sample, nthreads=orc.max_threads())
+        st = parity_stats(orc, want, got[:, sample])
+        out["outputs"].append(name)
+        out["max_rel"] = max(out["max_rel"], st["max_rel"])
+        out["rule_failures"] += st["rule_failures"]
+        out["elements"] += st["elements"]
+    if dist is not None:
+        import torch
+
+        t = torch.tensor([out["max_rel"], float(out["rule_failures"])], dtype=torch.float64)
+        mx = t.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        sm = t.clone()
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        out["max_rel"], out["rule_failures"] = float(mx[0]), int(sm[1])
+        out["elements"] *= world
+        out["ranks_checked"] = world
+    out["ok"] = bool(out["max_rel"] <= 1e-3)
+    return out
+
+
+def gemm_leg(ctx) -> dict:
+    """benchmark config 3: Q4_K prefill GEMM, M=512, N=14336, K=4096, bf16 activations, fp32 out.  Events around 64
+    calls over 8 rotating weight copies (264 MB of tiles, twice L2); the activation pre-pass is part of every call."""
+    from oracle import oracle as O
+    from warpforge_b200 import _native as N, quant as Q
+    from warpforge_b200.backend import QuantizedWeight
+
+    rows, k, m, copies, calls = 14336, 4096, 512, 8, 64
+    lib, qt = ctx._lib, Q.QuantizationType.Q4_K
+    blocks = Q.synth_q4_k(rows, k, Q.config_seed(3))
+    xb = Q.synth_activation_bf16(m, k, Q.config_seed(3))
+    ws = [QuantizedWeight(ctx, qt, blocks, rows, k) for _ in range(copies)]
+    dx, dy = ctx.allocate(xb.nbytes), ctx.allocate(m * rows * 4)
+    ctx.copy_to_device(dx, xb)
+    for i in range(copies):
+        ctx._ck("wf_qlinear", lib.wf_qlinear(ctx.handle, ws[i].handle, dx, N.WF_DTYPE_BF16, 1, m, dy, 1, 0))
+    ctx.synchronize()
+    e0, e1 = ctx.create_event(), ctx.create_event()
+    best = float("inf")
+    for _ in range(3):
+        ctx.record_event(e0)
+        for i in range(calls):
+            ctx._ck("wf_qlinear", lib.wf_qlinear(ctx.handle, ws[i % copies].handle, dx, N.WF_DTYPE_BF16, 1, m, dy, 1, 0))
+        ctx.record_event(e1)
+        ctx.synchronize()
+        best = min(best, ctx.elapsed_ms(e0, e1) / calls)
+    got = np.empty((m, rows), np.float32)
+    ctx.copy_to_host(got, dy)
+    orc = O.COracle()
+    rng = np.random.default_rng(3)
+    sample = np.sort(np.concatenate([b * 128 + rng.choice(128, 1) for b in range(rows // 128)]))
+    want = orc.qlinear_rows(O.Q4_K, blocks, k, Q.bf16_bits_to_float(xb), sample, nthreads=orc.max_threads())
+    par = parity_stats(orc, want, got[:, sample])
+    burst, sustained, src = tensor_peaks()
+    tf = 2.0 * m * rows * k / (best * 1e-3) / 1e12
+    for w in ws:
+        w.close()
+    ctx.free(dx)
+    ctx.free(dy)
+    return {"workload": "benchmark config 3: Q4_K [14336x4096] x 512 bf16 tokens, fp32 out", "us": round(best * 1e3, 2),
+            "TFLOP/s": round(tf, 1), "frac_of_measured_burst": round(tf / burst, 4), "frac_of_measured_sustained": round(tf / sustained, 4),
+            "peak_burst_tflops": burst, "peak_sustained_tflops": sustained, "peak_source": src,
+            "timed": f"{calls} calls over {copies} weight copies, activation pre-pass included, best of 3",
+            "parity": dict(par, rows_sampled=int(sample.size), note="one weight row per 128-row block, all 512 tokens; the GEMM rounds each "
+                           "dequantized weight once to fp16, so the elementwise rule is reported, not required")}
+
+
+def q8_0_leg(ctx, hbm_peak: float) -> dict:
+    """benchmark config 1: one Q8_0 linear [4096x4096], fp32 activations [1x4096], fp32 out."""
+    from oracle import oracle as O
+    from warpforge_b200 import _native as N, quant as Q
+    from warpforge_b200.backend import QuantizedWeight
+
+    rows, k, copies, iters = 4096, 4096, 12, 120
+    lib, qt = ctx._lib, Q.QuantizationType.Q8_0
+    blocks = Q.synth_q8_0(rows, k, Q.config_seed(1))
+    x = Q.synth_activation_f32(1, k, Q.config_seed(1))
+    ws = [QuantizedWeight(ctx, qt, blocks, rows, k) for _ in range(copies)]
+    dx, dy = ctx.allocate(x.nbytes), ctx.allocate(rows * 4)
+    ctx.copy_to_device(dx, x)
+    for i in range(copies):
+        ctx._ck("wf_qlinear", lib.wf_qlinear(ctx.handle, ws[i].handle, dx, N.WF_DTYPE_F32, 1, 1, dy, 1, 0))
+    ctx.synchronize()
+    ctx.graph_begin()
+    for i in range(iters):
+        ctx._ck("wf_qlinear", lib.wf_qlinear(ctx.handle, ws[i % copies].handle, dx, N.WF_DTYPE_F32, 1, 1, dy, 1, 0))
+    g = ctx.graph_end()
+    e0, e1 = ctx.create_event(), ctx.create_event()
+    ctx.graph_launch(g)
+    ctx.synchronize()
+    best = float("inf")
+    for _ in range(3):
+        ctx.record_event(e0)
+        ctx.graph_launch(g)
+        ctx.record_event(e1)
+        ctx.synchronize()
+        best = min(best, ctx.elapsed_ms(e0, e1) / iters)
+    got = np.empty((1, rows), np.float32)
+    ctx.copy_to_host(got, dy)
+    orc = O.COracle()
+    par = parity_stats(orc, orc.qlinear(O.Q8_0, blocks, rows, k, x, nthreads=orc.max_threads()), got)
+    alg = rows * qt.row_bytes(k) + x.nbytes + rows * 4
+    gbs = alg / best / 1e6
+    ctx.graph_destroy(g)
+    for w in ws:
+        w.close()
+    ctx.free(dx)
+    ctx.free(dy)
+    return {"workload": "benchmark config 1: Q8_0 [4096x4096], fp32 activations [1x4096]", "us": round(best * 1e3, 3), "GB/s": round(gbs, 1),
+            "frac_of_measured_peak": round(gbs / hbm_peak, 4), "timed": f"{iters} calls over {copies} weight copies in one CUDA graph, best of 3",
+            "parity": par}
+
+
+def config5_legs(ctx) -> list:
+    """One rank's shard of benchmark config 5 (70B-shape, Q4_K, 8 row shards) on this GPU: batch-16 decode and
+    2048-token prefill, three layers of distinct shard weights resident."""
+    from warpforge_b200 import bench_config5
+
+    return bench_config5.run(world=8, layers=3, iters=3, ctx=ctx)
+
+
+
 def run_ours(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -242,6 +406,15 @@ def run_ours(args) -> None:
 
     for _ in range(max(args.warmup, 3)):
         stack.step()
+    barrier()
+    # every rank's gathered outputs against the CPU oracle, before anything is timed
+    parity = None
+    if not args.kernel_only and stack.layers == spec.layers or os.environ.get("WF_BENCH_PARITY"):
+        parity = step_parity(stack, 0 if replicas else rank, 1 if replicas else world, None if replicas else dist)
+        if not parity["ok"]:
+            if rank == 0:
+                print(json.dumps({"metric": METRIC, "error": "parity check failed", "parity": parity}), flush=True)
+            raise SystemExit(3)
     barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -304,12 +477,13 @@ def run_ours(args) -> None:
                        "l2": "inputs larger than L2: 3.64 GB of distinct weights per step", "bytes_per_token": spec.bytes_per_token()},
             "e2e": {"value": 1e3 / (e2e_ms / args.steps) * (world if replicas else 1), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": int(y_out.nbytes)},
             "gpu_launches": int(launches),
+            "parity": parity,
             "clocks": clocks,
-            "roofline": {"bound": "hbm", "kernel": ("gemv_program_kernel" if mode in ("program", "replicas") else "gemv_kernel") + "<Q4_0, 1 column>", "achieved": gbs, "peak": hbm_peak, "unit": "GB/s",
+            "roofline": {"bound": "hbm", "kernel": ("gemv1_program_kernel" if mode in ("program", "replicas") else "gemv1_kernel") + "<Q4_0> (one token)", "achieved": gbs, "peak": hbm_peak, "unit": "GB/s",
                          "frac": gbs / hbm_peak, "frac_of_8TBs_nominal": gbs / 8000.0, "peak_source": peak_src,
                          "bytes_per_launch": alg_bytes / n_launch, "us_per_launch": ms_step * 1e3 / n_launch,
                          "traffic": NCU_TRAFFIC_BYTES_PER_LAYER * stack.layers / (1 if replicas else world) / n_launch,
-                         "traffic_source": "ncu dram bytes of a 2-layer capture, scaled by layers (and 1 / ranks)"},
+                         "traffic_source": "ncu dram bytes of a 2-layer capture (profiles/gemv_program_q4_0_decode_7b.md), scaled by layers (and 1 / ranks)"},
         }
         if stack.layers != spec.layers:
             line["partial"] = f"{stack.layers} of {spec.layers} layers: a profiling run, not a bench value"
@@ -327,6 +501,10 @@ def run_ours(args) -> None:
             t_layer = cpu_layer_time(orc, spec, threads, 2)
             line["cpu_baseline"] = {"value": 1.0 / (t_layer * spec.layers), "unit": UNIT, "cores": threads, "kind": "port",
                                     "sample": f"1 of {spec.layers} layers (7 projections), best of 2, x{spec.layers}"}
+            # the other configurations of the path, each a leg of its own (not part of `value`)
+            line["gemm"] = gemm_leg(ctx)
+            line["q8_0_config1"] = q8_0_leg(ctx, hbm_peak)
+            line["config5_rank_shard"] = config5_legs(ctx)
         print(json.dumps(line), flush=True)
     stack.close()
     if comm is not None:

@@ -167,6 +167,57 @@ def test_peer_wait_runs_out_and_is_reported(oracle):
         ctx.close()
 
 
+def test_absent_rank_ends_a_long_program_within_one_timeout():
+    """The failure is latched: after the first wait for the absent rank's rows has run out, the remaining
+    projections of the program neither poll landing buffers nor spin at grid barriers, so an 8-projection
+    program ends about as fast as a 2-projection one (not one timeout per projection)."""
+    import ctypes
+    import time
+
+    from warpforge_b200 import _native as N
+    from warpforge_b200.backend import CudaContext, QuantizedWeight
+
+    ctx = CudaContext(0)
+    lib = ctx._lib
+    try:
+        rows, k, world, n_ops = 256, 256, 2, 8
+        qt = Q.QuantizationType.Q4_0
+        blocks = Q.synth_q4_0(rows, k, 33)
+        xb = Q.synth_activation_bf16(1, k, 33)
+        dx = ctx.allocate(xb.nbytes)
+        ctx.copy_to_device(dx, xb)
+        ws = [QuantizedWeight(ctx, qt, blocks, rows, k, 0, world) for _ in range(n_ops)]
+        ys = [ctx.allocate(rows * 4) for _ in range(n_ops)]
+        landing = []
+        for _ in range(n_ops * world):
+            p = ctx.allocate(rows * 8)
+            ctx.copy_to_device(p, np.zeros(rows * 8, np.uint8))
+            landing.append(p)
+        arr = lambda v, t: (t * len(v))(*v)
+        flags = [N.WF_OP_NEW_X] + [N.WF_OP_NEW_X | N.WF_OP_DEPENDS] * (n_ops - 1)
+
+        def timed(n):
+            prog = ctypes.c_int64()
+            N.check("create", lib.wf_program_create(
+                ctx.handle, n, arr([w.handle for w in ws[:n]], ctypes.c_int64), arr([dx] * n, ctypes.c_int64),
+                arr(ys[:n], ctypes.c_int64), arr(flags[:n], ctypes.c_int), 1, world, 0, arr(landing[:n * world], ctypes.c_int64),
+                ctypes.byref(prog)), ctx.handle)
+            t = time.perf_counter()
+            N.check("run", lib.wf_program_run(ctx.handle, prog.value, 0), ctx.handle)
+            with pytest.raises(N.WfError) as err:
+                ctx.synchronize()
+            dt = time.perf_counter() - t
+            assert err.value.status == N.WF_ERR_DEVICE_WAIT
+            N.check("destroy", lib.wf_program_destroy(ctx.handle, prog.value), ctx.handle)
+            return dt
+
+        t2, t8 = timed(2), timed(n_ops)
+        assert t8 <= 2.0 * t2 + 0.5, f"8 projections took {t8:.2f} s, 2 took {t2:.2f} s"
+        assert t8 < 20.0
+    finally:
+        ctx.close()
+
+
 _TWO_RANK = r"""
 import os, sys
 sys.path.insert(0, %r)

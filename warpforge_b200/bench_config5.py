@@ -38,17 +38,21 @@ def peaks():
     return 6650.0, 1590.0, "fallback"
 
 
-def main() -> None:
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--world", type=int, default=8)
-    ap.add_argument("--layers", type=int, default=5, help="distinct layers resident (the step is extrapolated to 80)")
-    ap.add_argument("--iters", type=int, default=3)
-    a = ap.parse_args()
+def run(world: int = 8, layers: int = 5, iters: int = 3, ctx: CudaContext | None = None, legs=(("decode_batch16", 16), ("prefill_2048", 2048))) -> list:
+    """Times the legs and returns one dict per leg (rank 0; the other ranks return an empty list)."""
+    class A:
+        pass
+
+    a = A()
+    a.world, a.layers, a.iters = world, layers, iters
     spec = LLAMA_70B_Q4_K
     rank, nranks = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     gather = nranks > 1
     dist = comm = None
-    ctx = CudaContext(int(os.environ.get("LOCAL_RANK", "0")))
+    own_ctx = ctx is None
+    if own_ctx:
+        ctx = CudaContext(int(os.environ.get("LOCAL_RANK", "0")))
+    results = []
     if gather:
         import torch.distributed as dist  # control plane only: id exchange, barrier, max over ranks
 
@@ -84,7 +88,7 @@ def main() -> None:
     rmax = max(r // a.world for _, r, _ in spec.projections)
     hbm, tf, src = peaks()
     e0, e1 = ctx.create_event(), ctx.create_event()
-    for leg, m in (("decode_batch16", 16), ("prefill_2048", 2048)):
+    for leg, m in legs:
         x = Q.synth_activation_bf16(m, kmax, 5)
         dx = ctx.allocate(x.nbytes)
         ctx.copy_to_device(dx, x)
@@ -129,7 +133,7 @@ def main() -> None:
         if gather:
             out["execution"] = f"{nranks} ranks, NCCL all-gather after every projection, max over ranks"
         if rank == 0:
-            print(json.dumps(out), flush=True)
+            results.append(out)
         ctx.free(dx)
         ctx.free(dy)
     for row in weights:
@@ -137,10 +141,22 @@ def main() -> None:
             w.close()
     if comm is not None:
         comm.close()
-    ctx.close()
+    if own_ctx:
+        ctx.close()
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
+    return results
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--world", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=5, help="distinct layers resident (the step is extrapolated to 80)")
+    ap.add_argument("--iters", type=int, default=3)
+    a = ap.parse_args()
+    for out in run(a.world, a.layers, a.iters):
+        print(json.dumps(out), flush=True)
 
 
 if __name__ == "__main__":

@@ -73,8 +73,7 @@ struct Context {
     void* d_x16 = nullptr;  // fp16 copy of the activations for the tensor-core GEMM
     int64_t x16_bytes = 0;
     float* d_gemm_partial = nullptr;       // [sm_count][512][128] pieces of tiles cut by a share boundary
-    unsigned int* d_gemm_ready = nullptr;  // [sm_count][4] launch number whose piece is complete, per 32-row quarter
-    unsigned int gemm_launches = 0;
+    unsigned int* d_gemm_ready = nullptr;  // [sm_count][4] generation whose piece is complete, per 32-row quarter; then {generation, CTAs out}
     int64_t launches = 0;
     bool glue_exact = false;  // silu / softmax evaluate exp as the host does (double, one rounding) instead of expf
     int gemv_ctas_per_sm[3] = {0, 0, 0};

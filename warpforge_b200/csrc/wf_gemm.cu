@@ -85,8 +85,9 @@ struct GemmParams {
     // stream-K: the (tile, k-block) units form one sequence, CTA b owns units [b*q + min(b,r), ...)
     int unit_q, unit_r;
     float* partial;        // [ctas][GEMM_PIECE_TOKENS][128] fp32: a CTA's piece of a tile that begins in an earlier CTA
-    unsigned int* ready;   // [ctas][4] launch number whose piece (per 32-row quarter) is complete in `partial`
-    unsigned int launch;   // this launch's number (never 0)
+    unsigned int* ready;   // [ctas][4] generation whose piece (per 32-row quarter) is complete in `partial`
+    unsigned int* gen;     // [0] generations completed so far, [1] CTAs that have left the current launch: the kernel
+                           // numbers its own launches, so a launch recorded in a CUDA graph is a new generation on every replay
 };
 
 // One CTA's share of the unit sequence, cut into segments: a segment is a run of k-blocks of one tile.
@@ -602,6 +603,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmParams 
     uint64_t* acc_empty = acc_full + 2;                          // [2]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    // this launch's generation: the previous GEMM of the stream has ended before this kernel starts (the activation
+    // pre-pass between them is an ordinary launch), so its closing store is visible
+    unsigned int launch_gen = ld_acquire_u32(p.gen) + 1u;
+    if (launch_gen == 0u) launch_gen = 1u;  // 0 is what untouched flags hold
     const bool wide = p.halves == 2, k64 = wide;  // 64-k stages go with the two-half token tiles (alone they measured 25 % slower)
     const uint32_t a_bytes = k64 ? GEMM_WIDE_A_BYTES : GEMM_A_BYTES;
     const uint32_t b_bytes = wide ? 2u * GEMM_WIDE_B_HALF : (uint32_t)p.bm * 256;
@@ -783,7 +788,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmParams 
             if (!starts) {  // publish this warp's 32 rows of the piece
                 __threadfence();
                 __syncwarp();
-                if (lane == 0) st_release_u32(p.ready + blockIdx.x * 4 + quarter, p.launch);
+                if (lane == 0) st_release_u32(p.ready + blockIdx.x * 4 + quarter, launch_gen);
             }
             u += g.kb1 - g.kb0;
         }
@@ -896,7 +901,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmParams 
                 if (c0 == c1) continue;
                 last_cta = c;
                 int spins = 0;
-                while (ld_acquire_u32(p.ready + c * 4 + quarter) != p.launch && ++spins < GEMM_WAIT_SPINS) __nanosleep(64);
+                while (ld_acquire_u32(p.ready + c * 4 + quarter) != launch_gen && ++spins < GEMM_WAIT_SPINS) __nanosleep(64);
                 if (spins >= GEMM_WAIT_SPINS) ok = false;
             }
             if (!ok && lane == 0) fail();
@@ -931,6 +936,14 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmParams 
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, 512);
+    }
+    if (threadIdx.x == 0) {  // the last CTA out closes the generation
+        __threadfence();
+        if (atomicAdd(p.gen + 1, 1u) == gridDim.x - 1) {
+            p.gen[1] = 0u;
+            __threadfence();
+            st_release_u32(p.gen, launch_gen);
+        }
     }
 }
 
@@ -1062,13 +1075,12 @@ int gemm_launch(Context* c, const GemvCall& call, cudaStream_t s) {
     p.unit_r = (int)(units % grid);
     if (!c->d_gemm_partial) {
         WF_CUDA(c, cudaMalloc(&c->d_gemm_partial, (size_t)c->sm_count * GEMM_PIECE_TOKENS * GEMM_BN * sizeof(float)));
-        WF_CUDA(c, cudaMalloc(&c->d_gemm_ready, (size_t)c->sm_count * 4 * sizeof(unsigned int)));
-        WF_CUDA(c, cudaMemset(c->d_gemm_ready, 0, (size_t)c->sm_count * 4 * sizeof(unsigned int)));
+        WF_CUDA(c, cudaMalloc(&c->d_gemm_ready, ((size_t)c->sm_count * 4 + 2) * sizeof(unsigned int)));
+        WF_CUDA(c, cudaMemset(c->d_gemm_ready, 0, ((size_t)c->sm_count * 4 + 2) * sizeof(unsigned int)));
     }
     p.partial = c->d_gemm_partial;
     p.ready = c->d_gemm_ready;
-    if (++c->gemm_launches == 0) c->gemm_launches = 1;  // 0 means "nothing published"
-    p.launch = c->gemm_launches;
+    p.gen = c->d_gemm_ready + (size_t)c->sm_count * 4;
     const size_t smem = 1024 + (size_t)p.stages * stage_bytes;
     cudaError_t e = qt == WF_QTYPE_Q4_0   ? gemm_launch_one<WF_QTYPE_Q4_0>(p, map, grid, smem, s)
                     : qt == WF_QTYPE_Q4_1 ? gemm_launch_one<WF_QTYPE_Q4_1>(p, map, grid, smem, s)
