@@ -160,12 +160,13 @@ __global__ void __launch_bounds__(GEMV_CONSUMERS, 1) gemv1_kernel(const GemvPara
     const WsShare share{p.tiles, t0, t1, p.kt, 0, {0, 0}};
     auto share_of = [&](int) { return share; };
     R slots[WsGeom<QT>::DEPTH];
-    WsCursor cur, pf;
-    ws_prime<QT>(slots, cur, pf, share_of, 1, warp, lane);
+    WsCursor cur;
+    ws_prime<QT>(slots, cur, share_of, 1, warp, lane);
     if (threadIdx.x == 0) {
         *abort_flag = 0;
         ws_bars_init(smem);
     }
+    ws_clear_digits(xd, kp, GEMV_CONSUMERS);
     __syncthreads();
     const WsBars bar = ws_bars(smem);
 
@@ -179,7 +180,7 @@ __global__ void __launch_bounds__(GEMV_CONSUMERS, 1) gemv1_kernel(const GemvPara
     };
     stamp(2);
     uint32_t seq = 0;
-    ws_consume<QT>(share, p.chunk_q, p.chunk_r, warp, lane, slots, cur, pf, bar, pieces, seq, smem_u32(xd), smem_u32(recs),
+    ws_consume<QT>(share, p.chunk_q, p.chunk_r, warp, lane, slots, cur, bar, pieces, seq, smem_u32(xd), smem_u32(recs),
                    smem_u32(recs) + (uint32_t)(kp >> 5) * 16, p.scratch, p.status, smem_u32(const_cast<int*>(abort_flag)), share_of, 1,
                    emit_row);
     stamp(4);

@@ -80,24 +80,30 @@ __device__ __forceinline__ uint32_t lds16(uint32_t a) {
 }
 // Streaming loads of weight tiles straight from global memory (read-only for the kernel's lifetime, no reuse:
 // not kept in L1).  A warp's 16-byte loads of a plane half cover 512 contiguous bytes.
-__device__ __forceinline__ uint4 ldg128_stream(const uint8_t* p) {
+// The byte offset OFF is an immediate of the load: several loads off one lane pointer cost no address arithmetic.
+template <int OFF> __device__ __forceinline__ uint4 ldg128_stream(const uint8_t* p) {
     uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4+%5];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p), "n"(OFF));
     return v;
 }
-__device__ __forceinline__ uint2 ldg64_stream(const uint8_t* p) {
+template <int OFF> __device__ __forceinline__ uint2 ldg64_stream(const uint8_t* p) {
     uint2 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2+%3];" : "=r"(v.x), "=r"(v.y) : "l"(p), "n"(OFF));
     return v;
 }
-__device__ __forceinline__ uint32_t ldg32_stream(const uint8_t* p) {
+template <int OFF> __device__ __forceinline__ uint32_t ldg32_stream(const uint8_t* p) {
     uint32_t v;
-    asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
+    asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1+%2];" : "=r"(v) : "l"(p), "n"(OFF));
     return v;
 }
-__device__ __forceinline__ uint32_t ldg16_stream(const uint8_t* p) {
+template <int OFF> __device__ __forceinline__ uint32_t ldg16_stream(const uint8_t* p) {
     uint32_t v;
-    asm volatile("{\n\t.reg .b16 h;\n\tld.global.nc.L1::no_allocate.u16 h, [%1];\n\tcvt.u32.u16 %0, h;\n\t}" : "=r"(v) : "l"(p));
+    asm volatile("{\n\t.reg .b16 h;\n\tld.global.nc.L1::no_allocate.u16 h, [%1+%2];\n\tcvt.u32.u16 %0, h;\n\t}" : "=r"(v) : "l"(p), "n"(OFF));
+    return v;
+}
+template <int OFF> __device__ __forceinline__ uint4 lds128_at(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+%5];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a), "n"(OFF));
     return v;
 }
 // 16-byte load by the lanes whose `pred` is non-zero; the other lanes keep what `v` held.
@@ -255,12 +261,12 @@ __device__ __forceinline__ void block_mma(float (&d)[4], uint32_t wg, uint32_t w
 // start value -64 * (sum of the block's digits), prepared with the digits.
 //
 // Staged form of one token, per 128 k (a "unit" = four blocks j = 0..3, block pairs A = (0, 2) and
-// B = (1, 3)): 512 bytes of digits, lane L = 4 g + q reads 16 bytes at L * 16 holding digit (g & 3) of elements
-// 8q..8q+7 of block 2 (g >> 2) [pair A] and of block 2 (g >> 2) + 1 [pair B], each as the byte
-// quadruples of the first MMA (elements 0, 4, 1, 5) and of the second (2, 6, 3, 7).  A lane is a live
-// source for the low k-slots (its block is the pair's first) when g < 4 and for the high k-slots
-// otherwise; the registers of the other half stay zero for the whole kernel (predicated loads), so only
-// half a warp touches shared memory per load.
+// B = (1, 3)): 1024 bytes of digits, lane L = 4 g + q reads 32 bytes at L * 32: for pair A and then for pair B
+// the words {lo, hi} of the first MMA (elements 0, 4, 1, 5 of the lane's block) and {lo, hi} of the second
+// (elements 2, 6, 3, 7), holding digit (g & 3) of elements 8q..8q+7 of block 2 (g >> 2) [pair A] / 2 (g >> 2) + 1
+// [pair B].  A lane is a live source for the low k-slots (its block is the pair's first) when g < 4 and for
+// the high k-slots otherwise; the word of the other half is zero in shared memory (cleared once per kernel and
+// never written), so two plain 16-byte loads deliver the MMA operand pairs in consecutive registers.
 // Per unit and lane quad position q = 2 h + p a 16-byte record {W, f, W', f'} for blocks 2h and 2h+1 and
 // digit pair p: W = int32 correction beta * (256 * sum of digit 2p + sum of digit 2p+1) that cancels the
 // codes' offset, f = 2^e * 256^(2 - 2p) / 8 the factor that turns the integer block sum into the block's
@@ -272,7 +278,8 @@ constexpr uint32_t CODE8_MASK = 0x78787878u;
 // w01 / w11 = of its second block; bl = digit bytes for the low k-slots (first MMA, second MMA),
 // bh = for the high k-slots.
 __device__ __forceinline__ void pair_imma(int (&d)[4], uint32_t w00, uint32_t w10, uint32_t w01, uint32_t w11,
-                                          uint32_t bl1, uint32_t bl2, uint32_t bh1, uint32_t bh2, uint32_t mul28) {
+                                          uint32_t bl1, uint32_t bh1, uint32_t bl2, uint32_t bh2, uint32_t mul28) {
+    // d = (not +=): the first MMA starts from zero.  bl / bh: digit bytes for the low / high k-slots, first and second MMA.
     // The rotation by four bits for the second MMA goes through the multiplier (w * 2^28 as a 64-bit product:
     // low word w << 28, high word w >> 4) and one three-input logic op ((lo | hi) & mask), which leaves two
     // instead of three instructions per word on the half-rate integer pipe.  mul28 = 2^28, kept in a register the
@@ -289,7 +296,7 @@ __device__ __forceinline__ void pair_imma(int (&d)[4], uint32_t w00, uint32_t w1
         "mul.wide.u32 p1, %5, %13;\n\t"
         "mul.wide.u32 p2, %6, %13;\n\t"
         "mul.wide.u32 p3, %7, %13;\n\t"
-        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {a0,a1,a2,a3}, {%8,%10}, {%0,%1,%2,%3};\n\t"
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {a0,a1,a2,a3}, {%8,%9}, {%14,%14,%14,%14};\n\t"
         "mov.b64 {l0, h0}, p0;\n\t"
         "mov.b64 {l1, h1}, p1;\n\t"
         "mov.b64 {l2, h2}, p2;\n\t"
@@ -298,28 +305,29 @@ __device__ __forceinline__ void pair_imma(int (&d)[4], uint32_t w00, uint32_t w1
         "lop3.b32 a1, l1, h1, %12, 0xA8;\n\t"
         "lop3.b32 a2, l2, h2, %12, 0xA8;\n\t"
         "lop3.b32 a3, l3, h3, %12, 0xA8;\n\t"
-        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {a0,a1,a2,a3}, {%9,%11}, {%0,%1,%2,%3};\n\t"
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {a0,a1,a2,a3}, {%10,%11}, {%0,%1,%2,%3};\n\t"
         "}\n"
-        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
-        : "r"(w00), "r"(w10), "r"(w01), "r"(w11), "r"(bl1), "r"(bl2), "r"(bh1), "r"(bh2), "r"(CODE8_MASK), "r"(mul28));
+        : "=&r"(d[0]), "=&r"(d[1]), "=&r"(d[2]), "=&r"(d[3])
+        : "r"(w00), "r"(w10), "r"(w01), "r"(w11), "r"(bl1), "r"(bh1), "r"(bl2), "r"(bh2), "r"(CODE8_MASK), "r"(mul28), "r"(0));
 }
 
 // Lane-specific shared addresses of the staged token for the tile at hand.
 struct Q8Addr {
-    uint32_t x;    // this lane's 16 digit bytes of the tile's first unit
+    uint32_t x;    // this lane's 32 digit bytes of the tile's first unit
     uint32_t rec;  // this lane's record of the tile's first unit
     uint32_t sx;   // this lane's pair of activation sums
 };
-// The B registers of a warp: `lo` feeds the low k-slots and is loaded by lanes 0..15, `hi` the high k-slots by
-// lanes 16..31; the other half of each stays zero from construction on.
+// The B registers of a warp for one unit: {lo, hi} byte quadruples of the first and second MMA of block pair A (a)
+// and of pair B (b).  For a lane that feeds the low k-slots the hi words are zero in shared memory, and vice versa.
 struct Q8Digits {
-    uint4 lo = make_uint4(0u, 0u, 0u, 0u), hi = make_uint4(0u, 0u, 0u, 0u);
+    uint4 a, b;
     uint32_t mul28 = 0x10000000u | (gridDim.y >> 16);  // 2^28 (a grid has fewer than 2^16 CTAs in y), opaque to the compiler
-    __device__ __forceinline__ void load(uint32_t a, uint32_t is_lo) {
-        lds128_if(lo, a, is_lo);
-        lds128_if(hi, a, is_lo ^ 1u);
+    template <int OFF> __device__ __forceinline__ void load(uint32_t addr) {
+        a = lds128_at<OFF>(addr);
+        b = lds128_at<OFF + 16>(addr);
     }
 };
+constexpr int Q8_UNIT_BYTES = 1024;  // staged digits per 128 k: 32 lanes x 32 bytes
 
 // 256 D_even + D_odd as a float (|D| < 2^20 for the 4-bit formats, so the integer is exact and the conversion rounds once)
 __device__ __forceinline__ float digits_to_float(int de, int dodd) { return (float)(de * 256 + dodd); }
@@ -356,28 +364,32 @@ template <> struct TileRegs<WF_QTYPE_Q4_0> {
             s = lds128(sb);
         }
     }
-    // one token: the tile straight from global memory into registers
-    __device__ __forceinline__ void load_global(const uint8_t* tile, int lane) {
-        c[0] = ldg128_stream(tile + lane * 16);
-        c[1] = ldg128_stream(tile + 512 + lane * 16);
-        const uint8_t* sb = tile + Tile<WF_QTYPE_Q4_0>::SCALE_OFF + (lane >> 2) * 16 + (lane & 2) * 2;
-        sg2 = ldg32_stream(sb);
-        sh2 = ldg32_stream(sb + 8);
+    // one token: the tile straight from global memory into registers.  pc = tile + lane * 16, ps = tile + the lane's
+    // scale offset (see lane_scale_offset); OFF = byte offset of the tile from those pointers, an immediate.
+    static __device__ __forceinline__ int lane_scale_offset(int lane) { return (lane >> 2) * 16 + (lane & 2) * 2; }
+    template <int OFF> __device__ __forceinline__ void load_global(const uint8_t* pc, const uint8_t* ps) {
+        c[0] = ldg128_stream<OFF>(pc);
+        c[1] = ldg128_stream<OFF + 512>(pc);
+        sg2 = ldg32_stream<OFF + Tile<WF_QTYPE_Q4_0>::SCALE_OFF>(ps);
+        sh2 = ldg32_stream<OFF + Tile<WF_QTYPE_Q4_0>::SCALE_OFF + 8>(ps);
     }
     // One token: lane (g, q) adds its share of rows g (acc[0]) and g+8 (acc[2]); the four lanes of a quad
     // hold different digit pairs / blocks of the same rows and are summed when the row-tile is flushed.
-    __device__ __forceinline__ void compute_q8(float (&acc)[4], const Q8Addr& a, Q8Digits& dg, uint32_t is_lo) const {
-        dg.load(a.x, is_lo);
-        const uint4 r = lds128(a.rec);  // {W, f, W', f'}: the odd digit's accumulator starts at the offset correction
-        int da[4] = {0, (int)r.x, 0, (int)r.x}, db[4] = {0, (int)r.z, 0, (int)r.z};
-        pair_imma(da, c[0].x, c[1].x, c[0].z, c[1].z, dg.lo.x, dg.lo.y, dg.hi.x, dg.hi.y, dg.mul28);
-        pair_imma(db, c[0].y, c[1].y, c[0].w, c[1].w, dg.lo.z, dg.lo.w, dg.hi.z, dg.hi.w, dg.mul28);
+    // J: the tile's position after the one the addresses point at (immediate offsets).
+    template <int J> __device__ __forceinline__ void compute_q8(float (&acc)[4], const Q8Addr& a, Q8Digits& dg) const {
+        constexpr int TK = Tile<WF_QTYPE_Q4_0>::K;
+        dg.template load<J * (TK / 128) * Q8_UNIT_BYTES>(a.x);
+        const uint4 r = lds128_at<J * (TK >> 5) * 16>(a.rec);  // {W, f, W', f'}
+        int da[4], db[4];
+        pair_imma(da, c[0].x, c[1].x, c[0].z, c[1].z, dg.a.x, dg.a.y, dg.a.z, dg.a.w, dg.mul28);
+        pair_imma(db, c[0].y, c[1].y, c[0].w, c[1].w, dg.b.x, dg.b.y, dg.b.z, dg.b.w, dg.mul28);
         const float2 sg = half2_bits_to_float2(sg2), sh = half2_bits_to_float2(sh2);
         const float ea = __uint_as_float(r.y), eb = __uint_as_float(r.w);
-        acc[0] = fmaf(sg.x * ea, digits_to_float(da[0], da[1]), acc[0]);
-        acc[2] = fmaf(sh.x * ea, digits_to_float(da[2], da[3]), acc[2]);
-        acc[0] = fmaf(sg.y * eb, digits_to_float(db[0], db[1]), acc[0]);
-        acc[2] = fmaf(sh.y * eb, digits_to_float(db[2], db[3]), acc[2]);
+        const int wa = (int)r.x, wb = (int)r.z;
+        acc[0] = fmaf(sg.x * ea, digits_to_float(da[0], da[1] + wa), acc[0]);
+        acc[2] = fmaf(sh.x * ea, digits_to_float(da[2], da[3] + wa), acc[2]);
+        acc[0] = fmaf(sg.y * eb, digits_to_float(db[0], db[1] + wb), acc[0]);
+        acc[2] = fmaf(sh.y * eb, digits_to_float(db[2], db[3] + wb), acc[2]);
     }
     template <int XC>
     // xaddr: shared address of this lane's activations for k = kbase (row + q * 16 bytes);
@@ -423,26 +435,27 @@ template <> struct TileRegs<WF_QTYPE_Q4_1> {
             mn = lds128(mb);
         }
     }
-    // one token: the tile straight from global memory into registers
-    __device__ __forceinline__ void load_global(const uint8_t* tile, int lane) {
+    // one token: the tile straight from global memory into registers (pointers and OFF as for Q4_0)
+    static __device__ __forceinline__ int lane_scale_offset(int lane) { return (lane >> 2) * 16 + (lane & 2) * 2; }
+    template <int OFF> __device__ __forceinline__ void load_global(const uint8_t* pc, const uint8_t* ps) {
         using T = Tile<WF_QTYPE_Q4_1>;
-        c[0] = ldg128_stream(tile + lane * 16);
-        c[1] = ldg128_stream(tile + 512 + lane * 16);
-        const int so = (lane >> 2) * 16 + (lane & 2) * 2;
-        sg2 = ldg32_stream(tile + T::SCALE_OFF + so);
-        sh2 = ldg32_stream(tile + T::SCALE_OFF + so + 8);
-        mg2 = ldg32_stream(tile + T::MIN_OFF + so);
-        mh2 = ldg32_stream(tile + T::MIN_OFF + so + 8);
+        c[0] = ldg128_stream<OFF>(pc);
+        c[1] = ldg128_stream<OFF + 512>(pc);
+        sg2 = ldg32_stream<OFF + T::SCALE_OFF>(ps);
+        sh2 = ldg32_stream<OFF + T::SCALE_OFF + 8>(ps);
+        mg2 = ldg32_stream<OFF + T::MIN_OFF>(ps);
+        mh2 = ldg32_stream<OFF + T::MIN_OFF + 8>(ps);
     }
     // One token: 8 * code enters the MMA as is (no offset); the min term is min * (sum of the block's
     // activations), which only the lanes of the first digit pair carry (the others read zeros).
-    __device__ __forceinline__ void compute_q8(float (&acc)[4], const Q8Addr& a, Q8Digits& dg, uint32_t is_lo) const {
-        dg.load(a.x, is_lo);
-        const uint4 r = lds128(a.rec);
-        const uint2 sx = lds64(a.sx);
-        int da[4] = {0, 0, 0, 0}, db[4] = {0, 0, 0, 0};
-        pair_imma(da, c[0].x, c[1].x, c[0].z, c[1].z, dg.lo.x, dg.lo.y, dg.hi.x, dg.hi.y, dg.mul28);
-        pair_imma(db, c[0].y, c[1].y, c[0].w, c[1].w, dg.lo.z, dg.lo.w, dg.hi.z, dg.hi.w, dg.mul28);
+    template <int J> __device__ __forceinline__ void compute_q8(float (&acc)[4], const Q8Addr& a, Q8Digits& dg) const {
+        constexpr int TK = Tile<WF_QTYPE_Q4_1>::K;
+        dg.template load<J * (TK / 128) * Q8_UNIT_BYTES>(a.x);
+        const uint4 r = lds128_at<J * (TK >> 5) * 16>(a.rec);
+        const uint2 sx = lds64(a.sx + J * (TK >> 5) * 8);
+        int da[4], db[4];
+        pair_imma(da, c[0].x, c[1].x, c[0].z, c[1].z, dg.a.x, dg.a.y, dg.a.z, dg.a.w, dg.mul28);
+        pair_imma(db, c[0].y, c[1].y, c[0].w, c[1].w, dg.b.x, dg.b.y, dg.b.z, dg.b.w, dg.mul28);
         const float2 sg = half2_bits_to_float2(sg2), sh = half2_bits_to_float2(sh2);
         const float2 mg = half2_bits_to_float2(mg2), mh = half2_bits_to_float2(mh2);
         const float ea = __uint_as_float(r.y), eb = __uint_as_float(r.w);
@@ -493,23 +506,26 @@ template <> struct TileRegs<WF_QTYPE_Q8_0> {
             s = lds128(sb);
         }
     }
-    // one token: the tile straight from global memory into registers
-    __device__ __forceinline__ void load_global(const uint8_t* tile, int lane) {
-#pragma unroll
-        for (int i = 0; i < 4; i++) c[i] = ldg128_stream(tile + i * 512 + lane * 16);
-        const uint8_t* sb = tile + Tile<WF_QTYPE_Q8_0>::SCALE_OFF + (lane >> 2) * 16 + (lane & 2) * 2;
-        sg2 = ldg32_stream(sb);
-        sh2 = ldg32_stream(sb + 8);
+    // one token: the tile straight from global memory into registers (pointers and OFF as for Q4_0)
+    static __device__ __forceinline__ int lane_scale_offset(int lane) { return (lane >> 2) * 16 + (lane & 2) * 2; }
+    template <int OFF> __device__ __forceinline__ void load_global(const uint8_t* pc, const uint8_t* ps) {
+        c[0] = ldg128_stream<OFF>(pc);
+        c[1] = ldg128_stream<OFF + 512>(pc);
+        c[2] = ldg128_stream<OFF + 1024>(pc);
+        c[3] = ldg128_stream<OFF + 1536>(pc);
+        sg2 = ldg32_stream<OFF + Tile<WF_QTYPE_Q8_0>::SCALE_OFF>(ps);
+        sh2 = ldg32_stream<OFF + Tile<WF_QTYPE_Q8_0>::SCALE_OFF + 8>(ps);
     }
     // One token: value = 16 (hi - 8) + lo; the two planes accumulate separately and combine as integers.
-    __device__ __forceinline__ void compute_q8(float (&acc)[4], const Q8Addr& a, Q8Digits& dg, uint32_t is_lo) const {
-        dg.load(a.x, is_lo);
-        const uint4 r = lds128(a.rec);
-        int la[4] = {0, 0, 0, 0}, lb[4] = {0, 0, 0, 0}, ha[4] = {0, 0, 0, 0}, hb[4] = {0, 0, 0, 0};
-        pair_imma(ha, c[0].x, c[1].x, c[0].z, c[1].z, dg.lo.x, dg.lo.y, dg.hi.x, dg.hi.y, dg.mul28);
-        pair_imma(la, c[2].x, c[3].x, c[2].z, c[3].z, dg.lo.x, dg.lo.y, dg.hi.x, dg.hi.y, dg.mul28);
-        pair_imma(hb, c[0].y, c[1].y, c[0].w, c[1].w, dg.lo.z, dg.lo.w, dg.hi.z, dg.hi.w, dg.mul28);
-        pair_imma(lb, c[2].y, c[3].y, c[2].w, c[3].w, dg.lo.z, dg.lo.w, dg.hi.z, dg.hi.w, dg.mul28);
+    template <int J> __device__ __forceinline__ void compute_q8(float (&acc)[4], const Q8Addr& a, Q8Digits& dg) const {
+        constexpr int TK = Tile<WF_QTYPE_Q8_0>::K;
+        dg.template load<J * (TK / 128) * Q8_UNIT_BYTES>(a.x);
+        const uint4 r = lds128_at<J * (TK >> 5) * 16>(a.rec);
+        int la[4], lb[4], ha[4], hb[4];
+        pair_imma(ha, c[0].x, c[1].x, c[0].z, c[1].z, dg.a.x, dg.a.y, dg.a.z, dg.a.w, dg.mul28);
+        pair_imma(la, c[2].x, c[3].x, c[2].z, c[3].z, dg.a.x, dg.a.y, dg.a.z, dg.a.w, dg.mul28);
+        pair_imma(hb, c[0].y, c[1].y, c[0].w, c[1].w, dg.b.x, dg.b.y, dg.b.z, dg.b.w, dg.mul28);
+        pair_imma(lb, c[2].y, c[3].y, c[2].w, c[3].w, dg.b.x, dg.b.y, dg.b.z, dg.b.w, dg.mul28);
         const float2 sg = half2_bits_to_float2(sg2), sh = half2_bits_to_float2(sh2);
         const float ea = __uint_as_float(r.y), eb = __uint_as_float(r.w);
         const int wa = (int)r.x, wb = (int)r.z;
@@ -573,35 +589,43 @@ template <> struct TileRegs<WF_QTYPE_Q4_K> {
             mn = lds128(base + T::MN_OFF + (lane >> 2) * 16);
         }
     }
-    // one token: the tile straight from global memory into registers
-    __device__ __forceinline__ void load_global(const uint8_t* tile, int lane) {
+    // one token: the tile straight from global memory into registers.  pc = tile + lane * 16, ps = tile + the lane's
+    // scale offset; the (d, dmin) pairs sit at g * 8, which is half of the scale offset's g * 16: a third pointer
+    // is rebuilt from ps (the lane's bit (lane & 2) is removed first).
+    static __device__ __forceinline__ int lane_scale_offset(int lane) { return (lane >> 2) * 16 + (lane & 2); }
+    template <int OFF> __device__ __forceinline__ void load_global(const uint8_t* pc, const uint8_t* ps) {
         using T = Tile<WF_QTYPE_Q4_K>;
-#pragma unroll
-        for (int i = 0; i < 4; i++) c[i] = ldg128_stream(tile + i * 512 + lane * 16);
-        dd = ldg64_stream(tile + T::D_OFF + (lane >> 2) * 8);
-        const int so = (lane >> 2) * 16 + (lane & 2);  // row g: bytes 2h, 2h+1; +4: sub-blocks 4+2h, 5+2h; +8: row g+8
-#pragma unroll
-        for (int u = 0; u < 2; u++) {
-            scg[u] = ldg16_stream(tile + T::SC_OFF + so + 4 * u);
-            sch[u] = ldg16_stream(tile + T::SC_OFF + so + 8 + 4 * u);
-            mng[u] = ldg16_stream(tile + T::MN_OFF + so + 4 * u);
-            mnh[u] = ldg16_stream(tile + T::MN_OFF + so + 8 + 4 * u);
-        }
+        c[0] = ldg128_stream<OFF>(pc);
+        c[1] = ldg128_stream<OFF + 512>(pc);
+        c[2] = ldg128_stream<OFF + 1024>(pc);
+        c[3] = ldg128_stream<OFF + 1536>(pc);
+        const int lane = threadIdx.x & 31;
+        dd = ldg64_stream<OFF + T::D_OFF>(ps - lane_scale_offset(lane) + (lane >> 2) * 8);
+        // row g: bytes 2h, 2h+1; +4: sub-blocks 4+2h, 5+2h; +8: row g+8
+        scg[0] = ldg16_stream<OFF + T::SC_OFF>(ps);
+        scg[1] = ldg16_stream<OFF + T::SC_OFF + 4>(ps);
+        sch[0] = ldg16_stream<OFF + T::SC_OFF + 8>(ps);
+        sch[1] = ldg16_stream<OFF + T::SC_OFF + 12>(ps);
+        mng[0] = ldg16_stream<OFF + T::MN_OFF>(ps);
+        mng[1] = ldg16_stream<OFF + T::MN_OFF + 4>(ps);
+        mnh[0] = ldg16_stream<OFF + T::MN_OFF + 8>(ps);
+        mnh[1] = ldg16_stream<OFF + T::MN_OFF + 12>(ps);
     }
     // One token: the tile is two units of 128 k (sub-blocks 0..3 and 4..7).  8 * code enters the MMA as is;
     // the min term is (dmin * m) * (sum of the sub-block's activations), carried by the lanes of the first digit pair.
-    __device__ __forceinline__ void compute_q8(float (&acc)[4], const Q8Addr& a, Q8Digits& dg, uint32_t is_lo) const {
+    template <int J> __device__ __forceinline__ void compute_q8(float (&acc)[4], const Q8Addr& a, Q8Digits& dg) const {
         const float2 g = half2_bits_to_float2(dd.x), h = half2_bits_to_float2(dd.y);  // (d, dmin) of rows g / g+8
         const float BIG = 8388608.f;
         const float ngd = -BIG * g.x, ngm = BIG * g.y, nhd = -BIG * h.x, nhm = BIG * h.y;
 #pragma unroll
         for (int u = 0; u < 2; u++) {
-            dg.load(a.x + u * 512, is_lo);
-            const uint4 r = lds128(a.rec + u * 64);
-            const uint2 sx = lds64(a.sx + u * 32);
-            int da[4] = {0, 0, 0, 0}, db[4] = {0, 0, 0, 0};
-            pair_imma(da, c[2 * u].x, c[2 * u + 1].x, c[2 * u].z, c[2 * u + 1].z, dg.lo.x, dg.lo.y, dg.hi.x, dg.hi.y, dg.mul28);
-            pair_imma(db, c[2 * u].y, c[2 * u + 1].y, c[2 * u].w, c[2 * u + 1].w, dg.lo.z, dg.lo.w, dg.hi.z, dg.hi.w, dg.mul28);
+            if (u == 0) dg.template load<(2 * J) * Q8_UNIT_BYTES>(a.x);
+            else dg.template load<(2 * J + 1) * Q8_UNIT_BYTES>(a.x);
+            const uint4 r = u == 0 ? lds128_at<(2 * J) * 64>(a.rec) : lds128_at<(2 * J + 1) * 64>(a.rec);
+            const uint2 sx = lds64(a.sx + (2 * J + u) * 32);
+            int da[4], db[4];
+            pair_imma(da, c[2 * u].x, c[2 * u + 1].x, c[2 * u].z, c[2 * u + 1].z, dg.a.x, dg.a.y, dg.a.z, dg.a.w, dg.mul28);
+            pair_imma(db, c[2 * u].y, c[2 * u + 1].y, c[2 * u].w, c[2 * u + 1].w, dg.b.x, dg.b.y, dg.b.z, dg.b.w, dg.mul28);
             const uint32_t wsg = scg[u], wsh = sch[u], wmg = mng[u], wmh = mnh[u];
             const float ea = __uint_as_float(r.y), eb = __uint_as_float(r.w);
             const float xa = __uint_as_float(sx.x), xb = __uint_as_float(sx.y);
@@ -1003,10 +1027,15 @@ static __device__ __noinline__ void stage_x_q8(const void* x, int k, uint8_t* xd
             }
             if (c8 < groups) {
                 const int b = c8 >> 2, q = c8 & 3, unit = b >> 2, j = b & 3, pair = j & 1, hcol = j >> 1;
-                uint8_t* base = xd + (size_t)unit * 512 + pair * 8 + q * 16;
+                // lane (g = 4 hcol + digit, q): 32 bytes {lo, hi} first MMA, {lo, hi} second MMA for pair A, then pair B;
+                // this block fills the lo words when it is its pair's first block (hcol 0), the hi words otherwise
+                uint8_t* base = xd + (size_t)unit * Q8_UNIT_BYTES + q * 32 + pair * 16 + hcol * 4;
 #pragma unroll
-                for (int t = 0; t < 4; t++)  // digit t has weight 256^t; column digit index = 3 - t (most significant first)
-                    *reinterpret_cast<uint2*>(base + (4 * hcol + (3 - t)) * 64) = make_uint2(t1[t], t2[t]);
+                for (int t = 0; t < 4; t++) {  // digit t has weight 256^t; column digit index = 3 - t (most significant first)
+                    uint32_t* w = reinterpret_cast<uint32_t*>(base + (4 * hcol + (3 - t)) * 128);
+                    w[0] = t1[t];
+                    w[2] = t2[t];
+                }
                 if (q == 0) {
                     // x = X * 2^(e - 156); the MMA multiplies 8 * code; the lanes of the first digit pair hold
                     // 256^3 D + 256^2 D' = 2^16 (256 D + D')

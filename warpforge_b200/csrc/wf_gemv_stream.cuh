@@ -16,9 +16,18 @@
 // order.  A row-tile cut by the CTA's share boundary is then finished between CTAs exactly as in the
 // several-token kernel (publish / collect through tagged scratch slots, bounded waits).
 #pragma once
+#include <utility>
+
 #include "wf_gemv_core.cuh"
 
 namespace wf {
+
+// for (j = 0 .. N-1) with j a compile-time constant in the body: f(std::integral_constant<int, j>{})
+template <class F, int... I>
+__device__ __forceinline__ void static_for_impl(F& f, std::integer_sequence<int, I...>) {
+    (f(std::integral_constant<int, I>{}), ...);
+}
+template <int N, class F> __device__ __forceinline__ void static_for(F&& f) { static_for_impl(f, std::make_integer_sequence<int, N>{}); }
 
 constexpr int WS_SLOTS = 4;         // hand-over generations (weights) whose pieces may be alive at once
 constexpr int WS_TABLE_OPS = 256;   // weights of a program whose shares are kept in shared memory
@@ -36,9 +45,9 @@ template <int QT> struct WsGeom {
 };
 
 // Shared memory of the one-token kernels:
-//   control | pieces | share table (32 bytes per weight) | block records and sums (32 bytes per 32 k) | digits (4 bytes per k)
+//   control | pieces | share table (32 bytes per weight) | block records and sums (32 bytes per 32 k) | digits (8 bytes per k)
 inline size_t ws_smem(int kp, int table_ops) {
-    size_t b = WS_CTRL_BYTES + WS_PIECE_BYTES + (size_t)table_ops * 32 + (size_t)(kp / 32) * 32 + (size_t)kp * 4 + 64;
+    size_t b = WS_CTRL_BYTES + WS_PIECE_BYTES + (size_t)table_ops * 32 + (size_t)(kp / 32) * 32 + (size_t)kp * 8 + 64;
     return (b + 127) & ~(size_t)127;
 }
 inline bool ws_fits(int kp, int table_ops) { return ws_smem(kp, table_ops) <= 227 * 1024; }
@@ -123,37 +132,30 @@ __device__ __forceinline__ void ws_next_group(WsCursor& c, ShareFn& share_of, in
     base = c.tiles + (size_t)c.t * Tile<QT>::BYTES;
     c.t += cnt;
 }
-// The register pipeline is only a group deep (and the loads of a group are requested one by one as its slots
-// free up), which covers the latency of L2 but not of HBM.  A second cursor therefore runs WS_PREFETCH_GROUPS
-// groups ahead of the loads and asks for each group to be brought into L2 with one bulk prefetch (a group is
-// contiguous: at most DEPTH tiles of one weight).
-#ifndef WF_WS_PREFETCH_GROUPS
-#define WF_WS_PREFETCH_GROUPS 0
-#endif
-constexpr int WS_PREFETCH_GROUPS = WF_WS_PREFETCH_GROUPS;
-__device__ __forceinline__ void ws_prefetch_l2(const uint8_t* p, uint32_t bytes) {
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
-}
+// The two lane pointers a tile is loaded through (see TileRegs::load_global).
+template <int QT> struct WsLanePtrs {
+    const uint8_t* pc;
+    const uint8_t* ps;
+    __device__ __forceinline__ WsLanePtrs(const uint8_t* base, int lane)
+        : pc(base + lane * 16), ps(base + TileRegs<QT>::lane_scale_offset(lane)) {}
+};
+// Request the first group of the stream (the weights depend on nothing, so this comes before any wait).
 template <int QT, class ShareFn>
-__device__ __forceinline__ void ws_prefetch_group(WsCursor& pf, ShareFn& share_of, int n_ops, int warp, int lane) {
-    const uint8_t* base;
-    int cnt;
-    ws_next_group<QT>(pf, share_of, n_ops, warp, base, cnt);
-    if (cnt > 0 && lane == 0) ws_prefetch_l2(base, (uint32_t)cnt * Tile<QT>::BYTES);
-}
-// Request the first group of the stream and the prefetches ahead of it (the weights depend on nothing, so this
-// comes before any wait).
-template <int QT, class ShareFn>
-__device__ __forceinline__ void ws_prime(TileRegs<QT> (&slots)[WsGeom<QT>::DEPTH], WsCursor& c, WsCursor& pf, ShareFn& share_of,
-                                         int n_ops, int warp, int lane) {
+__device__ __forceinline__ void ws_prime(TileRegs<QT> (&slots)[WsGeom<QT>::DEPTH], WsCursor& c, ShareFn& share_of, int n_ops,
+                                         int warp, int lane) {
     const uint8_t* base;
     int cnt;
     ws_next_group<QT>(c, share_of, n_ops, warp, base, cnt);
-#pragma unroll
-    for (int j = 0; j < WsGeom<QT>::DEPTH; j++)
-        if (j < cnt) slots[j].load_global(base + (size_t)j * Tile<QT>::BYTES, lane);
-    pf = c;
-    for (int i = 0; i < WS_PREFETCH_GROUPS; i++) ws_prefetch_group<QT>(pf, share_of, n_ops, warp, lane);
+    const WsLanePtrs<QT> lp(base, lane);
+    static_for<WsGeom<QT>::DEPTH>([&](auto J) {
+        constexpr int j = decltype(J)::value;
+        if (j < cnt) slots[j].template load_global<j * Tile<QT>::BYTES>(lp.pc, lp.ps);
+    });
+}
+// Clear the digit words once per kernel: the staging only ever writes the word of the half a lane feeds.
+__device__ __forceinline__ void ws_clear_digits(uint8_t* xd, int kp, int nthreads) {
+    uint4* p = reinterpret_cast<uint4*>(xd);
+    for (int i = threadIdx.x; i < kp / 2; i += nthreads) p[i] = make_uint4(0u, 0u, 0u, 0u);
 }
 
 struct WsBars {  // 32-bit shared addresses
@@ -172,20 +174,19 @@ __device__ __forceinline__ void ws_bars_init(uint8_t* smem) {
 }
 
 // One weight, one warp: walk the run, hand the cut pieces over, finish the row-tiles this warp is first to hold.
-//   slots: the register sets holding the first group of this run (requested earlier); cur / pf: the load and the
-//   prefetch cursor;
+//   slots: the register sets holding the first group of this run (requested earlier); cur: the request cursor;
 //   x32 / c32 / s32: shared addresses of the staged digits, the block records and the activation sums;
 //   emit_row(n, value): store output row n of this weight (called by one lane per row);
 //   share_of(o): the CTA's share of weight o of the program.
 template <int QT, class EmitRow, class ShareFn>
 __device__ __forceinline__ void ws_consume(const WsShare& sh, int chunk_q, int chunk_r, int warp, int lane,
-                                           TileRegs<QT> (&slots)[WsGeom<QT>::DEPTH], WsCursor& cur, WsCursor& pf, const WsBars& bar,
+                                           TileRegs<QT> (&slots)[WsGeom<QT>::DEPTH], WsCursor& cur, const WsBars& bar,
                                            WsPiece* pieces, uint32_t& seq, uint32_t x32, uint32_t c32, uint32_t s32,
                                            uint2* slots_g, int* status, uint32_t abort32, ShareFn& share_of, int n_ops,
                                            EmitRow&& emit_row) {
     using T = Tile<QT>;
     constexpr int DEPTH = WsGeom<QT>::DEPTH;
-    constexpr uint32_t XSTEP = T::K * 4, RSTEP = (T::K >> 5) * 16, SSTEP = (T::K >> 5) * 8;  // staged bytes per tile
+    constexpr uint32_t XSTEP = (T::K / 128) * Q8_UNIT_BYTES, RSTEP = (T::K >> 5) * 16, SSTEP = (T::K >> 5) * 8;  // staged bytes per tile
     const int g = lane >> 2, q = lane & 3, kt = sh.kt;
     const uint32_t lane_is_0 = lane == 0;
     int a, b;
@@ -212,8 +213,7 @@ __device__ __forceinline__ void ws_consume(const WsShare& sh, int chunk_q, int c
             kk -= kt;
         }
         bool starts_here = kk == 0;  // the row-tile being walked began inside this run
-        const uint32_t is_lo = lane < 16 ? 1u : 0u;  // this lane feeds the low k-slots of the MMAs
-        const uint32_t x0 = x32 + lane * 16, rec0 = c32 + q * 16, sx0 = s32 + q * 8;
+        const uint32_t x0 = x32 + lane * 32, rec0 = c32 + q * 16, sx0 = s32 + q * 8;
         Q8Addr qa;
         qa.x = x0 + (uint32_t)kk * XSTEP;
         qa.rec = rec0 + (uint32_t)kk * RSTEP;
@@ -257,26 +257,48 @@ __device__ __forceinline__ void ws_consume(const WsShare& sh, int chunk_q, int c
             const uint8_t* nbase;
             int ncnt;
             ws_next_group<QT>(cur, share_of, n_ops, warp, nbase, ncnt);
-            ws_prefetch_group<QT>(pf, share_of, n_ops, warp, lane);
-#pragma unroll
-            for (int j = 0; j < DEPTH; j++) {
-                if (g0 + j < len) {
-                    slots[j].compute_q8(acc, qa, dg, is_lo);
-                    if (++kk == kt) {
-                        flush(true);
-                        kk = 0;
-                        rt++;
-                        starts_here = true;
-                        qa.x = x0;
-                        qa.rec = rec0;
-                        qa.sx = sx0;
-                    } else {
-                        qa.x += XSTEP;
-                        qa.rec += RSTEP;
-                        qa.sx += SSTEP;
-                    }
+            const WsLanePtrs<QT> lp(nbase, lane);
+            if (g0 + DEPTH <= len && kk + DEPTH <= kt && ncnt == DEPTH) {
+                // a whole group inside one row-tile, a whole group to request: straight-line code, immediate offsets
+                static_for<DEPTH>([&](auto J) {
+                    constexpr int j = decltype(J)::value;
+                    slots[j].template compute_q8<j>(acc, qa, dg);
+                    slots[j].template load_global<j * T::BYTES>(lp.pc, lp.ps);
+                });
+                kk += DEPTH;
+                qa.x += DEPTH * XSTEP;
+                qa.rec += DEPTH * RSTEP;
+                qa.sx += DEPTH * SSTEP;
+                if (kk == kt) {
+                    flush(true);
+                    kk = 0;
+                    rt++;
+                    starts_here = true;
+                    qa.x = x0;
+                    qa.rec = rec0;
+                    qa.sx = sx0;
                 }
-                if (j < ncnt) slots[j].load_global(nbase + (size_t)j * T::BYTES, lane);
+            } else {
+                static_for<DEPTH>([&](auto J) {
+                    constexpr int j = decltype(J)::value;
+                    if (g0 + j < len) {
+                        slots[j].template compute_q8<0>(acc, qa, dg);
+                        if (++kk == kt) {
+                            flush(true);
+                            kk = 0;
+                            rt++;
+                            starts_here = true;
+                            qa.x = x0;
+                            qa.rec = rec0;
+                            qa.sx = sx0;
+                        } else {
+                            qa.x += XSTEP;
+                            qa.rec += RSTEP;
+                            qa.sx += SSTEP;
+                        }
+                    }
+                    if (j < ncnt) slots[j].template load_global<j * T::BYTES>(lp.pc, lp.ps);
+                });
             }
         }
         if (kk != 0) flush(false);
