@@ -38,6 +38,8 @@ struct Weight {
 // Scratch for the GEMV fix-up between CTAs, one per stream that launches GEMVs.
 struct GemvScratch {
     uint2* d_slots = nullptr;  // [ctas][128] {value bits, tag}
+    float* d_part = nullptr;   // several-token kernel: partial sums of k-sliced launches
+    int* d_count = nullptr;    // several-token kernel: arrival counters per row-tile
     int ctas = 0;
 };
 

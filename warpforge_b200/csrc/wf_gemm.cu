@@ -968,10 +968,10 @@ static EncodeTiledFn encode_tiled_fn() {
 constexpr size_t GEMM_SMEM_LIMIT = 227 * 1024;
 
 bool gemm_supported(const Weight& w, int x_dtype, int64_t m, const void* d_x) {
-    // bf16 activations, more than the GEMV's 8 tokens; K a multiple of 8 elements and a 16-byte aligned activation
+    // bf16 activations, more than the 32 tokens the memory-bound decode kernel takes in one launch; K a multiple of 8 elements and a 16-byte aligned activation
     // pointer (the pre-pass reads 16-byte pieces, the TMA row stride must be a multiple of 16 bytes).  Whole
     // 128-row blocks exist for any row count: the weight buffer is padded to 8 row-tiles with zero scales.
-    return x_dtype == WF_DTYPE_BF16 && m > 8 && (w.g.k % 8) == 0 && (reinterpret_cast<uintptr_t>(d_x) & 15) == 0 &&
+    return x_dtype == WF_DTYPE_BF16 && m > 32 && (w.g.k % 8) == 0 && (reinterpret_cast<uintptr_t>(d_x) & 15) == 0 &&
            encode_tiled_fn() != nullptr;
 }
 

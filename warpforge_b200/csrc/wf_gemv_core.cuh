@@ -241,6 +241,41 @@ __device__ __forceinline__ void block_mma(float (&d)[4], uint32_t wg, uint32_t w
           "r"(0x00780078u), "r"(magic));
 }
 
+// The A fragments of one 32-k block alone (what block_mma builds before its two MMAs): a[0..3] feed the MMA over
+// elements 0..15 of the block, a[4..7] the one over elements 16..31.  For kernels that multiply one block of
+// weights with several groups of eight columns.
+__device__ __forceinline__ void unpack8(uint32_t (&a)[8], uint32_t wg, uint32_t wh, uint32_t magic) {
+    asm("{\n\t"
+        ".reg .b32 g1, g2, g3, h1, h2, h3;\n\t"
+        "shf.r.wrap.b32 g1, %8, %8, 4;\n\t"
+        "shf.r.wrap.b32 h1, %9, %9, 4;\n\t"
+        "shf.r.wrap.b32 g2, %8, %8, 8;\n\t"
+        "shf.r.wrap.b32 h2, %9, %9, 8;\n\t"
+        "shf.r.wrap.b32 g3, %8, %8, 12;\n\t"
+        "shf.r.wrap.b32 h3, %9, %9, 12;\n\t"
+        "lop3.b32 %0, %8, %10, %11, 0xEA;\n\t"
+        "lop3.b32 %1, %9, %10, %11, 0xEA;\n\t"
+        "lop3.b32 %2, g1, %10, %11, 0xEA;\n\t"
+        "lop3.b32 %3, h1, %10, %11, 0xEA;\n\t"
+        "lop3.b32 %4, g2, %10, %11, 0xEA;\n\t"
+        "lop3.b32 %5, h2, %10, %11, 0xEA;\n\t"
+        "lop3.b32 %6, g3, %10, %11, 0xEA;\n\t"
+        "lop3.b32 %7, h3, %10, %11, 0xEA;\n\t"
+        "}\n"
+        : "=&r"(a[0]), "=&r"(a[1]), "=&r"(a[2]), "=&r"(a[3]), "=&r"(a[4]), "=&r"(a[5]), "=&r"(a[6]), "=&r"(a[7])
+        : "r"(wg), "r"(wh), "r"(0x00780078u), "r"(magic));
+}
+// One block against one group of eight columns: d = c + A . B over the 32 k of the block.
+__device__ __forceinline__ void block_mma_pre(float (&d)[4], const uint32_t (&a)[8], const uint4& xb, float c0, float c1, float c2, float c3) {
+    mma_bf16(d, a[0], a[1], a[2], a[3], xb.x, xb.y, c0, c1, c2, c3);
+    mma_bf16(d, a[4], a[5], a[6], a[7], xb.z, xb.w, d[0], d[1], d[2], d[3]);
+}
+__device__ __forceinline__ float2 lds64f(uint32_t a) {
+    float2 v;
+    asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(a));
+    return v;
+}
+
 // ---- one token: integer MMAs, the eight accumulator columns = two blocks x four activation digits
 // With a single bf16 token seven of the eight columns of the B operand would be idle, and turning 4-bit
 // codes into bf16 operands costs seven half-rate integer instructions per word of eight codes.  The
@@ -391,6 +426,37 @@ template <> struct TileRegs<WF_QTYPE_Q4_0> {
         acc[0] = fmaf(sg.y * eb, digits_to_float(db[0], db[1] + wb), acc[0]);
         acc[2] = fmaf(sh.y * eb, digits_to_float(db[2], db[3] + wb), acc[2]);
     }
+    // Several tokens, register streaming: the tile from global memory (tile = its first byte); NG groups of eight
+    // columns; xg[i] = shared address of this lane's column of group i (row + q * 16 bytes) at the slice's first k,
+    // xoff = byte offset of the tile's first k in a staged row, caddr = the lane's start values of the tile's first
+    // block, group 0 ([block][group][q] float4).
+    __device__ __forceinline__ void load_global_n(const uint8_t* tile, int lane) {
+        c[0] = ldg128_stream<0>(tile + lane * 16);
+        c[1] = ldg128_stream<512>(tile + lane * 16);
+        s = ldg128_stream<Tile<WF_QTYPE_Q4_0>::SCALE_OFF>(tile + (lane >> 2) * 16);
+    }
+    template <int NG>
+    __device__ __forceinline__ void compute_n(float (&acc)[NG][4], const uint32_t (&xg)[NG], uint32_t xoff, uint32_t caddr) const {
+        const float2 s0 = half2_bits_to_float2(s.x), s1 = half2_bits_to_float2(s.y);
+        const float2 s2 = half2_bits_to_float2(s.z), s3 = half2_bits_to_float2(s.w);
+        const float sg[4] = {s0.x, s0.y, s1.x, s1.y}, sh[4] = {s2.x, s2.y, s3.x, s3.y};
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            uint32_t a[8];
+            unpack8(a, word_of(c[0], j), word_of(c[1], j), MAGIC_16);
+#pragma unroll
+            for (int gi = 0; gi < NG; gi++) {
+                const uint4 xb = lds128(xg[gi] + xoff + j * 64);
+                const float2 ci = lds64f(caddr + (j * NG + gi) * 32);
+                float d[4];
+                block_mma_pre(d, a, xb, ci.x, ci.y, ci.x, ci.y);
+                acc[gi][0] = fmaf(sg[j], d[0], acc[gi][0]);
+                acc[gi][2] = fmaf(sh[j], d[2], acc[gi][2]);
+                acc[gi][1] = fmaf(sg[j], d[1], acc[gi][1]);
+                acc[gi][3] = fmaf(sh[j], d[3], acc[gi][3]);
+            }
+        }
+    }
     template <int XC>
     // xaddr: shared address of this lane's activations for k = kbase (row + q * 16 bytes);
     // caddr: shared address of the start value(s) of block kbase / 32; live: lane owns a live column
@@ -465,6 +531,39 @@ template <> struct TileRegs<WF_QTYPE_Q4_1> {
         acc[0] = fmaf(sg.y * eb, digits_to_float(db[0], db[1]), fmaf(mg.y, xb, acc[0]));
         acc[2] = fmaf(sh.y * eb, digits_to_float(db[2], db[3]), fmaf(mh.y, xb, acc[2]));
     }
+    __device__ __forceinline__ void load_global_n(const uint8_t* tile, int lane) {
+        using T = Tile<WF_QTYPE_Q4_1>;
+        c[0] = ldg128_stream<0>(tile + lane * 16);
+        c[1] = ldg128_stream<512>(tile + lane * 16);
+        s = ldg128_stream<T::SCALE_OFF>(tile + (lane >> 2) * 16);
+        mn = ldg128_stream<T::MIN_OFF>(tile + (lane >> 2) * 16);
+    }
+    template <int NG>
+    __device__ __forceinline__ void compute_n(float (&acc)[NG][4], const uint32_t (&xg)[NG], uint32_t xoff, uint32_t caddr) const {
+        const float2 s0 = half2_bits_to_float2(s.x), s1 = half2_bits_to_float2(s.y);
+        const float2 s2 = half2_bits_to_float2(s.z), s3 = half2_bits_to_float2(s.w);
+        const float2 m0 = half2_bits_to_float2(mn.x), m1 = half2_bits_to_float2(mn.y);
+        const float2 m2 = half2_bits_to_float2(mn.z), m3 = half2_bits_to_float2(mn.w);
+        const float sg[4] = {s0.x, s0.y, s1.x, s1.y}, sh[4] = {s2.x, s2.y, s3.x, s3.y};
+        const float mg[4] = {m0.x * -0.0625f, m0.y * -0.0625f, m1.x * -0.0625f, m1.y * -0.0625f};
+        const float mh[4] = {m2.x * -0.0625f, m2.y * -0.0625f, m3.x * -0.0625f, m3.y * -0.0625f};
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            uint32_t a[8];
+            unpack8(a, word_of(c[0], j), word_of(c[1], j), MAGIC_16);
+#pragma unroll
+            for (int gi = 0; gi < NG; gi++) {
+                const uint4 xb = lds128(xg[gi] + xoff + j * 64);
+                const float2 ci = lds64f(caddr + (j * NG + gi) * 32);
+                float d[4];
+                block_mma_pre(d, a, xb, ci.x, ci.y, ci.x, ci.y);
+                acc[gi][0] = fmaf(sg[j], d[0], fmaf(mg[j], ci.x, acc[gi][0]));
+                acc[gi][2] = fmaf(sh[j], d[2], fmaf(mh[j], ci.x, acc[gi][2]));
+                acc[gi][1] = fmaf(sg[j], d[1], fmaf(mg[j], ci.y, acc[gi][1]));
+                acc[gi][3] = fmaf(sh[j], d[3], fmaf(mh[j], ci.y, acc[gi][3]));
+            }
+        }
+    }
     template <int XC>
     __device__ __forceinline__ void compute(float (&acc)[4], uint32_t xaddr, uint32_t caddr, uint32_t live) const {
         const float2 s0 = half2_bits_to_float2(s.x), s1 = half2_bits_to_float2(s.y);  // row g, blocks 0..3
@@ -533,6 +632,36 @@ template <> struct TileRegs<WF_QTYPE_Q8_0> {
         acc[2] = fmaf(sh.x * ea, wide_digits_to_float(16 * ha[2] + la[2], 16 * ha[3] + la[3], wa), acc[2]);
         acc[0] = fmaf(sg.y * eb, wide_digits_to_float(16 * hb[0] + lb[0], 16 * hb[1] + lb[1], wb), acc[0]);
         acc[2] = fmaf(sh.y * eb, wide_digits_to_float(16 * hb[2] + lb[2], 16 * hb[3] + lb[3], wb), acc[2]);
+    }
+    __device__ __forceinline__ void load_global_n(const uint8_t* tile, int lane) {
+        c[0] = ldg128_stream<0>(tile + lane * 16);
+        c[1] = ldg128_stream<512>(tile + lane * 16);
+        c[2] = ldg128_stream<1024>(tile + lane * 16);
+        c[3] = ldg128_stream<1536>(tile + lane * 16);
+        s = ldg128_stream<Tile<WF_QTYPE_Q8_0>::SCALE_OFF>(tile + (lane >> 2) * 16);
+    }
+    template <int NG>
+    __device__ __forceinline__ void compute_n(float (&acc)[NG][4], const uint32_t (&xg)[NG], uint32_t xoff, uint32_t caddr) const {
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            uint32_t ah[8], al[8];
+            unpack8(ah, word_of(c[0], j), word_of(c[1], j), MAGIC_256);
+            unpack8(al, word_of(c[2], j), word_of(c[3], j), MAGIC_16);
+            const float2 dg = half2_bits_to_float2(j < 2 ? s.x : s.y), dh = half2_bits_to_float2(j < 2 ? s.z : s.w);
+            const float sg = (j & 1) ? dg.y : dg.x, sh = (j & 1) ? dh.y : dh.x;
+#pragma unroll
+            for (int gi = 0; gi < NG; gi++) {
+                const uint4 xb = lds128(xg[gi] + xoff + j * 64);
+                const float2 ci = lds64f(caddr + (j * NG + gi) * 32);
+                float d[4];
+                block_mma_pre(d, ah, xb, ci.x, ci.y, ci.x, ci.y);
+                block_mma_pre(d, al, xb, d[0], d[1], d[2], d[3]);
+                acc[gi][0] = fmaf(sg, d[0], acc[gi][0]);
+                acc[gi][2] = fmaf(sh, d[2], acc[gi][2]);
+                acc[gi][1] = fmaf(sg, d[1], acc[gi][1]);
+                acc[gi][3] = fmaf(sh, d[3], acc[gi][3]);
+            }
+        }
     }
     template <int XC>
     // xaddr: shared address of this lane's activations for k = kbase (row + q * 16 bytes);
@@ -638,6 +767,43 @@ template <> struct TileRegs<WF_QTYPE_Q4_K> {
                           fmaf(byte_times(wmg, 1, -g.y, ngm), xb, acc[0]));
             acc[2] = fmaf(byte_times(wsh, 1, h.x, nhd) * eb, digits_to_float(db[2], db[3]),
                           fmaf(byte_times(wmh, 1, -h.y, nhm), xb, acc[2]));
+        }
+    }
+    __device__ __forceinline__ void load_global_n(const uint8_t* tile, int lane) {
+        using T = Tile<WF_QTYPE_Q4_K>;
+        c[0] = ldg128_stream<0>(tile + lane * 16);
+        c[1] = ldg128_stream<512>(tile + lane * 16);
+        c[2] = ldg128_stream<1024>(tile + lane * 16);
+        c[3] = ldg128_stream<1536>(tile + lane * 16);
+        dd = ldg64_stream<T::D_OFF>(tile + (lane >> 2) * 8);
+        sc = ldg128_stream<T::SC_OFF>(tile + (lane >> 2) * 16);
+        mn = ldg128_stream<T::MN_OFF>(tile + (lane >> 2) * 16);
+    }
+    template <int NG>
+    __device__ __forceinline__ void compute_n(float (&acc)[NG][4], const uint32_t (&xg)[NG], uint32_t xoff, uint32_t caddr) const {
+        const float2 g = half2_bits_to_float2(dd.x), h = half2_bits_to_float2(dd.y);  // (d, dmin)
+        const float BIG = 8388608.f;
+        const float gm = g.y * 0.0625f, hm = h.y * 0.0625f;
+        const float ngd = -BIG * g.x, ngm = -BIG * gm, nhd = -BIG * h.x, nhm = -BIG * hm;
+#pragma unroll
+        for (int jj = 0; jj < 8; jj++) {
+            uint32_t a[8];
+            unpack8(a, word_of(c[(jj >> 2) * 2], jj & 3), word_of(c[(jj >> 2) * 2 + 1], jj & 3), MAGIC_16);
+            const float ag = byte_times(jj < 4 ? sc.x : sc.y, jj & 3, g.x, ngd);
+            const float ah = byte_times(jj < 4 ? sc.z : sc.w, jj & 3, h.x, nhd);
+            const float cg = byte_times(jj < 4 ? mn.x : mn.y, jj & 3, gm, ngm);
+            const float ch = byte_times(jj < 4 ? mn.z : mn.w, jj & 3, hm, nhm);
+#pragma unroll
+            for (int gi = 0; gi < NG; gi++) {
+                const uint4 xb = lds128(xg[gi] + xoff + jj * 64);
+                const float2 ci = lds64f(caddr + (jj * NG + gi) * 32);
+                float d[4];
+                block_mma_pre(d, a, xb, ci.x, ci.y, ci.x, ci.y);
+                acc[gi][0] = fmaf(ag, d[0], fmaf(cg, ci.x, acc[gi][0]));
+                acc[gi][2] = fmaf(ah, d[2], fmaf(ch, ci.x, acc[gi][2]));
+                acc[gi][1] = fmaf(ag, d[1], fmaf(cg, ci.y, acc[gi][1]));
+                acc[gi][3] = fmaf(ah, d[3], fmaf(ch, ci.y, acc[gi][3]));
+            }
         }
     }
     template <int XC>

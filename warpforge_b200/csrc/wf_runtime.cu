@@ -227,7 +227,11 @@ int wf_destroy(int64_t ctx) {
     }
     for (auto& kv : c->allocs) cudaFree(reinterpret_cast<void*>(kv.first));
     for (void* h : c->host_allocs) cudaFreeHost(h);
-    for (auto& kv : c->gemv_scratch) cudaFree(kv.second.d_slots);
+    for (auto& kv : c->gemv_scratch) {
+        cudaFree(kv.second.d_slots);
+        cudaFree(kv.second.d_part);
+        cudaFree(kv.second.d_count);
+    }
     for (cudaGraphExec_t g : c->graphs) cudaGraphExecDestroy(g);
     for (cudaEvent_t ev : c->events) cudaEventDestroy(ev);
     for (cudaStream_t s : c->streams) cudaStreamDestroy(s);
@@ -280,6 +284,8 @@ int wf_stream_destroy(int64_t ctx, int64_t stream) {
     auto sc = c->gemv_scratch.find(s);
     if (sc != c->gemv_scratch.end()) {
         cudaFree(sc->second.d_slots);
+        cudaFree(sc->second.d_part);
+        cudaFree(sc->second.d_count);
         c->gemv_scratch.erase(sc);
     }
     c->streams.erase(it);
