@@ -171,8 +171,8 @@ def test_config2_q4_0_gemv_sweep(backend, oracle, rows, k, m):
 def test_many_tokens_are_chunked(backend, oracle):
     from warpforge_b200.backend import Tensor
 
-    # fp32 activations always take the GEMV (two tokens per pass): 21 tokens = 11 passes.
-    # (More than 8 bf16 tokens go to the tensor-core GEMM, tested in test_gpu_gemm.py.)
+    # fp32 activations always take the decode kernel (ten tokens = thirty columns per launch): 21 tokens = 3 launches.
+    # (More than 32 bf16 tokens go to the tensor-core GEMM, tested in test_gpu_gemm.py.)
     rows, k, m = 128, 1024, 21
     blocks = Q.synth_q4_0(rows, k, 3)
     x = Q.synth_activation_f32(m, k, 3)
