@@ -13,8 +13,9 @@ from inside the GEMV epilogue (graph mode: an NCCL all-gather after every projec
 Strong scaling: the same token stream on more GPUs.
 The dominant kernel is the Q4_0 decode GEMV, so `roofline` is the headline "Q4_0 GEMV HBM
 GB/s (% of peak)"; `gemv_sweep` adds benchmark config 2 (the [11008x4096] / [4096x11008]
-sweep at batch 1, 4, 8, and the [32000x4096] vocabulary projection of config 4 at batch 1), one launch per
-call, timed over rotating weight copies (300 MB, larger than L2).
+sweep at batch 1, 4, 8 -- plus 16 and 32, which the same memory-bound kernel takes -- and the [32000x4096]
+vocabulary projection of config 4 at batch 1), one launch per call, timed over rotating weight copies (300 MB,
+larger than L2).
 
 Inputs are seeded synthetic GGUF blocks with the configs' value distributions; there is no
 dataset behind this path.  `--impl reference` times the CPU restatement of the reference's
@@ -45,7 +46,7 @@ WORKLOAD = ("benchmark config 4: 7B-shape Llama decode, 224 Q4_0 projections (32
 # (dram__bytes_read.sum + dram__bytes_write.sum of one launch over two layers of this workload);
 # traffic grows in proportion to the layers run and splits evenly over row shards.  To be re-captured whenever the
 # kernel changes.
-NCU_TRAFFIC_BYTES_PER_LAYER = 232.6e6 / 2
+NCU_TRAFFIC_BYTES_PER_LAYER = (227.78e6 + 4.19e6) / 2
 
 
 def tensor_peaks():
@@ -160,14 +161,14 @@ def run_reference(args) -> None:
 
 
 def gemv_sweep(ctx, hbm_peak: float) -> list:
-    """benchmark config 2: cold-HBM Q4_0 GEMV at batch 1/4/8 over 12 rotating weight copies."""
+    """benchmark config 2: cold-HBM Q4_0 GEMV at batch 1/4/8 (and 16/32) over 12 rotating weight copies."""
     from warpforge_b200 import _native as N, quant as Q
     from warpforge_b200.backend import QuantizedWeight
 
     out, lib, qt = [], ctx._lib, Q.QuantizationType.Q4_0
     iters = 120
     # the two shapes of config 2 at batch 1 / 4 / 8, and config 4's vocabulary projection (lm_head, 73.7 MB) at batch 1
-    for rows, k, batches, copies in ((11008, 4096, (1, 4, 8), 12), (4096, 11008, (1, 4, 8), 12), (32000, 4096, (1,), 4)):
+    for rows, k, batches, copies in ((11008, 4096, (1, 4, 8, 16, 32), 12), (4096, 11008, (1, 4, 8, 16, 32), 12), (32000, 4096, (1,), 4)):
         blocks = Q.synth_q4_0(rows, k, Q.config_seed(2, rows))
         ws = [QuantizedWeight(ctx, qt, blocks, rows, k) for _ in range(copies)]
         for m in batches:
@@ -197,6 +198,8 @@ def gemv_sweep(ctx, hbm_peak: float) -> list:
                         "frac_of_measured_peak": round(gbs / hbm_peak, 4), "frac_of_8TBs": round(gbs / 8000.0, 4)})
             if rows == 32000:
                 out[-1]["role"] = "lm_head of config 4 (not part of the timed step)"
+            if m > 8:
+                out[-1]["note"] = "beyond config 2's batches: the several-token decode kernel's range"
             ctx.graph_destroy(g)
             ctx.free(dx)
             ctx.free(dy)

@@ -40,6 +40,8 @@ extern "C" {
 #define WF_ERR_TOO_LARGE (-11)       /* request exceeds a fixed capacity                 */
 #define WF_ERR_GGUF (-12)            /* not a GGUF file, unsupported version or type, truncated */
 #define WF_ERR_INDEX (-13)           /* an embedding index outside the table (reported by wf_stream_sync) */
+#define WF_ERR_RECORDING (-14)       /* the call would allocate device memory while its stream is being recorded into a graph */
+#define WF_ERR_IN_USE (-15)          /* the object is still referenced (a weight held by a live program)   */
 #define WF_ERR_CUDA_BASE 1000
 #define WF_ERR_NCCL_BASE 2000
 
@@ -95,7 +97,8 @@ int wf_memcpy_d2h(int64_t ctx, void* dst, int64_t src, int64_t bytes, int64_t st
  * the device in the library's tiled layout.  The reference has no counterpart: it would
  * dequantize to fp32 on the host (QuantizedTensorView.dequantizeToArray,
  * warpforge-data/.../quant/QuantizedTensorView.java:161-166) and upload 4 bytes per weight.
- * `blocks` points at the FULL tensor; only the shard is copied. */
+ * `blocks` points at the FULL tensor; only the shard is copied.  wf_weight_free returns
+ * WF_ERR_IN_USE while a live program (wf_program_create) holds the weight. */
 int wf_weight_upload(int64_t ctx, int qtype, const void* blocks, int64_t n_rows, int64_t k, int shard_rank,
                      int shard_world, int64_t* weight);
 int wf_weight_free(int64_t ctx, int64_t weight);
@@ -184,9 +187,11 @@ int wf_embedding(int64_t ctx, int64_t indices_dev, int64_t table_dev, int64_t y_
  * x_dtype is WF_DTYPE_BF16 or WF_DTYPE_F32.  x / y are device pointers (x_on_device /
  * y_on_device non-zero) or host pointers; host buffers are staged through pinned memory
  * and the call returns after the result is in `y`.  With device pointers the call only
- * enqueues work on `stream`.  Up to 8 bf16 tokens (2 fp32 tokens) per pass run on the decode GEMV;
- * more bf16 tokens run on the tensor-core GEMM, whose activation copy and tile-piece scratch belong
- * to the context: many-token calls of one context must not overlap on different streams. */
+ * enqueues work on `stream`; with a host pointer it waits for the result and reports a bounded
+ * device-side wait that ran out as WF_ERR_DEVICE_WAIT, like wf_stream_sync.  Up to 32 bf16 tokens
+ * (10 fp32 tokens) per launch run on the memory-bound decode kernels; more bf16 tokens run on the
+ * tensor-core GEMM, whose activation copy and tile-piece scratch belong to the context: many-token
+ * calls of one context must not overlap on different streams. */
 int wf_qlinear(int64_t ctx, int64_t weight, const void* x, int x_dtype, int x_on_device, int64_t m, void* y,
                int y_on_device, int64_t stream);
 
@@ -274,7 +279,11 @@ int wf_ipc_close(int64_t ctx, int64_t dptr);
  * A decode step is hundreds of microsecond-scale kernels, so the backend instead records a
  * sequence of device-pointer calls (wf_qlinear, wf_qlinear_allgather, wf_allgather, copies)
  * issued on `stream` between begin and end into a CUDA graph and replays it with one launch.
- * Only calls with device pointers may be recorded. */
+ * Only calls with device pointers may be recorded.  Nothing is allocated while a stream is being
+ * recorded: wf_graph_begin sizes the decode kernels' scratch, and a recorded call that would have to
+ * allocate or grow another buffer (the GEMM's activation copy and piece buffers, the gather buffer of
+ * wf_qlinear_allgather) returns WF_ERR_RECORDING and records nothing -- issue the same call once
+ * before wf_graph_begin. */
 int wf_graph_begin(int64_t ctx, int64_t stream);
 int wf_graph_end(int64_t ctx, int64_t stream, int64_t* graph);
 int wf_graph_launch(int64_t ctx, int64_t graph, int64_t stream);

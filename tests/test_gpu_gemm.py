@@ -130,3 +130,34 @@ def test_gemm_recorded_in_a_graph_replays_with_new_activations(oracle):
         w.close()
     finally:
         ctx.close()
+
+
+def test_recording_refuses_to_allocate():
+    """A many-token wf_qlinear recorded without having run once would have to allocate its scratch inside the
+    recording: it is refused with a status of its own, the recording stays usable, and after one eager call the
+    same recording works."""
+    from warpforge_b200 import _native as N
+    from warpforge_b200.backend import CudaContext, QuantizedWeight
+
+    ctx = CudaContext(0)
+    lib = ctx._lib
+    try:
+        rows, k, m = 256, 1024, 64
+        w = QuantizedWeight(ctx, Q.QuantizationType.Q4_0, Q.synth_q4_0(rows, k, 17), rows, k)
+        xb = Q.synth_activation_bf16(m, k, 17)
+        dx, dy = ctx.allocate(xb.nbytes), ctx.allocate(m * rows * 4)
+        ctx.copy_to_device(dx, xb)
+        ctx.graph_begin()
+        assert lib.wf_qlinear(ctx.handle, w.handle, dx, N.WF_DTYPE_BF16, 1, m, dy, 1, 0) == N.WF_ERR_RECORDING
+        ctx.graph_destroy(ctx.graph_end())  # an empty graph: nothing was recorded, nothing was broken
+        ctx._ck("wf_qlinear", lib.wf_qlinear(ctx.handle, w.handle, dx, N.WF_DTYPE_BF16, 1, m, dy, 1, 0))
+        ctx.synchronize()
+        ctx.graph_begin()
+        ctx._ck("wf_qlinear", lib.wf_qlinear(ctx.handle, w.handle, dx, N.WF_DTYPE_BF16, 1, m, dy, 1, 0))
+        g = ctx.graph_end()
+        ctx.graph_launch(g)
+        ctx.synchronize()
+        ctx.graph_destroy(g)
+        w.close()
+    finally:
+        ctx.close()

@@ -257,3 +257,23 @@ def test_two_rank_program_gathers_through_peer_memory(tmp_path):
                         "127.0.0.1", "--master-port", "29533", str(script)], capture_output=True, text=True, timeout=600, env=env)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert "RANK_OK 0" in r.stdout and "RANK_OK 1" in r.stdout
+
+
+def test_weight_held_by_a_program_cannot_be_freed():
+    """The program's op list points into the weights' device memory: wf_weight_free refuses while the program
+    lives and works once it is destroyed."""
+    from warpforge_b200 import _native as N
+    from warpforge_b200.backend import CudaContext
+    from warpforge_b200.decode import LLAMA_7B_Q4_0, ProjectionStack
+
+    ctx = CudaContext(0)
+    try:
+        st = ProjectionStack(ctx, LLAMA_7B_Q4_0, tokens=1, layers=1)
+        st.build_program()
+        w = st.weights[0][0]
+        assert ctx._lib.wf_weight_free(ctx.handle, w.handle) == N.WF_ERR_IN_USE
+        st.run_program()  # still whole
+        ctx.synchronize()
+        st.close()  # destroys the program first, then frees every weight
+    finally:
+        ctx.close()

@@ -48,6 +48,8 @@ def test_status_names():
     assert lib.wf_error_string(N.WF_ERR_SHAPE) == b"WF_ERR_SHAPE"
     assert lib.wf_error_string(N.WF_ERR_UNSUPPORTED_TYPE) == b"WF_ERR_UNSUPPORTED_TYPE"
     assert lib.wf_error_string(1002) == b"cudaErrorMemoryAllocation"
+    assert lib.wf_error_string(N.WF_ERR_RECORDING) == b"WF_ERR_RECORDING"
+    assert lib.wf_error_string(N.WF_ERR_IN_USE) == b"WF_ERR_IN_USE"
 
 
 def test_invalid_handles_and_arguments_without_a_device():

@@ -89,6 +89,7 @@ WF_ERR_INVALID_ARGUMENT, WF_ERR_INVALID_HANDLE, WF_ERR_UNSUPPORTED_TYPE, WF_ERR_
 WF_ERR_SHARD, WF_ERR_BUSY, WF_ERR_NO_DEVICE, WF_ERR_NOT_SM100 = -5, -6, -7, -8
 WF_ERR_NCCL_UNAVAILABLE, WF_ERR_DEVICE_WAIT, WF_ERR_TOO_LARGE, WF_ERR_GGUF = -9, -10, -11, -12
 WF_ERR_INDEX = -13
+WF_ERR_RECORDING, WF_ERR_IN_USE = -14, -15
 WF_Q4_0_ORDER_REFERENCE, WF_Q4_0_ORDER_GGML = 0, 1
 WF_DTYPE_F32, WF_DTYPE_BF16 = 0, 1
 WF_OP_NEW_X, WF_OP_DEPENDS = 1, 2

@@ -2,7 +2,7 @@
 dot_general path, over the C ABI in include/wfb200.h.
 
 The names follow the Java they stand in for (no JDK exists on the build or GPU machines,
-so the host side is Python; the Java binding a maintainer would add is in INTEGRATION.md):
+so the host side is Python; a Java binding would wrap the same C entry points one to one):
 
 * ``DotDimensionNumbers`` / ``DotGeneralOp`` -- the StableHLO records
   (snakeburger-core/src/main/java/io/surfworks/snakeburger/stablehlo/StableHloAst.java:211-239, 306-321).

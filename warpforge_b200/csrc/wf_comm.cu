@@ -209,6 +209,8 @@ int wf_qlinear_allgather(int64_t ctx, int64_t comm, int64_t weight, const void* 
     }
     const int64_t need = (int64_t)k->world * m * rows * 4 + m * rows * 4;
     if (need > k->tmp_bytes) {
+        const int rc = refuse_allocation_while_recording(c, s, "the gather buffer");
+        if (rc != WF_OK) return rc;
         if (k->d_tmp) cudaFree(k->d_tmp);
         k->d_tmp = nullptr;
         k->tmp_bytes = 0;

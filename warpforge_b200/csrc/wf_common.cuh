@@ -33,6 +33,7 @@ struct Weight {
     int64_t row0 = 0;        // first global row of this shard
     int64_t total_rows = 0;  // rows of the unsharded tensor
     uint8_t* d_tiles = nullptr;
+    int programs = 0;        // live programs whose op lists point at d_tiles
 };
 
 // Scratch for the GEMV fix-up between CTAs, one per stream that launches GEMVs.
@@ -83,6 +84,13 @@ struct Context {
 
 int set_error(Context* c, int status, const char* fmt, ...);
 int cuda_status(Context* c, cudaError_t e, const char* what);
+// Reads and clears the device status word after the stream has been waited for: WF_OK, or the failure a
+// kernel recorded there (a bounded wait that ran out, an index outside a table).
+int read_device_status(Context* c);
+// WF_OK, or WF_ERR_RECORDING when `s` is being recorded into a graph: the caller is about to allocate (or
+// grow) `what`, which a recording must not do -- recorded nodes would keep pointing at memory a later call
+// frees.  Running the same call once before wf_graph_begin sizes everything.
+int refuse_allocation_while_recording(Context* c, cudaStream_t s, const char* what);
 Context* get_context(int64_t h);
 Weight* get_weight(Context* c, int64_t h);
 cudaStream_t resolve_stream(Context* c, int64_t stream);

@@ -1,10 +1,15 @@
 // A decode step as ONE persistent kernel: a "program" of quantized GEMVs (the projections of
-// a token, in order) run by one CTA per SM.  The weight tiles of consecutive projections flow
-// through the same shared-memory ring without a break: the producer thread of each CTA walks
-// the whole program and keeps issuing bulk copies whenever a stage frees, so HBM stays busy
-// while the consumer warps finish one projection, synchronise, and stage the next
-// activations.  This removes the per-launch prologue and tail that dominate microsecond-scale
-// GEMV kernels.
+// a token, in order) run by one CTA per SM.  This removes the per-launch prologue and tail that
+// dominate microsecond-scale GEMV kernels, and lets the weights of the next projection be on
+// their way while the current one finishes.
+//
+// One token (gemv1_program_kernel): every warp streams its own run of tiles from global memory
+// straight into registers (wf_gemv_stream.cuh); its load requests run ahead over the following
+// projections, so the first tiles of the next projection are in flight while the grid barrier and
+// the staging of the next activations run.  Projections that read the same activations (Wq / Wk /
+// Wv, Wgate / Wup) are cut as one list of row-tiles.  Several tokens (gemv_program_kernel): the
+// producer thread of each CTA walks the whole program and keeps a shared-memory ring of tiles full
+// with bulk copies; sixteen consumer warps take their tile out of each ring stage.
 //
 // Projections that read an earlier projection's output are separated by a grid barrier
 // (an arrival counter in global memory, bounded spins).  With row-sharded tensor parallelism
@@ -14,10 +19,12 @@
 // and before the barrier each rank's CTAs poll their slice of the landing buffer until the
 // tag of the current barrier shows, copying the values into the plain y.  No collective is
 // launched.  (No multicast loads and no waits between separately launched kernels on one
-// GPU are involved: each rank runs exactly one kernel on its own GPU.)
+// GPU are involved: each rank runs exactly one kernel on its own GPU.)  The tag is the barrier's
+// number since the program was created, cut to 32 bits; a landing buffer is written again two
+// dependent barriers later at the earliest, so a stale tag could only be mistaken for a current
+// one after 2^32 barriers without the buffer being rewritten, which cannot happen.
 //
-// Per-op work split, fix-up between CTAs and the arithmetic are those of gemv_kernel
-// (wf_gemv.cu); the arithmetic replaces the reference's per-op launches at
+// The arithmetic replaces the reference's per-op launches at
 // warpforge-backend-nvidia/src/main/java/io/surfworks/warpforge/backend/nvidia/ops/DotGeneralKernel.java:263-283.
 #include <string.h>
 
@@ -425,6 +432,7 @@ __global__ void __launch_bounds__(GEMV_CONSUMERS, 1) gemv1_program_kernel(const 
 struct Program {
     uint32_t magic = 0x57465047;  // "WFPG"
     Context* ctx = nullptr;
+    std::vector<Weight*> held;    // the op list points into these weights: they cannot be freed while the program lives
     int qtype = 0, n_ops = 0, m = 0, world = 1, rank = 0;
     ProgOp* d_ops = nullptr;
     ProgSync* d_sync = nullptr;
@@ -605,6 +613,7 @@ int wf_program_create(int64_t ctx, int n_ops, const int64_t* weights, const int6
 
     Program* pr = new Program();
     pr->ctx = c;
+    for (int o = 0; o < n_ops; o++) pr->held.push_back(get_weight(c, weights[o]));
     pr->qtype = qt;
     pr->n_ops = n_ops;
     pr->m = (int)m;
@@ -649,6 +658,7 @@ int wf_program_create(int64_t ctx, int n_ops, const int64_t* weights, const int6
             P.timing = pr->d_timing;
         }
     }
+    for (Weight* w : pr->held) w->programs++;
     {
         std::lock_guard<std::mutex> g(g_prog_mu);
         g_programs.push_back(pr);
@@ -709,6 +719,7 @@ int wf_program_destroy(int64_t ctx, int64_t program) {
     cudaFree(pr->d_scratch);
     cudaFree(pr->d_shares);
     if (pr->d_timing) cudaFree(pr->d_timing);
+    for (Weight* w : pr->held) w->programs--;
     pr->magic = 0;
     delete pr;
     return WF_OK;

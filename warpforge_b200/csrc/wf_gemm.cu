@@ -1038,6 +1038,8 @@ int gemm_launch(Context* c, const GemvCall& call, cudaStream_t s) {
     // activation pre-pass into the context's fp16 scratch (grown on demand)
     const int64_t x16_bytes = ((call.m * w.g.k * 2 + 255) & ~255LL) + call.m * 4;
     if (x16_bytes > c->x16_bytes) {
+        const int rc = refuse_allocation_while_recording(c, s, "the fp16 activation scratch");
+        if (rc != WF_OK) return rc;
         if (c->d_x16) cudaFree(c->d_x16);
         c->d_x16 = nullptr;
         c->x16_bytes = 0;
@@ -1074,6 +1076,8 @@ int gemm_launch(Context* c, const GemvCall& call, cudaStream_t s) {
     p.unit_q = (int)(units / grid);
     p.unit_r = (int)(units % grid);
     if (!c->d_gemm_partial) {
+        const int rc = refuse_allocation_while_recording(c, s, "the GEMM's piece buffers");
+        if (rc != WF_OK) return rc;
         WF_CUDA(c, cudaMalloc(&c->d_gemm_partial, (size_t)c->sm_count * GEMM_PIECE_TOKENS * GEMM_BN * sizeof(float)));
         WF_CUDA(c, cudaMalloc(&c->d_gemm_ready, ((size_t)c->sm_count * 4 + 2) * sizeof(unsigned int)));
         WF_CUDA(c, cudaMemset(c->d_gemm_ready, 0, ((size_t)c->sm_count * 4 + 2) * sizeof(unsigned int)));

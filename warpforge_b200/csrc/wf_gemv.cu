@@ -162,6 +162,8 @@ static cudaError_t launch_qt_several(int qt, const GemvNParams& p, int grid, siz
 int gemv_prepare_stream(Context* c, cudaStream_t s) {
     GemvScratch& sc = c->gemv_scratch[s];
     if (sc.ctas >= c->sm_count) return WF_OK;
+    const int rc = refuse_allocation_while_recording(c, s, "the decode kernels' scratch");
+    if (rc != WF_OK) return rc;
     if (sc.d_slots) cudaFree(sc.d_slots);
     if (sc.d_part) cudaFree(sc.d_part);
     if (sc.d_count) cudaFree(sc.d_count);

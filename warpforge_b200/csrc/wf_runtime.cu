@@ -293,10 +293,10 @@ int wf_stream_destroy(int64_t ctx, int64_t stream) {
     return WF_OK;
 }
 
-int wf_stream_sync(int64_t ctx, int64_t stream) {
-    WF_ENTER(ctx);
-    cudaStream_t s = resolve_stream(c, stream);
-    WF_CUDA(c, cudaStreamSynchronize(s));
+}  // extern "C"
+
+namespace wf {
+int read_device_status(Context* c) {
     int st = 0;
     WF_CUDA(c, cudaMemcpy(&st, c->d_status, sizeof st, cudaMemcpyDeviceToHost));
     if (st != 0) {
@@ -305,6 +305,26 @@ int wf_stream_sync(int64_t ctx, int64_t stream) {
         return set_error(c, WF_ERR_DEVICE_WAIT, "a device-side bounded wait expired (status bits 0x%x)", st);
     }
     return WF_OK;
+}
+
+int refuse_allocation_while_recording(Context* c, cudaStream_t s, const char* what) {
+    cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(s, &st) != cudaSuccess) {
+        cudaGetLastError();
+        return WF_OK;
+    }
+    if (st == cudaStreamCaptureStatusNone) return WF_OK;
+    return set_error(c, WF_ERR_RECORDING, "%s would be allocated while the stream is being recorded: run the call once before wf_graph_begin", what);
+}
+}  // namespace wf
+
+extern "C" {
+
+int wf_stream_sync(int64_t ctx, int64_t stream) {
+    WF_ENTER(ctx);
+    cudaStream_t s = resolve_stream(c, stream);
+    WF_CUDA(c, cudaStreamSynchronize(s));
+    return read_device_status(c);
 }
 
 int wf_malloc(int64_t ctx, int64_t bytes, int64_t* dptr) {
@@ -427,6 +447,8 @@ int wf_weight_free(int64_t ctx, int64_t weight) {
     WF_ENTER(ctx);
     Weight* w = get_weight(c, weight);
     if (!w) return WF_ERR_INVALID_HANDLE;
+    if (w->programs > 0)
+        return set_error(c, WF_ERR_IN_USE, "weight is referenced by %d live program(s): destroy them first", w->programs);
     c->weights.erase(std::find(c->weights.begin(), c->weights.end(), w));
     WF_CUDA(c, cudaStreamSynchronize(c->stream));
     cudaFree(w->d_tiles);
@@ -466,7 +488,7 @@ int wf_dequant_rows(int64_t ctx, int64_t weight, int64_t row0, int64_t nrows, fl
     cudaFree(d_out);
     if (e != cudaSuccess) return cuda_status(c, e, "dequant rows");
     c->launches++;
-    return WF_OK;
+    return read_device_status(c);
 }
 
 int wf_qlinear(int64_t ctx, int64_t weight, const void* x, int x_dtype, int x_on_device, int64_t m, void* y,
@@ -510,8 +532,10 @@ int wf_qlinear(int64_t ctx, int64_t weight, const void* x, int x_dtype, int x_on
         WF_CUDA(c, cudaMemcpyAsync(static_cast<uint8_t*>(c->h_stage) + yo, d_y, (size_t)yb, cudaMemcpyDeviceToHost, s));
         WF_CUDA(c, cudaStreamSynchronize(s));
         memcpy(y, static_cast<uint8_t*>(c->h_stage) + yo, (size_t)yb);
+        return read_device_status(c);  // the result is in the caller's hands: a wait that ran out must not pass as success
     } else if (!x_on_device) {
         WF_CUDA(c, cudaStreamSynchronize(s));  // the staging buffer is reused by the next call
+        return read_device_status(c);
     }
     return WF_OK;
 }
@@ -594,6 +618,8 @@ const char* wf_error_string(int status) {
         case WF_ERR_TOO_LARGE: return "WF_ERR_TOO_LARGE";
         case WF_ERR_GGUF: return "WF_ERR_GGUF";
         case WF_ERR_INDEX: return "WF_ERR_INDEX";
+        case WF_ERR_RECORDING: return "WF_ERR_RECORDING";
+        case WF_ERR_IN_USE: return "WF_ERR_IN_USE";
         default: break;
     }
     if (status >= WF_ERR_NCCL_BASE) return "WF_ERR_NCCL";
