@@ -34,6 +34,13 @@ struct Weight {
     int64_t total_rows = 0;  // rows of the unsharded tensor
     uint8_t* d_tiles = nullptr;
     int programs = 0;        // live programs whose op lists point at d_tiles
+    // how the several-token decode kernel cuts this weight, per activation dtype (bf16 / fp32) and column count:
+    // {slices, k-tiles per slice, team size, uses partial sums}, slices = -1 until first asked for (0: no cut fits)
+    short split_cache[2][33][4];
+    Weight() {
+        for (auto& a : split_cache)
+            for (auto& b : a) b[0] = -1;
+    }
 };
 
 // Scratch for the GEMV fix-up between CTAs, one per stream that launches GEMVs.

@@ -79,18 +79,37 @@ __global__ void __launch_bounds__(GEMV_CONSUMERS, 1) gemv1_kernel(const GemvPara
 // ---------------------------------------------------------------- host side
 constexpr size_t GEMV_SMEM_LIMIT = 227 * 1024;
 
+// The cut of a weight for `cols` activation columns, worked out once per weight (the search walks a few thousand
+// candidates: too slow for every call of a microsecond-scale kernel).
+static GemvNPlan cached_plan(int sm_count, const Weight& w, int cols, bool x_f32) {
+    short* e = const_cast<Weight&>(w).split_cache[x_f32 ? 1 : 0][cols];
+    if (e[0] < 0) {
+        const GemvNPlan p = gemvn_plan(sm_count, w.g.qtype, w.g.rt, w.g.kt, cols, x_f32);
+        e[1] = (short)p.kc;
+        e[2] = (short)p.team;
+        e[3] = (short)p.uses_part;
+        e[0] = (short)p.slices;
+    }
+    GemvNPlan p;
+    p.slices = e[0];
+    p.kc = e[1];
+    p.team = e[2];
+    p.uses_part = e[3] != 0;
+    return p;
+}
+
 // Activation columns one launch of the several-token kernel can take for this weight: at most 32, fewer when the
 // partial sums of a k-sliced launch would not fit their buffer (very tall weights).
 static int gemvn_cols_per_pass(int sm_count, const Weight& w, bool x_f32) {
     for (int cols = GEMVN_MAX_COLS; cols >= (x_f32 ? 3 : 1); cols--)
-        if (gemvn_plan(sm_count, w.g.qtype, w.g.rt, w.g.kt, cols, x_f32).slices > 0) return cols;
+        if (cached_plan(sm_count, w, cols, x_f32).slices > 0) return cols;
     return 0;
 }
 
 // Largest number of tokens one launch can take (0: the weight does not fit any kernel).
 int gemv_max_tokens_per_pass(const Weight& w, int x_dtype) {
     const bool f32 = x_dtype == WF_DTYPE_F32;
-    const int cols = gemvn_cols_per_pass(148, w, f32);
+    const int cols = gemvn_cols_per_pass(w.ctx ? w.ctx->sm_count : 148, w, f32);
     const int n = f32 ? cols / 3 : cols;
     if (n == 0 && !f32 && ws_fits((int)w.g.kt * tile_k(w.g.qtype), 0)) return 1;
     return n;
@@ -244,7 +263,7 @@ static int launch_passes(Context* c, const GemvCall& call, cudaStream_t s, const
         p.m = (int)std::min<int64_t>(call.m - m0, per_pass);
         p.x_f32 = f32;
         p.cols = p.m * per_tok;
-        const GemvNPlan plan = gemvn_plan(c->sm_count, qt, w.g.rt, w.g.kt, p.cols, f32);
+        const GemvNPlan plan = cached_plan(c->sm_count, w, p.cols, f32);
         if (plan.slices < 1) return set_error(c, WF_ERR_TOO_LARGE, "no split of K=%lld fits %d activation columns", (long long)w.g.k, p.cols);
         p.slices = plan.slices;
         p.kc = plan.kc;
