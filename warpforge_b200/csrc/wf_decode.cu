@@ -399,7 +399,7 @@ __global__ void __launch_bounds__(GEMV_CONSUMERS, 1) gemv1_program_kernel(const 
             if (flags & OP_DEPENDS) run.grid_barrier(o);
             else run.consumers_sync();  // the staged activations are about to be replaced
             stamp();
-            stage_x_q8<R::BETA_INT>(op.x, op.k, xd, recs, kt * T::K, GEMV_CONSUMERS);
+            stage_x_q8<R::BETA_INT, false>(op.x, op.k, xd, recs, kt * T::K, GEMV_CONSUMERS);
             run.consumers_sync();
             stamp();
         } else {

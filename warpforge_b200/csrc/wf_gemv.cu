@@ -1,9 +1,9 @@
 // Decode GEMV, y[m, rows] = x[m, K] . W[rows, K]^T with W in the tiled quantized layout of wf_layout.cuh: the launch side
 // and the one-token kernel.  HBM-bound: every weight byte is read exactly once, from global memory straight into
 // the registers of the warp that multiplies it.
-//   * one bf16 token: gemv1_kernel below (integer MMAs on exact base-256 digits of the activations,
+//   * one token, bf16 or fp32: gemv1_kernel below (integer MMAs on exact base-256 digits of the activations,
 //     wf_gemv_stream.cuh);
-//   * 2 .. 32 activation columns (bf16 tokens, or fp32 tokens as three exact bf16 columns each): gemvn_kernel
+//   * 2 .. 32 activation columns (bf16 tokens, or two and more fp32 tokens as three exact bf16 columns each): gemvn_kernel
 //     (bf16 MMAs, k-sliced units, wf_gemv_multi.cuh); more tokens than that go through it in passes, or to the
 //     tensor-core GEMM (wf_gemm.cu) where the caller routes them there.
 //
@@ -14,7 +14,7 @@
 
 namespace wf {
 
-// ---------------------------------------------------------------- one bf16 token
+// ---------------------------------------------------------------- one token
 // Integer MMAs on exact base-256 digits of the activations, every warp streaming its own run of tiles from
 // global memory into registers (wf_gemv_stream.cuh).  512 threads, all of them consumers.
 template <int QT>
@@ -58,7 +58,8 @@ __global__ void __launch_bounds__(GEMV_CONSUMERS, 1) gemv1_kernel(const GemvPara
 
     asm volatile("griddepcontrol.wait;" ::: "memory");
     stamp(0);
-    stage_x_q8<R::BETA_INT>(p.x, p.k, xd, recs, kp, GEMV_CONSUMERS);
+    if (p.x_f32) stage_x_q8<R::BETA_INT, true>(p.x, p.k, xd, recs, kp, GEMV_CONSUMERS);
+    else stage_x_q8<R::BETA_INT, false>(p.x, p.k, xd, recs, kp, GEMV_CONSUMERS);
     __syncthreads();
     stamp(1);
     auto emit_row = [&](int n, float v) {
@@ -111,7 +112,7 @@ int gemv_max_tokens_per_pass(const Weight& w, int x_dtype) {
     const bool f32 = x_dtype == WF_DTYPE_F32;
     const int cols = gemvn_cols_per_pass(w.ctx ? w.ctx->sm_count : 148, w, f32);
     const int n = f32 ? cols / 3 : cols;
-    if (n == 0 && !f32 && ws_fits((int)w.g.kt * tile_k(w.g.qtype), 0)) return 1;
+    if (n == 0 && ws_fits((int)w.g.kt * tile_k(w.g.qtype), 0)) return 1;
     return n;
 }
 
@@ -214,7 +215,7 @@ static int launch_passes(Context* c, const GemvCall& call, cudaStream_t s, const
     const int kp = (int)w.g.kt * tile_k(qt);
     const bool f32 = call.x_dtype == WF_DTYPE_F32;
     const size_t esz = f32 ? 4 : 2;
-    if (!f32 && call.m == 1 && ws_fits(kp, 0)) {  // one bf16 token: the integer path, every warp streaming its own run
+    if (call.m == 1 && ws_fits(kp, 0)) {  // one token (bf16 or fp32): the integer path, every warp streaming its own run
         const WsSplit one = ws_split(c->sm_count, w.g.rt, w.g.kt);
         GemvParams p{};
         p.tiles = w.d_tiles;
@@ -231,6 +232,7 @@ static int launch_passes(Context* c, const GemvCall& call, cudaStream_t s, const
         p.kt = (int)w.g.kt;
         p.rt = (int)w.g.rt;
         p.m = 1;
+        p.x_f32 = f32;
         p.chunk_q = one.chunk_q;
         p.chunk_r = one.chunk_r;
         p.aligned = one.aligned;

@@ -1118,26 +1118,35 @@ static __device__ void stage_x_bf16(const GemvParams& p, uint8_t* xs, float* cin
     }
 }
 
-// One bf16 token for the integer path (layout and arithmetic: see pair_imma).  Per 32-k block the four
+// One token for the integer path (layout and arithmetic: see pair_imma).  Per 32-k block the four
 // threads that hold it find the largest magnitude, whose exponent field e (at least 40, so that every factor
 // below is a normal float) fixes the block's scale: X = trunc(x * 2^(156 - e)) is an integer below 2^30,
 // exact for every element within 2^-22 of the block's largest.  (X + 0x808080) XOR 0x808080 holds, byte by
 // byte, the four signed base-256 digits of X.  A block holding Inf (and no NaN) is staged as signs only with
 // an infinite factor, one holding a NaN with a NaN factor.  recs: 16 bytes per block of records followed by 8
 // bytes per block of activation sums.
-template <int BETA_INT>
+// F32: the token is fp32 instead of bf16 -- the same staging (an fp32 element has 24 significant bits, X keeps 30
+// below the block's largest magnitude, so elements within 2^-6 of it are exact and the others are cut at 2^-30 of it).
+template <int BETA_INT, bool F32>
 static __device__ __noinline__ void stage_x_q8(const void* x, int k, uint8_t* xd, uint8_t* recs, int kp, int nthreads) {
     const int groups = kp >> 3, padded = (groups + 31) & ~31, kgroups = k >> 3;
     const uint4* src = static_cast<const uint4*>(x);
     uint8_t* sums = recs + (size_t)(kp >> 5) * 16;  // the activation sums follow the records
-    constexpr int U = 3;  // loads in flight per thread
+    constexpr int U = F32 ? 2 : 3;  // element groups in flight per thread
     for (int c0 = threadIdx.x; c0 < padded; c0 += nthreads * U) {  // warp-uniform trip counts
-        uint4 pre[U];
+        uint4 pre[U], pre2[U];
 #pragma unroll
         for (int u = 0; u < U; u++) {
             const int c8 = c0 + u * nthreads;
-            pre[u] = make_uint4(0u, 0u, 0u, 0u);
-            if (c8 < kgroups) pre[u] = __ldcg(src + c8);
+            pre[u] = pre2[u] = make_uint4(0u, 0u, 0u, 0u);
+            if (c8 < kgroups) {
+                if (F32) {
+                    pre[u] = __ldcg(src + 2 * c8);
+                    pre2[u] = __ldcg(src + 2 * c8 + 1);
+                } else {
+                    pre[u] = __ldcg(src + c8);
+                }
+            }
         }
 #pragma unroll
         for (int u = 0; u < U; u++) {
@@ -1146,10 +1155,16 @@ static __device__ __noinline__ void stage_x_q8(const void* x, int k, uint8_t* xd
             const uint4 v = pre[u];
             const uint32_t w[4] = {v.x, v.y, v.z, v.w};
             float f[8];
+            if (F32) {
+                const uint4 v2 = pre2[u];
+                f[0] = __uint_as_float(v.x); f[1] = __uint_as_float(v.y); f[2] = __uint_as_float(v.z); f[3] = __uint_as_float(v.w);
+                f[4] = __uint_as_float(v2.x); f[5] = __uint_as_float(v2.y); f[6] = __uint_as_float(v2.z); f[7] = __uint_as_float(v2.w);
+            } else {
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
-                f[2 * i] = __uint_as_float(w[i] << 16);
-                f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+                for (int i = 0; i < 4; i++) {
+                    f[2 * i] = __uint_as_float(w[i] << 16);
+                    f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+                }
             }
             float sum = ((f[0] + f[1]) + (f[2] + f[3])) + ((f[4] + f[5]) + (f[6] + f[7]));
             float amax = fmaxf(fmaxf(fmaxf(fabsf(f[0]), fabsf(f[1])), fmaxf(fabsf(f[2]), fabsf(f[3]))),
