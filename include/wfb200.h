@@ -261,6 +261,26 @@ int wf_allgather(int64_t ctx, int64_t comm, int64_t send_dev, int64_t recv_dev, 
 #define WF_OP_DEPENDS 2
 int wf_program_create(int64_t ctx, int n_ops, const int64_t* weights, const int64_t* x_dev, const int64_t* y_dev,
                       const int* flags, int64_t m, int world, int rank, const int64_t* landing_dev, int64_t* program);
+/* The same with the fp32 operations that sit between a decoder layer's projections fused into the one-token
+ * kernel (m = 1), so that a projection reads the previous ones' fp32 outputs directly and no kernel runs in
+ * between (the reference runs each as its own custom_call / elementwise op with an allocation, two copies and a
+ * synchronisation: nvidia/ops/CudaCustomCallKernel.java:50-59, CPU arithmetic at
+ * cpu/ops/scalar/CustomCallKernel.java:173-224 (rms_norm), :262-280 (silu), MultiplyKernel, AddKernel).
+ * Per op o (each array may be NULL = all zero):
+ *   x_kind[o]  WF_X_BF16 (0): x_dev[o] is a bf16 row, as in wf_program_create;  WF_X_F32 (1): an fp32 row;
+ *              WF_X_RMSNORM_F32 (2): x = rms_norm(x_dev[o] fp32, gamma = x_aux_dev[o] fp32 or 0, eps[o]);
+ *              WF_X_SWIGLU_F32 (3): x = silu(x_dev[o]) * x_aux_dev[o], both fp32 rows of length k.
+ *              Only the op that stages new activations (WF_OP_NEW_X) is looked at.
+ *   residual_dev[o]  0, or an fp32 row [n_total] added to the result before it is stored (and before it is sent
+ *              to the other ranks); may be y_dev[o] itself (h += W x). */
+#define WF_X_BF16 0
+#define WF_X_F32 1
+#define WF_X_RMSNORM_F32 2
+#define WF_X_SWIGLU_F32 3
+int wf_program_create_fused(int64_t ctx, int n_ops, const int64_t* weights, const int64_t* x_dev, const int64_t* y_dev,
+                            const int* flags, const int* x_kind, const int64_t* x_aux_dev, const float* eps,
+                            const int64_t* residual_dev, int64_t m, int world, int rank, const int64_t* landing_dev,
+                            int64_t* program);
 int wf_program_run(int64_t ctx, int64_t program, int64_t stream);
 int wf_program_destroy(int64_t ctx, int64_t program);
 /* With wf_set_salt(ctx, 2) before wf_program_create: [sm_count][64] globaltimer stamps of the first ops

@@ -63,6 +63,8 @@ SIGNATURES = {
     "wf_comm_destroy": (c_int, [c_i64, c_i64]),
     "wf_allgather": (c_int, [c_i64, c_i64, c_i64, c_i64, c_i64, c_i64]),
     "wf_program_create": (c_int, [c_i64, c_int, P(c_i64), P(c_i64), P(c_i64), P(c_int), c_i64, c_int, c_int, P(c_i64), P(c_i64)]),
+    "wf_program_create_fused": (c_int, [c_i64, c_int, P(c_i64), P(c_i64), P(c_i64), P(c_int), P(c_int), P(c_i64), P(ctypes.c_float),
+                                        P(c_i64), c_i64, c_int, c_int, P(c_i64), P(c_i64)]),
     "wf_program_run": (c_int, [c_i64, c_i64, c_i64]),
     "wf_program_destroy": (c_int, [c_i64, c_i64]),
     "wf_program_read_timing": (c_int, [c_i64, c_i64, P(c_i64), c_i64]),
@@ -90,6 +92,7 @@ WF_ERR_SHARD, WF_ERR_BUSY, WF_ERR_NO_DEVICE, WF_ERR_NOT_SM100 = -5, -6, -7, -8
 WF_ERR_NCCL_UNAVAILABLE, WF_ERR_DEVICE_WAIT, WF_ERR_TOO_LARGE, WF_ERR_GGUF = -9, -10, -11, -12
 WF_ERR_INDEX = -13
 WF_ERR_RECORDING, WF_ERR_IN_USE = -14, -15
+WF_X_BF16, WF_X_F32, WF_X_RMSNORM_F32, WF_X_SWIGLU_F32 = 0, 1, 2, 3
 WF_Q4_0_ORDER_REFERENCE, WF_Q4_0_ORDER_GGML = 0, 1
 WF_DTYPE_F32, WF_DTYPE_BF16 = 0, 1
 WF_OP_NEW_X, WF_OP_DEPENDS = 1, 2

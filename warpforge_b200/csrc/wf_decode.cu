@@ -48,6 +48,11 @@ struct ProgOp {
     int rows, k, kt, rt;
     int chunk_q, chunk_r;      // CTA b < ctas owns tiles [b*q + min(b,r), (b+1)*q + min(b+1,r)); the others none
     int flags, ctas;
+    // one-token kernel: what is fused into the staging of x and into the store of y
+    int x_kind;                // XK_BF16 / XK_F32 / XK_RMSNORM_F32 / XK_SWIGLU_F32 (wf_gemv_core.cuh)
+    float eps;                 // rms_norm
+    const float* x_aux;        // rms_norm: gamma [k] or null; swiglu: the up projection's output [k]
+    const float* residual;     // y[n] = (x . W[n]) + residual[n] (null: plain store); may be y itself
 };
 
 struct ProgSync {                     // device memory owned by the program
@@ -390,6 +395,7 @@ __global__ void __launch_bounds__(GEMV_CONSUMERS, 1) gemv1_program_kernel(const 
         const int flags = sh.flags, kt = sh.kt;
         // what the row stores need, fetched before the tiles are walked
         float* const y = op.y;
+        const float* const residual = op.residual;
         const int rows = op.rows;
         const int64_t col0 = op.col0;
         uint2* slots_g = P.scratch + (size_t)(o & 1) * gridDim.x * 128;
@@ -399,7 +405,16 @@ __global__ void __launch_bounds__(GEMV_CONSUMERS, 1) gemv1_program_kernel(const 
             if (flags & OP_DEPENDS) run.grid_barrier(o);
             else run.consumers_sync();  // the staged activations are about to be replaced
             stamp();
-            stage_x_q8<R::BETA_INT, false>(op.x, op.k, xd, recs, kt * T::K, GEMV_CONSUMERS);
+            switch (op.x_kind) {
+                case XK_F32: stage_x_q8<R::BETA_INT, XK_F32>(op.x, op.k, xd, recs, kt * T::K, GEMV_CONSUMERS); break;
+                case XK_RMSNORM_F32: {
+                    const float inv = cta_rms_inv(static_cast<const float*>(op.x), op.k, op.eps, reinterpret_cast<float*>(smem + 192), GEMV_CONSUMERS);
+                    stage_x_q8<R::BETA_INT, XK_RMSNORM_F32>(op.x, op.k, xd, recs, kt * T::K, GEMV_CONSUMERS, op.x_aux, inv);
+                    break;
+                }
+                case XK_SWIGLU_F32: stage_x_q8<R::BETA_INT, XK_SWIGLU_F32>(op.x, op.k, xd, recs, kt * T::K, GEMV_CONSUMERS, op.x_aux); break;
+                default: stage_x_q8<R::BETA_INT, XK_BF16>(op.x, op.k, xd, recs, kt * T::K, GEMV_CONSUMERS); break;
+            }
             run.consumers_sync();
             stamp();
         } else {
@@ -411,6 +426,7 @@ __global__ void __launch_bounds__(GEMV_CONSUMERS, 1) gemv1_program_kernel(const 
         auto emit_row = [&](int n, float v) {
             if (n < rows) {
                 const int64_t off = col0 + n;
+                if (residual != nullptr) v += __ldcg(residual + off);  // the residual add fused into the store
                 y[off] = v;
                 if (P.world > 1) emit_to_peers(op.ll, P.world, P.rank, off, v, run.tag());
             }
@@ -491,6 +507,14 @@ extern "C" {
 
 int wf_program_create(int64_t ctx, int n_ops, const int64_t* weights, const int64_t* x_dev, const int64_t* y_dev, const int* flags,
                       int64_t m, int world, int rank, const int64_t* landing_dev, int64_t* program) {
+    return wf_program_create_fused(ctx, n_ops, weights, x_dev, y_dev, flags, nullptr, nullptr, nullptr, nullptr, m, world, rank,
+                                   landing_dev, program);
+}
+
+int wf_program_create_fused(int64_t ctx, int n_ops, const int64_t* weights, const int64_t* x_dev, const int64_t* y_dev,
+                            const int* flags, const int* x_kind, const int64_t* x_aux_dev, const float* eps,
+                            const int64_t* residual_dev, int64_t m, int world, int rank, const int64_t* landing_dev,
+                            int64_t* program) {
     Context* c = get_context(ctx);
     if (!c) return WF_ERR_INVALID_HANDLE;
     ScopedLock lk(c);
@@ -527,6 +551,17 @@ int wf_program_create(int64_t ctx, int n_ops, const int64_t* weights, const int6
         if (!op.x) return set_error(c, WF_ERR_INVALID_ARGUMENT, "op %d: null activation pointer", o);
         if ((x_dev[o] & 15) || (y_dev[o] & 3))
             return set_error(c, WF_ERR_INVALID_ARGUMENT, "op %d: misaligned pointer (activations 16 bytes, output 4 bytes)", o);
+        op.x_kind = x_kind ? x_kind[o] : XK_BF16;
+        op.eps = eps ? eps[o] : 0.f;
+        op.x_aux = x_aux_dev ? reinterpret_cast<const float*>(x_aux_dev[o]) : nullptr;
+        op.residual = residual_dev ? reinterpret_cast<const float*>(residual_dev[o]) : nullptr;
+        if (op.x_kind < XK_BF16 || op.x_kind > XK_SWIGLU_F32) return set_error(c, WF_ERR_INVALID_ARGUMENT, "op %d: unknown input kind %d", o, op.x_kind);
+        if ((op.x_kind != XK_BF16 || op.residual) && m != 1)
+            return set_error(c, WF_ERR_SHAPE, "op %d: fused inputs and residuals are for one-token programs", o);
+        if (op.x_kind == XK_SWIGLU_F32 && !op.x_aux) return set_error(c, WF_ERR_INVALID_ARGUMENT, "op %d: swiglu needs the up projection's output", o);
+        if ((reinterpret_cast<uintptr_t>(op.x_aux) & 15) || (reinterpret_cast<uintptr_t>(op.residual) & 3))
+            return set_error(c, WF_ERR_INVALID_ARGUMENT, "op %d: misaligned pointer (gamma / up 16 bytes, residual 4 bytes)", o);
+        if (op.x_kind != XK_BF16 && (w->g.k & 7)) return set_error(c, WF_ERR_SHAPE, "op %d: fp32 inputs need K a multiple of 8", o);
         op.ldy = w->total_rows;
         op.col0 = w->row0;
         op.rows = (int)w->g.rows;

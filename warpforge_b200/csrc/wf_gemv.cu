@@ -58,8 +58,8 @@ __global__ void __launch_bounds__(GEMV_CONSUMERS, 1) gemv1_kernel(const GemvPara
 
     asm volatile("griddepcontrol.wait;" ::: "memory");
     stamp(0);
-    if (p.x_f32) stage_x_q8<R::BETA_INT, true>(p.x, p.k, xd, recs, kp, GEMV_CONSUMERS);
-    else stage_x_q8<R::BETA_INT, false>(p.x, p.k, xd, recs, kp, GEMV_CONSUMERS);
+    if (p.x_f32) stage_x_q8<R::BETA_INT, XK_F32>(p.x, p.k, xd, recs, kp, GEMV_CONSUMERS);
+    else stage_x_q8<R::BETA_INT, XK_BF16>(p.x, p.k, xd, recs, kp, GEMV_CONSUMERS);
     __syncthreads();
     stamp(1);
     auto emit_row = [&](int n, float v) {

@@ -1125,24 +1125,66 @@ static __device__ void stage_x_bf16(const GemvParams& p, uint8_t* xs, float* cin
 // byte, the four signed base-256 digits of X.  A block holding Inf (and no NaN) is staged as signs only with
 // an infinite factor, one holding a NaN with a NaN factor.  recs: 16 bytes per block of records followed by 8
 // bytes per block of activation sums.
-// F32: the token is fp32 instead of bf16 -- the same staging (an fp32 element has 24 significant bits, X keeps 30
-// below the block's largest magnitude, so elements within 2^-6 of it are exact and the others are cut at 2^-30 of it).
-template <int BETA_INT, bool F32>
-static __device__ __noinline__ void stage_x_q8(const void* x, int k, uint8_t* xd, uint8_t* recs, int kp, int nthreads) {
+// KIND: where the token comes from.
+//   XK_BF16          a bf16 row;
+//   XK_F32           an fp32 row -- the same staging (an fp32 element has 24 significant bits, X keeps 30 below the
+//                    block's largest magnitude, so elements within 2^-6 of it are exact and the others are cut at 2^-30 of it);
+//   XK_RMSNORM_F32   (x[i] * inv) * gamma[i] of an fp32 row, inv = 1 / rms(x) worked out by the caller (cta_rms_inv),
+//                    gamma = aux (may be null): rms_norm fused into the staging
+//                    (warpforge-backend-cpu/src/main/java/io/surfworks/warpforge/backend/cpu/ops/scalar/CustomCallKernel.java:173-224);
+//   XK_SWIGLU_F32    (x[i] * sigmoid(x[i])) * aux[i], x = the gate projection's output, aux = the up projection's:
+//                    silu (CustomCallKernel.java:262-280) and the multiply fused into the staging of Wdown.
+constexpr int XK_BF16 = 0, XK_F32 = 1, XK_RMSNORM_F32 = 2, XK_SWIGLU_F32 = 3;
+
+// 1 / rms of an fp32 row for the whole CTA: rms = sqrt(sum x^2 / k + eps), the sum taken per thread, per warp, then
+// over the warps in warp order (every thread of every CTA gets the same bits).  scratch: 16 floats of shared
+// memory; all `nthreads` threads call it (one named barrier).
+static __device__ __noinline__ float cta_rms_inv(const float* x, int k, float eps, float* scratch, int nthreads) {
+    float ss = 0.f;
+    const float4* src = reinterpret_cast<const float4*>(x);
+    for (int i = threadIdx.x; i < (k >> 2); i += nthreads) {
+        const float4 v = __ldcg(src + i);
+        ss += v.x * v.x;
+        ss += v.y * v.y;
+        ss += v.z * v.z;
+        ss += v.w * v.w;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = ss;
+    asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+    float total = 0.f;
+    for (int w = 0; w < (nthreads >> 5); w++) total += scratch[w];
+    asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");  // scratch may be reused
+    const float rms = (float)sqrt((double)(total / (float)k + eps));
+    return 1.0f / rms;
+}
+
+template <int BETA_INT, int KIND>
+static __device__ __noinline__ void stage_x_q8(const void* x, int k, uint8_t* xd, uint8_t* recs, int kp, int nthreads,
+                                               const float* aux = nullptr, float inv = 1.f) {
+    constexpr bool F32 = KIND != XK_BF16, AUX = KIND == XK_RMSNORM_F32 || KIND == XK_SWIGLU_F32;
     const int groups = kp >> 3, padded = (groups + 31) & ~31, kgroups = k >> 3;
     const uint4* src = static_cast<const uint4*>(x);
+    const uint4* asrc = reinterpret_cast<const uint4*>(aux);
+    const bool has_aux = AUX && aux != nullptr;
     uint8_t* sums = recs + (size_t)(kp >> 5) * 16;  // the activation sums follow the records
     constexpr int U = F32 ? 2 : 3;  // element groups in flight per thread
     for (int c0 = threadIdx.x; c0 < padded; c0 += nthreads * U) {  // warp-uniform trip counts
-        uint4 pre[U], pre2[U];
+        uint4 pre[U], pre2[U], ax[U], ax2[U];
 #pragma unroll
         for (int u = 0; u < U; u++) {
             const int c8 = c0 + u * nthreads;
             pre[u] = pre2[u] = make_uint4(0u, 0u, 0u, 0u);
+            ax[u] = ax2[u] = make_uint4(0x3F800000u, 0x3F800000u, 0x3F800000u, 0x3F800000u);  // 1.0f
             if (c8 < kgroups) {
                 if (F32) {
                     pre[u] = __ldcg(src + 2 * c8);
                     pre2[u] = __ldcg(src + 2 * c8 + 1);
+                    if (has_aux) {
+                        ax[u] = __ldcg(asrc + 2 * c8);
+                        ax2[u] = __ldcg(asrc + 2 * c8 + 1);
+                    }
                 } else {
                     pre[u] = __ldcg(src + c8);
                 }
@@ -1159,6 +1201,21 @@ static __device__ __noinline__ void stage_x_q8(const void* x, int k, uint8_t* xd
                 const uint4 v2 = pre2[u];
                 f[0] = __uint_as_float(v.x); f[1] = __uint_as_float(v.y); f[2] = __uint_as_float(v.z); f[3] = __uint_as_float(v.w);
                 f[4] = __uint_as_float(v2.x); f[5] = __uint_as_float(v2.y); f[6] = __uint_as_float(v2.z); f[7] = __uint_as_float(v2.w);
+                if (AUX) {
+                    const uint4 a1 = ax[u], a2 = ax2[u];
+                    const float a[8] = {__uint_as_float(a1.x), __uint_as_float(a1.y), __uint_as_float(a1.z), __uint_as_float(a1.w),
+                                        __uint_as_float(a2.x), __uint_as_float(a2.y), __uint_as_float(a2.z), __uint_as_float(a2.w)};
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        if (KIND == XK_RMSNORM_F32) {
+                            f[i] = f[i] * inv;
+                            if (has_aux) f[i] *= a[i];
+                        } else {
+                            const float sig = 1.0f / (1.0f + expf(-f[i]));
+                            f[i] = (f[i] * sig) * a[i];
+                        }
+                    }
+                }
             } else {
 #pragma unroll
                 for (int i = 0; i < 4; i++) {

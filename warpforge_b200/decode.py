@@ -236,3 +236,102 @@ class ProjectionStack:
             for w in layer:
                 w.close()
         self.weights = []
+
+
+class FusedDecoderStack:
+    """A decoder's projections with the fp32 operations between them fused into the one-token program kernel
+    (`wf_program_create_fused`): per layer
+
+        q, k, v   = W{q,k,v} . rms_norm(h, gamma1)
+        h_mid     = h + Wo . attn                       (attn: the attention block's output, supplied by the caller --
+                                                         attention itself is outside this path)
+        gate, up  = W{gate,up} . rms_norm(h_mid, gamma2)
+        h_next    = h_mid + Wdown . (silu(gate) * up)
+
+    All activations are fp32 device buffers that the projections read and write directly; one kernel launch per
+    token.  Single rank.  `dims` = (d_model, ffn); weights are seeded synthetic blocks of `qtype`."""
+
+    NAMES = ("wq", "wk", "wv", "wo", "wgate", "wup", "wdown")
+
+    def __init__(self, context: CudaContext, qtype: Q.QuantizationType, d_model: int, ffn: int, layers: int, seed: int = 11,
+                 eps: float = 1e-5):
+        self.ctx, self.qtype, self.d, self.ffn, self.layers, self.eps = context, qtype, d_model, ffn, layers, eps
+        shapes = {"wq": (d_model, d_model), "wk": (d_model, d_model), "wv": (d_model, d_model), "wo": (d_model, d_model),
+                  "wgate": (ffn, d_model), "wup": (ffn, d_model), "wdown": (d_model, ffn)}
+        self.shapes = shapes
+        rng = np.random.default_rng(seed)
+        self.blocks, self.weights, self.gamma, self.host = [], [], [], {}
+        self.dev = {}
+
+        def buf(name, n, init=None):
+            p = context.allocate(n * 4)
+            a = np.zeros(n, np.float32) if init is None else np.ascontiguousarray(init, np.float32)
+            context.copy_to_device(p, a)
+            self.dev[name] = p
+            self.host[name] = a
+            return p
+
+        buf("h0", d_model, rng.standard_normal(d_model))
+        for l in range(layers):
+            blk = {n: Q.synth_weight(qtype, r, k, seed * 1000 + l * 7 + i) for i, (n, (r, k)) in enumerate(shapes.items())}
+            self.blocks.append(blk)
+            self.weights.append({n: QuantizedWeight(context, qtype, blk[n], *shapes[n]) for n in self.NAMES})
+            buf(f"gamma1_{l}", d_model, 1.0 + 0.1 * rng.standard_normal(d_model))
+            buf(f"gamma2_{l}", d_model, 1.0 + 0.1 * rng.standard_normal(d_model))
+            buf(f"attn_{l}", d_model, rng.standard_normal(d_model))
+            for n in ("q", "k", "v", "hmid"):
+                buf(f"{n}_{l}", d_model)
+            buf(f"gate_{l}", ffn)
+            buf(f"up_{l}", ffn)
+            buf(f"h{l + 1}", d_model)
+        self.program = 0
+        self._build()
+
+    def _build(self) -> None:
+        ctx, lib, d = self.ctx, self.ctx._lib, self.dev
+        new = ProjectionStack.OP_NEW_X | ProjectionStack.OP_DEPENDS
+        W, X, Y, F, K, A, E, R = [], [], [], [], [], [], [], []
+
+        def op(w, x, y, flags, kind=N.WF_X_BF16, aux=0, residual=0):
+            W.append(w.handle); X.append(x); Y.append(y); F.append(flags); K.append(kind); A.append(aux); E.append(self.eps); R.append(residual)
+
+        for l in range(self.layers):
+            w = self.weights[l]
+            op(w["wq"], d[f"h{l}"], d[f"q_{l}"], new, N.WF_X_RMSNORM_F32, d[f"gamma1_{l}"])
+            op(w["wk"], d[f"h{l}"], d[f"k_{l}"], 0)
+            op(w["wv"], d[f"h{l}"], d[f"v_{l}"], 0)
+            op(w["wo"], d[f"attn_{l}"], d[f"hmid_{l}"], new, N.WF_X_F32, 0, d[f"h{l}"])
+            op(w["wgate"], d[f"hmid_{l}"], d[f"gate_{l}"], new, N.WF_X_RMSNORM_F32, d[f"gamma2_{l}"])
+            op(w["wup"], d[f"hmid_{l}"], d[f"up_{l}"], 0)
+            op(w["wdown"], d[f"gate_{l}"], d[f"h{l + 1}"], new, N.WF_X_SWIGLU_F32, d[f"up_{l}"], d[f"hmid_{l}"])
+        n = len(W)
+        arr = lambda v, t: (t * len(v))(*v)
+        prog = ctypes.c_int64()
+        ctx._ck("wf_program_create_fused", lib.wf_program_create_fused(
+            ctx.handle, n, arr(W, ctypes.c_int64), arr(X, ctypes.c_int64), arr(Y, ctypes.c_int64), arr(F, ctypes.c_int),
+            arr(K, ctypes.c_int), arr(A, ctypes.c_int64), arr(E, ctypes.c_float), arr(R, ctypes.c_int64), 1, 1, 0, None,
+            ctypes.byref(prog)))
+        self.program = prog.value
+
+    def weight_bytes_per_token(self) -> int:
+        return self.layers * sum(r * self.qtype.row_bytes(k) for r, k in self.shapes.values())
+
+    def run(self, stream: int = 0) -> None:
+        self.ctx._ck("wf_program_run", self.ctx._lib.wf_program_run(self.ctx.handle, self.program, stream))
+
+    def read(self, name: str) -> np.ndarray:
+        out = np.empty_like(self.host[name])
+        self.ctx.copy_to_host(out, self.dev[name])
+        return out
+
+    def close(self) -> None:
+        if self.program:
+            self.ctx._ck("wf_program_destroy", self.ctx._lib.wf_program_destroy(self.ctx.handle, self.program))
+            self.program = 0
+        for layer in self.weights:
+            for w in layer.values():
+                w.close()
+        self.weights = []
+        for p in self.dev.values():
+            self.ctx.free(p)
+        self.dev = {}
