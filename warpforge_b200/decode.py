@@ -319,6 +319,34 @@ class FusedDecoderStack:
     def run(self, stream: int = 0) -> None:
         self.ctx._ck("wf_program_run", self.ctx._lib.wf_program_run(self.ctx.handle, self.program, stream))
 
+    def issue_unfused(self, stream: int = 0) -> None:
+        """The same data flow as separate launches: every fp32 operation a kernel of its own (wf_rms_norm,
+        wf_swiglu, wf_add) and every projection a wf_qlinear on one fp32 token -- twelve launches per layer.
+        Needs scratch rows "x1", "x2", "act", "t" (allocated on first use)."""
+        ctx, lib, d, h = self.ctx, self.ctx._lib, self.dev, self.ctx.handle
+        if "x1" not in d:
+            for n, size in (("x1", self.d), ("x2", self.d), ("act", self.ffn), ("t", self.d)):
+                d[n] = ctx.allocate(size * 4)
+                self.host[n] = np.zeros(size, np.float32)
+
+        def lin(w, x, y):
+            ctx._ck("wf_qlinear", lib.wf_qlinear(h, w.handle, x, N.WF_DTYPE_F32, 1, 1, y, 1, stream))
+
+        for l in range(self.layers):
+            w = self.weights[l]
+            ctx._ck("wf_rms_norm", lib.wf_rms_norm(h, d[f"h{l}"], d[f"gamma1_{l}"], d["x1"], 1, self.d, self.eps, stream))
+            lin(w["wq"], d["x1"], d[f"q_{l}"])
+            lin(w["wk"], d["x1"], d[f"k_{l}"])
+            lin(w["wv"], d["x1"], d[f"v_{l}"])
+            lin(w["wo"], d[f"attn_{l}"], d["t"])
+            ctx._ck("wf_add", lib.wf_add(h, d[f"h{l}"], d["t"], d[f"hmid_{l}"], self.d, stream))
+            ctx._ck("wf_rms_norm", lib.wf_rms_norm(h, d[f"hmid_{l}"], d[f"gamma2_{l}"], d["x2"], 1, self.d, self.eps, stream))
+            lin(w["wgate"], d["x2"], d[f"gate_{l}"])
+            lin(w["wup"], d["x2"], d[f"up_{l}"])
+            ctx._ck("wf_swiglu", lib.wf_swiglu(h, d[f"gate_{l}"], d[f"up_{l}"], d["act"], self.ffn, stream))
+            lin(w["wdown"], d["act"], d["t"])
+            ctx._ck("wf_add", lib.wf_add(h, d[f"hmid_{l}"], d["t"], d[f"h{l + 1}"], self.d, stream))
+
     def read(self, name: str) -> np.ndarray:
         out = np.empty_like(self.host[name])
         self.ctx.copy_to_host(out, self.dev[name])
