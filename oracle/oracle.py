@@ -78,6 +78,7 @@ class COracle:
         L.wfo_layer_norm.argtypes = [f32p, f32p, f32p, f32p, i64, i64, ctypes.c_float]
         L.wfo_softmax.argtypes = [f32p, f32p, i64, i64]
         L.wfo_silu.argtypes = [f32p, f32p, i64]
+        L.wfo_gelu.argtypes = [f32p, f32p, i64]
         L.wfo_swiglu.argtypes = [f32p, f32p, f32p, i64]
         L.wfo_add.argtypes = [f32p, f32p, f32p, i64]
         L.wfo_embedding.restype = ctypes.c_int
@@ -202,6 +203,12 @@ class COracle:
         x = self._f32(x)
         y = np.empty_like(x)
         self.lib.wfo_silu(_ptr(x, ctypes.c_float), _ptr(y, ctypes.c_float), x.size)
+        return y
+
+    def gelu(self, x) -> np.ndarray:
+        x = self._f32(x)
+        y = np.empty_like(x)
+        self.lib.wfo_gelu(_ptr(x, ctypes.c_float), _ptr(y, ctypes.c_float), x.size)
         return y
 
     def swiglu(self, gate, up) -> np.ndarray:

@@ -474,6 +474,17 @@ void wfo_silu(const float* x, float* y, int64_t n) {
     }
 }
 
+/* CustomCallKernel.java:226-260, the tanh form (the only one reachable: `approximate` is fixed to "tanh"):
+ * inner = 0.7978845608f * (x + 0.044715f * x * x * x) in float, left to right; 0.5f * x * (1.0f + (float) tanh(inner)). */
+void wfo_gelu(const float* x, float* y, int64_t n) {
+    const float SQRT_2_OVER_PI = 0.7978845608f, COEFF = 0.044715f;
+    for (int64_t i = 0; i < n; i++) {
+        float v = x[i];
+        float inner = SQRT_2_OVER_PI * (v + COEFF * v * v * v);
+        y[i] = 0.5f * v * (1.0f + (float)tanh((double)inner));
+    }
+}
+
 /* silu custom_call, then stablehlo.multiply (cpu/ops/scalar/MultiplyKernel: a[i] * b[i]) */
 void wfo_swiglu(const float* gate, const float* up, float* y, int64_t n) {
     for (int64_t i = 0; i < n; i++) {

@@ -119,6 +119,20 @@ def test_reference_test_cases(backend, oracle):
     assert abs(np.sqrt(float(np.sum(y * y)) / 2) - 1) < 1e-5
 
 
+@pytest.mark.parametrize("count", [1, 3, 4096, 1000003])
+def test_gelu(backend, oracle, count):
+    """gelu (tanh form): the float operations in the reference's order, tanh in double as the reference calls it; a
+    different libm may round the last bit of tanh differently, so 1 ulp on at most one element in 10^5."""
+    rng = np.random.default_rng(count)
+    a = (rng.standard_normal(count) * 3).astype(np.float32)
+    if count >= 16:
+        a[:8] = [0.0, -0.0, np.inf, -np.inf, np.nan, 100.0, -100.0, 1e-30]
+    got, want = _call(backend, "gelu", a), oracle.gelu(a)
+    _check_elements(got, want)
+    y = _call(backend, "gelu", np.array([0.0, 5.0, -5.0], np.float32))  # the reference test's cases
+    assert abs(float(y[0])) < 1e-5 and float(y[1]) > 4.9 and abs(float(y[2])) < 0.01
+
+
 @pytest.mark.parametrize("count", [1, 3, 4096, 11008, 1000003, 512 * 11008])
 def test_silu_swiglu_add(backend, oracle, count):
     rng = np.random.default_rng(count)

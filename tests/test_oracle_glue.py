@@ -39,6 +39,15 @@ def test_silu_is_x_times_sigmoid(oracle):
     assert y[3] == 0.0
 
 
+def test_gelu_reference_cases(oracle):
+    """CustomCallKernelTest.GeluTests: 0 at 0, close to x at 5, close to 0 at -5; and the tanh formula itself."""
+    y = oracle.gelu(np.array([0.0, 5.0, -5.0, 1.0, -0.5], np.float32))
+    assert abs(float(y[0])) < EPS and float(y[1]) > 4.9 and abs(float(y[2])) < 0.01
+    for x, got in zip((1.0, -0.5), y[3:]):
+        inner = np.float32(0.7978845608) * (np.float32(x) + np.float32(0.044715) * np.float32(x) * np.float32(x) * np.float32(x))
+        assert abs(0.5 * x * (1.0 + math.tanh(float(inner))) - float(got)) < 1e-6
+
+
 def test_rms_norm_normalizes_by_rms(oracle):
     y = oracle.rms_norm(np.array([[3, 4]], np.float32))
     assert abs(math.sqrt(float(np.sum(y * y)) / 2) - 1.0) < EPS

@@ -363,7 +363,7 @@ class CudaCustomCallKernel(CudaOpKernel):
     DeviceTensor inputs stay on the device and the call only enqueues.  Targets: rms_norm, layer_norm,
     softmax, silu, embedding, plus ``swiglu`` (silu(gate) * up in one pass)."""
 
-    TARGETS = ("rms_norm", "layer_norm", "softmax", "silu", "embedding", "swiglu")
+    TARGETS = ("rms_norm", "layer_norm", "softmax", "silu", "gelu", "embedding", "swiglu")
 
     def __init__(self, context: CudaContext, salt: int = 0, stream: int = 0):
         self.context, self.salt, self.stream = context, salt, stream
@@ -417,6 +417,8 @@ class CudaCustomCallKernel(CudaOpKernel):
                     rc = lib.wf_softmax(ctx.handle, ptrs[0], out, rows, n, s)
                 elif target == "silu":
                     rc = lib.wf_silu(ctx.handle, ptrs[0], out, total, s)
+                elif target == "gelu":
+                    rc = lib.wf_gelu(ctx.handle, ptrs[0], out, total, s)
                 else:
                     if len(ptrs) != 2 or tuple(inputs[1].shape()) != shape:
                         raise ValueError(f"{target} requires 2 inputs of one shape")

@@ -227,9 +227,19 @@ template <bool EXACT> __device__ __forceinline__ float silu_as_host(float x, con
     return __fmul_rn(x, sigmoid);
 }
 
-enum { EL_SILU = 0, EL_SWIGLU = 1, EL_ADD = 2 };
+enum { EL_SILU = 0, EL_SWIGLU = 1, EL_ADD = 2, EL_GELU = 3 };
+
+// CustomCallKernel.java:240-250, the tanh form, float operations in the reference's order; tanh itself in double
+// (the reference calls Math.tanh on the widened float), rounded to float once.
+__device__ __forceinline__ float gelu_as_host(float x) {
+    const float x3 = __fmul_rn(__fmul_rn(__fmul_rn(0.044715f, x), x), x);
+    const float inner = __fmul_rn(0.7978845608f, __fadd_rn(x, x3));
+    const float t = (float)tanh((double)inner);
+    return __fmul_rn(__fmul_rn(0.5f, x), __fadd_rn(1.0f, t));
+}
 
 template <int OP, bool EXACT> __device__ __forceinline__ float el(float a, float b, const double* tab) {
+    if (OP == EL_GELU) return gelu_as_host(a);
     if (OP == EL_SILU) return silu_as_host<EXACT>(a, tab);
     if (OP == EL_SWIGLU) return __fmul_rn(silu_as_host<EXACT>(a, tab), b);
     return __fadd_rn(a, b);
@@ -240,16 +250,16 @@ __global__ void __launch_bounds__(256) elementwise_kernel(const float* __restric
                                                           float* __restrict__ y, int64_t n, int vec) {
     const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, step = (int64_t)gridDim.x * blockDim.x;
     __shared__ double tab[32];
-    if (OP != EL_ADD && EXACT) load_exp_table(tab);
+    if (OP != EL_ADD && OP != EL_GELU && EXACT) load_exp_table(tab);
     if (vec) {
         for (int64_t i = tid; i < n / 4; i += step) {
             const float4 u = __ldcs(reinterpret_cast<const float4*>(a) + i);
-            const float4 v = OP == EL_SILU ? u : __ldcs(reinterpret_cast<const float4*>(b) + i);
+            const float4 v = (OP == EL_SILU || OP == EL_GELU) ? u : __ldcs(reinterpret_cast<const float4*>(b) + i);
             __stcs(reinterpret_cast<float4*>(y) + i, make_float4(el<OP, EXACT>(u.x, v.x, tab), el<OP, EXACT>(u.y, v.y, tab), el<OP, EXACT>(u.z, v.z, tab), el<OP, EXACT>(u.w, v.w, tab)));
         }
-        for (int64_t i = n / 4 * 4 + tid; i < n; i += step) y[i] = el<OP, EXACT>(a[i], OP == EL_SILU ? 0.f : b[i], tab);
+        for (int64_t i = n / 4 * 4 + tid; i < n; i += step) y[i] = el<OP, EXACT>(a[i], (OP == EL_SILU || OP == EL_GELU) ? 0.f : b[i], tab);
     } else {
-        for (int64_t i = tid; i < n; i += step) y[i] = el<OP, EXACT>(a[i], OP == EL_SILU ? 0.f : b[i], tab);
+        for (int64_t i = tid; i < n; i += step) y[i] = el<OP, EXACT>(a[i], (OP == EL_SILU || OP == EL_GELU) ? 0.f : b[i], tab);
     }
 }
 
@@ -351,15 +361,17 @@ int wf_softmax(int64_t ctx, int64_t x_dev, int64_t y_dev, int64_t rows, int64_t 
 static int elementwise(int64_t ctx, int op, const char* what, int64_t a_dev, int64_t b_dev, int64_t y_dev, int64_t count, int64_t stream) {
     GLUE_ENTER(ctx);
     const void *a = reinterpret_cast<void*>(a_dev), *b = reinterpret_cast<void*>(b_dev), *y = reinterpret_cast<void*>(y_dev);
-    if (!a || !y || (op != EL_SILU && !b)) return set_error(c, WF_ERR_INVALID_ARGUMENT, "%s: null pointer", what);
+    const bool unary = op == EL_SILU || op == EL_GELU;
+    if (!a || !y || (!unary && !b)) return set_error(c, WF_ERR_INVALID_ARGUMENT, "%s: null pointer", what);
     if (!aligned4(a) || !aligned4(b) || !aligned4(y)) return set_error(c, WF_ERR_INVALID_ARGUMENT, "%s: fp32 pointers must be 4-byte aligned", what);
     if (count < 0) return set_error(c, WF_ERR_SHAPE, "%s: negative element count", what);
     if (count == 0) return WF_OK;
-    const int vec = aligned16(a) && aligned16(y) && (op == EL_SILU || aligned16(b));
+    const int vec = aligned16(a) && aligned16(y) && (unary || aligned16(b));
     const float *fa = static_cast<const float*>(a), *fb = static_cast<const float*>(b);
     float* fy = reinterpret_cast<float*>(y_dev);
     const int grid = element_grid(c, count);
-    if (op == EL_SILU && c->glue_exact) elementwise_kernel<EL_SILU, true><<<grid, 256, 0, s>>>(fa, fb, fy, count, vec);
+    if (op == EL_GELU) elementwise_kernel<EL_GELU, false><<<grid, 256, 0, s>>>(fa, fb, fy, count, vec);
+    else if (op == EL_SILU && c->glue_exact) elementwise_kernel<EL_SILU, true><<<grid, 256, 0, s>>>(fa, fb, fy, count, vec);
     else if (op == EL_SILU) elementwise_kernel<EL_SILU, false><<<grid, 256, 0, s>>>(fa, fb, fy, count, vec);
     else if (op == EL_SWIGLU && c->glue_exact) elementwise_kernel<EL_SWIGLU, true><<<grid, 256, 0, s>>>(fa, fb, fy, count, vec);
     else if (op == EL_SWIGLU) elementwise_kernel<EL_SWIGLU, false><<<grid, 256, 0, s>>>(fa, fb, fy, count, vec);
@@ -369,6 +381,10 @@ static int elementwise(int64_t ctx, int op, const char* what, int64_t a_dev, int
 
 int wf_silu(int64_t ctx, int64_t x_dev, int64_t y_dev, int64_t count, int64_t stream) {
     return elementwise(ctx, EL_SILU, "silu", x_dev, 0, y_dev, count, stream);
+}
+
+int wf_gelu(int64_t ctx, int64_t x_dev, int64_t y_dev, int64_t count, int64_t stream) {
+    return elementwise(ctx, EL_GELU, "gelu", x_dev, 0, y_dev, count, stream);
 }
 
 int wf_swiglu(int64_t ctx, int64_t gate_dev, int64_t up_dev, int64_t y_dev, int64_t count, int64_t stream) {
