@@ -82,12 +82,21 @@ static int nccl_status(Context* c, int r, const char* what) {
     return set_error(c, WF_ERR_NCCL_BASE + r, "%s failed: %s (%d)", what, a.GetErrorString ? a.GetErrorString(r) : "nccl", r);
 }
 
-// [world][m][rows] -> [m][world*rows]
-__global__ void unshard_kernel(const float* __restrict__ src, float* __restrict__ dst, int64_t m, int64_t rows, int world) {
-    const int64_t n = (int64_t)world * rows, total = m * n;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t t = i / n, col = i % n, r = col / rows, j = col % rows;
-        dst[i] = src[(r * m + t) * rows + j];
+// [world][m][rows] -> [m][world*rows]: one strip of `rows` floats per (rank, token), copied by the CTAs of grid row
+// blockIdx.y = rank * m + token (grid-stride over y for very many tokens); 16-byte pieces when the strips allow it.
+__global__ void __launch_bounds__(256) unshard_kernel(const float* __restrict__ src, float* __restrict__ dst, int64_t m, int64_t rows,
+                                                      int world, int vec) {
+    const int64_t n = (int64_t)world * rows, strips = (int64_t)world * m;
+    for (int64_t sidx = blockIdx.y; sidx < strips; sidx += gridDim.y) {
+        const int64_t r = sidx / m, t = sidx - r * m;  // one division per strip, not per element
+        const float* s = src + sidx * rows;
+        float* d = dst + t * n + r * rows;
+        if (vec) {
+            for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < (rows >> 2); i += (int64_t)gridDim.x * blockDim.x)
+                reinterpret_cast<float4*>(d)[i] = __ldcs(reinterpret_cast<const float4*>(s) + i);
+        } else {
+            for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < rows; i += (int64_t)gridDim.x * blockDim.x) d[i] = s[i];
+        }
     }
 }
 
@@ -223,8 +232,10 @@ int wf_qlinear_allgather(int64_t ctx, int64_t comm, int64_t weight, const void* 
     if (rc != WF_OK) return rc;
     int r = nccl().AllGather(mine, k->d_tmp, (size_t)(m * rows), NCCL_FLOAT32, k->comm, s);
     if (r != NCCL_SUCCESS) return nccl_status(c, r, "ncclAllGather");
-    const int64_t total = m * n;
-    unshard_kernel<<<(unsigned)std::min<int64_t>((total + 255) / 256, 4096), 256, 0, s>>>(k->d_tmp, y, m, rows, k->world);
+    const int vec = (rows % 4 == 0) && (reinterpret_cast<uintptr_t>(y) % 16 == 0);
+    const dim3 grid((unsigned)std::max<int64_t>(1, std::min<int64_t>((rows / (vec ? 4 : 1) + 255) / 256, 8)),
+                    (unsigned)std::min<int64_t>((int64_t)k->world * m, 65535));
+    unshard_kernel<<<grid, 256, 0, s>>>(k->d_tmp, y, m, rows, k->world, vec);
     WF_CUDA(c, cudaGetLastError());
     c->launches++;
     return WF_OK;

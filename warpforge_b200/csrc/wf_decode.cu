@@ -481,8 +481,19 @@ static cudaError_t program_launch_one_token(const Program& pr, cudaStream_t s) {
         if (e != cudaSuccess) return e;
         attr_set[dev] = true;
     }
-    gemv1_program_kernel<QT><<<pr.grid, GEMV_CONSUMERS, pr.smem, s>>>(pr.params);
-    return cudaGetLastError();
+    // cooperative: the grid barrier needs every CTA resident at once, and a cooperative launch starts only when
+    // the device can place them all (another kernel holding SMs delays the start instead of starving the barrier)
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)pr.grid);
+    cfg.blockDim = dim3(GEMV_CONSUMERS);
+    cfg.dynamicSmemBytes = pr.smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative;
+    attr[0].val.cooperative = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, gemv1_program_kernel<QT>, pr.params);
 }
 
 template <int QT, int XC>
@@ -495,8 +506,17 @@ static cudaError_t program_launch(const Program& pr, cudaStream_t s) {
         if (e != cudaSuccess) return e;
         attr_set[dev] = true;
     }
-    gemv_program_kernel<QT, XC><<<pr.grid, GEMV_THREADS, pr.smem, s>>>(pr.params);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};  // cooperative, as for the one-token kernel
+    cfg.gridDim = dim3((unsigned)pr.grid);
+    cfg.blockDim = dim3(GEMV_THREADS);
+    cfg.dynamicSmemBytes = pr.smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative;
+    attr[0].val.cooperative = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, gemv_program_kernel<QT, XC>, pr.params);
 }
 
 }  // namespace wf
