@@ -331,6 +331,12 @@ int wf_set_salt(int64_t ctx, int salt);
 int wf_read_timing(int64_t ctx, int64_t* out, int64_t n);
 /* Number of kernel launches this context has issued (product kernels only). */
 int wf_launch_count(int64_t ctx, int64_t* launches);
+/* How the several-token decode kernel would cut a [rows x k] weight of type qtype for `cols` activation columns
+ * (1..32; an fp32 token counts three) on a device with sm_count SMs: k-slices, k-tiles per slice, warps per team,
+ * whether partial sums are used, shared-memory bytes.  Needs no device (host arithmetic only); slices = 0 means
+ * no cut fits and the call is run in several launches of fewer columns. */
+int wf_plan_several_tokens(int qtype, int64_t rows, int64_t k, int cols, int x_is_f32, int sm_count, int* slices,
+                           int* k_tiles_per_slice, int* team, int* uses_partial_sums, int64_t* smem_bytes);
 
 #ifdef __cplusplus
 }

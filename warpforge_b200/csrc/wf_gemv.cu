@@ -346,3 +346,20 @@ int gemv_launch_noalloc(Context* c, const GemvCall& call, cudaStream_t s) {
 }
 
 }  // namespace wf
+
+extern "C" int wf_plan_several_tokens(int qtype, int64_t rows, int64_t k, int cols, int x_is_f32, int sm_count, int* slices,
+                                      int* k_tiles_per_slice, int* team, int* uses_partial_sums, int64_t* smem_bytes) {
+    using namespace wf;
+    const int qt = device_qtype(qtype);
+    if (qt != WF_QTYPE_Q4_0 && qt != WF_QTYPE_Q4_1 && qt != WF_QTYPE_Q8_0 && qt != WF_QTYPE_Q4_K) return WF_ERR_UNSUPPORTED_TYPE;
+    if (rows < 1 || k < 1 || cols < 1 || cols > GEMVN_MAX_COLS || sm_count < 1 || !slices || !k_tiles_per_slice || !team) return WF_ERR_INVALID_ARGUMENT;
+    const int64_t rt = (rows + 15) / 16, kt = (k + tile_k(qt) - 1) / tile_k(qt);
+    const GemvNPlan p = gemvn_plan(sm_count, qt, rt, kt, cols, x_is_f32 != 0);
+    *slices = p.slices;
+    *k_tiles_per_slice = p.kc;
+    *team = p.team;
+    if (uses_partial_sums) *uses_partial_sums = p.uses_part ? 1 : 0;
+    const int ng = cols <= 8 ? 1 : cols <= 16 ? 2 : 4;
+    if (smem_bytes) *smem_bytes = p.slices > 0 ? (int64_t)gemvn_smem(qt, p.kc, cols, ng, p.team, nullptr, nullptr) : 0;
+    return WF_OK;
+}
