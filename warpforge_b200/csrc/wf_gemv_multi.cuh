@@ -29,6 +29,9 @@
 
 namespace wf {
 
+// weight of a staged activation byte against a streamed weight byte in the planner's estimate (measured: 1 - 3 give
+// the same cuts for up to 8 columns, 2 the best ones for 16; 6 and more cut K too finely)
+constexpr int GEMVN_STAGE_COST = 2;
 constexpr int GEMVN_MAX_COLS = 32;
 constexpr int GEMVN_MAX_SLICES = 64;
 constexpr size_t GEMVN_PART_BYTES = 8u << 20;  // partial sums a launch may use (the static array of the no-alloc entry is this large)
@@ -76,8 +79,7 @@ struct GemvNPlan {
 // ceil(row-tiles / teams of the slice) units; per unit the member's share of the kc tiles, the hand-over inside
 // the team (W > 1) and the partial sums written (cols x 64 bytes, S > 1); for the warp that completes a row-tile
 // the S partial sums read back and two tiles' worth of round trips; for every warp its sixteenth of the CTA's
-// activation staging (cols x kc tiles of k, bf16; all CTAs of a slice read the same lines of the L2, which serves
-// them at about two thirds of the rate the weights stream at).
+// activation staging (cols x kc tiles of k, bf16; all CTAs of a slice read the same lines of the L2).
 inline GemvNPlan gemvn_plan(int sm_count, int qt, int64_t rt, int64_t kt, int cols, bool x_f32) {
     GemvNPlan best;
     const int ng = cols <= 8 ? 1 : cols <= 16 ? 2 : 4;
@@ -103,7 +105,7 @@ inline GemvNPlan gemvn_plan(int sm_count, int qt, int64_t rt, int64_t kt, int co
             }
             if (part) cost += slices * part16 + 32;
             // every CTA stages cols x kc tiles of k of the activations (from L2, by all its warps together)
-            cost += ((int64_t)cols * kc * tile_k(qt) * 3 + tb - 1) / tb;
+            cost += ((int64_t)cols * kc * tile_k(qt) * GEMVN_STAGE_COST + tb - 1) / tb;
             if (best_cost < 0 || cost < best_cost) {
                 best_cost = cost;
                 best.slices = slices;
