@@ -371,9 +371,10 @@ __global__ void __launch_bounds__(GEMV_CONSUMERS, 1) gemv1_program_kernel(const 
     const WsBars bar = ws_bars(smem);
     auto share_of = [&](int o) { return o < n_table ? table[o] : share_from_global(o); };
     // the weights depend on nothing: request the first tiles of this warp's stream at once
-    R slots[WsGeom<QT>::DEPTH];
+    constexpr int DEPTH = WsGeom<QT, true>::DEPTH;
+    R slots[DEPTH];
     WsCursor cur;
-    ws_prime<QT>(slots, cur, share_of, P.n_ops, warp, lane);
+    ws_prime<QT, DEPTH>(slots, cur, share_of, P.n_ops, warp, lane);
 
     ProgRun run{P, reinterpret_cast<volatile int*>(smem) + 1, ld_acquire_gpu(&P.sync->epoch)};
     bool failed = false;
@@ -431,7 +432,7 @@ __global__ void __launch_bounds__(GEMV_CONSUMERS, 1) gemv1_program_kernel(const 
                 if (P.world > 1) emit_to_peers(op.ll, P.world, P.rank, off, v, run.tag());
             }
         };
-        ws_consume<QT>(sh, op.chunk_q, op.chunk_r, warp, lane, slots, cur, bar, pieces, seq, smem_u32(xd), smem_u32(recs),
+        ws_consume<QT, DEPTH>(sh, op.chunk_q, op.chunk_r, warp, lane, slots, cur, bar, pieces, seq, smem_u32(xd), smem_u32(recs),
                        smem_u32(recs) + (uint32_t)((kt * T::K) >> 5) * 16, slots_g, P.status, smem_u32(const_cast<int*>(abort_flag)),
                        share_of, P.n_ops, emit_row);
         if (*abort_flag) failed = true;

@@ -45,9 +45,10 @@ __global__ void __launch_bounds__(GEMV_CONSUMERS, 1) gemv1_kernel(const GemvPara
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const WsShare share{p.tiles, t0, t1, p.kt, 0, {0, 0}};
     auto share_of = [&](int) { return share; };
-    R slots[WsGeom<QT>::DEPTH];
+    constexpr int DEPTH = WsGeom<QT, false>::DEPTH;
+    R slots[DEPTH];
     WsCursor cur;
-    ws_prime<QT>(slots, cur, share_of, 1, warp, lane);
+    ws_prime<QT, DEPTH>(slots, cur, share_of, 1, warp, lane);
     if (threadIdx.x == 0) {
         *abort_flag = 0;
         ws_bars_init(smem);
@@ -67,7 +68,7 @@ __global__ void __launch_bounds__(GEMV_CONSUMERS, 1) gemv1_kernel(const GemvPara
     };
     stamp(2);
     uint32_t seq = 0;
-    ws_consume<QT>(share, p.chunk_q, p.chunk_r, warp, lane, slots, cur, bar, pieces, seq, smem_u32(xd), smem_u32(recs),
+    ws_consume<QT, DEPTH>(share, p.chunk_q, p.chunk_r, warp, lane, slots, cur, bar, pieces, seq, smem_u32(xd), smem_u32(recs),
                    smem_u32(recs) + (uint32_t)(kp >> 5) * 16, p.scratch, p.status, smem_u32(const_cast<int*>(abort_flag)), share_of, 1,
                    emit_row);
     stamp(4);

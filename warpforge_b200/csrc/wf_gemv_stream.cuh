@@ -40,8 +40,13 @@ struct WsPiece {  // the sums of one cut row-tile as far as one warp's run cover
 };
 constexpr int WS_PIECE_BYTES = WS_SLOTS * GEMV_WARPS * 2 * (int)sizeof(WsPiece);
 
-template <int QT> struct WsGeom {
-    static constexpr int DEPTH = Tile<QT>::BYTES <= 1280 ? 4 : 2;  // tiles a warp holds in registers
+// Tiles a warp holds in registers.  The per-projection kernel has room for six 1.1 KB tiles; the program kernel, which
+// keeps more state alive around the tile loop, spills from five on (506 against 791 tok/s at six), so it holds four.
+#ifndef WS_DEPTH_SINGLE
+#define WS_DEPTH_SINGLE 6
+#endif
+template <int QT, bool PROGRAM> struct WsGeom {
+    static constexpr int DEPTH = Tile<QT>::BYTES <= 1280 ? (PROGRAM ? 4 : WS_DEPTH_SINGLE) : 2;
 };
 
 // Shared memory of the one-token kernels:
@@ -114,7 +119,7 @@ struct WsCursor {
     const uint8_t* tiles = nullptr;
 };
 // The next group to request: address of its first tile and its number of tiles (0 once the program is exhausted).
-template <int QT, class ShareFn>
+template <int QT, int DEPTH, class ShareFn>
 __device__ __forceinline__ void ws_next_group(WsCursor& c, ShareFn& share_of, int n_ops, int warp, const uint8_t*& base, int& cnt) {
     while (c.t >= c.end) {
         if (c.op + 1 >= n_ops) {
@@ -128,7 +133,7 @@ __device__ __forceinline__ void ws_next_group(WsCursor& c, ShareFn& share_of, in
         ws_run(sh.t0, sh.t1, warp, c.t, c.end);
         c.tiles = sh.tiles;
     }
-    cnt = min(WsGeom<QT>::DEPTH, c.end - c.t);
+    cnt = min(DEPTH, c.end - c.t);
     base = c.tiles + (size_t)c.t * Tile<QT>::BYTES;
     c.t += cnt;
 }
@@ -140,14 +145,14 @@ template <int QT> struct WsLanePtrs {
         : pc(base + lane * 16), ps(base + TileRegs<QT>::lane_scale_offset(lane)) {}
 };
 // Request the first group of the stream (the weights depend on nothing, so this comes before any wait).
-template <int QT, class ShareFn>
-__device__ __forceinline__ void ws_prime(TileRegs<QT> (&slots)[WsGeom<QT>::DEPTH], WsCursor& c, ShareFn& share_of, int n_ops,
+template <int QT, int DEPTH, class ShareFn>
+__device__ __forceinline__ void ws_prime(TileRegs<QT> (&slots)[DEPTH], WsCursor& c, ShareFn& share_of, int n_ops,
                                          int warp, int lane) {
     const uint8_t* base;
     int cnt;
-    ws_next_group<QT>(c, share_of, n_ops, warp, base, cnt);
+    ws_next_group<QT, DEPTH>(c, share_of, n_ops, warp, base, cnt);
     const WsLanePtrs<QT> lp(base, lane);
-    static_for<WsGeom<QT>::DEPTH>([&](auto J) {
+    static_for<DEPTH>([&](auto J) {
         constexpr int j = decltype(J)::value;
         if (j < cnt) slots[j].template load_global<j * Tile<QT>::BYTES>(lp.pc, lp.ps);
     });
@@ -178,14 +183,13 @@ __device__ __forceinline__ void ws_bars_init(uint8_t* smem) {
 //   x32 / c32 / s32: shared addresses of the staged digits, the block records and the activation sums;
 //   emit_row(n, value): store output row n of this weight (called by one lane per row);
 //   share_of(o): the CTA's share of weight o of the program.
-template <int QT, class EmitRow, class ShareFn>
+template <int QT, int DEPTH, class EmitRow, class ShareFn>
 __device__ __forceinline__ void ws_consume(const WsShare& sh, int chunk_q, int chunk_r, int warp, int lane,
-                                           TileRegs<QT> (&slots)[WsGeom<QT>::DEPTH], WsCursor& cur, const WsBars& bar,
+                                           TileRegs<QT> (&slots)[DEPTH], WsCursor& cur, const WsBars& bar,
                                            WsPiece* pieces, uint32_t& seq, uint32_t x32, uint32_t c32, uint32_t s32,
                                            uint2* slots_g, int* status, uint32_t abort32, ShareFn& share_of, int n_ops,
                                            EmitRow&& emit_row) {
     using T = Tile<QT>;
-    constexpr int DEPTH = WsGeom<QT>::DEPTH;
     constexpr uint32_t XSTEP = (T::K / 128) * Q8_UNIT_BYTES, RSTEP = (T::K >> 5) * 16, SSTEP = (T::K >> 5) * 8;  // staged bytes per tile
     const int g = lane >> 2, q = lane & 3, kt = sh.kt;
     const uint32_t lane_is_0 = lane == 0;
@@ -256,7 +260,7 @@ __device__ __forceinline__ void ws_consume(const WsShare& sh, int chunk_q, int c
             // the slots of this group are used up
             const uint8_t* nbase;
             int ncnt;
-            ws_next_group<QT>(cur, share_of, n_ops, warp, nbase, ncnt);
+            ws_next_group<QT, DEPTH>(cur, share_of, n_ops, warp, nbase, ncnt);
             const WsLanePtrs<QT> lp(nbase, lane);
             if (g0 + DEPTH <= len && kk + DEPTH <= kt && ncnt == DEPTH) {
                 // a whole group inside one row-tile, a whole group to request: straight-line code, immediate offsets
