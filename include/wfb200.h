@@ -284,6 +284,12 @@ int wf_program_create_fused(int64_t ctx, int n_ops, const int64_t* weights, cons
                             const int64_t* residual_dev, int64_t m, int world, int rank, const int64_t* landing_dev,
                             int64_t* program);
 int wf_program_run(int64_t ctx, int64_t program, int64_t stream);
+/* One token end to end in one call: copy n_in activation buffers from (pinned) host memory to their device
+ * buffers, run the program, copy out_bytes of a result back to host memory, wait, and report a device-side wait
+ * that ran out (WF_ERR_DEVICE_WAIT) -- what a per-token loop of the reference does with copyToDevice / execute /
+ * copyToHost / synchronize (nvidia/ops/DotGeneralKernel.java:169-298), without the allocations. */
+int wf_program_step_host(int64_t ctx, int64_t program, int n_in, const void* const* host_src, const int64_t* dev_dst,
+                         const int64_t* bytes, void* host_out, int64_t dev_out, int64_t out_bytes, int64_t stream);
 int wf_program_destroy(int64_t ctx, int64_t program);
 /* With wf_set_salt(ctx, 2) before wf_program_create: [sm_count][64] globaltimer stamps of the first ops
  * (kernel start, then per op: start, after barrier, after staging, after compute). */

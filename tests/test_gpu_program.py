@@ -277,3 +277,27 @@ def test_weight_held_by_a_program_cannot_be_freed():
         st.close()  # destroys the program first, then frees every weight
     finally:
         ctx.close()
+
+
+def test_step_from_host_buffers_in_one_call(oracle):
+    """wf_program_step_host: activations from pinned host memory, the program, the last output back, one call."""
+    from warpforge_b200.backend import CudaContext
+    from warpforge_b200.decode import LLAMA_7B_Q4_0, ProjectionStack
+
+    ctx = CudaContext(0)
+    try:
+        st = ProjectionStack(ctx, LLAMA_7B_Q4_0, tokens=1, layers=1)
+        st.mode = "program"
+        st.build_program()
+        name, rows, k = st.spec.projections[-1]
+        pinned_in = {kk: ctx.host_alloc(v.nbytes) for kk, v in st.x_host.items()}
+        y_out = np.zeros((1, rows), np.float32)
+        pinned_out = ctx.host_alloc(y_out.nbytes)
+        # other activations than the ones uploaded at construction: the call must bring them over itself
+        x_new = {kk: Q.synth_activation_bf16(1, kk, 900 + kk) for kk in st.x_host}
+        st.step_host(x_new, y_out, pinned_in, pinned_out)
+        want = oracle.qlinear(O.Q4_0, st.blocks[name], rows, k, Q.bf16_bits_to_float(x_new[k]), nthreads=oracle.max_threads())
+        assert np.max(np.abs(y_out - want)) <= 1e-3 * np.max(np.abs(want))
+        st.close()
+    finally:
+        ctx.close()

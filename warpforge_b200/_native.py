@@ -65,6 +65,7 @@ SIGNATURES = {
     "wf_allgather": (c_int, [c_i64, c_i64, c_i64, c_i64, c_i64, c_i64]),
     "wf_program_create": (c_int, [c_i64, c_int, P(c_i64), P(c_i64), P(c_i64), P(c_int), c_i64, c_int, c_int, P(c_i64), P(c_i64)]),
     "wf_plan_several_tokens": (c_int, [c_int, c_i64, c_i64, c_int, c_int, c_int, P(c_int), P(c_int), P(c_int), P(c_int), P(c_i64)]),
+    "wf_program_step_host": (c_int, [c_i64, c_i64, c_int, P(c_vp), P(c_i64), P(c_i64), c_vp, c_i64, c_i64, c_i64]),
     "wf_program_create_fused": (c_int, [c_i64, c_int, P(c_i64), P(c_i64), P(c_i64), P(c_int), P(c_int), P(c_i64), P(ctypes.c_float),
                                         P(c_i64), c_i64, c_int, c_int, P(c_i64), P(c_i64)]),
     "wf_program_run": (c_int, [c_i64, c_i64, c_i64]),

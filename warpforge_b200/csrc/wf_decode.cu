@@ -743,6 +743,34 @@ int wf_program_run(int64_t ctx, int64_t program, int64_t stream) {
     return WF_OK;
 }
 
+int wf_program_step_host(int64_t ctx, int64_t program, int n_in, const void* const* host_src, const int64_t* dev_dst,
+                         const int64_t* bytes, void* host_out, int64_t dev_out, int64_t out_bytes, int64_t stream) {
+    {
+        Context* c = get_context(ctx);
+        if (!c) return WF_ERR_INVALID_HANDLE;
+        ScopedLock lk(c);
+        if (!lk.ok) return WF_ERR_BUSY;
+        if (n_in < 0 || (n_in > 0 && (!host_src || !dev_dst || !bytes)) || out_bytes < 0 || (out_bytes > 0 && (!host_out || !dev_out)))
+            return set_error(c, WF_ERR_INVALID_ARGUMENT, "null pointer or negative size");
+        WF_CUDA(c, cudaSetDevice(c->device));
+        cudaStream_t s = resolve_stream(c, stream);
+        for (int i = 0; i < n_in; i++) {
+            if (!host_src[i] || !dev_dst[i] || bytes[i] < 0) return set_error(c, WF_ERR_INVALID_ARGUMENT, "input %d: null pointer or negative size", i);
+            WF_CUDA(c, cudaMemcpyAsync(reinterpret_cast<void*>(dev_dst[i]), host_src[i], (size_t)bytes[i], cudaMemcpyHostToDevice, s));
+        }
+    }
+    const int rc = wf_program_run(ctx, program, stream);
+    if (rc != WF_OK) return rc;
+    Context* c = get_context(ctx);
+    if (!c) return WF_ERR_INVALID_HANDLE;
+    ScopedLock lk(c);
+    if (!lk.ok) return WF_ERR_BUSY;
+    cudaStream_t s = resolve_stream(c, stream);
+    if (out_bytes > 0) WF_CUDA(c, cudaMemcpyAsync(host_out, reinterpret_cast<const void*>(dev_out), (size_t)out_bytes, cudaMemcpyDeviceToHost, s));
+    WF_CUDA(c, cudaStreamSynchronize(s));
+    return read_device_status(c);
+}
+
 int wf_program_read_timing(int64_t ctx, int64_t program, int64_t* out, int64_t n) {
     Context* c = get_context(ctx);
     if (!c) return WF_ERR_INVALID_HANDLE;

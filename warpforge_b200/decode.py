@@ -208,15 +208,25 @@ class ProjectionStack:
             self.ctx.graph_launch(self.graph, stream)
 
     def step_host(self, x_host: dict, y_out: np.ndarray, pinned_in: dict, pinned_out: int, stream: int = 0) -> None:
-        """One token end to end: activations from pinned host memory, the step, the last
-        projection's output back to pinned host memory, then wait."""
+        """One token end to end: this step's activations are written into pinned host memory, copied to the device,
+        the step runs, the last projection's output comes back to pinned host memory, then wait."""
         ctx, lib = self.ctx, self.ctx._lib
-        for k, dptr in self.x_dev.items():
+        for k in self.x_dev:
             ctypes.memmove(pinned_in[k], x_host[k].ctypes.data, x_host[k].nbytes)
-            ctx._ck("wf_memcpy_h2d", lib.wf_memcpy_h2d(ctx.handle, dptr, pinned_in[k], x_host[k].nbytes, stream, 0))
-        self.step(stream)
         last = self.spec.projections[-1][0]
-        ctx._ck("wf_memcpy_d2h", lib.wf_memcpy_d2h(ctx.handle, pinned_out, self.y_dev[last], y_out.nbytes, stream, 1))
+        if self.mode == "program":  # copies, the kernel, the copy back and the wait in one native call
+            if not hasattr(self, "_step_args"):
+                ks = list(self.x_dev)
+                self._step_args = ((ctypes.c_void_p * len(ks))(*[pinned_in[k] for k in ks]), (ctypes.c_int64 * len(ks))(*[self.x_dev[k] for k in ks]),
+                                   (ctypes.c_int64 * len(ks))(*[x_host[k].nbytes for k in ks]), len(ks))
+            src, dst, nb, n = self._step_args
+            ctx._ck("wf_program_step_host", lib.wf_program_step_host(ctx.handle, self.program, n, src, dst, nb, pinned_out, self.y_dev[last],
+                                                                      y_out.nbytes, stream))
+        else:
+            for k, dptr in self.x_dev.items():
+                ctx._ck("wf_memcpy_h2d", lib.wf_memcpy_h2d(ctx.handle, dptr, pinned_in[k], x_host[k].nbytes, stream, 0))
+            self.step(stream)
+            ctx._ck("wf_memcpy_d2h", lib.wf_memcpy_d2h(ctx.handle, pinned_out, self.y_dev[last], y_out.nbytes, stream, 1))
         ctypes.memmove(y_out.ctypes.data, pinned_out, y_out.nbytes)
 
     def read_output(self, name: str) -> np.ndarray:
