@@ -539,6 +539,10 @@ constexpr int XPRE_THREADS = 256, XPRE_KEEP = 4;
 __global__ void __launch_bounds__(XPRE_THREADS) x_to_f16_kernel(const uint16_t* __restrict__ x, __half* __restrict__ x16,
                                                                 float* __restrict__ unscale, int k) {
     __shared__ int s_emax;
+    // Launched with programmatic stream serialization itself: its CTAs may be placed while the previous kernel of the
+    // stream drains, but nothing is read or written before that kernel has completed (it may have produced x, and a
+    // previous GEMM may still be reading the fp16 copy this kernel rewrites).
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the GEMM may set itself up while the rows are converted
     const uint4* row = reinterpret_cast<const uint4*>(x + (size_t)blockIdx.x * k);  // k is a multiple of 8
     uint4* out = reinterpret_cast<uint4*>(x16 + (size_t)blockIdx.x * k);
@@ -604,7 +608,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmParams 
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     // this launch's generation: the previous GEMM of the stream has ended before this kernel starts (the activation
-    // pre-pass between them is an ordinary launch), so its closing store is visible
+    // pre-pass between them waits for it before it lets this kernel go), so its closing store is visible
     unsigned int launch_gen = ld_acquire_u32(p.gen) + 1u;
     if (launch_gen == 0u) launch_gen = 1u;  // 0 is what untouched flags hold
     const bool wide = p.halves == 2, k64 = wide;  // 64-k stages go with the two-half token tiles (alone they measured 25 % slower)
@@ -1048,8 +1052,18 @@ int gemm_launch(Context* c, const GemvCall& call, cudaStream_t s) {
     }
     __half* x16 = static_cast<__half*>(c->d_x16);
     float* unscale = reinterpret_cast<float*>(static_cast<uint8_t*>(c->d_x16) + ((call.m * w.g.k * 2 + 255) & ~255LL));
-    x_to_f16_kernel<<<(unsigned)call.m, XPRE_THREADS, 0, s>>>(static_cast<const uint16_t*>(call.d_x), x16, unscale, (int)w.g.k);
-    WF_CUDA(c, cudaGetLastError());
+    {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)call.m);
+        cfg.blockDim = dim3(XPRE_THREADS);
+        cfg.stream = s;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        WF_CUDA(c, cudaLaunchKernelEx(&cfg, x_to_f16_kernel, static_cast<const uint16_t*>(call.d_x), x16, unscale, (int)w.g.k));
+    }
     c->launches++;
     p.row_unscale = unscale;
 
