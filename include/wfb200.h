@@ -174,6 +174,10 @@ int wf_layer_norm(int64_t ctx, int64_t x_dev, int64_t gamma_dev, int64_t beta_de
                   int64_t n, float eps, int64_t stream);
 int wf_softmax(int64_t ctx, int64_t x_dev, int64_t y_dev, int64_t rows, int64_t n, int64_t stream);
 int wf_silu(int64_t ctx, int64_t x_dev, int64_t y_dev, int64_t count, int64_t stream);
+/* stablehlo.dot on dense fp32 device operands: C[m,n] = A[m,k] . B[k,n], row-major (nvidia/ops/DotKernel.java:18-154;
+ * CPU arithmetic cpu/ops/scalar/DotKernel.java:51-59).  Each output is summed over k ascending with a separate
+ * multiply and add, as the CPU kernel does, so the bits are the CPU's.  A vector operand is a matrix with m = 1 or n = 1. */
+int wf_dot_f32(int64_t ctx, int64_t a_dev, int64_t b_dev, int64_t c_dev, int64_t m, int64_t n, int64_t k, int64_t stream);
 /* gelu, tanh form: 0.5 x (1 + tanh(0.7978845608 (x + 0.044715 x^3))), cpu/ops/scalar/CustomCallKernel.java:226-260. */
 int wf_gelu(int64_t ctx, int64_t x_dev, int64_t y_dev, int64_t count, int64_t stream);
 int wf_swiglu(int64_t ctx, int64_t gate_dev, int64_t up_dev, int64_t y_dev, int64_t count, int64_t stream);

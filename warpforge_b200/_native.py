@@ -41,6 +41,7 @@ SIGNATURES = {
     "wf_layer_norm": (c_int, [c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_f32, c_i64]),
     "wf_softmax": (c_int, [c_i64, c_i64, c_i64, c_i64, c_i64, c_i64]),
     "wf_silu": (c_int, [c_i64, c_i64, c_i64, c_i64, c_i64]),
+    "wf_dot_f32": (c_int, [c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_i64]),
     "wf_gelu": (c_int, [c_i64, c_i64, c_i64, c_i64, c_i64]),
     "wf_swiglu": (c_int, [c_i64, c_i64, c_i64, c_i64, c_i64, c_i64]),
     "wf_add": (c_int, [c_i64, c_i64, c_i64, c_i64, c_i64, c_i64]),

@@ -349,6 +349,13 @@ class AddOp:
 
 
 @dataclass(frozen=True)
+class DotOp:
+    """stablehlo.dot: [M,K] x [K,N], [M,K] x [K], [K] x [K,N] or [K] x [K] on dense fp32 tensors
+    (snakeburger-core/.../stablehlo/StableHloAst.java DotOp)."""
+    result_shape: Sequence[int]
+
+
+@dataclass(frozen=True)
 class MultiplyOp:
     """stablehlo.multiply; only the fused form silu(gate) * up exists on the device (``swiglu``)."""
     result_shape: Sequence[int]
@@ -440,12 +447,76 @@ class CudaCustomCallKernel(CudaOpKernel):
                 ctx.free(p)
 
 
+class DotKernel(CudaOpKernel):
+    """Mirror of nvidia/ops/DotKernel.java:18-154 (C[M,N] = A[M,K] * B[K,N], fp32), with the vector forms of the CPU
+    kernel (cpu/ops/scalar/DotKernel.java:18-102: [K] x [K] -> [1], [M,K] x [K] -> [M], [K] x [K,N] -> [N]).  Host tensors
+    are copied to the device, the kernel runs, the result comes back; DeviceTensor inputs stay on the device."""
+
+    def __init__(self, context: CudaContext, salt: int = 0, stream: int = 0):
+        self.context, self.salt, self.stream = context, salt, stream
+
+    def supports(self, op) -> bool:
+        return isinstance(op, DotOp)
+
+    def execute(self, op, inputs: List) -> List:
+        if not isinstance(op, DotOp):
+            raise ValueError(f"Expected DotOp, got: {type(op).__name__}")
+        if len(inputs) != 2:
+            raise ValueError(f"Dot requires exactly 2 inputs, got: {len(inputs)}")
+        lhs, rhs = inputs
+        ls, rs = tuple(lhs.shape()), tuple(rhs.shape())
+        if len(ls) == 1 and len(rs) == 1:
+            m, k, k2, n, out_shape = 1, ls[0], rs[0], 1, (1,)
+        elif len(ls) == 2 and len(rs) == 2:
+            m, k, k2, n, out_shape = ls[0], ls[1], rs[0], rs[1], (ls[0], rs[1])
+        elif len(ls) == 2 and len(rs) == 1:
+            m, k, k2, n, out_shape = ls[0], ls[1], rs[0], 1, (ls[0],)
+        elif len(ls) == 1 and len(rs) == 2:
+            m, k, k2, n, out_shape = 1, ls[0], rs[0], rs[1], (rs[1],)
+        else:
+            raise UnsupportedOperationError(f"Dot operation not supported for shapes: {list(ls)} x {list(rs)}")
+        if k != k2:
+            raise ValueError(f"Inner dimensions must match: A[{m},{k}] * B[{k2},{n}]")
+        for t in (lhs, rhs):
+            if t.dtype != "f32":
+                raise ValueError("Dot requires fp32 tensors")
+        ctx, lib, s = self.context, self.context._lib, self.stream
+        on_device = all(isinstance(t, DeviceTensor) for t in inputs)
+        temps, ptrs = [], []
+        try:
+            for t in inputs:
+                if isinstance(t, DeviceTensor):
+                    ptrs.append(t.ptr)
+                else:
+                    a = np.ascontiguousarray(t.data, np.float32)
+                    p = ctx.allocate(max(a.nbytes, 4))
+                    temps.append(p)
+                    if a.nbytes:
+                        ctx.copy_to_device(p, a, s)
+                    ptrs.append(p)
+            out = ctx.allocate(max(m * n * 4, 4))
+            ctx._ck("wf_dot_f32", lib.wf_dot_f32(ctx.handle, ptrs[0], ptrs[1], out, m, n, k, s))
+            if on_device:
+                return [DeviceTensor(out, out_shape, "f32", owner=ctx)]
+            host = np.empty(out_shape, np.float32)
+            try:
+                if host.nbytes:
+                    ctx.copy_to_host(host, out, s, sync=True)
+            finally:
+                ctx.free(out)
+            return [Tensor(host, "f32")]
+        finally:
+            for p in temps:
+                ctx.free(p)
+
+
 class NvidiaBackend:
     def __init__(self, device_index: int = 0, salt: int = 0):
         self._device_index, self._salt = device_index, salt
         self.cuda_context = CudaContext(device_index)
         glue = CudaCustomCallKernel(self.cuda_context, salt)
-        self._kernels = {DotGeneralOp: QuantizedLinearKernel(self.cuda_context, salt), CustomCallOp: glue, AddOp: glue}
+        self._kernels = {DotGeneralOp: QuantizedLinearKernel(self.cuda_context, salt), CustomCallOp: glue, AddOp: glue,
+                         DotOp: DotKernel(self.cuda_context, salt)}
         self._closed = False
         self._weights: List[QuantizedWeight] = []
 

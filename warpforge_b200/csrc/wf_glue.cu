@@ -263,6 +263,59 @@ __global__ void __launch_bounds__(256) elementwise_kernel(const float* __restric
     }
 }
 
+// stablehlo.dot on dense fp32 operands, C[M,N] = A[M,K] . B[K,N] (the reference's GPU kernel:
+// nvidia/ops/DotKernel.java:18-154 with the naive PTX of nvidia/cuda/CudaKernels.java; CPU arithmetic
+// cpu/ops/scalar/DotKernel.java:51-59).  Every output is summed by one thread over k ascending with a separate
+// multiply and add, exactly the CPU loop `sum += a * b`, so the result has the CPU's bits; tiles of 64 x 64 outputs
+// (4 x 4 per thread) and 16 k per step go through shared memory.  Not a hot path (the quantized linear is): plain
+// fp32 arithmetic, no tensor cores, because a reordered or fused sum would not be the reference's number.
+constexpr int DOT_TILE = 64, DOT_KSTEP = 16;
+__global__ void __launch_bounds__(256) dot_f32_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ c,
+                                                      int M, int N, int K) {
+    __shared__ float as[DOT_KSTEP][DOT_TILE + 1], bs[DOT_KSTEP][DOT_TILE];
+    const int tx = threadIdx.x, ty = threadIdx.y, tid = ty * 16 + tx;
+    const int n0 = blockIdx.x * DOT_TILE;
+    for (int m0 = blockIdx.y * DOT_TILE; m0 < M; m0 += gridDim.y * DOT_TILE) {
+        float acc[4][4];
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+#pragma unroll
+            for (int j = 0; j < 4; j++) acc[i][j] = 0.f;
+        for (int k0 = 0; k0 < K; k0 += DOT_KSTEP) {
+            // A tile [64 rows][16 k] (transposed into as[k][row]) and B tile [16 k][64 cols]: 1024 elements each, 4 per thread
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const int e = tid + u * 256;
+                const int ar = e >> 4, ak = e & 15;
+                as[ak][ar] = (m0 + ar < M && k0 + ak < K) ? a[(size_t)(m0 + ar) * K + k0 + ak] : 0.f;
+                const int bk = e >> 6, bc = e & 63;
+                bs[bk][bc] = (k0 + bk < K && n0 + bc < N) ? b[(size_t)(k0 + bk) * N + n0 + bc] : 0.f;
+            }
+            __syncthreads();
+            const int kmax = min(DOT_KSTEP, K - k0);  // never add the zero padding: (-0) + (+0) would lose a sign
+            for (int kk = 0; kk < kmax; kk++) {
+                float av[4], bv[4];
+#pragma unroll
+                for (int i = 0; i < 4; i++) av[i] = as[kk][ty * 4 + i];
+#pragma unroll
+                for (int j = 0; j < 4; j++) bv[j] = bs[kk][tx * 4 + j];
+#pragma unroll
+                for (int i = 0; i < 4; i++)
+#pragma unroll
+                    for (int j = 0; j < 4; j++) acc[i][j] = __fadd_rn(acc[i][j], __fmul_rn(av[i], bv[j]));
+            }
+            __syncthreads();
+        }
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int r = m0 + ty * 4 + i, col = n0 + tx * 4 + j;
+                if (r < M && col < N) c[(size_t)r * N + col] = acc[i][j];
+            }
+    }
+}
+
 // CustomCallKernel.java:282-318: row `index` of the table per looked-up position.  The CPU throws on an
 // index outside the table; here such a row is filled with zeros and the status word says so.
 __global__ void __launch_bounds__(256) embedding_kernel(const int64_t* __restrict__ indices, const float* __restrict__ table,
@@ -381,6 +434,18 @@ static int elementwise(int64_t ctx, int op, const char* what, int64_t a_dev, int
 
 int wf_silu(int64_t ctx, int64_t x_dev, int64_t y_dev, int64_t count, int64_t stream) {
     return elementwise(ctx, EL_SILU, "silu", x_dev, 0, y_dev, count, stream);
+}
+
+int wf_dot_f32(int64_t ctx, int64_t a_dev, int64_t b_dev, int64_t c_dev, int64_t m, int64_t n, int64_t k, int64_t stream) {
+    GLUE_ENTER(ctx);
+    if (m < 0 || n < 0 || k < 0 || m > (1LL << 30) || n > (1LL << 30) || k > (1LL << 30)) return set_error(c, WF_ERR_SHAPE, "dot: dimension out of range");
+    if (m == 0 || n == 0) return WF_OK;
+    if (!c_dev || (k > 0 && (!a_dev || !b_dev))) return set_error(c, WF_ERR_INVALID_ARGUMENT, "dot: null pointer");
+    if ((a_dev | b_dev | c_dev) & 3) return set_error(c, WF_ERR_INVALID_ARGUMENT, "dot: fp32 pointers must be 4-byte aligned");
+    const dim3 grid((unsigned)((n + DOT_TILE - 1) / DOT_TILE), (unsigned)std::min<int64_t>((m + DOT_TILE - 1) / DOT_TILE, 65535));
+    dot_f32_kernel<<<grid, dim3(16, 16), 0, s>>>(reinterpret_cast<const float*>(a_dev), reinterpret_cast<const float*>(b_dev),
+                                                 reinterpret_cast<float*>(c_dev), (int)m, (int)n, (int)k);
+    return launched(c, "dot");
 }
 
 int wf_gelu(int64_t ctx, int64_t x_dev, int64_t y_dev, int64_t count, int64_t stream) {
