@@ -58,6 +58,9 @@ def test_invalid_handles_and_arguments_without_a_device():
     assert lib.wf_destroy(0x1234) == N.WF_ERR_INVALID_HANDLE
     assert lib.wf_stream_sync(77, 0) == N.WF_ERR_INVALID_HANDLE
     assert lib.wf_qlinear(77, 1, None, 1, 0, 1, None, 0, 0) == N.WF_ERR_INVALID_HANDLE
+    assert lib.wf_program_step_host(77, 1, 0, None, None, None, None, 0, 0, 0) == N.WF_ERR_INVALID_HANDLE
+    assert lib.wf_dot_f32(77, 1, 1, 1, 1, 1, 1, 0) == N.WF_ERR_INVALID_HANDLE
+    assert lib.wf_gelu(77, 1, 1, 1, 0) == N.WF_ERR_INVALID_HANDLE
     assert lib.wf_init(0, None) == N.WF_ERR_INVALID_ARGUMENT
     assert lib.wf_device_count(None) == N.WF_ERR_INVALID_ARGUMENT
     assert lib.wf_comm_get_unique_id(None) == N.WF_ERR_INVALID_ARGUMENT
