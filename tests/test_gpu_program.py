@@ -301,3 +301,59 @@ def test_step_from_host_buffers_in_one_call(oracle):
         st.close()
     finally:
         ctx.close()
+
+
+@pytest.mark.parametrize("seed", [1, 2])
+def test_random_one_token_programs(oracle, seed):
+    """Seeded random op lists: 1 - 9 projections of random row counts (one row to 6000) over up to three input widths,
+    some sharing the staged activations with their predecessor (cut as one list of row-tiles), some staging anew after
+    a barrier; every output against the oracle, after the program has run twice."""
+    import ctypes
+
+    from warpforge_b200 import _native as N
+    from warpforge_b200.backend import CudaContext, QuantizedWeight
+
+    types = [(Q.QuantizationType.Q4_0, O.Q4_0), (Q.QuantizationType.Q8_0, O.Q8_0), (Q.QuantizationType.Q4_K, O.Q4_K), (Q.QuantizationType.Q4_1, O.Q4_1)]
+    rng = np.random.default_rng(seed)
+    ctx = CudaContext(0)
+    lib = ctx._lib
+    try:
+        for it in range(12):
+            qt, oq = types[rng.integers(len(types))]
+            blk = 256 if qt == Q.QuantizationType.Q4_K else 32
+            widths = [blk * int(rng.integers(1, 12288 // blk + 1)) for _ in range(3)]
+            ops, xs, prev_k = [], {}, None
+            for _ in range(int(rng.integers(1, 10))):
+                k = widths[rng.integers(3)] if (prev_k is None or rng.random() < 0.4) else prev_k
+                rows = int(rng.choice([1, 16, 33, 100, 512, 1000, 2368, 4096, 6000]))
+                ops.append((rows, k, 3 if (prev_k is None or k != prev_k or rng.random() < 0.4) else 0))
+                prev_k = k
+                if k not in xs:
+                    xb = Q.synth_activation_bf16(1, k, 77 + k)
+                    d = ctx.allocate(xb.nbytes)
+                    ctx.copy_to_device(d, xb)
+                    xs[k] = (xb, d)
+            blocks = [Q.synth_weight(qt, rows, k, 500 + it * 20 + i) for i, (rows, k, _) in enumerate(ops)]
+            ws = [QuantizedWeight(ctx, qt, b, rows, k) for b, (rows, k, _) in zip(blocks, ops)]
+            ys = [ctx.allocate(rows * 4) for rows, _, _ in ops]
+            arr = lambda v, t: (t * len(v))(*v)
+            prog = ctypes.c_int64()
+            ctx._ck("wf_program_create", lib.wf_program_create(
+                ctx.handle, len(ops), arr([w.handle for w in ws], ctypes.c_int64), arr([xs[k][1] for _, k, _ in ops], ctypes.c_int64),
+                arr(ys, ctypes.c_int64), arr([f for _, _, f in ops], ctypes.c_int), 1, 1, 0, None, ctypes.byref(prog)))
+            for _ in range(2):
+                ctx._ck("wf_program_run", lib.wf_program_run(ctx.handle, prog.value, 0))
+            ctx.synchronize()
+            for i, (rows, k, _) in enumerate(ops):
+                got = np.empty((1, rows), np.float32)
+                ctx.copy_to_host(got, ys[i])
+                want = oracle.qlinear(oq, blocks[i], rows, k, Q.bf16_bits_to_float(xs[k][0]), nthreads=oracle.max_threads())
+                rel = float(np.max(np.abs(got - want)) / max(float(np.max(np.abs(want))), 1e-30))
+                assert np.isfinite(got).all() and rel <= 1e-3, f"{qt.name} program {it} op {i} of {ops}: {rel:.3e}"
+            ctx._ck("wf_program_destroy", lib.wf_program_destroy(ctx.handle, prog.value))
+            for w in ws:
+                w.close()
+            for p in ys + [d for _, d in xs.values()]:
+                ctx.free(p)
+    finally:
+        ctx.close()
