@@ -1,8 +1,8 @@
-// Device-side building blocks of the decode GEMV, shared by the single-op kernel (wf_gemv.cu)
-// and the persistent multi-op kernel (wf_decode.cu): shared-memory ring primitives, the walk over
-// a CTA's share of a weight (producer and consumer side, segment reduction, fix-up between
-// CTAs), the unpack + tensor-core block routine, the per-format tile code and the activation
-// staging.
+// Device-side building blocks of the decode kernels (wf_gemv.cu, wf_gemv_stream.cuh, wf_gemv_multi.cuh, wf_decode.cu):
+// the per-format tile code (loads into registers, the one-token integer arithmetic on activation digits, the
+// several-token bf16 arithmetic), the activation staging, the exchange of cut row-tiles between CTAs, and -- for
+// the several-token program kernel only -- the shared-memory ring primitives and the walk over a CTA's share of a
+// weight (producer and consumer side, segment reduction).
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
