@@ -241,6 +241,13 @@ int wf_qlinear_noalloc(int64_t ctx, int64_t weight, int64_t x_dev, int x_dtype, 
 int wf_comm_get_unique_id(void* id128);
 int wf_comm_init(int64_t ctx, const void* id128, int rank, int world, int64_t* comm);
 int wf_comm_destroy(int64_t ctx, int64_t comm);
+/* rank, world and whether the ranks could map each other's landing buffers (cudaIpc, one node): with
+ * peer_stores == 1, wf_qlinear_allgather of up to 32 tokens (outputs of at most 2 M floats over all ranks)
+ * exchanges the row blocks by one kernel of 8-byte {value, tag} stores into the peers' memory instead of an
+ * NCCL all-gather plus a copy; larger outputs and the tensor-core path keep NCCL.  A rank waits at most
+ * WF_GATHER_WAIT_MS (environment, default 5000) for its peers' stores, then sets the peer-wait status.
+ * WF_GATHER=nccl in the environment at wf_comm_init keeps every gather on NCCL.  Any pointer may be null. */
+int wf_comm_info(int64_t ctx, int64_t comm, int* rank, int* world, int* peer_stores);
 int wf_allgather(int64_t ctx, int64_t comm, int64_t send_dev, int64_t recv_dev, int64_t bytes_per_rank,
                  int64_t stream);
 

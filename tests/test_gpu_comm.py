@@ -132,3 +132,118 @@ def test_two_rank_allgather_lands_rank_major(tmp_path):
                         "127.0.0.1", "--master-port", "29534", str(script)], capture_output=True, text=True, timeout=600, env=env)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert "RANK_OK 0" in r.stdout and "RANK_OK 1" in r.stdout
+
+
+_PEER_STORES = r"""
+import os, sys
+sys.path.insert(0, %r)
+import numpy as np
+import torch.distributed as dist
+from oracle import oracle as O
+from warpforge_b200 import _native as N, quant as Q
+from warpforge_b200.backend import CudaContext, QuantizedWeight
+from warpforge_b200.decode import Communicator
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+dist.init_process_group("gloo", rank=rank, world_size=world)
+ctx = CudaContext(int(os.environ["LOCAL_RANK"]))
+ids = [Communicator.create_unique_id() if rank == 0 else None for _ in range(3)]
+dist.broadcast_object_list(ids, src=0)
+peer = Communicator(ctx, ids[0], rank, world)
+os.environ["WF_GATHER"] = "nccl"
+nccl = Communicator(ctx, ids[1], rank, world)
+os.environ["WF_GATHER"] = "registers"   # large gathers by loads into registers instead of bulk copies through shared memory
+regs = Communicator(ctx, ids[2], rank, world)
+del os.environ["WF_GATHER"]
+assert peer.peer_stores and regs.peer_stores and not nccl.peer_stores
+lib, orc = ctx._lib, O.COracle()
+rows, k = 2048 + 64 * world, 1024     # 1056 or so rows per rank: a ragged last row tile
+rows -= rows %% world
+def gathered(comm, w, dx, dtype, m, dy):
+    ctx.copy_to_device(dy, np.full((m, rows), np.nan, np.float32))
+    ctx._ck("wf_qlinear_allgather", lib.wf_qlinear_allgather(ctx.handle, comm.handle, w.handle, dx, dtype, m, dy, 0))
+    ctx.synchronize()
+    got = np.empty((m, rows), np.float32)
+    ctx.copy_to_host(got, dy)
+    return got
+calls = 0
+for qt, oq in ((Q.QuantizationType.Q4_0, O.Q4_0), (Q.QuantizationType.Q8_0, O.Q8_0), (Q.QuantizationType.Q4_K, O.Q4_K)):
+    blocks = Q.synth_weight(qt, rows, k, 47)
+    w = QuantizedWeight(ctx, qt, blocks, rows, k, rank, world)
+    for m, f32 in ((1, False), (1, True), (2, False), (5, True), (16, False), (32, False), (48, False), (70, True), (200, False)):
+        xb = Q.synth_activation_bf16(m, k, 47 + m)
+        xf = Q.bf16_bits_to_float(xb)
+        src = xf.astype(np.float32) if f32 else xb
+        dx, dy = ctx.allocate(src.nbytes), ctx.allocate(m * rows * 4)
+        ctx.copy_to_device(dx, src)
+        dtype = N.WF_DTYPE_F32 if f32 else N.WF_DTYPE_BF16
+        a = gathered(peer, w, dx, dtype, m, dy)
+        b = gathered(nccl, w, dx, dtype, m, dy)
+        a2 = gathered(peer, w, dx, dtype, m, dy)   # an odd number of peer gathers per case: both halves of the landing buffer take every shape
+        calls += 2
+        assert np.array_equal(a, b) and np.array_equal(a, a2), (qt.name, m, f32)
+        if m > 32:
+            assert np.array_equal(gathered(regs, w, dx, dtype, m, dy), b), (qt.name, m, f32, "registers")
+        want = orc.qlinear(oq, blocks, rows, k, xf, nthreads=4)
+        assert np.max(np.abs(a - want)) <= 1e-3 * np.max(np.abs(want)), (qt.name, m)
+        ctx.free(dx); ctx.free(dy)
+    # a recorded run of gathers replays: the gather counts live on the device.  3 tokens: tagged stores into the
+    # peers' landing buffers; 40 tokens: the tensor-core kernel, blocks read out of the peers' staging areas
+    for m in (3, 40):
+        xb = Q.synth_activation_bf16(m, k, 5)
+        dx, dy, dz = ctx.allocate(xb.nbytes), ctx.allocate(m * rows * 4), ctx.allocate(m * rows * 4)
+        ctx.copy_to_device(dx, xb)
+        want = gathered(nccl, w, dx, N.WF_DTYPE_BF16, m, dy)
+        s = ctx.create_stream()
+        ctx.graph_begin(s)
+        for out in (dy, dz, dy):
+            ctx._ck("wf_qlinear_allgather", lib.wf_qlinear_allgather(ctx.handle, peer.handle, w.handle, dx, N.WF_DTYPE_BF16, m, out, s))
+        g = ctx.graph_end(s)
+        for _ in range(3):
+            ctx.copy_to_device(dy, np.zeros((m, rows), np.float32))
+            ctx.copy_to_device(dz, np.zeros((m, rows), np.float32))
+            ctx.graph_launch(g, s)
+            ctx.synchronize(s)
+            for buf in (dy, dz):
+                got = np.empty((m, rows), np.float32)
+                ctx.copy_to_host(got, buf)
+                assert np.array_equal(got, want), qt.name
+        ctx.graph_destroy(g)
+        ctx.destroy_stream(s)
+    w.close()
+# strips of 17 KB per (rank, token): the bulk copies through shared memory, two pieces per strip, the second a short one
+rows, k = 4352 * world, 512
+qt = Q.QuantizationType.Q4_0
+blocks = Q.synth_weight(qt, rows, k, 53)
+w = QuantizedWeight(ctx, qt, blocks, rows, k, rank, world)
+for m in (40, 130):
+    xb = Q.synth_activation_bf16(m, k, 53 + m)
+    dx, dy = ctx.allocate(xb.nbytes), ctx.allocate(m * rows * 4)
+    ctx.copy_to_device(dx, xb)
+    a = gathered(peer, w, dx, N.WF_DTYPE_BF16, m, dy)
+    assert np.array_equal(a, gathered(nccl, w, dx, N.WF_DTYPE_BF16, m, dy)), ("bulk", m)
+    assert np.array_equal(a, gathered(regs, w, dx, N.WF_DTYPE_BF16, m, dy)), ("registers", m)
+    assert np.array_equal(a, gathered(peer, w, dx, N.WF_DTYPE_BF16, m, dy)), ("bulk again", m)
+    want = orc.qlinear(O.Q4_0, blocks, rows, k, Q.bf16_bits_to_float(xb), nthreads=4)
+    assert np.max(np.abs(a - want)) <= 1e-3 * np.max(np.abs(want)), m
+    ctx.free(dx); ctx.free(dy)
+w.close()
+dist.barrier()
+peer.close(); nccl.close(); regs.close(); ctx.close(); dist.destroy_process_group()
+os.write(1, f"RANK_OK {rank}\n".encode())
+"""
+
+
+def test_two_rank_peer_store_gather_equals_nccl_gather(tmp_path):
+    """Small gathers go by 8-byte tagged stores into the peers' landing buffers; the result must be bit-identical to
+    the NCCL all-gather + copy of a second communicator that was told to stay on NCCL, eagerly and from a replayed graph."""
+    from warpforge_b200.backend import CudaContext
+
+    if CudaContext.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    script = tmp_path / "peer_store_gather.py"
+    script.write_text(_PEER_STORES % ROOT)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+                        "127.0.0.1", "--master-port", "29535", str(script)], capture_output=True, text=True, timeout=600, env=env)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert "RANK_OK 0" in r.stdout and "RANK_OK 1" in r.stdout

@@ -63,6 +63,7 @@ SIGNATURES = {
     "wf_comm_get_unique_id": (c_int, [c_vp]),
     "wf_comm_init": (c_int, [c_i64, c_vp, c_int, c_int, P(c_i64)]),
     "wf_comm_destroy": (c_int, [c_i64, c_i64]),
+    "wf_comm_info": (c_int, [c_i64, c_i64, c_vp, c_vp, c_vp]),
     "wf_allgather": (c_int, [c_i64, c_i64, c_i64, c_i64, c_i64, c_i64]),
     "wf_program_create": (c_int, [c_i64, c_int, P(c_i64), P(c_i64), P(c_i64), P(c_int), c_i64, c_int, c_int, P(c_i64), P(c_i64)]),
     "wf_plan_several_tokens": (c_int, [c_int, c_i64, c_i64, c_int, c_int, c_int, P(c_int), P(c_int), P(c_int), P(c_int), P(c_i64)]),

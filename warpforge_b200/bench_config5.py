@@ -38,7 +38,8 @@ def peaks():
     return 6650.0, 1590.0, "fallback"
 
 
-def run(world: int = 8, layers: int = 5, iters: int = 3, ctx: CudaContext | None = None, legs=(("decode_batch16", 16), ("prefill_2048", 2048))) -> list:
+def run(world: int = 8, layers: int = 5, iters: int = 3, ctx: CudaContext | None = None, legs=(("decode_batch16", 16), ("prefill_2048", 2048)),
+        graph: bool = False) -> list:
     """Times the legs and returns one dict per leg (rank 0; the other ranks return an empty list)."""
     class A:
         pass
@@ -94,26 +95,46 @@ def run(world: int = 8, layers: int = 5, iters: int = 3, ctx: CudaContext | None
         ctx.copy_to_device(dx, x)
         dy = ctx.allocate(m * rmax * 4 * (nranks if gather else 1))
 
-        def walk():
+        def walk(s=0):
             for row in weights:
                 for name, r, k, w in row:
                     # the activation buffer is read as [m, k] (row stride k): same bytes for every projection
                     if gather:
-                        N.check(name, lib.wf_qlinear_allgather(h, comm.handle, w.handle, dx, N.WF_DTYPE_BF16, m, dy, 0), h)
+                        N.check(name, lib.wf_qlinear_allgather(h, comm.handle, w.handle, dx, N.WF_DTYPE_BF16, m, dy, s), h)
                     else:
-                        N.check(name, lib.wf_qlinear(h, w.handle, dx, N.WF_DTYPE_BF16, 1, m, dy, 1, 0), h)
+                        N.check(name, lib.wf_qlinear(h, w.handle, dx, N.WF_DTYPE_BF16, 1, m, dy, 1, s), h)
+
+        if gather:
+            dist.barrier()  # the ranks enter the first gather together (a peer-store gather waits a bounded time)
+        recorded = 0
+        if graph and m <= 32:  # the walk recorded once and replayed: the host's per-call cost leaves the timed region
+            walk()
+            ctx.synchronize()
+            stream = ctx.create_stream()
+            ctx.graph_begin(stream)
+            walk(stream)
+            recorded = ctx.graph_end(stream)
+
+            def walk(s=0, _g=recorded, _s=stream):
+                ctx.graph_launch(_g, _s)
 
         for _ in range(3):
             walk()
         ctx.synchronize()
         if gather:
             dist.barrier()
-        ctx.record_event(e0)
+        ts = stream if recorded else 0
+        if recorded:
+            ctx.synchronize(ts)
+        ctx.record_event(e0, ts)
         for _ in range(a.iters):
             walk()
-        ctx.record_event(e1)
-        ctx.synchronize()
+        ctx.record_event(e1, ts)
+        ctx.synchronize(ts)
         ms = ctx.elapsed_ms(e0, e1)
+        if recorded:
+            ctx.graph_destroy(recorded)
+            ctx.destroy_stream(stream)
         if gather:
             import torch
 
@@ -131,7 +152,10 @@ def run(world: int = 8, layers: int = 5, iters: int = 3, ctx: CudaContext | None
             tfs = 2.0 * m * shard_macs / us_layer / 1e6
             out.update({"bound": "tensor", "achieved_tflops": round(tfs, 1), "peak_tflops": tf, "frac": round(tfs / tf, 3), "peak": src})
         if gather:
-            out["execution"] = f"{nranks} ranks, NCCL all-gather after every projection, max over ranks"
+            how = "peer-store gather (NCCL when the tensor-core kernel runs)" if comm.peer_stores else "NCCL all-gather"
+            out["execution"] = f"{nranks} ranks, {how} after every projection, max over ranks"
+        if recorded:
+            out["execution"] = out.get("execution", "one rank's shard") + "; the walk over the layers replayed from one CUDA graph"
         if rank == 0:
             results.append(out)
         ctx.free(dx)
@@ -154,8 +178,9 @@ def main() -> None:
     ap.add_argument("--world", type=int, default=8)
     ap.add_argument("--layers", type=int, default=5, help="distinct layers resident (the step is extrapolated to 80)")
     ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--graph", action="store_true", help="record the decode walk once and replay it as a CUDA graph")
     a = ap.parse_args()
-    for out in run(a.world, a.layers, a.iters):
+    for out in run(a.world, a.layers, a.iters, graph=a.graph):
         print(json.dumps(out), flush=True)
 
 

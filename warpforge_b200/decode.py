@@ -61,6 +61,14 @@ class Communicator:
         N.check("wf_comm_get_unique_id", N.load().wf_comm_get_unique_id(buf))
         return buf.raw
 
+    @property
+    def peer_stores(self) -> bool:
+        """True when small gathers of wf_qlinear_allgather go by stores into the peers' memory instead of NCCL."""
+        flag = ctypes.c_int(0)
+        c = self.context
+        c._ck("wf_comm_info", c._lib.wf_comm_info(c.handle, self.handle, None, None, ctypes.byref(flag)))
+        return bool(flag.value)
+
     def all_gather(self, send_dev: int, recv_dev: int, bytes_per_rank: int, stream: int = 0) -> None:
         c = self.context
         c._ck("wf_allgather", c._lib.wf_allgather(c.handle, self.handle, send_dev, recv_dev, bytes_per_rank, stream))
