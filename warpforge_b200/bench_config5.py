@@ -11,8 +11,10 @@ The per-layer time times 80 layers is the per-rank step time of the full configu
 extrapolation in the output).  Events on the launching stream, three warm-up walks.  One JSON line per leg.
 
 Under `python -m torch.distributed.run --nproc-per-node N -m warpforge_b200.bench_config5 --world N` the N ranks run
-the configuration as it is specified: every projection row-sharded N ways, each followed by the NCCL all-gather of
-`wf_qlinear_allgather`, so that every rank holds all rows; the time is the maximum over the ranks.
+the configuration as it is specified: every projection row-sharded N ways, each followed by the gather of
+`wf_qlinear_allgather` (peer stores / peer loads over NVLink on one node; NCCL with WF_GATHER=nccl in the
+environment), so that every rank holds all rows; the time is the maximum over the ranks.  `--graph` records the
+decode walk once and replays it as a CUDA graph.
 """
 from __future__ import annotations
 
@@ -152,7 +154,7 @@ def run(world: int = 8, layers: int = 5, iters: int = 3, ctx: CudaContext | None
             tfs = 2.0 * m * shard_macs / us_layer / 1e6
             out.update({"bound": "tensor", "achieved_tflops": round(tfs, 1), "peak_tflops": tf, "frac": round(tfs / tf, 3), "peak": src})
         if gather:
-            how = "peer-store gather (NCCL when the tensor-core kernel runs)" if comm.peer_stores else "NCCL all-gather"
+            how = "gather by the library's own kernels over NVLink (no NCCL)" if comm.peer_stores else "NCCL all-gather + copy"
             out["execution"] = f"{nranks} ranks, {how} after every projection, max over ranks"
         if recorded:
             out["execution"] = out.get("execution", "one rank's shard") + "; the walk over the layers replayed from one CUDA graph"

@@ -6,6 +6,10 @@
 // host buffers over UCC / RoCE.  libnccl is resolved at run time with dlopen, the way the
 // reference resolves libucc (io/collective/Collective.java:45-71), so the library loads on
 // machines without NCCL and reports WF_ERR_NCCL_UNAVAILABLE only when a communicator is asked for.
+// NCCL carries the bootstrap and the plain wf_allgather.  The gather behind wf_qlinear_allgather goes, between
+// the GPUs of one node, by this file's own kernels over peer-mapped memory (plain stores and loads, bulk copies
+// without multicast): gather_small_kernel for the decode kernels' outputs, gather_bulk_kernel /
+// gather_large_kernel for the tensor-core kernel's; NCCL + unshard_kernel is the fallback.
 #include <dlfcn.h>
 #include <stdlib.h>
 #include <string.h>
