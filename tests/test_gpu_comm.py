@@ -226,7 +226,41 @@ for m in (40, 130):
     want = orc.qlinear(O.Q4_0, blocks, rows, k, Q.bf16_bits_to_float(xb), nthreads=4)
     assert np.max(np.abs(a - want)) <= 1e-3 * np.max(np.abs(want)), m
     ctx.free(dx); ctx.free(dy)
+# Failure detection without a GPU fault: rank 1 never enters these gathers.  Rank 0's waits run out (0.3 s here), its
+# kernels end by themselves, the next synchronisation reports WF_ERR_DEVICE_WAIT, its own columns are right and the
+# context stays usable.  Rank 1 keeps its buffers mapped until rank 0 is through.
+os.environ["WF_GATHER_WAIT_MS"] = "300"
+ids = [Communicator.create_unique_id() if rank == 0 else None]
+dist.broadcast_object_list(ids, src=0)
+short = Communicator(ctx, ids[0], rank, world)
+del os.environ["WF_GATHER_WAIT_MS"]
+assert short.peer_stores
+r = rows // world
+if rank == 0:
+    import time
+    for m in (3, 40):
+        xb = Q.synth_activation_bf16(m, k, 59 + m)
+        dx, dy = ctx.allocate(xb.nbytes), ctx.allocate(m * rows * 4)
+        ctx.copy_to_device(dx, xb)
+        ctx.copy_to_device(dy, np.zeros((m, rows), np.float32))
+        t0 = time.time()
+        ctx._ck("wf_qlinear_allgather", lib.wf_qlinear_allgather(ctx.handle, short.handle, w.handle, dx, N.WF_DTYPE_BF16, m, dy, 0))
+        try:
+            ctx.synchronize()
+            raise SystemExit("the gather of an absent peer did not report its wait")
+        except N.WfError as err:
+            assert err.status == N.WF_ERR_DEVICE_WAIT, err.status
+        assert time.time() - t0 < 5.0
+        got = np.empty((m, rows), np.float32)
+        ctx.copy_to_host(got, dy)
+        want = orc.qlinear(O.Q4_0, blocks, rows, k, Q.bf16_bits_to_float(xb), nthreads=4)
+        if m <= 32:  # the decode kernels write this rank's columns into y themselves
+            assert np.max(np.abs(got[:, :r] - want[:, :r])) <= 1e-3 * np.max(np.abs(want)), m
+        ctx.synchronize()  # the status was cleared by reporting it
+        ctx.free(dx); ctx.free(dy)
+dist.barrier()
 w.close()
+short.close()
 dist.barrier()
 peer.close(); nccl.close(); regs.close(); ctx.close(); dist.destroy_process_group()
 os.write(1, f"RANK_OK {rank}\n".encode())
