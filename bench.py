@@ -9,7 +9,7 @@ HBM cold).  One step = one token = all projections in layer order, run as ONE pe
 kernel per GPU (`--mode graph`: one kernel per projection, recorded once as a CUDA graph).
 With N > 1 ranks the weights are row-sharded and every rank ends with all rows of every
 projection: the persistent kernel stores its rows into the other ranks' buffers over NVLink
-from inside the GEMV epilogue (graph mode: an NCCL all-gather after every projection).
+from inside the GEMV epilogue (graph mode: a gather kernel after every projection).
 Strong scaling: the same token stream on more GPUs.
 The dominant kernel is the Q4_0 decode GEMV, so `roofline` is the headline "Q4_0 GEMV HBM
 GB/s (% of peak)"; `gemv_sweep` adds benchmark config 2 (the [11008x4096] / [4096x11008]
@@ -42,7 +42,7 @@ WORKLOAD = ("benchmark config 4: 7B-shape Llama decode, 224 Q4_0 projections (32
             "{4x[4096x4096], 2x[11008x4096], [4096x11008]}), batch 1, bf16 activations, fp32 out")
 
 
-# DRAM traffic of the decode kernel, from the ncu capture summarised in profiles/gemv_program_q4_0_decode_7b.md
+# DRAM traffic of the decode kernel, from the ncu capture summarised in profiles/gemv1_program_q4_0_decode_7b.md
 # (dram__bytes_read.sum + dram__bytes_write.sum of one launch over two layers of this workload);
 # traffic grows in proportion to the layers run and splits evenly over row shards.  To be re-captured whenever the
 # kernel changes.
@@ -534,7 +534,7 @@ def run_ours(args) -> None:
                                        else f"row-sharded tp{world}" if world > 1 else "single GPU"),
                        "execution": ("one persistent kernel per token, gather fused into the GEMV epilogue (peer stores)"
                                      if mode == "program" else "one persistent kernel per token and replica" if replicas else "CUDA graph of one GEMV kernel per projection"
-                                     + (" + NCCL all-gather" if world > 1 else "")),
+                                     + (" + its gather (one kernel of peer stores; NCCL with WF_GATHER=nccl)" if world > 1 else "")),
                        "l2": "inputs larger than L2: 3.64 GB of distinct weights per step", "bytes_per_token": spec.bytes_per_token()},
             "e2e": {"value": 1e3 / (e2e_ms / args.steps) * (world if replicas else 1), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": int(y_out.nbytes)},
             "gpu_launches": int(launches),
@@ -544,7 +544,7 @@ def run_ours(args) -> None:
                          "frac": gbs / hbm_peak, "frac_of_8TBs_nominal": gbs / 8000.0, "peak_source": peak_src,
                          "bytes_per_launch": alg_bytes / n_launch, "us_per_launch": ms_step * 1e3 / n_launch,
                          "traffic": NCU_TRAFFIC_BYTES_PER_LAYER * stack.layers / (1 if replicas else world) / n_launch,
-                         "traffic_source": "ncu dram bytes of a 2-layer capture (profiles/gemv_program_q4_0_decode_7b.md), scaled by layers (and 1 / ranks)"},
+                         "traffic_source": "ncu dram bytes of a 2-layer capture (profiles/gemv1_program_q4_0_decode_7b.md), scaled by layers (and 1 / ranks)"},
         }
         if stack.layers != spec.layers:
             line["partial"] = f"{stack.layers} of {spec.layers} layers: a profiling run, not a bench value"

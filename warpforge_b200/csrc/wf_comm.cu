@@ -645,12 +645,19 @@ int wf_comm_destroy(int64_t ctx, int64_t comm) {
         g_comms.erase(std::find(g_comms.begin(), g_comms.end(), k));
     }
     cudaSetDevice(c->device);
-    if (k->peer_ok) {  // the peers may still be reading this rank's block of the last large gather
+    cudaDeviceSynchronize();
+    if (k->peer_ok) {
+        // The peers may still be reading this rank's block of the last large gather: wait for their "done".  A peer
+        // that has gone lets this wait run out; that is no failure of any call of this context, so the status word
+        // is put back afterwards.
+        int before = 0;
+        cudaMemcpy(&before, c->d_status, sizeof before, cudaMemcpyDeviceToHost);
         GatherPeers peers;
         for (int r = 0; r < WF_MAX_GATHER_RANKS; r++) peers.land[r] = k->land[r];
         gather_wait_done_kernel<<<1, 32, 0, c->stream>>>(peers, k->d_epoch, c->d_status, k->world, k->rank, k->wait_ns);
+        cudaDeviceSynchronize();
+        cudaMemcpy(c->d_status, &before, sizeof before, cudaMemcpyHostToDevice);
     }
-    cudaDeviceSynchronize();
     release_peer_landing(k);
     nccl().CommDestroy(k->comm);
     if (k->d_tmp) cudaFree(k->d_tmp);
