@@ -246,7 +246,9 @@ int wf_comm_destroy(int64_t ctx, int64_t comm);
  * exchanges the row blocks by one kernel of 8-byte {value, tag} stores into the peers' memory instead of an
  * NCCL all-gather plus a copy; larger outputs and the tensor-core path keep NCCL.  A rank waits at most
  * WF_GATHER_WAIT_MS (environment, default 5000) for its peers' stores, then sets the peer-wait status.
- * WF_GATHER=nccl in the environment at wf_comm_init keeps every gather on NCCL.  Any pointer may be null. */
+ * WF_GATHER=nccl in the environment at wf_comm_init keeps every gather on NCCL.  The mapped block costs each rank
+ * 32 MB + WF_GATHER_STAGE_MB (environment, default 128, the same on every rank) of device memory; blocks of more
+ * tokens than the staging area holds (m * rows * 4 bytes per rank) go by NCCL.  Any pointer may be null. */
 int wf_comm_info(int64_t ctx, int64_t comm, int* rank, int* world, int* peer_stores);
 int wf_allgather(int64_t ctx, int64_t comm, int64_t send_dev, int64_t recv_dev, int64_t bytes_per_rank,
                  int64_t stream);

@@ -69,11 +69,11 @@ struct Comm {
     Context* ctx = nullptr;
     NcclComm comm = nullptr;
     int rank = 0, world = 1;
-    float* d_tmp = nullptr;  // [world][m][rows] staging for multi-token gathers
+    float* d_tmp = nullptr;  // NCCL route: [world][m][rows] gathered rank-major, then this rank's [m][rows]
     int64_t tmp_bytes = 0;
-    // Peer-store gather of small outputs: every rank owns a landing buffer that the other ranks of the node
-    // write through IPC mappings.  land[r] is rank r's buffer (land[rank] the own one); all null when the
-    // mappings could not be made on every rank, and the NCCL path is then the only one.
+    // Gathers by this file's own kernels: every rank owns one block (landing buffer, flags, staging area) that
+    // the other ranks of the node map through IPC.  land[r] is rank r's block (land[rank] the own one); all null
+    // when the mappings could not be made on every rank, and the NCCL path is then the only one.
     uint2* land[WF_MAX_GATHER_RANKS] = {};
     unsigned int* d_epoch = nullptr;  // [0] small gathers done so far, [1] CTAs that finished the current one; [2], [3] the same for large ones
     int64_t stage_bytes = 0;          // size of the staging area behind the landing buffer and the flags
@@ -535,12 +535,14 @@ static void setup_peer_landing(Context* c, Comm* k) {
     }
     int flags[WF_MAX_GATHER_RANKS] = {};
     int* d_f = reinterpret_cast<int*>(d_x + (size_t)k->world * 64);
-    flags[k->rank] = ok ? 1 : 0;
+    // the flag carries the size of the staging area: ranks that disagreed on it would route the same gather differently
+    const int mine = ok ? (int)(stage >> 20) + 1 : 0;
+    flags[k->rank] = mine;
     cudaMemcpyAsync(d_f + k->rank, &flags[k->rank], 4, cudaMemcpyHostToDevice, s);
     bool agreed = a.AllGather(d_f + k->rank, d_f, 4, NCCL_INT8, k->comm, s) == NCCL_SUCCESS;
     cudaMemcpyAsync(flags, d_f, (size_t)k->world * 4, cudaMemcpyDeviceToHost, s);
     agreed = agreed && cudaStreamSynchronize(s) == cudaSuccess;
-    for (int r = 0; r < k->world; r++) agreed = agreed && flags[r] == 1;
+    for (int r = 0; r < k->world; r++) agreed = agreed && mine != 0 && flags[r] == mine;
     cudaFree(d_x);
     if (!agreed) {
         for (int r = 0; r < k->world; r++) {
