@@ -1,5 +1,6 @@
-"""The NCCL all-gather behind a row-sharded qlinear, through the C ABI (wf_comm_get_unique_id -> wf_comm_init ->
-wf_allgather / wf_qlinear_allgather), against the CPU oracle.
+"""The all-gather behind a row-sharded qlinear, through the C ABI (wf_comm_get_unique_id -> wf_comm_init ->
+wf_allgather / wf_qlinear_allgather), against the CPU oracle: the NCCL route and, between two GPUs, the library's
+own gather kernels (tagged peer stores, peer loads out of staging areas), which must give the same bits.
 
 A communicator of world size 1 runs on the single GPU of the test box: it exercises the run-time loading of
 libnccl, communicator set-up, the gather call on the compute stream and the rank-major -> token-major copy.
@@ -45,13 +46,13 @@ def test_world_one_communicator_allgather_and_qlinear(oracle):
         back = np.empty_like(src)
         ctx.copy_to_host(back, d_dst)
         assert np.array_equal(back, src)
-        # sharded qlinear + gather: 1 token (gathered in place), 5 tokens (GEMV, rank-major -> token-major copy),
-        # 24 tokens (tensor-core GEMM)
+        # sharded qlinear + gather: 1 token (gathered in place), 5 and 24 tokens (decode kernels, rank-major ->
+        # token-major copy), 48 tokens (tensor-core GEMM)
         rows, k = 1040, 1024
         for qt, oq in ((Q.QuantizationType.Q4_0, O.Q4_0), (Q.QuantizationType.Q4_K, O.Q4_K)):
             blocks = Q.synth_weight(qt, rows, k, 41)
             w = QuantizedWeight(ctx, qt, blocks, rows, k, 0, 1)
-            for m in (1, 5, 24):
+            for m in (1, 5, 24, 48):
                 xb = Q.synth_activation_bf16(m, k, 41 + m)
                 dx, dy = ctx.allocate(xb.nbytes), ctx.allocate(m * rows * 4)
                 ctx.copy_to_device(dx, xb)
@@ -103,7 +104,7 @@ rows, k = 2048, 1024
 for qt, oq in ((Q.QuantizationType.Q4_0, O.Q4_0), (Q.QuantizationType.Q4_K, O.Q4_K)):
     blocks = Q.synth_weight(qt, rows, k, 43)
     w = QuantizedWeight(ctx, qt, blocks, rows, k, rank, world)
-    for m in (1, 5, 24):
+    for m in (1, 5, 24, 48):
         xb = Q.synth_activation_bf16(m, k, 43 + m)
         dx, dy = ctx.allocate(xb.nbytes), ctx.allocate(m * rows * 4)
         ctx.copy_to_device(dx, xb)
