@@ -201,8 +201,12 @@ int wf_embedding(int64_t ctx, int64_t indices_dev, int64_t table_dev, int64_t y_
 int wf_qlinear(int64_t ctx, int64_t weight, const void* x, int x_dtype, int x_on_device, int64_t m, void* y,
                int y_on_device, int64_t stream);
 
-/* Same op with the row-sharded gather fused behind it: every rank passes its own shard
- * handle and receives the full y[m, n_total] (rank-major row ranges).  See wf_allgather. */
+/* Same op followed by the gather of the row shards: every rank passes its own shard handle and
+ * receives the full y[m, n_total] (columns [r * rows, (r + 1) * rows) of every token are rank r's),
+ * the result of CollectiveApi.allGather on the shards' outputs.  Device pointers only; the call
+ * enqueues on `stream`.  A collective: every rank of the communicator makes the same calls in the
+ * same order.  How the rows travel is described at wf_comm_info; a peer that does not arrive within
+ * the wait limit shows as WF_ERR_DEVICE_WAIT at the next synchronisation. */
 int wf_qlinear_allgather(int64_t ctx, int64_t comm, int64_t weight, const void* x_dev, int x_dtype, int64_t m,
                          void* y_full_dev, int64_t stream);
 
