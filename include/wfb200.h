@@ -206,7 +206,9 @@ int wf_qlinear(int64_t ctx, int64_t weight, const void* x, int x_dtype, int x_on
  * the result of CollectiveApi.allGather on the shards' outputs.  Device pointers only; the call
  * enqueues on `stream`.  A collective: every rank of the communicator makes the same calls in the
  * same order.  How the rows travel is described at wf_comm_info; a peer that does not arrive within
- * the wait limit shows as WF_ERR_DEVICE_WAIT at the next synchronisation. */
+ * the wait limit shows as WF_ERR_DEVICE_WAIT at the next synchronisation.  The gathers of one communicator
+ * are numbered on the device in the order they execute: issue them on one stream (or on streams ordered by
+ * events), never on two streams that may run concurrently. */
 int wf_qlinear_allgather(int64_t ctx, int64_t comm, int64_t weight, const void* x_dev, int x_dtype, int64_t m,
                          void* y_full_dev, int64_t stream);
 
