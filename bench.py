@@ -458,6 +458,8 @@ def run_ours(args) -> None:
             dist.broadcast_object_list(ids, src=0)
             comm = Communicator(ctx, ids[0], rank, world)
         stack = ProjectionStack(ctx, spec, tokens=1, comm=comm, layers=args.layers or None)
+        if dist is not None:
+            dist.barrier()  # the ranks enter their first gather together: its waits for the peers are bounded
         stack.record()
 
     def barrier():
